@@ -1,0 +1,86 @@
+/* C ABI of libfluxb. Every function returns 0 on success or a fluxb error code
+ * (1 invalid argument, 2 CUDA error, 3 unsupported, 4 device wait timed out);
+ * fluxb_last_error() gives the message of the calling thread's last failure.
+ * Pointers are device pointers unless stated otherwise; `stream` is a cudaStream_t. */
+#ifndef FLUXB_H_
+#define FLUXB_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FLUXB_MAX_RANKS 8
+
+const char* fluxb_last_error(void);
+
+/* element types */
+enum { FLUXB_BF16 = 0, FLUXB_FP8_E4M3 = 1, FLUXB_FP16 = 2, FLUXB_FP32 = 3 };
+/* dense modes */
+enum { FLUXB_PLAIN = 0, FLUXB_ALLGATHER = 1, FLUXB_REDUCE_SCATTER = 2 };
+
+/* Status record written by device code when a bounded wait gives up. 16 bytes. */
+typedef struct {
+  uint32_t code, block, detail0, detail1;
+} fluxb_status_t;
+
+/* D = A * B^T (+ bias). A [rows, K] and B [N, K] row-major with K contiguous, D row-major.
+ *   FLUXB_PLAIN          D[M, N]
+ *   FLUXB_ALLGATHER      a = this rank's shard [M/world, K]; D[M, N]; peers' shards arrive in
+ *                        ag_land[rank] ([world][M/world][K]) pushed by the peers' kernels
+ *   FLUXB_REDUCE_SCATTER a = [M, K]; partial tiles go to rs_stage[owner] ([world][M/world][N]);
+ *                        rs_out [M/world, N] receives the sum over ranks
+ * With world == 1 every mode degenerates to FLUXB_PLAIN on (a, d / rs_out). */
+typedef struct {
+  const void* a;
+  const void* b;
+  void* d;
+  const void* bias;
+  int64_t lda, ldb, ldd;     /* elements */
+  int64_t bias_row_stride;   /* 0: bias is one row of N */
+  int32_t M, N, K;
+  int32_t in_dtype;          /* FLUXB_BF16 | FLUXB_FP8_E4M3 ; output is bf16 */
+  int32_t mode, rank, world;
+  int32_t group_m;           /* 0 = default raster group */
+  int32_t num_sms;           /* 0 = all */
+  int32_t tile_n;            /* 0 = auto, else 128 | 256 */
+  uint32_t epoch;            /* call number of the owning op, starting at 1 */
+  uint32_t reserved;
+  uint64_t timeout_ns;       /* 0 = default (2 s) */
+  fluxb_status_t* status;    /* device memory, may be null */
+  void* ag_land[FLUXB_MAX_RANKS];
+  uint32_t* ag_flags[FLUXB_MAX_RANKS];
+  uint32_t* start_ctr[FLUXB_MAX_RANKS];
+  void* rs_stage[FLUXB_MAX_RANKS];
+  uint32_t* rs_ctr[FLUXB_MAX_RANKS];
+  void* rs_out;
+  uint32_t* rs_work;
+  void* stream;
+} fluxb_dense_args_t;
+
+int fluxb_dense_gemm(const fluxb_dense_args_t* args);
+/* number of kernels libfluxb launched from this process so far */
+uint64_t fluxb_launch_count(void);
+
+/* ---- symmetric memory (CUDA IPC). `handle` is 64 bytes of host memory. ---- */
+int fluxb_symm_alloc(uint64_t bytes, void** ptr, void* handle);
+int fluxb_symm_open(const void* handle, void** ptr);
+int fluxb_symm_close(void* ptr);
+int fluxb_symm_free(void* ptr);
+/* can `dev` read and write `peer`'s memory directly? */
+int fluxb_can_access_peer(int dev, int peer, int* out);
+
+/* ---- cross-rank barrier on a stream. flags[r] points at rank r's flag block of `world`
+ * uint32 (one word per source rank). Every rank passes the same, ever-growing `epoch`. ---- */
+int fluxb_barrier_all(uint32_t* const* flags, int rank, int world, uint32_t epoch,
+                      uint64_t timeout_ns, fluxb_status_t* status, void* stream);
+/* Wait-only probe used by failure-detection tests: waits until *flag >= expected or the time
+ * limit passes, then returns; the outcome is in `status`. */
+int fluxb_wait_flag(const uint32_t* flag, uint32_t expected, uint64_t timeout_ns,
+                    fluxb_status_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLUXB_H_ */

@@ -1,0 +1,166 @@
+// Host side of the dense GEMM family (GemmOnly, AG+GEMM, GEMM+RS): argument checks, tensor
+// maps, tile-shape choice and the launch of dense_gemm_kernel.
+#include "../include/fluxb.h"
+#include "../runtime/host_common.h"
+#include "../sm100/gemm_dense.cuh"
+
+#include <atomic>
+
+namespace fluxb {
+
+std::atomic<uint64_t> g_launches{0};
+
+namespace {
+
+template <class Cfg>
+int launch_dense(const DenseGemmParams& p, int grid, cudaStream_t stream) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  FLUXB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev >= 64 || !configured[dev]) {
+    FLUXB_CUDA_OK(cudaFuncSetAttribute(dense_gemm_kernel<Cfg>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    if (dev < 64) configured[dev] = true;
+  }
+  dense_gemm_kernel<Cfg><<<grid, 256, Cfg::SMEM_BYTES, stream>>>(p);
+  FLUXB_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return kOk;
+}
+
+}  // namespace
+}  // namespace fluxb
+
+using namespace fluxb;
+
+extern "C" uint64_t fluxb_launch_count(void) { return g_launches.load(); }
+
+extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
+  FLUXB_REQUIRE(a != nullptr, "null args");
+  FLUXB_REQUIRE(a->M > 0 && a->N > 0 && a->K > 0, "empty problem");
+  FLUXB_REQUIRE(a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP8_E4M3, "input dtype");
+  FLUXB_REQUIRE(a->world >= 1 && a->world <= FLUXB_MAX_RANKS, "world size 1..8");
+  FLUXB_REQUIRE(a->rank >= 0 && a->rank < a->world, "rank");
+  const int elt = a->in_dtype == FLUXB_BF16 ? 2 : 1;
+  const bool multi = a->world > 1 && a->mode != FLUXB_PLAIN;
+  FLUXB_REQUIRE((a->K * elt) % 16 == 0, "K row bytes must be a multiple of 16");
+  FLUXB_REQUIRE(a->N % 8 == 0, "N must be a multiple of 8");
+  if (multi) FLUXB_REQUIRE(a->M % a->world == 0, "M must divide evenly over ranks");
+
+  DenseGemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = a->M;
+  p.N = a->N;
+  p.K = a->K;
+  p.rank = a->rank;
+  p.world = a->world;
+  p.mode = multi ? a->mode : kModePlain;
+  p.num_seg = multi ? a->world : 1;
+  p.seg_rows = a->M / p.num_seg;
+  p.epoch = a->epoch;
+  p.timeout_ns = a->timeout_ns ? a->timeout_ns : 2000000000ull;
+  p.status = reinterpret_cast<Status*>(a->status);
+  p.bias = a->bias;
+  p.bias_row_stride = a->bias_row_stride;
+
+  int bn = a->tile_n;
+  if (bn == 0) bn = (a->N % 256 == 0 || a->N > 2048) ? 256 : 128;
+  FLUXB_REQUIRE(bn == 128 || bn == 256, "tile_n must be 128 or 256");
+  const int bk = 128 / elt;
+  const CUtensorMapDataType in_dt =
+      a->in_dtype == FLUXB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+
+  int rc;
+  // ---- A
+  {
+    const uint64_t rows = (p.mode == kModeAllGather) ? p.seg_rows : a->M;
+    uint64_t dims[2] = {static_cast<uint64_t>(a->K), rows};
+    uint64_t str[1] = {static_cast<uint64_t>(a->lda) * elt};
+    uint32_t box[2] = {static_cast<uint32_t>(bk), 128};
+    if ((rc = encode_tmap(&p.tm_a, in_dt, 2, a->a, dims, str, box, Swz::B128))) return rc;
+  }
+  if (p.mode == kModeAllGather) {
+    FLUXB_REQUIRE(a->ag_land[a->rank] != nullptr, "all-gather landing buffer missing");
+    uint64_t dims[2] = {static_cast<uint64_t>(a->K), static_cast<uint64_t>(a->M)};
+    uint64_t str[1] = {static_cast<uint64_t>(a->K) * elt};
+    uint32_t box[2] = {static_cast<uint32_t>(bk), 128};
+    if ((rc = encode_tmap(&p.tm_a_land, in_dt, 2, a->ag_land[a->rank], dims, str, box, Swz::B128)))
+      return rc;
+    FLUXB_REQUIRE(a->lda == a->K, "all-gather input shard must be contiguous");
+    p.ag_src = a->a;
+    for (int r = 0; r < a->world; ++r) {
+      p.ag_land[r] = a->ag_land[r];
+      p.ag_flags[r] = a->ag_flags[r];
+      FLUXB_REQUIRE(p.ag_land[r] && p.ag_flags[r], "all-gather peer pointers missing");
+    }
+  }
+  // ---- B
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(a->K), static_cast<uint64_t>(a->N)};
+    uint64_t str[1] = {static_cast<uint64_t>(a->ldb) * elt};
+    uint32_t box[2] = {static_cast<uint32_t>(bk), static_cast<uint32_t>(bn)};
+    if ((rc = encode_tmap(&p.tm_b, in_dt, 2, a->b, dims, str, box, Swz::B128))) return rc;
+  }
+  // ---- D
+  {
+    uint32_t box[3] = {64, 32, 1};
+    if (p.mode == kModeReduceScatter) {
+      FLUXB_REQUIRE(a->rs_out && a->rs_work, "reduce-scatter output / work counter missing");
+      for (int r = 0; r < a->world; ++r) {
+        FLUXB_REQUIRE(a->rs_stage[r] && a->rs_ctr[r], "reduce-scatter peer pointers missing");
+        uint64_t dims[3] = {static_cast<uint64_t>(a->N), static_cast<uint64_t>(p.seg_rows),
+                            static_cast<uint64_t>(a->world)};
+        uint64_t str[2] = {static_cast<uint64_t>(a->N) * 2,
+                           static_cast<uint64_t>(a->N) * 2 * p.seg_rows};
+        if ((rc = encode_tmap(&p.tm_d[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a->rs_stage[r], dims,
+                              str, box, Swz::B128)))
+          return rc;
+        p.rs_ctr[r] = a->rs_ctr[r];
+      }
+      p.rs_stage = a->rs_stage[a->rank];
+      p.rs_out = a->rs_out;
+      p.rs_work = a->rs_work;
+    } else {
+      void* out = a->d ? a->d : a->rs_out;
+      const int64_t ldd = a->d ? a->ldd : a->N;
+      FLUXB_REQUIRE(out != nullptr, "output missing");
+      uint64_t dims[3] = {static_cast<uint64_t>(a->N), static_cast<uint64_t>(p.seg_rows),
+                          static_cast<uint64_t>(p.num_seg)};
+      uint64_t str[2] = {static_cast<uint64_t>(ldd) * 2, static_cast<uint64_t>(ldd) * 2 * p.seg_rows};
+      if ((rc = encode_tmap(&p.tm_d[0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, out, dims, str, box,
+                            Swz::B128)))
+        return rc;
+    }
+  }
+  if (multi) {
+    for (int r = 0; r < a->world; ++r) {
+      FLUXB_REQUIRE(a->start_ctr[r] != nullptr, "start counters missing");
+      p.start_ctr[r] = a->start_ctr[r];
+    }
+  }
+  // segment visiting order: all-gather starts with the own shard, reduce-scatter ends with it
+  p.seg_first = 0;
+  if (p.mode == kModeAllGather) p.seg_first = a->rank;
+  if (p.mode == kModeReduceScatter) p.seg_first = (a->rank + 1) % a->world;
+
+  const int m_tiles_seg = (p.seg_rows + 127) / 128;
+  p.group_m = a->group_m > 0 ? a->group_m : 16;
+  if (p.group_m > m_tiles_seg) p.group_m = m_tiles_seg;
+
+  int sms = 0;
+  if ((rc = device_sm_count(&sms))) return rc;
+  if (a->num_sms > 0 && a->num_sms < sms) sms = a->num_sms;
+  const int64_t tiles = static_cast<int64_t>(p.num_seg) * m_tiles_seg * ((a->N + bn - 1) / bn);
+  int grid = sms;
+  // every CTA of a multi-rank launch takes part in the flag protocol, so the grid stays full
+  if (!multi && tiles < grid) grid = static_cast<int>(tiles);
+
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
+  if (a->in_dtype == FLUXB_BF16) {
+    if (bn == 256) return launch_dense<DenseCfg<256, 0, 4>>(p, grid, stream);
+    return launch_dense<DenseCfg<128, 0, 6>>(p, grid, stream);
+  } else {
+    if (bn == 256) return launch_dense<DenseCfg<256, 1, 4>>(p, grid, stream);
+    return launch_dense<DenseCfg<128, 1, 6>>(p, grid, stream);
+  }
+}

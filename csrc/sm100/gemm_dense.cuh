@@ -1,0 +1,459 @@
+// Dense GEMM core for sm_100a: D[M,N] = A[M,K] * B[N,K]^T (+bias), fp32 accumulation in TMEM.
+//
+// One persistent CTA per SM, 8 warps with fixed roles:
+//   warp 0      TMA producer    (one lane): A/B k-blocks -> shared-memory ring
+//   warp 1      MMA issuer      (one lane): tcgen05.mma from the ring into one of two TMEM
+//                                accumulators; tcgen05.commit frees ring slots / publishes tiles
+//   warps 2,3   communication   cross-rank "everyone entered this call" handshake; in all-gather
+//                                mode they push this rank's A shard into every peer's landing
+//                                buffer with 16-byte peer stores and bump arrival flags
+//   warps 4..7  epilogue        tcgen05.ld -> (+bias) -> bf16 -> swizzled smem -> TMA store, to
+//                                local memory or, in reduce-scatter mode, straight into the
+//                                owner rank's staging buffer over NVLink
+// After the role loops a reduce-scatter launch sums the W partial slabs that the peers pushed
+// into this rank's staging buffer (all 256 threads, work claimed dynamically).
+//
+// The same kernel serves the three dense ops of the library; they differ only in how the M
+// dimension is cut into per-rank segments and where tiles come from / go to:
+//   GemmOnly        1 segment.                                   (reference: src/comm_none)
+//   AllGather+GEMM  W segments, own first; A of a remote segment is read from the local
+//                   landing buffer once its flags show that the owner's push has landed.
+//                                                                (reference: src/ag_gemm, src/coll)
+//   GEMM+ReduceScatter  W segments, own last; a tile of segment s is stored into rank s's
+//                   staging slab [this rank]; the owner reduces.  (reference: src/gemm_rs)
+#pragma once
+
+#include "ptx.cuh"
+
+namespace fluxb {
+
+constexpr int kMaxRanks = 8;
+
+enum DenseMode : int32_t { kModePlain = 0, kModeAllGather = 1, kModeReduceScatter = 2 };
+
+struct DenseGemmParams {
+  CUtensorMap tm_a;              // A rows owned by this launch: [rows, K], box {BK, 128}
+  CUtensorMap tm_a_land;         // all-gather landing buffer viewed as [W*seg_rows, K]
+  CUtensorMap tm_b;              // B [N, K], box {BK, BN}
+  CUtensorMap tm_d[kMaxRanks];   // 3-D store maps [slab][seg_rows][N], box {64, 32, 1}
+  int32_t M, N, K;
+  int32_t num_seg, seg_rows, seg_first;
+  int32_t rank, world;
+  int32_t mode;
+  int32_t group_m;
+  uint32_t epoch;                // call number of the owning op object, starts at 1
+  uint32_t reserved0;
+  uint64_t timeout_ns;
+  Status* status;
+  const void* bias;              // bf16, may be null
+  int64_t bias_row_stride;       // elements between bias rows; 0 = one row broadcast over M
+  // all-gather
+  const void* ag_src;            // this rank's shard [seg_rows, K]
+  void* ag_land[kMaxRanks];      // landing buffer of every rank, [W][seg_rows][K]
+  uint32_t* ag_flags[kMaxRanks]; // on every rank: [W][m_tiles_seg] arrival counters
+  // cross-rank start handshake
+  uint32_t* start_ctr[kMaxRanks];  // on every rank: [W] last call number entered, by source
+  // reduce-scatter
+  uint32_t* rs_ctr[kMaxRanks];   // on every rank: [m_tiles_seg] arrival counters
+  const void* rs_stage;          // local staging [W][seg_rows][N] bf16
+  void* rs_out;                  // [seg_rows, N] bf16
+  uint32_t* rs_work;             // local work-claim counter
+};
+
+template <int BN_, int KIND_, int STAGES_>
+struct DenseCfg {
+  static constexpr int BM = 128;
+  static constexpr int BN = BN_;
+  static constexpr int KIND = KIND_;                       // 0 = bf16, 1 = fp8 e4m3
+  static constexpr int ELT = KIND_ == 0 ? 2 : 1;
+  static constexpr int BK = 128 / ELT;                     // one 128-byte swizzle row
+  static constexpr int UMMA_K = 32 / ELT;
+  static constexpr int STAGES = STAGES_;
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int EPI_BUF_BYTES = 32 * 128;           // 32 rows x 64 bf16
+  static constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;
+  static constexpr int TMEM_COLS = 512;
+  static_assert(2 * BN <= TMEM_COLS, "two accumulators must fit TMEM");
+};
+
+struct TileCoord {
+  int seg;       // segment (owner rank) of the tile
+  int m_in_seg;  // first row inside the segment
+  int m_tile;    // tile row index inside the segment
+  int n0;        // first output column
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const DenseGemmParams& p, int t, int m_tiles_seg,
+                                                 int n_tiles, int BM, int BN) {
+  const int per_seg = m_tiles_seg * n_tiles;
+  const int si = t / per_seg;
+  int r = t - si * per_seg;
+  int seg = p.seg_first + si;
+  if (seg >= p.num_seg) seg -= p.num_seg;
+  const int G = p.group_m;
+  const int per_group = G * n_tiles;
+  const int gid = r / per_group;
+  const int first_m = gid * G;
+  const int gsz = min(G, m_tiles_seg - first_m);
+  r -= gid * per_group;
+  const int mt = first_m + r % gsz;
+  const int nt = r / gsz;
+  TileCoord c;
+  c.seg = seg;
+  c.m_tile = mt;
+  c.m_in_seg = mt * BM;
+  c.n0 = nt * BN;
+  return c;
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constant__ DenseGemmParams p) {
+  constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t smem_base = raw_addr + pad;
+
+  const uint32_t epi_base = smem_base + STAGES * Cfg::STAGE_BYTES;
+  uint8_t* epi_ptr = smem + STAGES * Cfg::STAGE_BYTES;
+  const uint32_t bar_base = epi_base + Cfg::EPI_BYTES;
+  uint8_t* bar_ptr = epi_ptr + Cfg::EPI_BYTES;
+  // barrier block: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then two words
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * STAGES + 4));
+  volatile uint32_t* abort_word = tmem_slot + 1;
+  volatile uint32_t* claim_slot = tmem_slot + 2;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 4);
+    }
+    *abort_word = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tmap(&p.tm_a);
+    ptx::prefetch_tmap(&p.tm_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<1>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
+    ptx::tmem_relinquish<1>();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  WaitCtx wc{p.status, abort_word, p.timeout_ns};
+
+  const int m_tiles_seg = (p.seg_rows + BM - 1) / BM;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int total_tiles = p.num_seg * m_tiles_seg * n_tiles;
+  const int k_blocks = (p.K + BK - 1) / BK;
+  const bool multi = p.world > 1 && p.mode != kModePlain;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
+        const CUtensorMap* tma = &p.tm_a;
+        int a_row = c.seg * p.seg_rows + c.m_in_seg;
+        if (p.mode == kModeAllGather && multi) {
+          if (c.seg == p.rank) {
+            a_row = c.m_in_seg;  // own shard straight from the caller's tensor
+          } else {
+            tma = &p.tm_a_land;
+            const uint32_t* f = p.ag_flags[p.rank] + c.seg * m_tiles_seg + c.m_tile;
+            flag_wait_ge(wc, f, p.epoch * gridDim.x * 2u, kSiteShardFlag);
+            ptx::fence_proxy_async_all();
+          }
+        }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          mbar_wait(wc, empty_bar(stage), phase ^ 1u, kSiteSmemEmpty);
+          const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+          ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+          ptx::tma_load_2d(sa, tma, full_bar(stage), kb * BK, a_row);
+          ptx::tma_load_2d(sa + Cfg::A_BYTES, &p.tm_b, full_bar(stage), kb * BK, c.n0);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = Cfg::KIND == 0 ? ptx::umma_idesc(1, 1, BM, BN)
+                                                : ptx::umma_idesc(0, 0, BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        mbar_wait(wc, tempty_bar(acc), acc_phase ^ 1u, kSiteTmemEmpty);
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          mbar_wait(wc, full_bar(stage), phase, kSiteSmemFull);
+          ptx::tc_fence_after();
+          const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint64_t adesc = ptx::umma_desc_k_sw128(sa);
+          const uint64_t bdesc = ptx::umma_desc_k_sw128(sa + Cfg::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / Cfg::UMMA_K; ++k) {
+            // 32 bytes per UMMA_K step inside the 128-byte swizzled row: +2 in 16-byte units
+            ptx::umma_ss<1, Cfg::KIND>(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc,
+                                       (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(empty_bar(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        ptx::umma_commit(tfull_bar(acc));
+      }
+    }
+  } else if (warp == 2 || warp == 3) {
+    // ------------------------------------------------------------------ handshake + all-gather push
+    if (multi && warp == 3 && blockIdx.x == 0 && lane < p.world) {
+      // "this rank has entered call `epoch`": nobody writes into a peer before that peer is
+      // done with the previous call's buffers. One word per source rank, so a fast rank's
+      // next call can never be mistaken for a slow rank's current one.
+      ptx::st_release_sys(p.start_ctr[lane] + p.rank, p.epoch);
+    }
+    if (p.mode == kModeAllGather && multi) {
+      if (lane < p.world) flag_wait_ge(wc, p.start_ctr[p.rank] + lane, p.epoch, kSiteStartBarrier);
+      __syncwarp();
+      constexpr int U = 8;  // independent 16-byte chunks per lane per trip
+      const int64_t row_chunks = (static_cast<int64_t>(p.K) * Cfg::ELT) >> 4;
+      const uint4* src = reinterpret_cast<const uint4*>(p.ag_src);
+      const int64_t slab = static_cast<int64_t>(p.rank) * p.seg_rows * row_chunks;
+      const int64_t cw = static_cast<int64_t>(blockIdx.x) * 2 + (warp - 2);
+      const int64_t ncw = static_cast<int64_t>(gridDim.x) * 2;
+      // The peer that consumes this shard first (rank-1 starts with segment rank) is served
+      // first; all ranks walk the same rotation, so every step is a permutation on NVSwitch.
+      for (int d = 1; d < p.world; ++d) {
+        int peer = p.rank - d;
+        if (peer < 0) peer += p.world;
+        uint4* land = reinterpret_cast<uint4*>(p.ag_land[peer]) + slab;
+        for (int mt = 0; mt < m_tiles_seg; ++mt) {
+          const int rows = min(BM, p.seg_rows - mt * BM);
+          const int64_t first = static_cast<int64_t>(mt) * BM * row_chunks;
+          const int64_t count = static_cast<int64_t>(rows) * row_chunks;
+          for (int64_t i = cw * U * 32 + lane; i < count; i += ncw * U * 32) {
+            uint4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+              if (i + u * 32 < count) v[u] = ptx::ld_global_v4(src + first + i + u * 32);
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+              if (i + u * 32 < count) ptx::st_global_v4(land + first + i + u * 32, v[u]);
+          }
+          __syncwarp();
+          if (lane == 0) ptx::red_add_release_sys(p.ag_flags[peer] + p.rank * m_tiles_seg + mt, 1u);
+          __syncwarp();
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    uint8_t* my_epi = epi_ptr + q * 2 * Cfg::EPI_BUF_BYTES;
+    const uint32_t my_epi_u32 = epi_base + q * 2 * Cfg::EPI_BUF_BYTES;
+    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(p.bias);
+    int it = 0;
+    uint32_t nstore = 0;
+    bool started = !(multi && p.mode == kModeReduceScatter);
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+      const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const CUtensorMap* tmd = &p.tm_d[0];
+      int z = c.seg;
+      if (p.mode == kModeReduceScatter && multi) {
+        tmd = &p.tm_d[c.seg];
+        z = p.rank;
+        if (!started) {
+          // peers may still be reducing the previous call's slabs until they enter this call
+          if (lane < p.world) flag_wait_ge(wc, p.start_ctr[p.rank] + lane, p.epoch, kSiteStartBarrier);
+          __syncwarp();
+          started = true;
+        }
+      }
+      mbar_wait(wc, tfull_bar(acc), acc_phase, kSiteTmemFull);
+      ptx::tc_fence_after();
+      const int row = c.m_in_seg + q * 32 + lane;              // row inside the segment
+      const int64_t grow = static_cast<int64_t>(c.seg) * p.seg_rows + row;  // global row
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 64; ++ch) {
+        uint32_t r0[32], r1[32];
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + ch * 64;
+        ptx::tmem_ld_32x32b_x32(taddr, r0);
+        ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
+        ptx::tmem_ld_wait();
+        if (ch == BN / 64 - 1) {
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+        }
+        const int col0 = c.n0 + ch * 64;
+        if (bias != nullptr && col0 < p.N) {
+          const __nv_bfloat16* brow = bias + (p.bias_row_stride ? grow * p.bias_row_stride : 0);
+          const bool row_ok = row < p.seg_rows;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (row_ok && col0 + j < p.N)
+              r0[j] = __float_as_uint(__uint_as_float(r0[j]) + __bfloat162float(brow[col0 + j]));
+            if (row_ok && col0 + 32 + j < p.N)
+              r1[j] = __float_as_uint(__uint_as_float(r1[j]) + __bfloat162float(brow[col0 + 32 + j]));
+          }
+        }
+        const uint32_t buf = nstore & 1u;
+        if (lane == 0) ptx::bulk_wait_read<1>();
+        __syncwarp();
+        uint8_t* dst = my_epi + buf * Cfg::EPI_BUF_BYTES + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 v;
+          v.x = ptx::pack_bf16x2(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+          v.y = ptx::pack_bf16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+          v.z = ptx::pack_bf16x2(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+          v.w = ptx::pack_bf16x2(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+          *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = v;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 v;
+          v.x = ptx::pack_bf16x2(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+          v.y = ptx::pack_bf16x2(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+          v.z = ptx::pack_bf16x2(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+          v.w = ptx::pack_bf16x2(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+          *reinterpret_cast<uint4*>(dst + (((j + 4) ^ (lane & 7)) << 4)) = v;
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && col0 < p.N && c.m_in_seg + q * 32 < p.seg_rows) {
+          ptx::tma_store_3d(tmd, my_epi_u32 + buf * Cfg::EPI_BUF_BYTES, col0, c.m_in_seg + q * 32, z);
+        }
+        if (lane == 0) ptx::bulk_commit();
+        ++nstore;
+      }
+      if (p.mode == kModeReduceScatter && multi) {
+        // the tile's slab rows have fully landed at the owner -> count this warp's arrival
+        if (lane == 0) {
+          ptx::bulk_wait<0>();
+          ptx::fence_proxy_async_all();
+          ptx::red_add_release_sys(p.rs_ctr[c.seg] + c.m_tile, 1u);
+        }
+        __syncwarp();
+      }
+    }
+    if (lane == 0) ptx::bulk_wait<0>();
+    __syncwarp();
+  }
+
+  // -------------------------------------------------------------------- teardown of the GEMM
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc<1>(tmem_base, Cfg::TMEM_COLS);
+  }
+
+  // -------------------------------------------------------------------- reduce-scatter tail
+  if (p.mode == kModeReduceScatter && multi) {
+    // Sum the W slabs of the local staging buffer into rs_out. A work unit is kUnit 16-byte
+    // chunks (8 bf16) of the [seg_rows, N] output; units are claimed from a counter that only
+    // grows: every CTA makes exactly one failing claim per call.
+    constexpr int kUnit = 256 * 8;
+    const int64_t chunks_per_row = p.N >> 3;
+    const int64_t total_chunks = static_cast<int64_t>(p.seg_rows) * chunks_per_row;
+    const uint32_t units = static_cast<uint32_t>((total_chunks + kUnit - 1) / kUnit);
+    const uint32_t claim_base = (p.epoch - 1u) * (units + gridDim.x);
+    const uint32_t per_mtile = p.epoch * static_cast<uint32_t>(p.world) * n_tiles * 4u;
+    const uint4* stage = reinterpret_cast<const uint4*>(p.rs_stage);
+    uint4* out = reinterpret_cast<uint4*>(p.rs_out);
+    const int64_t slab_chunks = total_chunks;
+    int verified_mt = -1;
+    while (true) {
+      __syncthreads();
+      if (threadIdx.x == 0) *claim_slot = atomicAdd(p.rs_work, 1u) - claim_base;
+      __syncthreads();
+      const uint32_t u = *claim_slot;
+      if (u >= units) break;
+#pragma unroll 1
+      for (int rep = 0; rep < kUnit / 256; rep += 2) {
+        int64_t idx[2];
+        bool ok[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          idx[h] = static_cast<int64_t>(u) * kUnit + (rep + h) * 256 + threadIdx.x;
+          ok[h] = idx[h] < total_chunks;
+          if (ok[h]) {
+            const int mt = static_cast<int>((idx[h] / chunks_per_row) / BM);
+            if (mt != verified_mt) {
+              flag_wait_ge(wc, p.rs_ctr[p.rank] + mt, per_mtile, kSiteTileCounter);
+              verified_mt = mt;
+            }
+          }
+        }
+        float accv[2][8];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) accv[h][e] = 0.f;
+        uint4 v[kMaxRanks][2];
+#pragma unroll
+        for (int s = 0; s < kMaxRanks; ++s)
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+            if (s < p.world && ok[h]) v[s][h] = ptx::ld_global_cs_v4(stage + s * slab_chunks + idx[h]);
+#pragma unroll
+        for (int s = 0; s < kMaxRanks; ++s)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (s < p.world && ok[h]) {
+              const uint32_t w[4] = {v[s][h].x, v[s][h].y, v[s][h].z, v[s][h].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                accv[h][2 * e] += __uint_as_float(w[e] << 16);
+                accv[h][2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+              }
+            }
+          }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (!ok[h]) continue;
+          uint4 v;
+          v.x = ptx::pack_bf16x2(accv[h][0], accv[h][1]);
+          v.y = ptx::pack_bf16x2(accv[h][2], accv[h][3]);
+          v.z = ptx::pack_bf16x2(accv[h][4], accv[h][5]);
+          v.w = ptx::pack_bf16x2(accv[h][6], accv[h][7]);
+          out[idx[h]] = v;
+        }
+      }
+    }
+  }
+}
+
+}  // namespace fluxb
