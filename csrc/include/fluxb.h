@@ -16,7 +16,7 @@ extern "C" {
 const char* fluxb_last_error(void);
 
 /* element types */
-enum { FLUXB_BF16 = 0, FLUXB_FP8_E4M3 = 1, FLUXB_FP16 = 2, FLUXB_FP32 = 3 };
+enum { FLUXB_BF16 = 0, FLUXB_FP8_E4M3 = 1, FLUXB_FP16 = 2, FLUXB_FP32 = 3, FLUXB_FP8_E5M2 = 4 };
 /* dense modes */
 enum { FLUXB_PLAIN = 0, FLUXB_ALLGATHER = 1, FLUXB_REDUCE_SCATTER = 2 };
 
@@ -40,7 +40,10 @@ typedef struct {
   int64_t lda, ldb, ldd;     /* elements */
   int64_t bias_row_stride;   /* 0: bias is one row of N */
   int32_t M, N, K;
-  int32_t in_dtype;          /* FLUXB_BF16 | FLUXB_FP8_E4M3 ; output is bf16 */
+  int32_t in_dtype;          /* FLUXB_BF16 | FLUXB_FP16 | FLUXB_FP8_E4M3 | FLUXB_FP8_E5M2 */
+  int32_t out_dtype;         /* FLUXB_BF16 | FLUXB_FP16 (also the dtype of bias and rs_stage) */
+  const float* scale_a;      /* optional device scalars: D = (A*B^T) * scale_a * scale_b */
+  const float* scale_b;
   int32_t mode, rank, world;
   int32_t group_m;           /* 0 = default raster group */
   int32_t num_sms;           /* 0 = all */
@@ -55,7 +58,8 @@ typedef struct {
   void* rs_stage[FLUXB_MAX_RANKS];
   uint32_t* rs_ctr[FLUXB_MAX_RANKS];
   void* rs_out;
-  uint32_t* rs_work;
+  uint32_t* rs_work;         /* local uint32, zero at first use */
+  uint32_t* local_cnt;       /* local scratch of world * ceil(M/world/128) uint32, zero at first use */
   void* stream;
 } fluxb_dense_args_t;
 

@@ -38,10 +38,14 @@ extern "C" uint64_t fluxb_launch_count(void) { return g_launches.load(); }
 extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   FLUXB_REQUIRE(a != nullptr, "null args");
   FLUXB_REQUIRE(a->M > 0 && a->N > 0 && a->K > 0, "empty problem");
-  FLUXB_REQUIRE(a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP8_E4M3, "input dtype");
+  FLUXB_REQUIRE(a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP8_E4M3 ||
+                    a->in_dtype == FLUXB_FP16 || a->in_dtype == FLUXB_FP8_E5M2,
+                "input dtype");
+  FLUXB_REQUIRE(a->out_dtype == FLUXB_BF16 || a->out_dtype == FLUXB_FP16, "output dtype");
   FLUXB_REQUIRE(a->world >= 1 && a->world <= FLUXB_MAX_RANKS, "world size 1..8");
   FLUXB_REQUIRE(a->rank >= 0 && a->rank < a->world, "rank");
-  const int elt = a->in_dtype == FLUXB_BF16 ? 2 : 1;
+  const bool in16 = a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP16;
+  const int elt = in16 ? 2 : 1;
   const bool multi = a->world > 1 && a->mode != FLUXB_PLAIN;
   FLUXB_REQUIRE((a->K * elt) % 16 == 0, "K row bytes must be a multiple of 16");
   FLUXB_REQUIRE(a->N % 8 == 0, "N must be a multiple of 8");
@@ -62,13 +66,18 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   p.status = reinterpret_cast<Status*>(a->status);
   p.bias = a->bias;
   p.bias_row_stride = a->bias_row_stride;
+  p.scale_a = a->scale_a;
+  p.scale_b = a->scale_b;
+  p.ab_fmt = (a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP8_E5M2) ? 1 : 0;
+  p.out_f16 = a->out_dtype == FLUXB_FP16 ? 1 : 0;
 
   int bn = a->tile_n;
   if (bn == 0) bn = (a->N % 256 == 0 || a->N > 2048) ? 256 : 128;
   FLUXB_REQUIRE(bn == 128 || bn == 256, "tile_n must be 128 or 256");
   const int bk = 128 / elt;
   const CUtensorMapDataType in_dt =
-      a->in_dtype == FLUXB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+      in16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const CUtensorMapDataType out_dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;  // any 16-bit type moves alike
 
   int rc;
   // ---- A
@@ -112,7 +121,7 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
                             static_cast<uint64_t>(a->world)};
         uint64_t str[2] = {static_cast<uint64_t>(a->N) * 2,
                            static_cast<uint64_t>(a->N) * 2 * p.seg_rows};
-        if ((rc = encode_tmap(&p.tm_d[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a->rs_stage[r], dims,
+        if ((rc = encode_tmap(&p.tm_d[r], out_dt, 3, a->rs_stage[r], dims,
                               str, box, Swz::B128)))
           return rc;
         p.rs_ctr[r] = a->rs_ctr[r];
@@ -127,12 +136,14 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
       uint64_t dims[3] = {static_cast<uint64_t>(a->N), static_cast<uint64_t>(p.seg_rows),
                           static_cast<uint64_t>(p.num_seg)};
       uint64_t str[2] = {static_cast<uint64_t>(ldd) * 2, static_cast<uint64_t>(ldd) * 2 * p.seg_rows};
-      if ((rc = encode_tmap(&p.tm_d[0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, out, dims, str, box,
+      if ((rc = encode_tmap(&p.tm_d[0], out_dt, 3, out, dims, str, box,
                             Swz::B128)))
         return rc;
     }
   }
   if (multi) {
+    FLUXB_REQUIRE(a->local_cnt != nullptr, "local arrival scratch missing");
+    p.local_cnt = a->local_cnt;
     for (int r = 0; r < a->world; ++r) {
       FLUXB_REQUIRE(a->start_ctr[r] != nullptr, "start counters missing");
       p.start_ctr[r] = a->start_ctr[r];
@@ -156,7 +167,7 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   if (!multi && tiles < grid) grid = static_cast<int>(tiles);
 
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
-  if (a->in_dtype == FLUXB_BF16) {
+  if (in16) {
     if (bn == 256) return launch_dense<DenseCfg<256, 0, 4>>(p, grid, stream);
     return launch_dense<DenseCfg<128, 0, 6>>(p, grid, stream);
   } else {

@@ -45,19 +45,26 @@ struct DenseGemmParams {
   uint32_t reserved0;
   uint64_t timeout_ns;
   Status* status;
-  const void* bias;              // bf16, may be null
+  const void* bias;              // output dtype, may be null
   int64_t bias_row_stride;       // elements between bias rows; 0 = one row broadcast over M
+  const float* scale_a;          // optional per-tensor scales (fp8): D = (A*B^T) * sa * sb
+  const float* scale_b;
+  int32_t ab_fmt;                // tcgen05 operand format: kind::f16 0 = f16, 1 = bf16;
+                                 // kind::f8f6f4 0 = e4m3, 1 = e5m2
+  int32_t out_f16;               // 1: D, bias and staging are fp16 instead of bf16
   // all-gather
   const void* ag_src;            // this rank's shard [seg_rows, K]
   void* ag_land[kMaxRanks];      // landing buffer of every rank, [W][seg_rows][K]
-  uint32_t* ag_flags[kMaxRanks]; // on every rank: [W][m_tiles_seg] arrival counters
+  uint32_t* ag_flags[kMaxRanks]; // on every rank: [W src][m_tiles_seg] = last call whose rows landed
   // cross-rank start handshake
   uint32_t* start_ctr[kMaxRanks];  // on every rank: [W] last call number entered, by source
   // reduce-scatter
-  uint32_t* rs_ctr[kMaxRanks];   // on every rank: [m_tiles_seg] arrival counters
+  uint32_t* rs_ctr[kMaxRanks];   // on every rank: [m_tiles_seg][8 src] = last call whose tiles landed
+  uint32_t* local_cnt;           // local scratch [W][m_tiles_seg], zero between calls: counts the
+                                 // warps of this GPU that finished their part of one (peer, tile row)
   const void* rs_stage;          // local staging [W][seg_rows][N] bf16
   void* rs_out;                  // [seg_rows, N] bf16
-  uint32_t* rs_work;             // local work-claim counter
+  uint32_t* rs_work;             // local work-claim counter, zero between calls
 };
 
 template <int BN_, int KIND_, int STAGES_>
@@ -181,7 +188,7 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
           } else {
             tma = &p.tm_a_land;
             const uint32_t* f = p.ag_flags[p.rank] + c.seg * m_tiles_seg + c.m_tile;
-            flag_wait_ge(wc, f, p.epoch * gridDim.x * 2u, kSiteShardFlag);
+            flag_wait_ge(wc, f, p.epoch, kSiteShardFlag);
             ptx::fence_proxy_async_all();
           }
         }
@@ -201,8 +208,7 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = Cfg::KIND == 0 ? ptx::umma_idesc(1, 1, BM, BN)
-                                                : ptx::umma_idesc(0, 0, BM, BN);
+      const uint32_t idesc = ptx::umma_idesc(p.ab_fmt, p.ab_fmt, BM, BN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -270,7 +276,14 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
               if (i + u * 32 < count) ptx::st_global_v4(land + first + i + u * 32, v[u]);
           }
           __syncwarp();
-          if (lane == 0) ptx::red_add_release_sys(p.ag_flags[peer] + p.rank * m_tiles_seg + mt, 1u);
+          if (lane == 0) {
+            // the last of the 2*gridDim.x pushing warps publishes the tile row to the peer
+            uint32_t* cnt = p.local_cnt + d * m_tiles_seg + mt;
+            if (ptx::atom_add_acq_rel_sys(cnt, 1u) == static_cast<uint32_t>(ncw) - 1u) {
+              *cnt = 0;
+              ptx::st_release_sys(p.ag_flags[peer] + p.rank * m_tiles_seg + mt, p.epoch);
+            }
+          }
           __syncwarp();
         }
       }
@@ -280,7 +293,12 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     uint8_t* my_epi = epi_ptr + q * 2 * Cfg::EPI_BUF_BYTES;
     const uint32_t my_epi_u32 = epi_base + q * 2 * Cfg::EPI_BUF_BYTES;
-    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(p.bias);
+    const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.bias);
+    const bool f16 = p.out_f16 != 0;
+    float alpha = 1.f;
+    if (p.scale_a != nullptr) alpha *= *p.scale_a;
+    if (p.scale_b != nullptr) alpha *= *p.scale_b;
+    const bool scaled = p.scale_a != nullptr || p.scale_b != nullptr;
     int it = 0;
     uint32_t nstore = 0;
     bool started = !(multi && p.mode == kModeReduceScatter);
@@ -317,15 +335,23 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
           if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
         }
         const int col0 = c.n0 + ch * 64;
+        if (scaled) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            r0[j] = __float_as_uint(__uint_as_float(r0[j]) * alpha);
+            r1[j] = __float_as_uint(__uint_as_float(r1[j]) * alpha);
+          }
+        }
         if (bias != nullptr && col0 < p.N) {
-          const __nv_bfloat16* brow = bias + (p.bias_row_stride ? grow * p.bias_row_stride : 0);
+          const uint16_t* brow = bias + (p.bias_row_stride ? grow * p.bias_row_stride : 0);
           const bool row_ok = row < p.seg_rows;
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (row_ok && col0 + j < p.N)
-              r0[j] = __float_as_uint(__uint_as_float(r0[j]) + __bfloat162float(brow[col0 + j]));
+              r0[j] = __float_as_uint(__uint_as_float(r0[j]) + ptx::half_bits_to_float(brow[col0 + j], f16));
             if (row_ok && col0 + 32 + j < p.N)
-              r1[j] = __float_as_uint(__uint_as_float(r1[j]) + __bfloat162float(brow[col0 + 32 + j]));
+              r1[j] = __float_as_uint(__uint_as_float(r1[j]) +
+                                      ptx::half_bits_to_float(brow[col0 + 32 + j], f16));
           }
         }
         const uint32_t buf = nstore & 1u;
@@ -335,19 +361,19 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           uint4 v;
-          v.x = ptx::pack_bf16x2(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
-          v.y = ptx::pack_bf16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
-          v.z = ptx::pack_bf16x2(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
-          v.w = ptx::pack_bf16x2(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+          v.x = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+          v.y = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+          v.z = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+          v.w = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
           *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = v;
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           uint4 v;
-          v.x = ptx::pack_bf16x2(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
-          v.y = ptx::pack_bf16x2(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
-          v.z = ptx::pack_bf16x2(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
-          v.w = ptx::pack_bf16x2(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+          v.x = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+          v.y = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+          v.z = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+          v.w = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
           *reinterpret_cast<uint4*>(dst + (((j + 4) ^ (lane & 7)) << 4)) = v;
         }
         ptx::fence_proxy_async_smem();
@@ -363,7 +389,12 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
         if (lane == 0) {
           ptx::bulk_wait<0>();
           ptx::fence_proxy_async_all();
-          ptx::red_add_release_sys(p.rs_ctr[c.seg] + c.m_tile, 1u);
+          // the last of the n_tiles*4 warps that store into this tile row tells the owner
+          uint32_t* cnt = p.local_cnt + c.seg * m_tiles_seg + c.m_tile;
+          if (ptx::atom_add_acq_rel_sys(cnt, 1u) == static_cast<uint32_t>(n_tiles) * 4u - 1u) {
+            *cnt = 0;
+            ptx::st_release_sys(p.rs_ctr[c.seg] + c.m_tile * kMaxRanks + p.rank, p.epoch);
+          }
         }
         __syncwarp();
       }
@@ -383,21 +414,25 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
   // -------------------------------------------------------------------- reduce-scatter tail
   if (p.mode == kModeReduceScatter && multi) {
     // Sum the W slabs of the local staging buffer into rs_out. A work unit is kUnit 16-byte
-    // chunks (8 bf16) of the [seg_rows, N] output; units are claimed from a counter that only
-    // grows: every CTA makes exactly one failing claim per call.
+    // chunks (8 elements) of the [seg_rows, N] output; units are claimed from a counter. Every
+    // CTA makes exactly one failing claim, and whoever makes the very last claim of the launch
+    // puts the counter back to zero for the next call.
     constexpr int kUnit = 256 * 8;
     const int64_t chunks_per_row = p.N >> 3;
     const int64_t total_chunks = static_cast<int64_t>(p.seg_rows) * chunks_per_row;
     const uint32_t units = static_cast<uint32_t>((total_chunks + kUnit - 1) / kUnit);
-    const uint32_t claim_base = (p.epoch - 1u) * (units + gridDim.x);
-    const uint32_t per_mtile = p.epoch * static_cast<uint32_t>(p.world) * n_tiles * 4u;
     const uint4* stage = reinterpret_cast<const uint4*>(p.rs_stage);
     uint4* out = reinterpret_cast<uint4*>(p.rs_out);
     const int64_t slab_chunks = total_chunks;
     int verified_mt = -1;
+    const bool tail_f16 = p.out_f16 != 0;
     while (true) {
       __syncthreads();
-      if (threadIdx.x == 0) *claim_slot = atomicAdd(p.rs_work, 1u) - claim_base;
+      if (threadIdx.x == 0) {
+        const uint32_t got = atomicAdd(p.rs_work, 1u);
+        if (got == units + gridDim.x - 1u) atomicExch(p.rs_work, 0u);
+        *claim_slot = got;
+      }
       __syncthreads();
       const uint32_t u = *claim_slot;
       if (u >= units) break;
@@ -412,7 +447,8 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
           if (ok[h]) {
             const int mt = static_cast<int>((idx[h] / chunks_per_row) / BM);
             if (mt != verified_mt) {
-              flag_wait_ge(wc, p.rs_ctr[p.rank] + mt, per_mtile, kSiteTileCounter);
+              for (int src = 0; src < p.world; ++src)
+                flag_wait_ge(wc, p.rs_ctr[p.rank] + mt * kMaxRanks + src, p.epoch, kSiteTileCounter);
               verified_mt = mt;
             }
           }
@@ -436,20 +472,20 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
               const uint32_t w[4] = {v[s][h].x, v[s][h].y, v[s][h].z, v[s][h].w};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                accv[h][2 * e] += __uint_as_float(w[e] << 16);
-                accv[h][2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+                accv[h][2 * e] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] & 0xFFFFu), tail_f16);
+                accv[h][2 * e + 1] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] >> 16), tail_f16);
               }
             }
           }
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           if (!ok[h]) continue;
-          uint4 v;
-          v.x = ptx::pack_bf16x2(accv[h][0], accv[h][1]);
-          v.y = ptx::pack_bf16x2(accv[h][2], accv[h][3]);
-          v.z = ptx::pack_bf16x2(accv[h][4], accv[h][5]);
-          v.w = ptx::pack_bf16x2(accv[h][6], accv[h][7]);
-          out[idx[h]] = v;
+          uint4 o;
+          o.x = ptx::pack_half2(tail_f16, accv[h][0], accv[h][1]);
+          o.y = ptx::pack_half2(tail_f16, accv[h][2], accv[h][3]);
+          o.z = ptx::pack_half2(tail_f16, accv[h][4], accv[h][5]);
+          o.w = ptx::pack_half2(tail_f16, accv[h][6], accv[h][7]);
+          out[idx[h]] = o;
         }
       }
     }

@@ -1,2 +1,19 @@
-"""B200-native compute/communication overlap kernel library (work in progress)."""
+"""B200-native compute/communication overlap kernel library.
+
+The public names follow the reference's ``flux`` package (``python/flux/cpp_mod.py``): code
+written as ``import flux`` runs with ``import tempname_new_b200 as flux`` (or ``import fluxb as
+flux``).
+"""
 __version__ = "0.1.0"
+
+from . import _native  # noqa: F401
+from .ops.options import (A2ARingMode, AGRingMode, AllGatherOption, AllToAllOption,  # noqa: F401
+                          PreAttnAllToAllCommOp, ReduceScatterOption, RingMode,
+                          get_default_a2a_ring_mode, get_default_ag_ring_mode,
+                          get_default_rs_ring_mode)
+from .parallel.symm import (FluxTimeoutError, GroupBarrier, SymmBuffer, create_tensor_list,  # noqa: F401
+                            init_flux_shm)
+from .parallel.dist_env import DistEnvTP, DistEnvTPWithEP, MoeArguments  # noqa: F401
+from .ops.gemm_only import GemmOnly  # noqa: F401
+from .ops.gemm_rs import GemmRS  # noqa: F401
+from .ops.ag_gemm import AGKernel  # noqa: F401

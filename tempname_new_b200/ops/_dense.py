@@ -11,7 +11,7 @@ from .. import _native
 
 MAX_RANKS = 8
 PLAIN, ALLGATHER, REDUCE_SCATTER = 0, 1, 2
-BF16, FP8_E4M3, FP16, FP32 = 0, 1, 2, 3
+BF16, FP8_E4M3, FP16, FP32, FP8_E5M2 = 0, 1, 2, 3, 4
 
 _VP = ctypes.c_void_p
 
@@ -22,7 +22,8 @@ class DenseArgs(ctypes.Structure):
         ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldd", ctypes.c_int64),
         ("bias_row_stride", ctypes.c_int64),
         ("M", ctypes.c_int32), ("N", ctypes.c_int32), ("K", ctypes.c_int32),
-        ("in_dtype", ctypes.c_int32),
+        ("in_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
+        ("scale_a", _VP), ("scale_b", _VP),
         ("mode", ctypes.c_int32), ("rank", ctypes.c_int32), ("world", ctypes.c_int32),
         ("group_m", ctypes.c_int32), ("num_sms", ctypes.c_int32), ("tile_n", ctypes.c_int32),
         ("epoch", ctypes.c_uint32), ("reserved", ctypes.c_uint32),
@@ -31,7 +32,7 @@ class DenseArgs(ctypes.Structure):
         ("ag_land", _VP * MAX_RANKS), ("ag_flags", _VP * MAX_RANKS),
         ("start_ctr", _VP * MAX_RANKS),
         ("rs_stage", _VP * MAX_RANKS), ("rs_ctr", _VP * MAX_RANKS),
-        ("rs_out", _VP), ("rs_work", _VP),
+        ("rs_out", _VP), ("rs_work", _VP), ("local_cnt", _VP),
         ("stream", _VP),
     ]
 
@@ -45,6 +46,8 @@ def dtype_code(dt: torch.dtype) -> int:
         return FP16
     if dt == torch.float32:
         return FP32
+    if dt == torch.float8_e5m2:
+        return FP8_E5M2
     raise TypeError(f"unsupported dtype {dt}")
 
 
@@ -64,29 +67,64 @@ def run(args: DenseArgs) -> None:
     _native.check(rc, "fluxb_dense_gemm")
 
 
-def plain_gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor,
-               bias: Optional[torch.Tensor] = None, *, tile_n: int = 0, group_m: int = 0,
-               num_sms: int = 0, status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[M,N] = a[M,K] @ b[N,K]^T (+bias) on the tcgen05 kernel."""
-    assert a.is_cuda and b.is_cuda and out.is_cuda, "the sm_100a GEMM needs CUDA tensors"
-    assert a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1]
-    assert a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1
-    assert out.dtype == torch.bfloat16
-    M, K = a.shape
-    N = b.shape[0]
+def _as_scale(t: Optional[torch.Tensor], dev) -> Optional[torch.Tensor]:
+    if t is None:
+        return None
+    if t.dtype != torch.float32 or t.device != dev:
+        t = t.to(device=dev, dtype=torch.float32)
+    return t.reshape(-1)[:1].contiguous()
+
+
+def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
+              scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None, *,
+              tile_n: int = 0, group_m: int = 0, num_sms: int = 0,
+              status: Optional[torch.Tensor] = None, keep: Optional[list] = None) -> DenseArgs:
+    """Fill the operand part of a DenseArgs for A[rows,K], B[N,K]."""
+    if not (a.is_cuda and b.is_cuda):
+        raise RuntimeError("the sm_100a GEMM kernels need CUDA tensors")
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
+        raise ValueError(f"shape mismatch: A {tuple(a.shape)} B {tuple(b.shape)} (B is [N, K])")
+    if a.stride(1) != 1 or b.stride(1) != 1:
+        raise ValueError("A and B must have a contiguous K dimension")
+    if a.dtype != b.dtype:
+        raise TypeError("A and B must share a dtype")
     args = DenseArgs()
-    args.a, args.b, args.d = a.data_ptr(), b.data_ptr(), out.data_ptr()
-    args.lda, args.ldb, args.ldd = a.stride(0), b.stride(0), out.stride(0)
+    args.a, args.b = a.data_ptr(), b.data_ptr()
+    args.lda, args.ldb = a.stride(0), b.stride(0)
+    args.N, args.K = b.shape[0], a.shape[1]
+    args.in_dtype = dtype_code(a.dtype)
+    args.out_dtype = dtype_code(out_dtype)
     if bias is not None:
-        assert bias.dtype == torch.bfloat16 and bias.shape[-1] == N
+        if bias.dtype != out_dtype or bias.shape[-1] != b.shape[0] or bias.stride(-1) != 1:
+            raise ValueError("bias must be [1|M, N] in the output dtype")
         args.bias = bias.data_ptr()
         args.bias_row_stride = 0 if (bias.dim() == 1 or bias.shape[0] == 1) else bias.stride(0)
-    args.M, args.N, args.K = M, N, K
-    args.in_dtype = dtype_code(a.dtype)
-    args.mode, args.rank, args.world = PLAIN, 0, 1
+    sa, sb = _as_scale(scale_a, a.device), _as_scale(scale_b, a.device)
+    if sa is not None:
+        args.scale_a = sa.data_ptr()
+    if sb is not None:
+        args.scale_b = sb.data_ptr()
+    if keep is not None:
+        keep.extend([sa, sb])
     args.group_m, args.num_sms, args.tile_n = group_m, num_sms, tile_n
-    args.epoch = 1
     args.status = status.data_ptr() if status is not None else None
     args.stream = current_stream_ptr(a.device)
+    return args
+
+
+def plain_gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor,
+               bias: Optional[torch.Tensor] = None, scale_a: Optional[torch.Tensor] = None,
+               scale_b: Optional[torch.Tensor] = None, *, tile_n: int = 0, group_m: int = 0,
+               num_sms: int = 0, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M,N] = a[M,K] @ b[N,K]^T (* scales) (+bias) on the tcgen05 kernel."""
+    keep: list = []
+    args = base_args(a, b, bias, out.dtype, scale_a, scale_b, tile_n=tile_n, group_m=group_m,
+                     num_sms=num_sms, status=status, keep=keep)
+    if out.stride(1) != 1 or out.shape != (a.shape[0], b.shape[0]):
+        raise ValueError("output must be [M, N] with contiguous rows")
+    args.d, args.ldd = out.data_ptr(), out.stride(0)
+    args.M = a.shape[0]
+    args.mode, args.rank, args.world = PLAIN, 0, 1
+    args.epoch = 1
     run(args)
     return out

@@ -1,0 +1,80 @@
+"""State shared by the fused dense ops: the per-op control block in symmetric memory (start
+flags, arrival counters), the call counter ("epoch") that replaces per-call flag resets, and
+the device status word that bounded waits report into."""
+from __future__ import annotations
+
+import os
+import time
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..parallel.symm import FluxTimeoutError, SymmBuffer
+
+# byte offsets inside the control block
+OFF_START = 0          # [8] uint32  last call number entered, by source rank
+OFF_WORK = 64          # [1] uint32  work-claim counter of the reduce tail
+OFF_CTR = 128          # arrival flags written by peers, op specific (up to 32 KiB)
+OFF_LOCAL = 32 * 1024  # local arrival scratch (never touched by peers)
+CTRL_BYTES = 64 * 1024
+MAX_FLAG_WORDS = (OFF_LOCAL - OFF_CTR) // 4
+
+SITE_NAMES = {
+    1: "smem-empty barrier", 2: "smem-full barrier", 3: "tmem-empty barrier", 4: "tmem-full barrier",
+    5: "start handshake", 6: "all-gather shard flag", 7: "reduce-scatter tile counter",
+    8: "barrier_all", 9: "inplace cast", 10: "all-to-all flag", 11: "MoE flag", 12: "test wait",
+}
+
+
+class FusedOpBase:
+    def __init__(self, pg, nnodes: int = 1, timeout_s: Optional[float] = None):
+        if nnodes != 1:
+            raise NotImplementedError(
+                "multi-node operation is outside the single NVSwitch domain this library targets")
+        self.pg = pg if pg is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.pg)
+        self.world = dist.get_world_size(self.pg)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks (one NVSwitch node)")
+        self.epoch = 0
+        env_t = os.environ.get("FLUXB_WAIT_TIMEOUT_S")
+        self.timeout_s = timeout_s if timeout_s is not None else (float(env_t) if env_t else 5.0)
+        self.ctrl = SymmBuffer(CTRL_BYTES, self.pg)
+        self.is_cuda = self.ctrl.is_cuda
+        self.device = self.ctrl.device
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device) if self.is_cuda else None
+        self.check_every_call = os.environ.get("FLUXB_CHECK_STATUS", "0") == "1"
+
+    # -- device status ---------------------------------------------------------------
+    def check_status(self) -> None:
+        """Synchronise and raise FluxTimeoutError if a device wait of this op gave up."""
+        if self.status is None:
+            return
+        st = self.status.tolist()
+        if st[0] != 0:
+            self.status.zero_()
+            raise FluxTimeoutError(
+                f"{type(self).__name__}: device wait '{SITE_NAMES.get(st[0], st[0])}' timed out in "
+                f"block {st[1]} (saw {st[2] & 0xFFFFFFFF}, expected {st[3] & 0xFFFFFFFF})")
+
+    def _after_launch(self) -> None:
+        if self.check_every_call:
+            self.check_status()
+
+    # -- CPU emulation of the flag protocol -------------------------------------------
+    def _cpu_words(self, r: int, off: int, n: int) -> torch.Tensor:
+        return self.ctrl.view(r, torch.int32, (n,), off)
+
+    def _cpu_wait(self, words: torch.Tensor, expected: int, what: str) -> None:
+        deadline = time.monotonic() + self.timeout_s
+        while int(words.min()) < expected:
+            if time.monotonic() > deadline:
+                late = [i for i in range(words.numel()) if int(words[i]) < expected]
+                raise FluxTimeoutError(f"{type(self).__name__}: {what} timed out waiting for {late}")
+            time.sleep(0.0002)
+
+    def _cpu_start_handshake(self) -> None:
+        for r in range(self.world):
+            self._cpu_words(r, OFF_START, 8)[self.rank] = self.epoch
+        self._cpu_wait(self._cpu_words(self.rank, OFF_START, 8)[: self.world], self.epoch, "start handshake")

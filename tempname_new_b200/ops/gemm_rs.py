@@ -1,0 +1,124 @@
+"""``GemmRS``: GEMM fused with reduce-scatter (row-parallel linear forward).
+
+``out[M/W, N] = reduce_scatter_M(input[M, K/W] @ weight[N, K/W]^T (+bias))``
+
+On CUDA one persistent tcgen05 kernel does everything: each output tile of M-segment ``s``
+leaves the epilogue as a TMA store straight into rank ``s``'s staging slab ``[this rank]``
+over NVLink, segments are visited ``rank+1, rank+2, …, rank`` so that every step is a
+permutation on the switch, an arrival counter per tile row is bumped once the store has
+landed, and the tail of the same kernel sums the ``W`` slabs in fp32 in a fixed order.
+Reference: ``flux.GemmRS`` (``src/pybind/gemm_rs.cc:28-92``,
+``src/gemm_rs/ths_op/gemm_reduce_scatter.cc``); there the sm90 path pulls tiles with TMA into
+a ``[W, M/W, N]`` buffer and a separate kernel reduces it.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _dense
+from ._fused_base import MAX_FLAG_WORDS, OFF_CTR, OFF_LOCAL, OFF_START, OFF_WORK, FusedOpBase
+from .gemm_only import _out_dtype, as_nk
+from .options import ReduceScatterOption
+from ..parallel.symm import SymmBuffer, _ELEM
+
+
+class GemmRS(FusedOpBase):
+    def __init__(self, tp_group, nnodes: int, max_m: int, n_dim: int, input_dtype: torch.dtype,
+                 output_dtype: Optional[torch.dtype] = None, transpose_weight: bool = False,
+                 fuse_reduction: bool = False, ring_reduction: bool = False,
+                 timeout_s: Optional[float] = None):
+        super().__init__(tp_group, nnodes, timeout_s)
+        self.max_m, self.n_dim = max_m, n_dim
+        self.input_dtype = input_dtype
+        self.output_dtype = _out_dtype(input_dtype, output_dtype)
+        self.transpose_weight = transpose_weight
+        self.fuse_reduction = fuse_reduction      # accepted; the reduction is always fused in-kernel
+        self.ring_reduction = ring_reduction      # accepted; the sum order is fixed (rank 0..W-1)
+        if max_m % self.world != 0:
+            raise ValueError("max_m must be a multiple of the world size")
+        if (max_m // self.world + 127) // 128 * 8 > MAX_FLAG_WORDS:
+            raise ValueError("max_m too large for the flag block")
+        # staging: W slabs of [max_m / W, N] on every rank
+        self.stage = SymmBuffer(max_m * n_dim * _ELEM[self.output_dtype], self.pg) if self.world > 1 else None
+
+    def zero_buffers(self) -> None:
+        """Kept for API compatibility: counters carry the call number, nothing needs zeroing."""
+
+    # ------------------------------------------------------------------------------------
+    def forward(self, input: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                input_scale: Optional[torch.Tensor] = None, weight_scale: Optional[torch.Tensor] = None,
+                output_scale: Optional[torch.Tensor] = None, fast_accum: bool = False,
+                reduce_scatter_option: Optional[ReduceScatterOption] = None) -> torch.Tensor:
+        w = as_nk(weight, self.transpose_weight)
+        M, N = input.shape[0], w.shape[0]
+        if M > self.max_m or N != self.n_dim:
+            raise ValueError(f"GemmRS was built for M <= {self.max_m}, N = {self.n_dim}; got M={M}, N={N}")
+        if M % self.world != 0:
+            raise ValueError("M must be a multiple of the world size")
+        self.epoch += 1
+        if not input.is_cuda:
+            return self._forward_cpu(input, w, bias, input_scale, weight_scale)
+        a = input if input.stride(-1) == 1 else input.contiguous()
+        out = torch.empty((M // self.world, N), dtype=self.output_dtype, device=input.device)
+        keep: list = []
+        args = _dense.base_args(a, w, bias, self.output_dtype, input_scale, weight_scale,
+                                status=self.status, keep=keep)
+        args.M = M
+        args.mode, args.rank, args.world = _dense.REDUCE_SCATTER, self.rank, self.world
+        args.epoch = self.epoch
+        args.timeout_ns = int(self.timeout_s * 1e9)
+        args.rs_out = out.data_ptr()
+        if self.world > 1:
+            for r in range(self.world):
+                args.rs_stage[r] = self.stage.ptr(r)
+                args.rs_ctr[r] = self.ctrl.ptr(r, OFF_CTR)
+                args.start_ctr[r] = self.ctrl.ptr(r, OFF_START)
+            args.rs_work = self.ctrl.ptr(self.rank, OFF_WORK)
+            args.local_cnt = self.ctrl.ptr(self.rank, OFF_LOCAL)
+        _dense.run(args)
+        self._after_launch()
+        return out
+
+    __call__ = forward
+
+    def forward_barrier(self, input, weight, bias=None):
+        """Reference API: the barrier between GEMM and reduction. The fused kernel needs none."""
+
+    def forward_reduce_scatter(self, input, weight, bias=None, input_scale=None, weight_scale=None):
+        return self.forward(input, weight, bias, input_scale, weight_scale)
+
+    def profiling(self, input, weight, bias=None, input_scale=None, weight_scale=None, output_scale=None,
+                  fast_accum=False, reduce_scatter_option=None, prof_ctx=None):
+        from ..tuning.profiling import profile_call
+        return profile_call(self, "gemm_rs", lambda: self.forward(input, weight, bias, input_scale, weight_scale),
+                            prof_ctx)
+
+    # ------------------------------------------------------------------------------------
+    def _forward_cpu(self, a, w, bias, sa, sb):
+        """Same data movement on shared host memory: push each partial segment into the owner's
+        slab, signal, then the owner sums its W slabs in rank order."""
+        W, r = self.world, self.rank
+        M, N = a.shape[0], w.shape[0]
+        seg = M // W
+        part = a.float() @ w.float().t()
+        if sa is not None:
+            part = part * sa.float()
+        if sb is not None:
+            part = part * sb.float()
+        if bias is not None:
+            part = part + bias.float()
+        part = part.to(self.output_dtype)
+        if W == 1:
+            return part
+        self._cpu_start_handshake()
+        for d in range(1, W + 1):
+            s = (r + d) % W
+            slab = self.stage.view(s, self.output_dtype, (W, seg, N))
+            slab[r].copy_(part[s * seg:(s + 1) * seg])
+            self._cpu_words(s, OFF_CTR, 8)[r] = self.epoch
+        self._cpu_wait(self._cpu_words(r, OFF_CTR, 8)[:W], self.epoch, "reduce-scatter arrivals")
+        mine = self.stage.view(r, self.output_dtype, (W, seg, N))
+        return mine.float().sum(0).to(self.output_dtype)

@@ -1,0 +1,83 @@
+"""CPU/gloo world_size=2 plumbing: GEMM-RS and AG-GEMM through the public ops on shared host
+memory, checked against torch.matmul + dist.reduce_scatter / all_gather."""
+import torch
+import torch.distributed as dist
+
+from conftest import run_gloo
+
+
+def _data(rows, cols, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(rows, cols, generator=g) / (k ** 0.5)
+
+
+def _gemm_rs(rank, world):
+    import tempname_new_b200 as flux
+    flux.init_flux_shm()
+    M, Kl, N = 256, 256, 384
+    a = _data(M, Kl, Kl * world, 0 + rank)
+    w = _data(N, Kl, Kl * world, 100 + rank)
+    op = flux.GemmRS(dist.group.WORLD, 1, M, N, torch.float32)
+    for _ in range(3):  # repeated calls exercise the call-number flags
+        out = op.forward(a, w)
+        full = a @ w.t()
+        ref = torch.empty(M // world, N)
+        dist.reduce_scatter(ref, list(full.chunk(world)))
+        assert out.shape == ref.shape
+        torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
+    bias = _data(M, N, 1, 7)
+    out = op.forward(a, w, bias=bias)  # bias is added on every rank, i.e. W times after the sum
+    full = a @ w.t() + bias
+    dist.reduce_scatter(ref, list(full.chunk(world)))
+    torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
+
+
+def _ag_gemm(rank, world):
+    import tempname_new_b200 as flux
+    flux.init_flux_shm()
+    seg, K, Nl = 128, 512, 192
+    a = _data(seg, K, K, 0 + rank)
+    w = _data(Nl, K, K, 100 + rank)
+    op = flux.AGKernel(dist.group.WORLD, 1, seg * world, Nl, K, torch.float32)
+    for _ in range(3):
+        gathered = torch.empty(seg * world, K)
+        out = op.forward(a, w, gathered_input=gathered)
+        parts = [torch.empty_like(a) for _ in range(world)]
+        dist.all_gather(parts, a)
+        full = torch.cat(parts)
+        torch.testing.assert_close(gathered, full, rtol=0, atol=0)
+        torch.testing.assert_close(out, full @ w.t(), rtol=1e-5, atol=1e-5)
+    wt = w.t().contiguous()
+    out_t = op.forward(a, wt, transpose_weight=True)
+    torch.testing.assert_close(out_t, out, rtol=1e-6, atol=1e-6)
+
+
+def _symm(rank, world):
+    import tempname_new_b200 as flux
+    ts = flux.create_tensor_list((4, 8), torch.float32)
+    assert len(ts) == world
+    ts[rank].fill_(rank + 1)
+    gb = flux.GroupBarrier()
+    gb.barrier_all()
+    for r in range(world):
+        assert float(ts[r].sum()) == (r + 1) * 32
+    gb.barrier_all()
+    ts[(rank + 1) % world][0, 0] = -5.0  # write into the neighbour's block
+    gb.barrier_all()
+    assert float(ts[rank][0, 0]) == -5.0
+
+
+def test_gemm_rs_gloo_w2():
+    run_gloo(_gemm_rs, 2)
+
+
+def test_ag_gemm_gloo_w2():
+    run_gloo(_ag_gemm, 2)
+
+
+def test_gemm_rs_gloo_w4():
+    run_gloo(_gemm_rs, 4)
+
+
+def test_symmetric_memory_and_barrier_gloo():
+    run_gloo(_symm, 3)
