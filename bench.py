@@ -1,0 +1,269 @@
+#!/usr/bin/env python
+"""Headline benchmark: the tensor-parallel MLP block of GPT-3-175B (hidden 12288, ffn 49152,
+8192 tokens) as AG+GEMM followed by GEMM+RS, bf16, TP = number of GPUs.
+
+    python bench.py --gpus N --steps K --warmup W            # this library (default)
+    python bench.py --impl reference ...                     # the reference (unavailable here)
+    python bench.py --impl torch ...                         # torch.matmul + NCCL, same step
+
+For N > 1 launch with ``python -m torch.distributed.run --nnodes=1 --nproc-per-node N
+--master-addr 127.0.0.1 --master-port P bench.py --gpus N ...``. Rank 0 prints one JSON line.
+
+A step is: all-gather the sequence-sharded activations [8192/N, 12288] fused into the fc1 GEMM
+(weight shard [49152/N, 12288]), then the fc2 GEMM (weight shard [12288, 49152/N]) fused with
+the reduce-scatter back to [8192/N, 12288]. Total work is fixed as N grows (strong scaling):
+4 * 8192 * 12288 * 49152 FLOP per step over the whole job.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+TOKENS, HIDDEN, FFN = 8192, 12288, 49152
+METRIC = "fused-op TFLOPS (AG-GEMM + GEMM-RS, GPT-3-175B TP MLP shapes)"
+REFERENCE_UNAVAILABLE = (
+    "reference (Flux 1.1.2 fork) cannot be installed offline: pip install --no-index of /root/reference "
+    "fails (setup.py tries to download a cached wheel, then builds with no sources because 3rdparty/cutlass, "
+    "3rdparty/nccl are empty submodules and NVSHMEM is absent); it also has no sm_100 kernels")
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="fluxb", choices=["fluxb", "reference", "torch"])
+    ap.add_argument("--tokens", type=int, default=TOKENS)
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled while the benchmark runs (read-only)."""
+
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.windows = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.gpu_index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def mark(self, t0, t1):
+        self.windows.append((t0, t1))
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        import datetime
+        rows = []
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(parts[2]), float(parts[3]), parts[5:9]))
+            except ValueError:
+                continue
+        sel = [r for r in rows if any(a - 0.05 <= r[0] <= b + 0.05 for a, b in self.windows)] or rows
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in sel:
+            for n, v in zip(names, r[3]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {
+            "sm_mhz": statistics.median(r[1] for r in sel) if sel else None,
+            "sm_max_mhz": sel[0][2] if sel else None,
+            "reasons": sorted(reasons),
+            "samples": len(sel),
+        }
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29500")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    pg = dist.group.WORLD
+
+    import tempname_new_b200 as flux
+    from tempname_new_b200 import _native
+    from tempname_new_b200.models.tp_mlp import TPMLP
+
+    flux.init_flux_shm(pg)
+    M = args.tokens
+    seg = M // world
+    torch.manual_seed(1234 + rank)
+    x = torch.randn(seg, HIDDEN, device=dev).bfloat16()          # inputs N(0,1)
+    x_pinned = torch.randn(seg, HIDDEN).bfloat16().pin_memory()
+    flops_step = 4.0 * M * HIDDEN * FFN
+
+    if args.impl == "fluxb":
+        mlp = TPMLP(HIDDEN, FFN, pg, bias=False, dtype=torch.bfloat16, device=dev, act="none")  # weights N(0,0.02)
+        mlp.requires_grad_(False)
+
+        def step():
+            with torch.no_grad():
+                return mlp(x)
+
+        res_pinned = torch.empty(1 + HIDDEN, dtype=torch.float32).pin_memory()
+
+        def step_e2e():
+            return mlp.forward_host(x_pinned, res_pinned)
+    else:
+        w1 = (torch.randn(FFN // world, HIDDEN, device=dev) * 0.02).bfloat16()
+        w2 = (torch.randn(HIDDEN, FFN // world, device=dev) * 0.02).bfloat16()
+        full = torch.empty(M, HIDDEN, device=dev, dtype=torch.bfloat16)
+        out = torch.empty(seg, HIDDEN, device=dev, dtype=torch.bfloat16)
+        res_pinned = torch.empty(1 + HIDDEN, dtype=torch.float32).pin_memory()
+
+        def torch_step(xin):
+            if world > 1:
+                dist.all_gather_into_tensor(full, xin)
+                h = torch.matmul(full, w1.t())
+                part = torch.matmul(h, w2.t())
+                dist.reduce_scatter_tensor(out, part)
+                return out
+            h = torch.matmul(xin, w1.t())
+            return torch.matmul(h, w2.t())
+
+        def step():
+            return torch_step(x)
+
+        def step_e2e():
+            y = torch_step(x_pinned.to(dev, non_blocking=True))
+            res = torch.cat([y.float().abs().mean().reshape(1), y[0].float()])
+            res_pinned.copy_(res, non_blocking=True)
+            return res_pinned
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.time()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t1 = time.time()
+        dist.barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        if sampler:
+            sampler.mark(t0, t1)
+        return float(ms.item()) / steps
+
+    warmup = max(args.warmup, 3)
+    launches0 = _native.launch_count()
+    ms_step = timed(step, args.steps, warmup)
+    launches = _native.launch_count() - launches0 - (warmup * 2 if args.impl == "fluxb" else 0)
+
+    e2e = None
+    if not args.no_e2e:
+        ms_e2e = timed(step_e2e, args.steps, warmup)
+        e2e = {"value": flops_step / ms_e2e / 1e9, "unit": "TFLOPS", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": x_pinned.numel() * x_pinned.element_size(),
+               "d2h_bytes_per_step": res_pinned.numel() * res_pinned.element_size()}
+
+    clocks = sampler.stop() if sampler else None
+
+    # informational: the same step on torch.matmul + NCCL, and each fused op alone
+    extra = {}
+    if args.impl == "fluxb":
+        op_ag = mlp.fc1._cache.ag(M, FFN // world, HIDDEN, torch.bfloat16)
+        op_rs = mlp.fc2._cache.rs(M, HIDDEN, torch.bfloat16)
+        h = torch.empty(M, FFN // world, device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():
+            extra["ag_gemm_ms"] = timed(lambda: op_ag.forward(x, mlp.fc1.weight, output=h), 10, 3)
+            extra["gemm_rs_ms"] = timed(lambda: op_rs.forward(h, mlp.fc2.weight), 10, 3)
+        op_ag.check_status()
+        op_rs.check_status()
+        peaks = {}
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peaks = json.load(f)
+        except OSError:
+            pass
+        peak_tf = peaks.get("bf16_tflops_sustained", 1400.0)
+        link_gbs = 770.0
+        half = flops_step / 2 / world
+        t_compute = half / (peak_tf * 1e9)                                 # ms per op per GPU
+        ag_bytes = (world - 1) / world * M * HIDDEN * 2
+        rs_bytes = (world - 1) / world * M * HIDDEN * 2
+        extra["roofline"] = {
+            "peak_tflops": peak_tf, "peak_source": "measured sustained" if peaks else "fallback",
+            "nvlink_gbs": link_gbs,
+            "ag_gemm_frac": max(t_compute, ag_bytes / (link_gbs * 1e6)) / extra["ag_gemm_ms"],
+            "gemm_rs_frac": max(t_compute, rs_bytes / (link_gbs * 1e6)) / extra["gemm_rs_ms"],
+        }
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": flops_step / ms_step / 1e9, "unit": "TFLOPS", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": "fluxb" if args.impl == "fluxb" else "torch_nccl",
+            "config": {"model": "GPT-3-175B TP MLP block (AG-GEMM M=8192 K=12288 N=49152/W; GEMM-RS M=8192 "
+                                "K=49152/W N=12288)", "global_batch": M, "seq_len": M,
+                       "parallelism": f"tp{world}",
+                       "l2": "weights (>=151 MB per GEMM) exceed the 126 MB L2, no extra flush"},
+            "clocks": clocks, "e2e": e2e,
+            "gpu_launches": max(launches, 0),
+        }
+        line.update(extra)
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

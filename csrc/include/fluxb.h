@@ -48,6 +48,8 @@ typedef struct {
   int32_t group_m;           /* 0 = default raster group */
   int32_t num_sms;           /* 0 = all */
   int32_t tile_n;            /* 0 = auto, else 128 | 256 */
+  int32_t act;               /* epilogue activation after bias: 0 none, 1 gelu(tanh), 2 relu, 3 silu */
+  int32_t reserved2;
   uint32_t epoch;            /* call number of the owning op, starting at 1 */
   uint32_t reserved;
   uint64_t timeout_ns;       /* 0 = default (2 s) */

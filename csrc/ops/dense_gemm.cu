@@ -70,6 +70,7 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   p.scale_b = a->scale_b;
   p.ab_fmt = (a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP8_E5M2) ? 1 : 0;
   p.out_f16 = a->out_dtype == FLUXB_FP16 ? 1 : 0;
+  p.act = a->act;
 
   int bn = a->tile_n;
   if (bn == 0) bn = (a->N % 256 == 0 || a->N > 2048) ? 256 : 128;

@@ -52,6 +52,8 @@ struct DenseGemmParams {
   int32_t ab_fmt;                // tcgen05 operand format: kind::f16 0 = f16, 1 = bf16;
                                  // kind::f8f6f4 0 = e4m3, 1 = e5m2
   int32_t out_f16;               // 1: D, bias and staging are fp16 instead of bf16
+  int32_t act;                   // epilogue activation after bias: 0 none, 1 gelu(tanh), 2 relu, 3 silu
+  int32_t reserved1;
   // all-gather
   const void* ag_src;            // this rank's shard [seg_rows, K]
   void* ag_land[kMaxRanks];      // landing buffer of every rank, [W][seg_rows][K]
@@ -352,6 +354,13 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
             if (row_ok && col0 + 32 + j < p.N)
               r1[j] = __float_as_uint(__uint_as_float(r1[j]) +
                                       ptx::half_bits_to_float(brow[col0 + 32 + j], f16));
+          }
+        }
+        if (p.act != 0) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            r0[j] = __float_as_uint(ptx::activate(__uint_as_float(r0[j]), p.act));
+            r1[j] = __float_as_uint(ptx::activate(__uint_as_float(r1[j]), p.act));
           }
         }
         const uint32_t buf = nstore & 1u;

@@ -396,6 +396,19 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// epilogue activations: 1 gelu (tanh form), 2 relu, 3 silu
+__device__ __forceinline__ float activate(float x, int kind) {
+  if (kind == 1) {
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    // tanh(u) = 1 - 2 / (exp(2u) + 1)
+    const float t = 1.f - 2.f / (__expf(2.f * u) + 1.f);
+    return 0.5f * x * (1.f + t);
+  }
+  if (kind == 2) return fmaxf(x, 0.f);
+  if (kind == 3) return x / (1.f + __expf(-x));
+  return x;
+}
+
 // 16-bit float (bf16 or fp16, chosen at run time) helpers for epilogues
 __device__ __forceinline__ float half_bits_to_float(uint16_t b, bool f16) {
   if (f16) return __half2float(__ushort_as_half(b));

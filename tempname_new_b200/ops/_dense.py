@@ -11,6 +11,7 @@ from .. import _native
 
 MAX_RANKS = 8
 PLAIN, ALLGATHER, REDUCE_SCATTER = 0, 1, 2
+ACT = {None: 0, "none": 0, "gelu": 1, "gelu_tanh": 1, "relu": 2, "silu": 3}
 BF16, FP8_E4M3, FP16, FP32, FP8_E5M2 = 0, 1, 2, 3, 4
 
 _VP = ctypes.c_void_p
@@ -26,6 +27,7 @@ class DenseArgs(ctypes.Structure):
         ("scale_a", _VP), ("scale_b", _VP),
         ("mode", ctypes.c_int32), ("rank", ctypes.c_int32), ("world", ctypes.c_int32),
         ("group_m", ctypes.c_int32), ("num_sms", ctypes.c_int32), ("tile_n", ctypes.c_int32),
+        ("act", ctypes.c_int32), ("reserved2", ctypes.c_int32),
         ("epoch", ctypes.c_uint32), ("reserved", ctypes.c_uint32),
         ("timeout_ns", ctypes.c_uint64),
         ("status", _VP),
@@ -77,7 +79,7 @@ def _as_scale(t: Optional[torch.Tensor], dev) -> Optional[torch.Tensor]:
 
 def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
               scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None, *,
-              tile_n: int = 0, group_m: int = 0, num_sms: int = 0,
+              tile_n: int = 0, group_m: int = 0, num_sms: int = 0, act: Optional[str] = None,
               status: Optional[torch.Tensor] = None, keep: Optional[list] = None) -> DenseArgs:
     """Fill the operand part of a DenseArgs for A[rows,K], B[N,K]."""
     if not (a.is_cuda and b.is_cuda):
@@ -107,6 +109,7 @@ def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], ou
     if keep is not None:
         keep.extend([sa, sb])
     args.group_m, args.num_sms, args.tile_n = group_m, num_sms, tile_n
+    args.act = ACT[act]
     args.status = status.data_ptr() if status is not None else None
     args.stream = current_stream_ptr(a.device)
     return args
@@ -115,11 +118,12 @@ def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], ou
 def plain_gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor,
                bias: Optional[torch.Tensor] = None, scale_a: Optional[torch.Tensor] = None,
                scale_b: Optional[torch.Tensor] = None, *, tile_n: int = 0, group_m: int = 0,
-               num_sms: int = 0, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+               num_sms: int = 0, act: Optional[str] = None,
+               status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[M,N] = a[M,K] @ b[N,K]^T (* scales) (+bias) on the tcgen05 kernel."""
     keep: list = []
     args = base_args(a, b, bias, out.dtype, scale_a, scale_b, tile_n=tile_n, group_m=group_m,
-                     num_sms=num_sms, status=status, keep=keep)
+                     num_sms=num_sms, act=act, status=status, keep=keep)
     if out.stride(1) != 1 or out.shape != (a.shape[0], b.shape[0]):
         raise ValueError("output must be [M, N] with contiguous rows")
     args.d, args.ldd = out.data_ptr(), out.stride(0)

@@ -18,7 +18,7 @@ import torch
 
 from . import _dense
 from ._fused_base import MAX_FLAG_WORDS, OFF_CTR, OFF_LOCAL, OFF_START, FusedOpBase
-from .gemm_only import _out_dtype, as_nk
+from .gemm_only import _out_dtype, apply_act, as_nk
 from .options import AllGatherOption
 from ..parallel.symm import SymmBuffer, _ELEM
 
@@ -43,7 +43,8 @@ class AGKernel(FusedOpBase):
                 weight_scale: Optional[torch.Tensor] = None, output_scale: Optional[torch.Tensor] = None,
                 fast_accum: bool = False, transpose_weight: bool = False,
                 all_gather_option: Optional[AllGatherOption] = None,
-                gathered_input: Optional[torch.Tensor] = None) -> torch.Tensor:
+                gathered_input: Optional[torch.Tensor] = None, act: Optional[str] = None) -> torch.Tensor:
+        """``act`` (not in the reference API) fuses gelu / relu / silu after the bias."""
         w = as_nk(weight, transpose_weight)
         seg, K = input.shape
         M, N = seg * self.world, w.shape[0]
@@ -51,12 +52,12 @@ class AGKernel(FusedOpBase):
             raise ValueError(f"AGKernel was built for M <= {self.full_m}, K = {self.k_dim}; got M={M}, K={K}")
         self.epoch += 1
         if not input.is_cuda:
-            return self._forward_cpu(input, w, bias, output, input_scale, weight_scale, gathered_input)
+            return self._forward_cpu(input, w, bias, output, input_scale, weight_scale, gathered_input, act)
         a = input if input.is_contiguous() else input.contiguous()
         out = output if output is not None else torch.empty((M, N), dtype=self.output_dtype, device=input.device)
         keep: list = []
         args = _dense.base_args(a, w, bias, self.output_dtype, input_scale, weight_scale,
-                                status=self.status, keep=keep)
+                                act=act, status=self.status, keep=keep)
         args.M = M
         args.d, args.ldd = out.data_ptr(), out.stride(0)
         args.mode, args.rank, args.world = _dense.ALLGATHER, self.rank, self.world
@@ -103,7 +104,7 @@ class AGKernel(FusedOpBase):
         return profile_call(self, "ag_gemm", lambda: self.forward(
             input, weight, bias, output, input_scale, weight_scale, transpose_weight=transpose_weight), prof_ctx)
 
-    def _forward_cpu(self, a, w, bias, output, sa, sb, gathered_input):
+    def _forward_cpu(self, a, w, bias, output, sa, sb, gathered_input, act=None):
         W, r = self.world, self.rank
         seg, K = a.shape
         if W > 1:
@@ -127,6 +128,7 @@ class AGKernel(FusedOpBase):
             acc = acc * sb.float()
         if bias is not None:
             acc = acc + bias.float()
+        acc = apply_act(acc, act)
         res = acc.to(self.output_dtype)
         if gathered_input is not None:
             gathered_input.copy_(full)

@@ -27,6 +27,19 @@ def as_nk(weight: torch.Tensor, transpose_weight: bool) -> torch.Tensor:
     return w if w.stride(-1) == 1 else w.contiguous()
 
 
+def apply_act(x: torch.Tensor, act: Optional[str]) -> torch.Tensor:
+    """Torch statement of the epilogue activations of the dense kernel."""
+    if act in (None, "none"):
+        return x
+    if act in ("gelu", "gelu_tanh"):
+        return torch.nn.functional.gelu(x, approximate="tanh")
+    if act == "relu":
+        return torch.relu(x)
+    if act == "silu":
+        return torch.nn.functional.silu(x)
+    raise ValueError(f"unknown activation {act}")
+
+
 class GemmOnly:
     def __init__(self, input_dtype: torch.dtype, weight_dtype: Optional[torch.dtype] = None,
                  output_dtype: Optional[torch.dtype] = None, transpose_weight: bool = False,

@@ -51,8 +51,10 @@ class GemmRS(FusedOpBase):
     def forward(self, input: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
                 input_scale: Optional[torch.Tensor] = None, weight_scale: Optional[torch.Tensor] = None,
                 output_scale: Optional[torch.Tensor] = None, fast_accum: bool = False,
-                reduce_scatter_option: Optional[ReduceScatterOption] = None) -> torch.Tensor:
-        w = as_nk(weight, self.transpose_weight)
+                reduce_scatter_option: Optional[ReduceScatterOption] = None,
+                transpose_weight_override: Optional[bool] = None) -> torch.Tensor:
+        tw = self.transpose_weight if transpose_weight_override is None else transpose_weight_override
+        w = as_nk(weight, tw)
         M, N = input.shape[0], w.shape[0]
         if M > self.max_m or N != self.n_dim:
             raise ValueError(f"GemmRS was built for M <= {self.max_m}, N = {self.n_dim}; got M={M}, N={N}")

@@ -1,0 +1,132 @@
+"""GPU numerics of the tcgen05 dense kernel against a plain fp32 PyTorch statement."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    return torch.device("cuda", 0)
+
+
+def _ab(M, N, K, dev, dtype=torch.bfloat16, seed=0):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    a = (torch.randn(M, K, device=dev, generator=g) * (2.0 / K ** 0.5)).to(dtype)
+    b = (torch.randn(N, K, device=dev, generator=g)).to(dtype)
+    return a, b
+
+
+def _tol(ref):
+    return 2e-2 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("M,N,K,tile_n", [
+    (128, 256, 64, 256), (128, 128, 64, 128), (256, 512, 512, 256), (384, 640, 1024, 128),
+    (200, 264, 72, 256), (200, 264, 72, 128), (1000, 1000, 1000, 0), (4096, 2048, 4096, 0),
+])
+def test_gemm_only_bf16(dev, M, N, K, tile_n):
+    from tempname_new_b200.ops import _dense
+    a, b = _ab(M, N, K, dev)
+    out = torch.full((M, N), float("nan"), device=dev, dtype=torch.bfloat16)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    _dense.plain_gemm(a, b, out, tile_n=tile_n, status=status)
+    ref = a.float() @ b.float().t()
+    assert status.tolist()[0] == 0
+    assert not torch.isnan(out).any()
+    assert (out.float() - ref).abs().max().item() <= _tol(ref)
+
+
+@pytest.mark.parametrize("act", [None, "gelu", "relu", "silu"])
+def test_gemm_only_bias_act(dev, act):
+    import tempname_new_b200 as flux
+    from tempname_new_b200.ops import _dense
+    from tempname_new_b200.ops.gemm_only import apply_act
+    a, b = _ab(512, 768, 512, dev)
+    bias = torch.randn(768, device=dev).bfloat16()
+    out = torch.empty(512, 768, device=dev, dtype=torch.bfloat16)
+    _dense.plain_gemm(a, b, out, bias, act=act)
+    ref = apply_act(a.float() @ b.float().t() + bias.float(), act)
+    assert (out.float() - ref).abs().max().item() <= _tol(ref)
+    bias2 = torch.randn(512, 768, device=dev).bfloat16()   # full [M, N] bias
+    op = flux.GemmOnly(torch.bfloat16)
+    out2 = op.forward(a, b, bias=bias2)
+    ref2 = a.float() @ b.float().t() + bias2.float()
+    assert (out2.float() - ref2).abs().max().item() <= _tol(ref2)
+
+
+def test_gemm_only_fp16_and_transpose_weight(dev):
+    import tempname_new_b200 as flux
+    a, b = _ab(256, 384, 256, dev, torch.float16)
+    op = flux.GemmOnly(torch.float16, transpose_weight=True)
+    out = op.forward(a, b.t().contiguous())
+    ref = a.float() @ b.float().t()
+    assert out.dtype == torch.float16
+    assert (out.float() - ref).abs().max().item() <= 1e-2 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("dtype", [torch.float8_e4m3fn, torch.float8_e5m2])
+def test_gemm_only_fp8_per_tensor_scale(dev, dtype):
+    import tempname_new_b200 as flux
+    a, b = _ab(256, 512, 1024, dev)
+    a8, b8 = a.to(dtype), (b * 0.25).to(dtype)
+    sa = torch.tensor([0.5], device=dev)
+    sb = torch.tensor([4.0], device=dev)
+    op = flux.GemmOnly(dtype, output_dtype=torch.bfloat16, use_fp8_gemm=True)
+    out = op.forward(a8, b8, input_scale=sa, weight_scale=sb)
+    ref = (a8.float() @ b8.float().t()) * 2.0
+    assert (out.float() - ref).abs().max().item() <= 3e-2 * max(1.0, ref.abs().max().item())
+
+
+def test_single_rank_fused_ops_match_matmul(dev):
+    """World size 1: AGKernel and GemmRS reduce to the plain kernel and must agree with it."""
+    import os
+    import torch.distributed as dist
+    import tempname_new_b200 as flux
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29541")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    a, b = _ab(512, 256, 384, dev)
+    ref = a.float() @ b.float().t()
+    ag = flux.AGKernel(dist.group.WORLD, 1, 512, 256, 384, torch.bfloat16)
+    rs = flux.GemmRS(dist.group.WORLD, 1, 512, 256, torch.bfloat16)
+    gathered = torch.empty_like(a)
+    o1 = ag.forward(a, b, gathered_input=gathered)
+    o2 = rs.forward(a, b)
+    assert torch.equal(gathered, a)
+    assert (o1.float() - ref).abs().max().item() <= _tol(ref)
+    assert (o2.float() - ref).abs().max().item() <= _tol(ref)
+    ag.check_status()
+    rs.check_status()
+
+
+def test_bounded_wait_reports_timeout(dev):
+    """A device wait on a flag that nothing sets gives up after its limit and reports it in the
+    status record; the context stays usable."""
+    import ctypes
+    from tempname_new_b200 import _native
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    rc = _native.lib().fluxb_wait_flag(ctypes.c_void_p(flag.data_ptr()), ctypes.c_uint32(1),
+                                       ctypes.c_uint64(200_000_000), ctypes.c_void_p(status.data_ptr()),
+                                       ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    st = status.tolist()
+    assert st[0] == 12 and st[2] == 0 and st[3] == 1
+    # a satisfied wait leaves the status clean, and the device still works
+    flag.fill_(3)
+    status.zero_()
+    _native.lib().fluxb_wait_flag(ctypes.c_void_p(flag.data_ptr()), ctypes.c_uint32(2),
+                                  ctypes.c_uint64(200_000_000), ctypes.c_void_p(status.data_ptr()),
+                                  ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0
+
+
+def test_smoke_entry(dev):
+    import __graft_entry__ as g
+    g.smoke()
