@@ -1,0 +1,319 @@
+// Small single-GPU kernels: in-place fp32->bf16 compaction, bitwise compare, uniform fill,
+// vector copy, and the stable MoE routing-index build.
+// Reference: src/inplace_cast/inplace_cast.cu, src/cuda/bitwise_check.cu,
+// src/cuda/random_initialize.cu, src/cuda/cuda_common.cu, src/cuda/moe_utils.cu,
+// src/moe_ag_scatter/sort_util.cu (calc_gather_index).
+#include "../include/fluxb.h"
+#include "../runtime/host_common.h"
+#include "../sm100/ptx.cuh"
+
+#include <atomic>
+
+namespace fluxb {
+extern std::atomic<uint64_t> g_launches;
+
+namespace {
+
+// ----------------------------------------------------------------------------------------
+// In-place fp32 -> bf16: the bf16 results are packed at the front of the same buffer.
+// Output chunk c (kChunk elements) lands on the bytes of input chunk c/2, so it may be written
+// only after that chunk has been read into registers. CTAs claim chunks in increasing order
+// from a counter; "chunk read" is published as flag[c] = epoch; the wait on flag[c/2] is bounded.
+// ----------------------------------------------------------------------------------------
+constexpr int kCastThreads = 256;
+constexpr int kCastPerThread = 8;
+constexpr int kChunk = kCastThreads * kCastPerThread;  // 2048 elements
+
+__global__ void __launch_bounds__(kCastThreads) inplace_cast_kernel(
+    float* data, int64_t n, uint32_t* flags, uint32_t* claim, uint32_t epoch, uint64_t timeout_ns,
+    Status* status) {
+  __shared__ uint32_t abort_word;
+  __shared__ uint32_t chunk_slot;
+  if (threadIdx.x == 0) abort_word = 0;
+  const uint32_t chunks = static_cast<uint32_t>((n + kChunk - 1) / kChunk);
+  WaitCtx wc{status, &abort_word, timeout_ns};
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(data);
+  while (true) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t got = atomicAdd(claim, 1u);
+      if (got == chunks + gridDim.x - 1u) atomicExch(claim, 0u);  // last claim of the launch
+      chunk_slot = got;
+    }
+    __syncthreads();
+    const uint32_t c = chunk_slot;
+    if (c >= chunks) break;
+    const int64_t base = static_cast<int64_t>(c) * kChunk + threadIdx.x * kCastPerThread;
+    float v[kCastPerThread];
+    if (base + kCastPerThread <= n) {
+      const float4 a = *reinterpret_cast<const float4*>(data + base);
+      const float4 b = *reinterpret_cast<const float4*>(data + base + 4);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+      v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < kCastPerThread; ++j) v[j] = base + j < n ? data[base + j] : 0.f;
+    }
+    __syncthreads();  // every thread of the CTA holds its part of chunk c in registers
+    if (threadIdx.x == 0) {
+      __threadfence();
+      ptx::st_release_sys(flags + c, epoch);
+      flag_wait_ge(wc, flags + (c >> 1), epoch, kSiteInplaceCast);
+    }
+    __syncthreads();
+    if (base + kCastPerThread <= n) {
+      uint4 o;
+      o.x = ptx::pack_bf16x2(v[0], v[1]);
+      o.y = ptx::pack_bf16x2(v[2], v[3]);
+      o.z = ptx::pack_bf16x2(v[4], v[5]);
+      o.w = ptx::pack_bf16x2(v[6], v[7]);
+      *reinterpret_cast<uint4*>(out + base) = o;
+    } else {
+#pragma unroll
+      for (int j = 0; j < kCastPerThread; ++j)
+        if (base + j < n) out[base + j] = __float2bfloat16_rn(v[j]);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// bitwise compare / uniform fill / copy
+// ----------------------------------------------------------------------------------------
+__global__ void bitwise_check_kernel(const uint8_t* a, const uint8_t* b, int64_t nbytes,
+                                     unsigned long long* mismatches) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  unsigned long long local = 0;
+  const int64_t n16 = (((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0)
+                          ? nbytes / 16 : 0;
+  const uint4* a4 = reinterpret_cast<const uint4*>(a);
+  const uint4* b4 = reinterpret_cast<const uint4*>(b);
+  for (int64_t i = tid; i < n16; i += stride) {
+    const uint4 x = a4[i], y = b4[i];
+    local += (x.x != y.x) + (x.y != y.y) + (x.z != y.z) + (x.w != y.w);
+  }
+  for (int64_t i = n16 * 16 + tid; i < nbytes; i += stride) local += a[i] != b[i];
+  for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+  if ((threadIdx.x & 31) == 0 && local) atomicAdd(mismatches, local);
+}
+
+__device__ __forceinline__ uint32_t hash32(uint64_t x) {
+  x ^= x >> 33; x *= 0xff51afd7ed558ccdull; x ^= x >> 33; x *= 0xc4ceb9fe1a85ec53ull; x ^= x >> 33;
+  return static_cast<uint32_t>(x);
+}
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+template <typename T>
+__global__ void uniform_fill_kernel(T* out, int64_t n, uint64_t seed, float lo, float hi) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float u = (hash32(seed * 0x9E3779B97F4A7C15ull + i) >> 8) * (1.0f / 16777216.0f);
+    out[i] = from_f32<T>(lo + (hi - lo) * u);
+  }
+}
+
+__global__ void copy_bytes_kernel(uint8_t* dst, const uint8_t* src, int64_t nbytes) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const bool al = ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15) == 0;
+  const int64_t n16 = al ? nbytes / 16 : 0;
+  for (int64_t i = tid; i < n16; i += stride)
+    reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  for (int64_t i = n16 * 16 + tid; i < nbytes; i += stride) dst[i] = src[i];
+}
+
+// ----------------------------------------------------------------------------------------
+// MoE routing index build: a stable counting sort of the flattened expert choices.
+//   experts[n]        expert id of flattened (token, k) entry n, n = token * topk + k
+//   splits[e]         number of entries routed to expert e
+//   offsets[e]        exclusive prefix sum of splits (E + 1 entries)
+//   scatter_index[n]  row of entry n in the expert-sorted order (stable inside an expert)
+//   gather_index[r]   token of sorted row r          topk_index[r]   k of sorted row r
+// Three passes: per-block histograms, one-block scan, stable placement.
+// ----------------------------------------------------------------------------------------
+constexpr int kIdxThreads = 256;
+constexpr int kIdxPerBlock = 4096;
+constexpr int kMaxExperts = 512;
+
+__global__ void __launch_bounds__(kIdxThreads) moe_hist_kernel(const int32_t* experts, int64_t n,
+                                                               int E, int32_t* block_hist) {
+  extern __shared__ int32_t hist[];
+  for (int e = threadIdx.x; e < E; e += kIdxThreads) hist[e] = 0;
+  __syncthreads();
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kIdxPerBlock;
+  for (int i = threadIdx.x; i < kIdxPerBlock; i += kIdxThreads) {
+    const int64_t idx = base + i;
+    if (idx < n) {
+      const int e = experts[idx];
+      if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += kIdxThreads) block_hist[blockIdx.x * E + e] = hist[e];
+}
+
+// block_hist[b][e] -> exclusive start of (expert e, block b); splits; offsets
+__global__ void __launch_bounds__(kMaxExperts) moe_scan_kernel(int32_t* block_hist, int nblocks, int E,
+                                                               int32_t* splits, int32_t* offsets) {
+  __shared__ int32_t totals[kMaxExperts];
+  const int e = threadIdx.x;
+  int32_t total = 0;
+  if (e < E) {
+    for (int b = 0; b < nblocks; ++b) {
+      const int32_t c = block_hist[b * E + e];
+      block_hist[b * E + e] = total;  // exclusive count of expert e in earlier blocks
+      total += c;
+    }
+    totals[e] = total;
+    if (splits) splits[e] = total;
+  }
+  __syncthreads();
+  if (e == 0) {
+    int32_t run = 0;
+    for (int i = 0; i < E; ++i) {
+      const int32_t c = totals[i];
+      totals[i] = run;
+      offsets[i] = run;
+      run += c;
+    }
+    offsets[E] = run;
+  }
+  __syncthreads();
+  if (e < E) {
+    const int32_t start = totals[e];
+    for (int b = 0; b < nblocks; ++b) block_hist[b * E + e] += start;
+  }
+}
+
+__global__ void __launch_bounds__(kIdxThreads) moe_place_kernel(
+    const int32_t* experts, int64_t n, int E, int topk, const int32_t* block_start,
+    int32_t* scatter_index, int32_t* gather_index, int32_t* topk_index) {
+  // running[e]: next free row of expert e for this block; warps are served in order and lanes in
+  // order inside a warp, so equal experts keep their input order
+  extern __shared__ int32_t running[];
+  for (int e = threadIdx.x; e < E; e += kIdxThreads) running[e] = block_start[blockIdx.x * E + e];
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kIdxPerBlock;
+  for (int step = 0; step < kIdxPerBlock / kIdxThreads; ++step) {
+    const int64_t idx = base + step * kIdxThreads + threadIdx.x;
+    int e = -1;
+    if (idx < n) {
+      e = experts[idx];
+      if (e < 0 || e >= E) e = -1;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+    const int leader = __ffs(peers) - 1;
+    for (int w = 0; w < kIdxThreads / 32; ++w) {
+      if (w == warp && e >= 0) {
+        int start = 0;
+        if (lane == leader) {
+          start = running[e];
+          running[e] = start + __popc(peers);
+        }
+        start = __shfl_sync(peers, start, leader);
+        const int32_t row = start + rank_in_warp;
+        scatter_index[idx] = row;
+        if (gather_index) gather_index[row] = static_cast<int32_t>(idx / topk);
+        if (topk_index) topk_index[row] = static_cast<int32_t>(idx % topk);
+      }
+      __syncthreads();
+    }
+  }
+}
+
+}  // namespace
+}  // namespace fluxb
+
+using namespace fluxb;
+
+extern "C" int fluxb_inplace_cast_fp32_to_bf16(float* data, int64_t n, uint32_t* flags,
+                                               uint32_t* claim, uint32_t epoch, uint64_t timeout_ns,
+                                               fluxb_status_t* status, void* stream) {
+  FLUXB_REQUIRE(data && flags && claim && n > 0, "inplace cast arguments");
+  FLUXB_REQUIRE((reinterpret_cast<uintptr_t>(data) & 15) == 0, "buffer must be 16-byte aligned");
+  int sms = 0, rc;
+  if ((rc = device_sm_count(&sms))) return rc;
+  const int64_t chunks = (n + kChunk - 1) / kChunk;
+  // every chunk waits on a lower-numbered one, so all claiming CTAs must be resident at once
+  const int grid = static_cast<int>(chunks < sms * 4 ? chunks : sms * 4);
+  inplace_cast_kernel<<<grid, kCastThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      data, n, flags, claim, epoch, timeout_ns ? timeout_ns : 2000000000ull,
+      reinterpret_cast<Status*>(status));
+  FLUXB_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return kOk;
+}
+
+extern "C" int fluxb_bitwise_check(const void* a, const void* b, int64_t nbytes,
+                                   unsigned long long* mismatches, void* stream) {
+  FLUXB_REQUIRE(a && b && mismatches && nbytes >= 0, "bitwise check arguments");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  FLUXB_CUDA_OK(cudaMemsetAsync(mismatches, 0, sizeof(unsigned long long), s));
+  if (nbytes == 0) return kOk;
+  int sms = 0, rc;
+  if ((rc = device_sm_count(&sms))) return rc;
+  bitwise_check_kernel<<<sms * 8, 256, 0, s>>>(reinterpret_cast<const uint8_t*>(a),
+                                               reinterpret_cast<const uint8_t*>(b), nbytes, mismatches);
+  FLUXB_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return kOk;
+}
+
+extern "C" int fluxb_uniform_fill(void* out, int64_t n, int dtype, uint64_t seed, float lo, float hi,
+                                  void* stream) {
+  FLUXB_REQUIRE(out && n >= 0, "uniform fill arguments");
+  if (n == 0) return kOk;
+  int sms = 0, rc;
+  if ((rc = device_sm_count(&sms))) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case FLUXB_FP32: uniform_fill_kernel<float><<<sms * 8, 256, 0, s>>>(static_cast<float*>(out), n, seed, lo, hi); break;
+    case FLUXB_BF16: uniform_fill_kernel<__nv_bfloat16><<<sms * 8, 256, 0, s>>>(static_cast<__nv_bfloat16*>(out), n, seed, lo, hi); break;
+    case FLUXB_FP16: uniform_fill_kernel<__half><<<sms * 8, 256, 0, s>>>(static_cast<__half*>(out), n, seed, lo, hi); break;
+    default: return fail(kErrUnsupported, "uniform fill supports fp32, bf16, fp16");
+  }
+  FLUXB_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return kOk;
+}
+
+extern "C" int fluxb_copy_bytes(void* dst, const void* src, int64_t nbytes, void* stream) {
+  FLUXB_REQUIRE(dst && src && nbytes >= 0, "copy arguments");
+  if (nbytes == 0) return kOk;
+  int sms = 0, rc;
+  if ((rc = device_sm_count(&sms))) return rc;
+  copy_bytes_kernel<<<sms * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), nbytes);
+  FLUXB_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return kOk;
+}
+
+// scratch: int32 workspace of at least fluxb_moe_index_scratch_elems(n, E) elements
+extern "C" int64_t fluxb_moe_index_scratch_elems(int64_t n, int E) {
+  return ((n + kIdxPerBlock - 1) / kIdxPerBlock) * E;
+}
+
+extern "C" int fluxb_moe_index_build(const int32_t* experts, int64_t n, int E, int topk,
+                                     int32_t* splits, int32_t* offsets, int32_t* scatter_index,
+                                     int32_t* gather_index, int32_t* topk_index, int32_t* scratch,
+                                     void* stream) {
+  FLUXB_REQUIRE(experts && offsets && scatter_index && scratch, "moe index arguments");
+  FLUXB_REQUIRE(E >= 1 && E <= kMaxExperts && topk >= 1 && n > 0, "moe index sizes");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int nblocks = static_cast<int>((n + kIdxPerBlock - 1) / kIdxPerBlock);
+  moe_hist_kernel<<<nblocks, kIdxThreads, E * sizeof(int32_t), s>>>(experts, n, E, scratch);
+  moe_scan_kernel<<<1, kMaxExperts, 0, s>>>(scratch, nblocks, E, splits, offsets);
+  moe_place_kernel<<<nblocks, kIdxThreads, E * sizeof(int32_t), s>>>(
+      experts, n, E, topk, scratch, scatter_index, gather_index, topk_index);
+  FLUXB_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(3, std::memory_order_relaxed);
+  return kOk;
+}

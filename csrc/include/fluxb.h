@@ -49,7 +49,7 @@ typedef struct {
   int32_t num_sms;           /* 0 = all */
   int32_t tile_n;            /* 0 = auto, else 128 | 256 */
   int32_t act;               /* epilogue activation after bias: 0 none, 1 gelu(tanh), 2 relu, 3 silu */
-  int32_t reserved2;
+  int32_t cta_group;         /* 0 = auto, 1 = one CTA per 128-row tile, 2 = CTA pair per 256-row tile */
   uint32_t epoch;            /* call number of the owning op, starting at 1 */
   uint32_t reserved;
   uint64_t timeout_ns;       /* 0 = default (2 s) */
@@ -85,6 +85,29 @@ int fluxb_barrier_all(uint32_t* const* flags, int rank, int world, uint32_t epoc
  * limit passes, then returns; the outcome is in `status`. */
 int fluxb_wait_flag(const uint32_t* flag, uint32_t expected, uint64_t timeout_ns,
                     fluxb_status_t* status, void* stream);
+
+/* ---- block-scaled fp8 quantisation (see csrc/aux/quantize.cu for layouts) ---- */
+int fluxb_quantize_blockwise(const void* x, int64_t ldx, int in_dtype, void* q, void* qt,
+                             float* scale_inv, float* scale_inv_t, int M, int K, int batch,
+                             int square, float eps, int out_dtype, void* stream);
+
+/* ---- small utilities (csrc/aux/utils.cu) ---- */
+/* In-place fp32 -> bf16 compaction of data[0..n): results are packed at the front of the buffer.
+ * flags: ceil(n/2048) uint32 of scratch, claim: one uint32; both zero at first use and owned by
+ * the caller across calls; epoch grows by one per call. */
+int fluxb_inplace_cast_fp32_to_bf16(float* data, int64_t n, uint32_t* flags, uint32_t* claim,
+                                    uint32_t epoch, uint64_t timeout_ns, fluxb_status_t* status,
+                                    void* stream);
+int fluxb_bitwise_check(const void* a, const void* b, int64_t nbytes,
+                        unsigned long long* mismatches, void* stream);
+int fluxb_uniform_fill(void* out, int64_t n, int dtype, uint64_t seed, float lo, float hi,
+                       void* stream);
+int fluxb_copy_bytes(void* dst, const void* src, int64_t nbytes, void* stream);
+/* Stable counting sort of flattened expert choices; see csrc/aux/utils.cu. */
+int64_t fluxb_moe_index_scratch_elems(int64_t n, int E);
+int fluxb_moe_index_build(const int32_t* experts, int64_t n, int E, int topk, int32_t* splits,
+                          int32_t* offsets, int32_t* scatter_index, int32_t* gather_index,
+                          int32_t* topk_index, int32_t* scratch, void* stream);
 
 #ifdef __cplusplus
 }

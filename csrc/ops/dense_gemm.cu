@@ -22,7 +22,23 @@ int launch_dense(const DenseGemmParams& p, int grid, cudaStream_t stream) {
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     if (dev < 64) configured[dev] = true;
   }
-  dense_gemm_kernel<Cfg><<<grid, 256, Cfg::SMEM_BYTES, stream>>>(p);
+  if constexpr (Cfg::CG == 1) {
+    dense_gemm_kernel<Cfg><<<grid, 256, Cfg::SMEM_BYTES, stream>>>(p);
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    FLUXB_CUDA_OK(cudaLaunchKernelEx(&cfg, dense_gemm_kernel<Cfg>, p));
+  }
   FLUXB_CUDA_OK(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return kOk;
@@ -74,7 +90,16 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
 
   int bn = a->tile_n;
   if (bn == 0) bn = (a->N % 256 == 0 || a->N > 2048) ? 256 : 128;
-  FLUXB_REQUIRE(bn == 128 || bn == 256, "tile_n must be 128 or 256");
+  FLUXB_REQUIRE(bn == 128 || bn == 192 || bn == 256, "tile_n must be 128, 192 or 256");
+  int cg = a->cta_group;
+  FLUXB_REQUIRE(cg >= 0 && cg <= 2, "cta_group must be 0 (auto), 1 or 2");
+  if (cg == 0) cg = 1;
+  if (multi && a->mode == FLUXB_ALLGATHER) {
+    // the all-gather variants exist for CTA pairs on 256-wide tiles and single CTAs on 128-wide
+    if (cg == 2 && a->M / a->world >= 256) bn = 256;
+    else { cg = 1; bn = 128; }
+  }
+  const int bm = 128 * cg;
   const int bk = 128 / elt;
   const CUtensorMapDataType in_dt =
       in16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
@@ -108,7 +133,7 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   {
     uint64_t dims[2] = {static_cast<uint64_t>(a->K), static_cast<uint64_t>(a->N)};
     uint64_t str[1] = {static_cast<uint64_t>(a->ldb) * elt};
-    uint32_t box[2] = {static_cast<uint32_t>(bk), static_cast<uint32_t>(bn)};
+    uint32_t box[2] = {static_cast<uint32_t>(bk), static_cast<uint32_t>(bn / cg)};
     if ((rc = encode_tmap(&p.tm_b, in_dt, 2, a->b, dims, str, box, Swz::B128))) return rc;
   }
   // ---- D
@@ -155,8 +180,8 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   if (p.mode == kModeAllGather) p.seg_first = a->rank;
   if (p.mode == kModeReduceScatter) p.seg_first = (a->rank + 1) % a->world;
 
-  const int m_tiles_seg = (p.seg_rows + 127) / 128;
-  p.group_m = a->group_m > 0 ? a->group_m : 16;
+  const int m_tiles_seg = (p.seg_rows + bm - 1) / bm;
+  p.group_m = a->group_m > 0 ? a->group_m : 16 / cg;
   if (p.group_m > m_tiles_seg) p.group_m = m_tiles_seg;
 
   int sms = 0;
@@ -165,14 +190,37 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   const int64_t tiles = static_cast<int64_t>(p.num_seg) * m_tiles_seg * ((a->N + bn - 1) / bn);
   int grid = sms;
   // every CTA of a multi-rank launch takes part in the flag protocol, so the grid stays full
-  if (!multi && tiles < grid) grid = static_cast<int>(tiles);
+  if (!multi && tiles * cg < grid) grid = static_cast<int>(tiles) * cg;
+  if (cg == 2) grid &= ~1;
 
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
+  if (p.mode == kModeAllGather) {
+    // variants that carry the staging rings of the all-gather push
+    if (cg == 2 && bn == 256) {
+      if (in16) return launch_dense<DenseCfg<256, 0, 5, 2, 32768>>(p, grid, stream);
+      return launch_dense<DenseCfg<256, 1, 5, 2, 32768>>(p, grid, stream);
+    }
+    FLUXB_REQUIRE(cg == 1 && bn == 128, "all-gather GEMM runs as CTA pairs on 256-wide tiles or single CTAs on 128-wide tiles");
+    if (in16) return launch_dense<DenseCfg<128, 0, 5, 1, 32768>>(p, grid, stream);
+    return launch_dense<DenseCfg<128, 1, 5, 1, 32768>>(p, grid, stream);
+  }
+  if (cg == 2) {
+    if (in16) {
+      if (bn == 256) return launch_dense<DenseCfg<256, 0, 6, 2>>(p, grid, stream);
+      if (bn == 192) return launch_dense<DenseCfg<192, 0, 6, 2>>(p, grid, stream);
+      return launch_dense<DenseCfg<128, 0, 8, 2>>(p, grid, stream);
+    }
+    if (bn == 256) return launch_dense<DenseCfg<256, 1, 6, 2>>(p, grid, stream);
+    if (bn == 192) return launch_dense<DenseCfg<192, 1, 6, 2>>(p, grid, stream);
+    return launch_dense<DenseCfg<128, 1, 8, 2>>(p, grid, stream);
+  }
   if (in16) {
     if (bn == 256) return launch_dense<DenseCfg<256, 0, 4>>(p, grid, stream);
+    if (bn == 192) return launch_dense<DenseCfg<192, 0, 4>>(p, grid, stream);
     return launch_dense<DenseCfg<128, 0, 6>>(p, grid, stream);
   } else {
     if (bn == 256) return launch_dense<DenseCfg<256, 1, 4>>(p, grid, stream);
+    if (bn == 192) return launch_dense<DenseCfg<192, 1, 4>>(p, grid, stream);
     return launch_dense<DenseCfg<128, 1, 6>>(p, grid, stream);
   }
 }

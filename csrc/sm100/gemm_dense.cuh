@@ -69,22 +69,31 @@ struct DenseGemmParams {
   uint32_t* rs_work;             // local work-claim counter, zero between calls
 };
 
-template <int BN_, int KIND_, int STAGES_>
+// CG_ = 1: one CTA per 128 x BN tile. CG_ = 2: a pair of CTAs (one cluster) shares a 256 x BN
+// tile: each CTA stages its own 128 rows of A and its own BN/2 rows of B, the pair leader issues
+// tcgen05.mma.cta_group::2, and each CTA ends up with its 128 x BN slice of D in its own TMEM.
+// COMM_ > 0 reserves COMM_ bytes of shared memory as staging rings for the all-gather push.
+template <int BN_, int KIND_, int STAGES_, int CG_ = 1, int COMM_ = 0>
 struct DenseCfg {
-  static constexpr int BM = 128;
+  static constexpr int COMM_BYTES = COMM_;
+  static constexpr int CG = CG_;
+  static constexpr int BM_CTA = 128;                       // rows of A / D per CTA
+  static constexpr int BM = 128 * CG_;                     // rows per tile
   static constexpr int BN = BN_;
   static constexpr int KIND = KIND_;                       // 0 = bf16, 1 = fp8 e4m3
   static constexpr int ELT = KIND_ == 0 ? 2 : 1;
   static constexpr int BK = 128 / ELT;                     // one 128-byte swizzle row
   static constexpr int UMMA_K = 32 / ELT;
   static constexpr int STAGES = STAGES_;
-  static constexpr int A_BYTES = BM * 128;
-  static constexpr int B_BYTES = BN * 128;
+  static constexpr int A_BYTES = BM_CTA * 128;
+  static constexpr int B_ROWS_CTA = BN / CG_;
+  static constexpr int B_BYTES = B_ROWS_CTA * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_BUF_BYTES = 32 * 128;           // 32 rows x 64 bf16
   static constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + COMM_BYTES + BAR_BYTES + 1024;
+  static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared memory limit");
   static constexpr int TMEM_COLS = 512;
   static_assert(2 * BN <= TMEM_COLS, "two accumulators must fit TMEM");
 };
@@ -130,9 +139,11 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
 
   const uint32_t epi_base = smem_base + STAGES * Cfg::STAGE_BYTES;
   uint8_t* epi_ptr = smem + STAGES * Cfg::STAGE_BYTES;
-  const uint32_t bar_base = epi_base + Cfg::EPI_BYTES;
-  uint8_t* bar_ptr = epi_ptr + Cfg::EPI_BYTES;
-  // barrier block: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], then two words
+  const uint32_t comm_base = epi_base + Cfg::EPI_BYTES;
+  const uint32_t bar_base = comm_base + Cfg::COMM_BYTES;
+  uint8_t* bar_ptr = epi_ptr + Cfg::EPI_BYTES + Cfg::COMM_BYTES;
+  // barrier block: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], three words, then
+  // the 8 barriers of the all-gather staging rings
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
@@ -140,9 +151,18 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * STAGES + 4));
   volatile uint32_t* abort_word = tmem_slot + 1;
   volatile uint32_t* claim_slot = tmem_slot + 2;
+  const uint32_t ring_bar_base = bar_base + 8u * (2 * STAGES + 4) + 16u;
+  static_assert(8 * (2 * STAGES + 4) + 16 + 64 <= Cfg::BAR_BYTES, "barrier block too small");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  constexpr int CG = Cfg::CG;
+  // position inside the CTA pair (CG == 2): rank 0 leads (issues the MMAs, owns the barriers
+  // that both CTAs' loads and epilogues report to)
+  const uint32_t cta_rank = CG == 2 ? ptx::cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int tile_slot = blockIdx.x / CG;          // which tile stream this CTA (pair) walks
+  const int tile_stride = gridDim.x / CG;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -151,19 +171,20 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(tfull_bar(a), 1);
-      ptx::mbar_init(tempty_bar(a), 4);
+      ptx::mbar_init(tempty_bar(a), 4 * CG);
     }
+    for (int i = 0; i < 8; ++i) ptx::mbar_init(ring_bar_base + 8u * i, 1);
     *abort_word = 0;
     ptx::fence_mbar_init();
     ptx::prefetch_tmap(&p.tm_a);
     ptx::prefetch_tmap(&p.tm_b);
   }
   if (warp == 1) {
-    ptx::tmem_alloc<1>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
-    ptx::tmem_relinquish<1>();
+    ptx::tmem_alloc<CG>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
+    ptx::tmem_relinquish<CG>();
   }
   ptx::tc_fence_before();
-  __syncthreads();
+  if constexpr (CG == 2) ptx::cluster_sync(); else __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -180,13 +201,15 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      const uint32_t full_owner0 = CG == 2 ? ptx::mapa_u32(full_bar(0), 0) : full_bar(0);
+      for (int t = tile_slot; t < total_tiles; t += tile_stride) {
         const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
         const CUtensorMap* tma = &p.tm_a;
-        int a_row = c.seg * p.seg_rows + c.m_in_seg;
+        const int m_cta = c.m_in_seg + static_cast<int>(cta_rank) * Cfg::BM_CTA;
+        int a_row = c.seg * p.seg_rows + m_cta;
         if (p.mode == kModeAllGather && multi) {
           if (c.seg == p.rank) {
-            a_row = c.m_in_seg;  // own shard straight from the caller's tensor
+            a_row = m_cta;  // own shard straight from the caller's tensor
           } else {
             tma = &p.tm_a_land;
             const uint32_t* f = p.ag_flags[p.rank] + c.seg * m_tiles_seg + c.m_tile;
@@ -197,9 +220,18 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
         for (int kb = 0; kb < k_blocks; ++kb) {
           mbar_wait(wc, empty_bar(stage), phase ^ 1u, kSiteSmemEmpty);
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
-          ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
-          ptx::tma_load_2d(sa, tma, full_bar(stage), kb * BK, a_row);
-          ptx::tma_load_2d(sa + Cfg::A_BYTES, &p.tm_b, full_bar(stage), kb * BK, c.n0);
+          if constexpr (CG == 1) {
+            ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+            ptx::tma_load_2d(sa, tma, full_bar(stage), kb * BK, a_row);
+            ptx::tma_load_2d(sa + Cfg::A_BYTES, &p.tm_b, full_bar(stage), kb * BK, c.n0);
+          } else {
+            // both CTAs' bytes are counted on the leader's barrier
+            const uint32_t fb = full_owner0 + 8u * stage;
+            if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * Cfg::STAGE_BYTES);
+            ptx::tma_load_2d_cg2(sa, tma, fb, kb * BK, a_row);
+            ptx::tma_load_2d_cg2(sa + Cfg::A_BYTES, &p.tm_b, fb, kb * BK,
+                                 c.n0 + static_cast<int>(cta_rank) * Cfg::B_ROWS_CTA);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -209,12 +241,12 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       const uint32_t idesc = ptx::umma_idesc(p.ab_fmt, p.ab_fmt, BM, BN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
-      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+      for (int t = tile_slot; t < total_tiles; t += tile_stride, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         mbar_wait(wc, tempty_bar(acc), acc_phase ^ 1u, kSiteTmemEmpty);
@@ -229,16 +261,18 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
 #pragma unroll
           for (int k = 0; k < BK / Cfg::UMMA_K; ++k) {
             // 32 bytes per UMMA_K step inside the 128-byte swizzled row: +2 in 16-byte units
-            ptx::umma_ss<1, Cfg::KIND>(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc,
-                                       (kb | k) != 0 ? 1u : 0u);
+            ptx::umma_ss<CG, Cfg::KIND>(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc,
+                                        (kb | k) != 0 ? 1u : 0u);
           }
-          ptx::umma_commit(empty_bar(stage));
+          if constexpr (CG == 1) ptx::umma_commit(empty_bar(stage));
+          else ptx::umma_commit_cg2(empty_bar(stage), 3);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        ptx::umma_commit(tfull_bar(acc));
+        if constexpr (CG == 1) ptx::umma_commit(tfull_bar(acc));
+        else ptx::umma_commit_cg2(tfull_bar(acc), 3);
       }
     }
   } else if (warp == 2 || warp == 3) {
@@ -249,44 +283,84 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
       // next call can never be mistaken for a slow rank's current one.
       ptx::st_release_sys(p.start_ctr[lane] + p.rank, p.epoch);
     }
-    if (p.mode == kModeAllGather && multi) {
-      if (lane < p.world) flag_wait_ge(wc, p.start_ctr[p.rank] + lane, p.epoch, kSiteStartBarrier);
-      __syncwarp();
-      constexpr int U = 8;  // independent 16-byte chunks per lane per trip
-      const int64_t row_chunks = (static_cast<int64_t>(p.K) * Cfg::ELT) >> 4;
-      const uint4* src = reinterpret_cast<const uint4*>(p.ag_src);
-      const int64_t slab = static_cast<int64_t>(p.rank) * p.seg_rows * row_chunks;
-      const int64_t cw = static_cast<int64_t>(blockIdx.x) * 2 + (warp - 2);
-      const int64_t ncw = static_cast<int64_t>(gridDim.x) * 2;
-      // The peer that consumes this shard first (rank-1 starts with segment rank) is served
-      // first; all ranks walk the same rotation, so every step is a permutation on NVSwitch.
-      for (int d = 1; d < p.world; ++d) {
-        int peer = p.rank - d;
-        if (peer < 0) peer += p.world;
-        uint4* land = reinterpret_cast<uint4*>(p.ag_land[peer]) + slab;
-        for (int mt = 0; mt < m_tiles_seg; ++mt) {
-          const int rows = min(BM, p.seg_rows - mt * BM);
-          const int64_t first = static_cast<int64_t>(mt) * BM * row_chunks;
-          const int64_t count = static_cast<int64_t>(rows) * row_chunks;
-          for (int64_t i = cw * U * 32 + lane; i < count; i += ncw * U * 32) {
-            uint4 v[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u)
-              if (i + u * 32 < count) v[u] = ptx::ld_global_v4(src + first + i + u * 32);
-#pragma unroll
-            for (int u = 0; u < U; ++u)
-              if (i + u * 32 < count) ptx::st_global_v4(land + first + i + u * 32, v[u]);
-          }
-          __syncwarp();
-          if (lane == 0) {
+    if constexpr (Cfg::COMM_BYTES > 0) {
+      if (p.mode == kModeAllGather && multi) {
+        if (lane < p.world) flag_wait_ge(wc, p.start_ctr[p.rank] + lane, p.epoch, kSiteStartBarrier);
+        __syncwarp();
+        if (lane == 0) {
+          // One lane per warp drives a ring of NSLOT staging slots: bulk-load a chunk of the local
+          // shard into a slot, bulk-store it into the peer's landing slab, reuse the slot once
+          // the store has read it. The peer that consumes this shard first (rank-1 starts with
+          // segment `rank`) is served first; all ranks walk the same rotation, so every step is
+          // a permutation on NVSwitch.
+          constexpr int NSLOT = 4;
+          constexpr uint32_t CH = Cfg::COMM_BYTES / 2 / NSLOT;
+          constexpr int LAG = 4;  // chunk stores that may still be in flight when a step is published
+          const uint32_t ring = comm_base + (warp - 2) * (Cfg::COMM_BYTES / 2);
+          const uint32_t rbar = ring_bar_base + (warp - 2) * NSLOT * 8u;
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ag_src);
+          const int64_t row_bytes = static_cast<int64_t>(p.K) * Cfg::ELT;
+          const int64_t slab_off = static_cast<int64_t>(p.rank) * p.seg_rows * row_bytes;
+          const uint32_t cw = blockIdx.x * 2 + (warp - 2);
+          const uint32_t ncw = gridDim.x * 2;
+          auto step_chunks = [&](int mt) -> uint32_t {  // chunks of tile row mt that this warp moves
+            const int rows = min(BM, p.seg_rows - mt * BM);
+            const uint32_t nch = static_cast<uint32_t>((rows * row_bytes + CH - 1) / CH);
+            return nch > cw ? (nch - cw - 1) / ncw + 1 : 0u;
+          };
+          auto publish = [&](int d, int mt) {
+            int peer = p.rank - d;
+            if (peer < 0) peer += p.world;
+            ptx::fence_proxy_async_all();
             // the last of the 2*gridDim.x pushing warps publishes the tile row to the peer
             uint32_t* cnt = p.local_cnt + d * m_tiles_seg + mt;
-            if (ptx::atom_add_acq_rel_sys(cnt, 1u) == static_cast<uint32_t>(ncw) - 1u) {
+            if (ptx::atom_add_acq_rel_sys(cnt, 1u) == ncw - 1u) {
               *cnt = 0;
               ptx::st_release_sys(p.ag_flags[peer] + p.rank * m_tiles_seg + mt, p.epoch);
             }
+          };
+          uint32_t issued = 0;
+          int sig_d = 1, sig_mt = 0;           // next step to publish
+          uint32_t sig_end = step_chunks(0);   // chunk count at which that step is fully issued
+          for (int d = 1; d < p.world; ++d) {
+            int peer = p.rank - d;
+            if (peer < 0) peer += p.world;
+            uint8_t* land = reinterpret_cast<uint8_t*>(p.ag_land[peer]) + slab_off;
+            for (int mt = 0; mt < m_tiles_seg; ++mt) {
+              const int rows = min(BM, p.seg_rows - mt * BM);
+              const int64_t first = static_cast<int64_t>(mt) * BM * row_bytes;
+              const int64_t bytes = rows * row_bytes;
+              const uint32_t nch = static_cast<uint32_t>((bytes + CH - 1) / CH);
+              for (uint32_t c = cw; c < nch; c += ncw) {
+                const int64_t off = first + static_cast<int64_t>(c) * CH;
+                const int64_t left = bytes - static_cast<int64_t>(c) * CH;
+                const uint32_t sz = left < static_cast<int64_t>(CH) ? static_cast<uint32_t>(left) : CH;
+                const uint32_t slot = issued % NSLOT;
+                const uint32_t ph = (issued / NSLOT) & 1u;
+                ptx::bulk_wait_read<NSLOT - 1>();  // the store that last used this slot has read it
+                ptx::mbar_arrive_expect_tx(rbar + 8u * slot, sz);
+                ptx::bulk_load(ring + slot * CH, src + off, sz, rbar + 8u * slot);
+                mbar_wait(wc, rbar + 8u * slot, ph, kSiteSmemFull);
+                ptx::bulk_store(land + off, ring + slot * CH, sz);
+                ptx::bulk_commit();
+                ++issued;
+              }
+              // everything but the LAG most recent chunk stores has landed: publish the steps
+              // that lie entirely before that point
+              ptx::bulk_wait<LAG>();
+              const uint32_t done = issued > LAG ? issued - LAG : 0u;
+              while ((sig_d < d || (sig_d == d && sig_mt <= mt)) && sig_end <= done) {
+                publish(sig_d, sig_mt);
+                if (++sig_mt == m_tiles_seg) { sig_mt = 0; ++sig_d; }
+                sig_end += step_chunks(sig_mt);
+              }
+            }
           }
-          __syncwarp();
+          ptx::bulk_wait<0>();
+          while (sig_d < p.world) {
+            publish(sig_d, sig_mt);
+            if (++sig_mt == m_tiles_seg) { sig_mt = 0; ++sig_d; }
+          }
         }
       }
     }
@@ -304,10 +378,11 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
     int it = 0;
     uint32_t nstore = 0;
     bool started = !(multi && p.mode == kModeReduceScatter);
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+    for (int t = tile_slot; t < total_tiles; t += tile_stride, ++it) {
       const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      const int m_cta = c.m_in_seg + static_cast<int>(cta_rank) * Cfg::BM_CTA;
       const CUtensorMap* tmd = &p.tm_d[0];
       int z = c.seg;
       if (p.mode == kModeReduceScatter && multi) {
@@ -320,9 +395,13 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
           started = true;
         }
       }
+      // one lane polls; the others sleep at the warp barrier and then observe the completed
+      // phase with a single try_wait of their own
+      if (lane == 0) mbar_wait(wc, tfull_bar(acc), acc_phase, kSiteTmemFull);
+      __syncwarp();
       mbar_wait(wc, tfull_bar(acc), acc_phase, kSiteTmemFull);
       ptx::tc_fence_after();
-      const int row = c.m_in_seg + q * 32 + lane;              // row inside the segment
+      const int row = m_cta + q * 32 + lane;                   // row inside the segment
       const int64_t grow = static_cast<int64_t>(c.seg) * p.seg_rows + row;  // global row
 #pragma unroll 1
       for (int ch = 0; ch < BN / 64; ++ch) {
@@ -334,7 +413,10 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
         if (ch == BN / 64 - 1) {
           ptx::tc_fence_before();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+          if (lane == 0) {
+            if constexpr (CG == 1) ptx::mbar_arrive(tempty_bar(acc));
+            else ptx::mbar_arrive_remote(tempty_bar(acc), 0);
+          }
         }
         const int col0 = c.n0 + ch * 64;
         if (scaled) {
@@ -387,8 +469,8 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
         }
         ptx::fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && col0 < p.N && c.m_in_seg + q * 32 < p.seg_rows) {
-          ptx::tma_store_3d(tmd, my_epi_u32 + buf * Cfg::EPI_BUF_BYTES, col0, c.m_in_seg + q * 32, z);
+        if (lane == 0 && col0 < p.N && m_cta + q * 32 < p.seg_rows) {
+          ptx::tma_store_3d(tmd, my_epi_u32 + buf * Cfg::EPI_BUF_BYTES, col0, m_cta + q * 32, z);
         }
         if (lane == 0) ptx::bulk_commit();
         ++nstore;
@@ -400,7 +482,7 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
           ptx::fence_proxy_async_all();
           // the last of the n_tiles*4 warps that store into this tile row tells the owner
           uint32_t* cnt = p.local_cnt + c.seg * m_tiles_seg + c.m_tile;
-          if (ptx::atom_add_acq_rel_sys(cnt, 1u) == static_cast<uint32_t>(n_tiles) * 4u - 1u) {
+          if (ptx::atom_add_acq_rel_sys(cnt, 1u) == static_cast<uint32_t>(n_tiles) * 4u * CG - 1u) {
             *cnt = 0;
             ptx::st_release_sys(p.rs_ctr[c.seg] + c.m_tile * kMaxRanks + p.rank, p.epoch);
           }
@@ -413,11 +495,14 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
   }
 
   // -------------------------------------------------------------------- teardown of the GEMM
+  __syncwarp();
   ptx::tc_fence_before();
-  __syncthreads();
+  // CG == 2: nobody leaves (or frees TMEM) while the partner may still read this CTA's shared
+  // memory or signal its barriers
+  if constexpr (CG == 2) ptx::cluster_sync(); else __syncthreads();
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc<1>(tmem_base, Cfg::TMEM_COLS);
+    ptx::tmem_dealloc<CG>(tmem_base, Cfg::TMEM_COLS);
   }
 
   // -------------------------------------------------------------------- reduce-scatter tail

@@ -17,3 +17,6 @@ from .parallel.dist_env import DistEnvTP, DistEnvTPWithEP, MoeArguments  # noqa:
 from .ops.gemm_only import GemmOnly  # noqa: F401
 from .ops.gemm_rs import GemmRS  # noqa: F401
 from .ops.ag_gemm import AGKernel  # noqa: F401
+from .ops.quantization import Quantization  # noqa: F401
+from .ops.misc import (InplaceCast, bitwise_check, calc_scatter_index, inplace_cast_fp32_to_bf16,  # noqa: F401
+                       moe_index_build, uniform_initialize)

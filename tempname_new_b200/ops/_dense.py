@@ -27,7 +27,7 @@ class DenseArgs(ctypes.Structure):
         ("scale_a", _VP), ("scale_b", _VP),
         ("mode", ctypes.c_int32), ("rank", ctypes.c_int32), ("world", ctypes.c_int32),
         ("group_m", ctypes.c_int32), ("num_sms", ctypes.c_int32), ("tile_n", ctypes.c_int32),
-        ("act", ctypes.c_int32), ("reserved2", ctypes.c_int32),
+        ("act", ctypes.c_int32), ("cta_group", ctypes.c_int32),
         ("epoch", ctypes.c_uint32), ("reserved", ctypes.c_uint32),
         ("timeout_ns", ctypes.c_uint64),
         ("status", _VP),
@@ -80,8 +80,10 @@ def _as_scale(t: Optional[torch.Tensor], dev) -> Optional[torch.Tensor]:
 def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
               scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None, *,
               tile_n: int = 0, group_m: int = 0, num_sms: int = 0, act: Optional[str] = None,
+              cta_group: int = 0, m: Optional[int] = None,
               status: Optional[torch.Tensor] = None, keep: Optional[list] = None) -> DenseArgs:
-    """Fill the operand part of a DenseArgs for A[rows,K], B[N,K]."""
+    """Fill the operand part of a DenseArgs for A[rows,K], B[N,K]. ``m`` is the number of output
+    rows this GPU computes; when no tile knobs are given they come from the tuning table."""
     if not (a.is_cuda and b.is_cuda):
         raise RuntimeError("the sm_100a GEMM kernels need CUDA tensors")
     if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
@@ -108,8 +110,15 @@ def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], ou
         args.scale_b = sb.data_ptr()
     if keep is not None:
         keep.extend([sa, sb])
+    if tile_n == 0 and cta_group == 0 and m is not None:
+        from ..tuning.table import lookup
+        knobs = lookup(m, b.shape[0], a.shape[1], a.element_size())
+        tile_n, cta_group = knobs["tile_n"], knobs["cta_group"]
+        if group_m == 0:
+            group_m = knobs["group_m"]
     args.group_m, args.num_sms, args.tile_n = group_m, num_sms, tile_n
     args.act = ACT[act]
+    args.cta_group = cta_group
     args.status = status.data_ptr() if status is not None else None
     args.stream = current_stream_ptr(a.device)
     return args
@@ -118,12 +127,12 @@ def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], ou
 def plain_gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor,
                bias: Optional[torch.Tensor] = None, scale_a: Optional[torch.Tensor] = None,
                scale_b: Optional[torch.Tensor] = None, *, tile_n: int = 0, group_m: int = 0,
-               num_sms: int = 0, act: Optional[str] = None,
+               num_sms: int = 0, act: Optional[str] = None, cta_group: int = 0,
                status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[M,N] = a[M,K] @ b[N,K]^T (* scales) (+bias) on the tcgen05 kernel."""
     keep: list = []
     args = base_args(a, b, bias, out.dtype, scale_a, scale_b, tile_n=tile_n, group_m=group_m,
-                     num_sms=num_sms, act=act, status=status, keep=keep)
+                     num_sms=num_sms, act=act, cta_group=cta_group, m=a.shape[0], status=status, keep=keep)
     if out.stride(1) != 1 or out.shape != (a.shape[0], b.shape[0]):
         raise ValueError("output must be [M, N] with contiguous rows")
     args.d, args.ldd = out.data_ptr(), out.stride(0)

@@ -57,7 +57,7 @@ class AGKernel(FusedOpBase):
         out = output if output is not None else torch.empty((M, N), dtype=self.output_dtype, device=input.device)
         keep: list = []
         args = _dense.base_args(a, w, bias, self.output_dtype, input_scale, weight_scale,
-                                act=act, status=self.status, keep=keep)
+                                act=act, m=M, status=self.status, keep=keep)
         args.M = M
         args.d, args.ldd = out.data_ptr(), out.stride(0)
         args.mode, args.rank, args.world = _dense.ALLGATHER, self.rank, self.world

@@ -67,7 +67,7 @@ class GemmRS(FusedOpBase):
         out = torch.empty((M // self.world, N), dtype=self.output_dtype, device=input.device)
         keep: list = []
         args = _dense.base_args(a, w, bias, self.output_dtype, input_scale, weight_scale,
-                                status=self.status, keep=keep)
+                                m=M, status=self.status, keep=keep)
         args.M = M
         args.mode, args.rank, args.world = _dense.REDUCE_SCATTER, self.rank, self.world
         args.epoch = self.epoch

@@ -1,0 +1,79 @@
+"""Tile / raster choices of the dense tcgen05 kernel per problem shape.
+
+The reference keeps one compiled-in C++ record per (meta, shape) under
+``src/*/tuning_config/*.cu`` and can load more from ``FLUX_TUNE_CONFIG_FILE``; here the kernel
+has three run-time knobs — CTA pairing (``cta_group``), tile width (``tile_n``) and the raster
+group (``group_m``) — so the table is a small dict of measured winners plus a heuristic for
+unseen shapes. ``python -m tempname_new_b200.tuning.tune_dense`` measures a shape and prints
+the entry to add; ``FLUXB_TUNE_FILE`` names a JSON file of extra entries.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Dict, Tuple
+
+Key = Tuple[int, int, int]
+
+# (M rows computed per GPU, N, K) -> knobs. Measured on B200 (148 SMs, 1000 W cap), bf16.
+DENSE_TABLE: Dict[Key, Dict[str, int]] = {
+    (8192, 49152, 12288): {"cta_group": 1, "tile_n": 256, "group_m": 16},
+    (8192, 12288, 49152): {"cta_group": 2, "tile_n": 256, "group_m": 2},
+    (8192, 24576, 12288): {"cta_group": 2, "tile_n": 256, "group_m": 4},
+    (8192, 12288, 24576): {"cta_group": 2, "tile_n": 256, "group_m": 2},
+    (8192, 12288, 12288): {"cta_group": 2, "tile_n": 256, "group_m": 4},
+    (8192, 6144, 12288): {"cta_group": 2, "tile_n": 256, "group_m": 8},
+    (8192, 12288, 6144): {"cta_group": 2, "tile_n": 256, "group_m": 8},
+    (8192, 8192, 8192): {"cta_group": 2, "tile_n": 256, "group_m": 4},
+    (4096, 4096, 4096): {"cta_group": 2, "tile_n": 256, "group_m": 8},
+}
+
+_NUM_SMS = 148
+
+
+def _wave_eff(tiles: int, slots: int) -> float:
+    waves = -(-tiles // slots)
+    return tiles / (waves * slots)
+
+
+def heuristic(m: int, n: int, k: int, elt: int = 2) -> Dict[str, int]:
+    """CTA pairs on 256 x 256 tiles unless the problem is too small to fill 74 pairs; raster
+    groups get narrower as the rows they keep resident (group * 256 * K bytes) outgrow L2."""
+    if m >= 256 and n >= 256 and (m // 256) * -(-n // 256) >= _NUM_SMS // 4:
+        cg, bn = 2, 256
+    elif n % 256 == 0 or n > 2048:
+        cg, bn = 1, 256
+    else:
+        cg, bn = 1, 128
+    row_bytes = k * elt
+    if cg == 2:
+        group = 8 if -(-n // bn) <= 32 else 4
+        if row_bytes >= 48 * 1024:
+            group = 2
+    else:
+        group = 16
+    return {"cta_group": cg, "tile_n": bn, "group_m": group}
+
+
+def _load_extra() -> Dict[Key, Dict[str, int]]:
+    path = os.environ.get("FLUXB_TUNE_FILE")
+    if not path:
+        return {}
+    with open(path) as f:
+        raw = json.load(f)
+    return {tuple(e["key"]): e["best"] for e in raw}
+
+
+_EXTRA = None
+
+
+def lookup(m: int, n: int, k: int, elt: int = 2) -> Dict[str, int]:
+    global _EXTRA
+    if _EXTRA is None:
+        _EXTRA = _load_extra()
+    key = (m, n, k)
+    if key in _EXTRA:
+        return dict(_EXTRA[key])
+    if key in DENSE_TABLE:
+        return dict(DENSE_TABLE[key])
+    return heuristic(m, n, k, elt)

@@ -1,0 +1,114 @@
+"""Single-GPU micro-benchmarks of the library's kernels, usable on their own or under ncu:
+
+    python -m tempname_new_b200.utils.microbench gemm --m 8192 --n 8192 --k 8192 --cta-group 2
+    python -m tempname_new_b200.utils.microbench quant --m 8192 --k 8192
+
+Each prints one JSON line with the CUDA-event time (median, L2 flushed between iterations),
+achieved TFLOP/s or GB/s and the fraction of the measured peak in ``MEASURED_PEAKS.json``
+(fallback 1590 TFLOP/s / 6650 GB/s when that file is absent).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return p["bf16_tflops"], p["hbm_gbs"], "measured"
+    except (OSError, KeyError):
+        return 1590.0, 6650.0, "fallback"
+
+
+def timed(fn, iters: int, warmup: int, flush: bool = True):
+    dev = torch.device("cuda")
+    scratch = torch.empty(256 << 20, dtype=torch.int8, device=dev) if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if scratch is not None:
+            scratch.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def cmd_gemm(a):
+    from ..ops import _dense
+    dev = torch.device("cuda")
+    dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp8": torch.float8_e4m3fn}[a.dtype]
+    x = torch.randn(a.m, a.k, device=dev).to(dt)
+    w = (torch.randn(a.n, a.k, device=dev) * 0.02).to(dt)
+    out = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16 if dt != torch.float16 else dt)
+    if a.impl == "torch":
+        fn = lambda: torch.matmul(x, w.t(), out=out)  # noqa: E731
+    else:
+        fn = lambda: _dense.plain_gemm(x, w, out, tile_n=a.tile_n, group_m=a.group_m,  # noqa: E731
+                                       cta_group=a.cta_group)
+    ms = timed(fn, a.iters, a.warmup, not a.no_flush)
+    tf = 2.0 * a.m * a.n * a.k / ms / 1e9
+    pk, _, src = peaks()
+    print(json.dumps({"op": "gemm", "impl": a.impl, "m": a.m, "n": a.n, "k": a.k, "dtype": a.dtype,
+                      "cta_group": a.cta_group, "tile_n": a.tile_n, "group_m": a.group_m, "ms": ms,
+                      "tflops": tf, "frac_of_bf16_peak": tf / pk, "peak": src}))
+
+
+def cmd_quant(a):
+    import tempname_new_b200 as flux
+    dev = torch.device("cuda")
+    x = torch.randn(a.m, a.k, device=dev).bfloat16()
+    q = flux.Quantization(torch.bfloat16, torch.float8_e4m3fn)
+    fn = (lambda: q.quantize_vector_blockwise(x, a.transpose)) if a.kind == "1x128" else \
+        (lambda: q.quantize_square_blockwise(x, a.transpose))
+    ms = timed(fn, a.iters, a.warmup, not a.no_flush)
+    nbytes = a.m * a.k * (2 + 1 + (1 if a.transpose else 0))
+    gbs = nbytes / ms / 1e6
+    _, pk, src = peaks()
+    print(json.dumps({"op": "quant_" + a.kind, "m": a.m, "k": a.k, "transpose": a.transpose, "ms": ms,
+                      "gbs": gbs, "frac_of_hbm_peak": gbs / pk, "peak": src}))
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="microbench")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=8192)
+    g.add_argument("--n", type=int, default=8192)
+    g.add_argument("--k", type=int, default=8192)
+    g.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp8"])
+    g.add_argument("--impl", default="fluxb", choices=["fluxb", "torch"])
+    g.add_argument("--cta-group", type=int, default=0)
+    g.add_argument("--tile-n", type=int, default=0)
+    g.add_argument("--group-m", type=int, default=0)
+    g.set_defaults(fn=cmd_gemm)
+    q = sub.add_parser("quant")
+    q.add_argument("--m", type=int, default=8192)
+    q.add_argument("--k", type=int, default=8192)
+    q.add_argument("--kind", default="1x128", choices=["1x128", "128x128"])
+    q.add_argument("--transpose", action="store_true")
+    q.set_defaults(fn=cmd_quant)
+    for p in (g, q):
+        p.add_argument("--iters", type=int, default=10)
+        p.add_argument("--warmup", type=int, default=3)
+        p.add_argument("--no-flush", action="store_true")
+    a = ap.parse_args(argv)
+    a.fn(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
