@@ -62,6 +62,15 @@ typedef struct {
   void* rs_out;
   uint32_t* rs_work;         /* local uint32, zero at first use */
   uint32_t* local_cnt;       /* local scratch of world * ceil(M/world/128) uint32, zero at first use */
+  /* block-scaled fp8 (blockscale != 0): inverse scales as fluxb_quantize_blockwise stores them.
+   * sa [rows/128, K/128, 128] for the rows of `a`; sb [N/128, K/128]. In all-gather mode the
+   * scales of the peers' shards arrive in ag_scale_land[rank] ([M/128, K/128, 128]). Needs
+   * in_dtype FLUXB_FP8_E4M3, K % 128 == 0, N % 128 == 0 and M/world % 128 == 0. */
+  const float* sa;
+  const float* sb;
+  float* ag_scale_land[FLUXB_MAX_RANKS];
+  int32_t blockscale;
+  int32_t reserved3;
   void* stream;
 } fluxb_dense_args_t;
 

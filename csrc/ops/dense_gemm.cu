@@ -14,6 +14,7 @@ namespace {
 
 template <class Cfg>
 int launch_dense(const DenseGemmParams& p, int grid, cudaStream_t stream) {
+  constexpr int kThreads = Cfg::THREADS;
   static bool configured[64] = {false};
   int dev = 0;
   FLUXB_CUDA_OK(cudaGetDevice(&dev));
@@ -23,11 +24,11 @@ int launch_dense(const DenseGemmParams& p, int grid, cudaStream_t stream) {
     if (dev < 64) configured[dev] = true;
   }
   if constexpr (Cfg::CG == 1) {
-    dense_gemm_kernel<Cfg><<<grid, 256, Cfg::SMEM_BYTES, stream>>>(p);
+    dense_gemm_kernel<Cfg><<<grid, kThreads, Cfg::SMEM_BYTES, stream>>>(p);
   } else {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(256, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -84,6 +85,8 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   p.bias_row_stride = a->bias_row_stride;
   p.scale_a = a->scale_a;
   p.scale_b = a->scale_b;
+  p.sa = a->sa;
+  p.sb = a->sb;
   p.ab_fmt = (a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP8_E5M2) ? 1 : 0;
   p.out_f16 = a->out_dtype == FLUXB_FP16 ? 1 : 0;
   p.act = a->act;
@@ -94,7 +97,14 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   int cg = a->cta_group;
   FLUXB_REQUIRE(cg >= 0 && cg <= 2, "cta_group must be 0 (auto), 1 or 2");
   if (cg == 0) cg = 1;
-  if (multi && a->mode == FLUXB_ALLGATHER) {
+  if (a->blockscale) {
+    FLUXB_REQUIRE(a->in_dtype == FLUXB_FP8_E4M3, "block-scaled GEMM takes e4m3 operands");
+    FLUXB_REQUIRE(a->sa && a->sb, "block scales missing");
+    FLUXB_REQUIRE(a->K % 128 == 0 && a->N % 128 == 0, "block-scaled GEMM needs K and N multiples of 128");
+    FLUXB_REQUIRE((a->M / (multi ? a->world : 1)) % 128 == 0, "block-scaled GEMM needs rows per rank in multiples of 128");
+    cg = 1;
+    bn = 128;
+  } else if (multi && a->mode == FLUXB_ALLGATHER) {
     // the all-gather variants exist for CTA pairs on 256-wide tiles and single CTAs on 128-wide
     if (cg == 2 && a->M / a->world >= 256) bn = 256;
     else { cg = 1; bn = 128; }
@@ -127,7 +137,13 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
       p.ag_land[r] = a->ag_land[r];
       p.ag_flags[r] = a->ag_flags[r];
       FLUXB_REQUIRE(p.ag_land[r] && p.ag_flags[r], "all-gather peer pointers missing");
+      if (a->blockscale) {
+        FLUXB_REQUIRE(a->ag_scale_land[r] != nullptr, "all-gather scale landing buffers missing");
+        p.ag_scale_land[r] = a->ag_scale_land[r];
+      }
     }
+    p.ag_scale_src = a->sa;
+    p.sa_land = a->ag_scale_land[a->rank];
   }
   // ---- B
   {
@@ -194,6 +210,10 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   if (cg == 2) grid &= ~1;
 
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
+  if (a->blockscale) {
+    if (p.mode == kModeAllGather) return launch_dense<DenseCfg<128, 1, 4, 1, 32768, true>>(p, grid, stream);
+    return launch_dense<DenseCfg<128, 1, 4, 1, 0, true>>(p, grid, stream);
+  }
   if (p.mode == kModeAllGather) {
     // variants that carry the staging rings of the all-gather push
     if (cg == 2 && bn == 256) {

@@ -54,6 +54,12 @@ struct DenseGemmParams {
   int32_t out_f16;               // 1: D, bias and staging are fp16 instead of bf16
   int32_t act;                   // epilogue activation after bias: 0 none, 1 gelu(tanh), 2 relu, 3 silu
   int32_t reserved1;
+  // block scales (fp8 block-scaled variant): inverse scales as the quantiser stores them
+  const float* sa;               // for the rows of tm_a:      [rows/128, K/128, 128]
+  const float* sa_land;          // for the rows of tm_a_land: [W*seg_rows/128, K/128, 128]
+  const float* sb;               // [N/128, K/128]
+  const float* ag_scale_src;     // all-gather: this rank's A scales (== sa), pushed with the shard
+  float* ag_scale_land[kMaxRanks];
   // all-gather
   const void* ag_src;            // this rank's shard [seg_rows, K]
   void* ag_land[kMaxRanks];      // landing buffer of every rank, [W][seg_rows][K]
@@ -73,9 +79,17 @@ struct DenseGemmParams {
 // tile: each CTA stages its own 128 rows of A and its own BN/2 rows of B, the pair leader issues
 // tcgen05.mma.cta_group::2, and each CTA ends up with its 128 x BN slice of D in its own TMEM.
 // COMM_ > 0 reserves COMM_ bytes of shared memory as staging rings for the all-gather push.
-template <int BN_, int KIND_, int STAGES_, int CG_ = 1, int COMM_ = 0>
+// BS_ = true: block-scaled fp8 (1x128 A scales, 128x128 B scales): every 128-deep k-block is
+// accumulated into a fresh TMEM buffer and promoted into fp32 registers, multiplied by its
+// scales, by eight epilogue warps (two per TMEM lane quadrant, 64 columns each).
+template <int BN_, int KIND_, int STAGES_, int CG_ = 1, int COMM_ = 0, bool BS_ = false>
 struct DenseCfg {
   static constexpr int COMM_BYTES = COMM_;
+  static constexpr bool BS = BS_;
+  static constexpr int EPI_WARPS = BS_ ? 8 : 4;
+  static constexpr int THREADS = 128 + 32 * EPI_WARPS;
+  static constexpr int ACC_BUFS = BS_ ? 4 : 2;
+  static_assert(!BS_ || (KIND_ == 1 && BN_ == 128 && CG_ == 1), "block-scaled variant: fp8, 128x128 tiles");
   static constexpr int CG = CG_;
   static constexpr int BM_CTA = 128;                       // rows of A / D per CTA
   static constexpr int BM = 128 * CG_;                     // rows per tile
@@ -90,12 +104,12 @@ struct DenseCfg {
   static constexpr int B_BYTES = B_ROWS_CTA * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_BUF_BYTES = 32 * 128;           // 32 rows x 64 bf16
-  static constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;
+  static constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_BUF_BYTES;
   static constexpr int BAR_BYTES = 256;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + COMM_BYTES + BAR_BYTES + 1024;
   static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared memory limit");
   static constexpr int TMEM_COLS = 512;
-  static_assert(2 * BN <= TMEM_COLS, "two accumulators must fit TMEM");
+  static_assert(ACC_BUFS * BN <= TMEM_COLS, "accumulators must fit TMEM");
 };
 
 struct TileCoord {
@@ -129,7 +143,7 @@ __device__ __forceinline__ TileCoord decode_tile(const DenseGemmParams& p, int t
 }
 
 template <class Cfg>
-__global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constant__ DenseGemmParams p) {
+__global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __grid_constant__ DenseGemmParams p) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -146,13 +160,15 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
   // the 8 barriers of the all-gather staging rings
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  constexpr int NACC = Cfg::ACC_BUFS;
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
-  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * STAGES + 4));
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + NACC + a); };
+  volatile uint32_t* tmem_slot =
+      reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * STAGES + 2 * NACC));
   volatile uint32_t* abort_word = tmem_slot + 1;
   volatile uint32_t* claim_slot = tmem_slot + 2;
-  const uint32_t ring_bar_base = bar_base + 8u * (2 * STAGES + 4) + 16u;
-  static_assert(8 * (2 * STAGES + 4) + 16 + 64 <= Cfg::BAR_BYTES, "barrier block too small");
+  const uint32_t ring_bar_base = bar_base + 8u * (2 * STAGES + 2 * NACC) + 16u;
+  static_assert(8 * (2 * STAGES + 2 * NACC) + 16 + 64 <= Cfg::BAR_BYTES, "barrier block too small");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -169,9 +185,9 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
       ptx::mbar_init(full_bar(s), 1);
       ptx::mbar_init(empty_bar(s), 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < NACC; ++a) {
       ptx::mbar_init(tfull_bar(a), 1);
-      ptx::mbar_init(tempty_bar(a), 4 * CG);
+      ptx::mbar_init(tempty_bar(a), Cfg::EPI_WARPS * CG);
     }
     for (int i = 0; i < 8; ++i) ptx::mbar_init(ring_bar_base + 8u * i, 1);
     *abort_word = 0;
@@ -247,6 +263,30 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
       uint32_t phase = 0;
       int it = 0;
       for (int t = tile_slot; t < total_tiles; t += tile_stride, ++it) {
+        if constexpr (Cfg::BS) {
+          // every k-block goes to its own TMEM buffer; the epilogue warps promote it
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            const uint32_t n = static_cast<uint32_t>(it) * k_blocks + kb;
+            const int buf = n % NACC;
+            mbar_wait(wc, tempty_bar(buf), ((n / NACC) & 1u) ^ 1u, kSiteTmemEmpty);
+            mbar_wait(wc, full_bar(stage), phase, kSiteSmemFull);
+            ptx::tc_fence_after();
+            const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+            const uint64_t adesc = ptx::umma_desc_k_sw128(sa);
+            const uint64_t bdesc = ptx::umma_desc_k_sw128(sa + Cfg::A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / Cfg::UMMA_K; ++k)
+              ptx::umma_ss<CG, Cfg::KIND>(tmem_base + buf * BN, adesc + 2u * k, bdesc + 2u * k, idesc,
+                                          k != 0 ? 1u : 0u);
+            ptx::umma_commit(empty_bar(stage));
+            ptx::umma_commit(tfull_bar(buf));
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          continue;
+        }
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         mbar_wait(wc, tempty_bar(acc), acc_phase ^ 1u, kSiteTmemEmpty);
@@ -303,9 +343,21 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
           const int64_t slab_off = static_cast<int64_t>(p.rank) * p.seg_rows * row_bytes;
           const uint32_t cw = blockIdx.x * 2 + (warp - 2);
           const uint32_t ncw = gridDim.x * 2;
-          auto step_chunks = [&](int mt) -> uint32_t {  // chunks of tile row mt that this warp moves
+          // scales of a block-scaled shard ride along as a second byte range per tile row:
+          // [rows/128][K/128][128] floats
+          const int64_t srow_bytes = Cfg::BS ? static_cast<int64_t>(k_blocks) * 512 : 0;  // per 128 rows
+          const int64_t sslab_off = static_cast<int64_t>(p.rank) * (p.seg_rows / 128) * srow_bytes;
+          const uint8_t* ssrc = reinterpret_cast<const uint8_t*>(p.ag_scale_src);
+          auto payload_chunks = [&](int mt) -> uint32_t {
             const int rows = min(BM, p.seg_rows - mt * BM);
-            const uint32_t nch = static_cast<uint32_t>((rows * row_bytes + CH - 1) / CH);
+            return static_cast<uint32_t>((rows * row_bytes + CH - 1) / CH);
+          };
+          auto scale_bytes = [&](int mt) -> int64_t {
+            const int rows = min(BM, p.seg_rows - mt * BM);
+            return static_cast<int64_t>((rows + 127) / 128) * srow_bytes;
+          };
+          auto step_chunks = [&](int mt) -> uint32_t {  // chunks of tile row mt that this warp moves
+            const uint32_t nch = payload_chunks(mt) + static_cast<uint32_t>((scale_bytes(mt) + CH - 1) / CH);
             return nch > cw ? (nch - cw - 1) / ncw + 1 : 0u;
           };
           auto publish = [&](int d, int mt) {
@@ -326,22 +378,38 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
             int peer = p.rank - d;
             if (peer < 0) peer += p.world;
             uint8_t* land = reinterpret_cast<uint8_t*>(p.ag_land[peer]) + slab_off;
+            uint8_t* sland = Cfg::BS ? reinterpret_cast<uint8_t*>(p.ag_scale_land[peer]) + sslab_off : nullptr;
             for (int mt = 0; mt < m_tiles_seg; ++mt) {
               const int rows = min(BM, p.seg_rows - mt * BM);
               const int64_t first = static_cast<int64_t>(mt) * BM * row_bytes;
               const int64_t bytes = rows * row_bytes;
-              const uint32_t nch = static_cast<uint32_t>((bytes + CH - 1) / CH);
+              const uint32_t nch_p = payload_chunks(mt);
+              const int64_t sfirst = static_cast<int64_t>(mt) * (BM / 128) * srow_bytes;
+              const int64_t sbytes = scale_bytes(mt);
+              const uint32_t nch = nch_p + static_cast<uint32_t>((sbytes + CH - 1) / CH);
               for (uint32_t c = cw; c < nch; c += ncw) {
-                const int64_t off = first + static_cast<int64_t>(c) * CH;
-                const int64_t left = bytes - static_cast<int64_t>(c) * CH;
+                const uint8_t* from;
+                uint8_t* to;
+                int64_t left;
+                if (c < nch_p) {
+                  const int64_t off = first + static_cast<int64_t>(c) * CH;
+                  from = src + off;
+                  to = land + off;
+                  left = bytes - static_cast<int64_t>(c) * CH;
+                } else {
+                  const int64_t off = sfirst + static_cast<int64_t>(c - nch_p) * CH;
+                  from = ssrc + off;
+                  to = sland + off;
+                  left = sbytes - static_cast<int64_t>(c - nch_p) * CH;
+                }
                 const uint32_t sz = left < static_cast<int64_t>(CH) ? static_cast<uint32_t>(left) : CH;
                 const uint32_t slot = issued % NSLOT;
                 const uint32_t ph = (issued / NSLOT) & 1u;
                 ptx::bulk_wait_read<NSLOT - 1>();  // the store that last used this slot has read it
                 ptx::mbar_arrive_expect_tx(rbar + 8u * slot, sz);
-                ptx::bulk_load(ring + slot * CH, src + off, sz, rbar + 8u * slot);
+                ptx::bulk_load(ring + slot * CH, from, sz, rbar + 8u * slot);
                 mbar_wait(wc, rbar + 8u * slot, ph, kSiteSmemFull);
-                ptx::bulk_store(land + off, ring + slot * CH, sz);
+                ptx::bulk_store(to, ring + slot * CH, sz);
                 ptx::bulk_commit();
                 ++issued;
               }
@@ -366,9 +434,10 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    const int q = warp & 3;  // TMEM lane quadrant this warp may read
-    uint8_t* my_epi = epi_ptr + q * 2 * Cfg::EPI_BUF_BYTES;
-    const uint32_t my_epi_u32 = epi_base + q * 2 * Cfg::EPI_BUF_BYTES;
+    const int q = warp & 3;              // TMEM lane quadrant this warp may read
+    const int ew = warp - 4;             // epilogue warp index
+    uint8_t* my_epi = epi_ptr + ew * 2 * Cfg::EPI_BUF_BYTES;
+    const uint32_t my_epi_u32 = epi_base + ew * 2 * Cfg::EPI_BUF_BYTES;
     const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.bias);
     const bool f16 = p.out_f16 != 0;
     float alpha = 1.f;
@@ -378,10 +447,69 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
     int it = 0;
     uint32_t nstore = 0;
     bool started = !(multi && p.mode == kModeReduceScatter);
+
+    // 32 rows x 64 columns of fp32 results (r0: columns 0..31, r1: 32..63 of the chunk, this
+    // thread's row) -> scale, bias, activation -> 16-bit -> swizzled staging -> TMA store
+    auto emit_chunk = [&](uint32_t (&r0)[32], uint32_t (&r1)[32], int col0, int row, int64_t grow,
+                          int store_row0, const CUtensorMap* tmd, int z) {
+      if (scaled) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          r0[j] = __float_as_uint(__uint_as_float(r0[j]) * alpha);
+          r1[j] = __float_as_uint(__uint_as_float(r1[j]) * alpha);
+        }
+      }
+      if (bias != nullptr && col0 < p.N) {
+        const uint16_t* brow = bias + (p.bias_row_stride ? grow * p.bias_row_stride : 0);
+        const bool row_ok = row < p.seg_rows;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (row_ok && col0 + j < p.N)
+            r0[j] = __float_as_uint(__uint_as_float(r0[j]) + ptx::half_bits_to_float(brow[col0 + j], f16));
+          if (row_ok && col0 + 32 + j < p.N)
+            r1[j] = __float_as_uint(__uint_as_float(r1[j]) +
+                                    ptx::half_bits_to_float(brow[col0 + 32 + j], f16));
+        }
+      }
+      if (p.act != 0) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          r0[j] = __float_as_uint(ptx::activate(__uint_as_float(r0[j]), p.act));
+          r1[j] = __float_as_uint(ptx::activate(__uint_as_float(r1[j]), p.act));
+        }
+      }
+      const uint32_t buf = nstore & 1u;
+      if (lane == 0) ptx::bulk_wait_read<1>();
+      __syncwarp();
+      uint8_t* dst = my_epi + buf * Cfg::EPI_BUF_BYTES + lane * 128;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 v;
+        v.x = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+        v.y = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+        v.z = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+        v.w = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+        *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = v;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 v;
+        v.x = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+        v.y = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+        v.z = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+        v.w = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+        *reinterpret_cast<uint4*>(dst + (((j + 4) ^ (lane & 7)) << 4)) = v;
+      }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && col0 < p.N && store_row0 < p.seg_rows)
+        ptx::tma_store_3d(tmd, my_epi_u32 + buf * Cfg::EPI_BUF_BYTES, col0, store_row0, z);
+      if (lane == 0) ptx::bulk_commit();
+      ++nstore;
+    };
+
     for (int t = tile_slot; t < total_tiles; t += tile_stride, ++it) {
       const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
-      const int acc = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
       const int m_cta = c.m_in_seg + static_cast<int>(cta_rank) * Cfg::BM_CTA;
       const CUtensorMap* tmd = &p.tm_d[0];
       int z = c.seg;
@@ -395,94 +523,104 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
           started = true;
         }
       }
-      // one lane polls; the others sleep at the warp barrier and then observe the completed
-      // phase with a single try_wait of their own
-      if (lane == 0) mbar_wait(wc, tfull_bar(acc), acc_phase, kSiteTmemFull);
-      __syncwarp();
-      mbar_wait(wc, tfull_bar(acc), acc_phase, kSiteTmemFull);
-      ptx::tc_fence_after();
       const int row = m_cta + q * 32 + lane;                   // row inside the segment
       const int64_t grow = static_cast<int64_t>(c.seg) * p.seg_rows + row;  // global row
-#pragma unroll 1
-      for (int ch = 0; ch < BN / 64; ++ch) {
-        uint32_t r0[32], r1[32];
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + ch * 64;
-        ptx::tmem_ld_32x32b_x32(taddr, r0);
-        ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
-        ptx::tmem_ld_wait();
-        if (ch == BN / 64 - 1) {
+
+      if constexpr (Cfg::BS) {
+        // ---- block-scaled: promote every k-block's partial product into fp32 registers.
+        // This warp owns 64 of the tile's 128 columns (warps 4..7: 0..63, warps 8..11: 64..127).
+        const int half = ew >> 2;
+        const int kbs = k_blocks;                               // scale blocks along K (BK == 128)
+        const float* sa_rows = p.sa;
+        int64_t srow = grow;                                    // row in the scale tensor's frame
+        if (p.mode == kModeAllGather && multi) {
+          if (c.seg == p.rank) {
+            srow = row;
+          } else {
+            sa_rows = p.sa_land;
+            // the scales travelled with the shard: make this thread's reads follow the flag
+            const uint32_t* f = p.ag_flags[p.rank] + c.seg * m_tiles_seg + c.m_tile;
+            if (lane == 0) flag_wait_ge(wc, f, p.epoch, kSiteShardFlag);
+            __syncwarp();
+          }
+        }
+        const float* sa_ptr = sa_rows + (srow >> 7) * static_cast<int64_t>(kbs) * 128 + (srow & 127);
+        const float* sb_ptr = p.sb + static_cast<int64_t>(c.n0 >> 7) * kbs;
+        uint64_t acc2[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc2[j] = 0ull;
+        float s_next = sa_ptr[0] * sb_ptr[0];
+        for (int kb = 0; kb < kbs; ++kb) {
+          const float sc = s_next;
+          if (kb + 1 < kbs) s_next = sa_ptr[static_cast<int64_t>(kb + 1) * 128] * sb_ptr[kb + 1];
+          const uint32_t n = static_cast<uint32_t>(it) * kbs + kb;
+          const int buf = n % NACC;
+          const uint32_t par = (n / NACC) & 1u;
+          if (lane == 0) mbar_wait(wc, tfull_bar(buf), par, kSiteTmemFull);
+          __syncwarp();
+          mbar_wait(wc, tfull_bar(buf), par, kSiteTmemFull);
+          ptx::tc_fence_after();
+          uint32_t r0[32], r1[32];
+          const uint32_t taddr =
+              tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + half * 64;
+          ptx::tmem_ld_32x32b_x32(taddr, r0);
+          ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
+          ptx::tmem_ld_wait();
           ptx::tc_fence_before();
           __syncwarp();
-          if (lane == 0) {
-            if constexpr (CG == 1) ptx::mbar_arrive(tempty_bar(acc));
-            else ptx::mbar_arrive_remote(tempty_bar(acc), 0);
-          }
-        }
-        const int col0 = c.n0 + ch * 64;
-        if (scaled) {
+          if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+          const uint64_t sc2 = ptx::pack_f32x2(sc, sc);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            r0[j] = __float_as_uint(__uint_as_float(r0[j]) * alpha);
-            r1[j] = __float_as_uint(__uint_as_float(r1[j]) * alpha);
+          for (int j = 0; j < 16; ++j) {
+            acc2[j] = ptx::ffma2(ptx::pack_b32x2(r0[2 * j], r0[2 * j + 1]), sc2, acc2[j]);
+            acc2[16 + j] = ptx::ffma2(ptx::pack_b32x2(r1[2 * j], r1[2 * j + 1]), sc2, acc2[16 + j]);
           }
         }
-        if (bias != nullptr && col0 < p.N) {
-          const uint16_t* brow = bias + (p.bias_row_stride ? grow * p.bias_row_stride : 0);
-          const bool row_ok = row < p.seg_rows;
+        uint32_t o0[32], o1[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (row_ok && col0 + j < p.N)
-              r0[j] = __float_as_uint(__uint_as_float(r0[j]) + ptx::half_bits_to_float(brow[col0 + j], f16));
-            if (row_ok && col0 + 32 + j < p.N)
-              r1[j] = __float_as_uint(__uint_as_float(r1[j]) +
-                                      ptx::half_bits_to_float(brow[col0 + 32 + j], f16));
-          }
+        for (int j = 0; j < 16; ++j) {
+          o0[2 * j] = static_cast<uint32_t>(acc2[j]);
+          o0[2 * j + 1] = static_cast<uint32_t>(acc2[j] >> 32);
+          o1[2 * j] = static_cast<uint32_t>(acc2[16 + j]);
+          o1[2 * j + 1] = static_cast<uint32_t>(acc2[16 + j] >> 32);
         }
-        if (p.act != 0) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            r0[j] = __float_as_uint(ptx::activate(__uint_as_float(r0[j]), p.act));
-            r1[j] = __float_as_uint(ptx::activate(__uint_as_float(r1[j]), p.act));
-          }
-        }
-        const uint32_t buf = nstore & 1u;
-        if (lane == 0) ptx::bulk_wait_read<1>();
+        emit_chunk(o0, o1, c.n0 + half * 64, row, grow, m_cta + q * 32, tmd, z);
+      } else {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        // one lane polls; the others sleep at the warp barrier and then observe the completed
+        // phase with a single try_wait of their own
+        if (lane == 0) mbar_wait(wc, tfull_bar(acc), acc_phase, kSiteTmemFull);
         __syncwarp();
-        uint8_t* dst = my_epi + buf * Cfg::EPI_BUF_BYTES + lane * 128;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 v;
-          v.x = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
-          v.y = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
-          v.z = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
-          v.w = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
-          *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = v;
+        mbar_wait(wc, tfull_bar(acc), acc_phase, kSiteTmemFull);
+        ptx::tc_fence_after();
+#pragma unroll 1
+        for (int ch = 0; ch < BN / 64; ++ch) {
+          uint32_t r0[32], r1[32];
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + ch * 64;
+          ptx::tmem_ld_32x32b_x32(taddr, r0);
+          ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
+          ptx::tmem_ld_wait();
+          if (ch == BN / 64 - 1) {
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (CG == 1) ptx::mbar_arrive(tempty_bar(acc));
+              else ptx::mbar_arrive_remote(tempty_bar(acc), 0);
+            }
+          }
+          emit_chunk(r0, r1, c.n0 + ch * 64, row, grow, m_cta + q * 32, tmd, z);
         }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 v;
-          v.x = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
-          v.y = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
-          v.z = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
-          v.w = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
-          *reinterpret_cast<uint4*>(dst + (((j + 4) ^ (lane & 7)) << 4)) = v;
-        }
-        ptx::fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0 && col0 < p.N && m_cta + q * 32 < p.seg_rows) {
-          ptx::tma_store_3d(tmd, my_epi_u32 + buf * Cfg::EPI_BUF_BYTES, col0, m_cta + q * 32, z);
-        }
-        if (lane == 0) ptx::bulk_commit();
-        ++nstore;
       }
       if (p.mode == kModeReduceScatter && multi) {
         // the tile's slab rows have fully landed at the owner -> count this warp's arrival
         if (lane == 0) {
           ptx::bulk_wait<0>();
           ptx::fence_proxy_async_all();
-          // the last of the n_tiles*4 warps that store into this tile row tells the owner
+          // the last of the warps that store into this tile row tells the owner
           uint32_t* cnt = p.local_cnt + c.seg * m_tiles_seg + c.m_tile;
-          if (ptx::atom_add_acq_rel_sys(cnt, 1u) == static_cast<uint32_t>(n_tiles) * 4u * CG - 1u) {
+          if (ptx::atom_add_acq_rel_sys(cnt, 1u) ==
+              static_cast<uint32_t>(n_tiles) * Cfg::EPI_WARPS * CG - 1u) {
             *cnt = 0;
             ptx::st_release_sys(p.rs_ctr[c.seg] + c.m_tile * kMaxRanks + p.rank, p.epoch);
           }
@@ -530,6 +668,7 @@ __global__ void __launch_bounds__(256, 1) dense_gemm_kernel(const __grid_constan
       __syncthreads();
       const uint32_t u = *claim_slot;
       if (u >= units) break;
+      if (threadIdx.x >= 256) continue;  // (block-scaled variant runs 384 threads)
 #pragma unroll 1
       for (int rep = 0; rep < kUnit / 256; rep += 2) {
         int64_t idx[2];

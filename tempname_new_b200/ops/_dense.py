@@ -35,6 +35,8 @@ class DenseArgs(ctypes.Structure):
         ("start_ctr", _VP * MAX_RANKS),
         ("rs_stage", _VP * MAX_RANKS), ("rs_ctr", _VP * MAX_RANKS),
         ("rs_out", _VP), ("rs_work", _VP), ("local_cnt", _VP),
+        ("sa", _VP), ("sb", _VP), ("ag_scale_land", _VP * MAX_RANKS),
+        ("blockscale", ctypes.c_int32), ("reserved3", ctypes.c_int32),
         ("stream", _VP),
     ]
 

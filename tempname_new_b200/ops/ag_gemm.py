@@ -37,6 +37,7 @@ class AGKernel(FusedOpBase):
         if (full_m + 127) // 128 + 8 > MAX_FLAG_WORDS:
             raise ValueError("full_m too large for the flag block")
         self.land = SymmBuffer(full_m * k_dim * _ELEM[input_dtype], self.pg) if self.world > 1 else None
+        self.scale_land = None  # allocated at the first block-scaled call
 
     def forward(self, input: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
                 output: Optional[torch.Tensor] = None, input_scale: Optional[torch.Tensor] = None,
@@ -52,12 +53,29 @@ class AGKernel(FusedOpBase):
             raise ValueError(f"AGKernel was built for M <= {self.full_m}, K = {self.k_dim}; got M={M}, K={K}")
         self.epoch += 1
         if not input.is_cuda:
+            if input_scale is not None and input_scale.dim() == 3:
+                raise NotImplementedError("block-scaled AG+GEMM has no CPU path")
             return self._forward_cpu(input, w, bias, output, input_scale, weight_scale, gathered_input, act)
         a = input if input.is_contiguous() else input.contiguous()
         out = output if output is not None else torch.empty((M, N), dtype=self.output_dtype, device=input.device)
         keep: list = []
-        args = _dense.base_args(a, w, bias, self.output_dtype, input_scale, weight_scale,
-                                act=act, m=M, status=self.status, keep=keep)
+        blockscale = input_scale is not None and input_scale.dim() == 3
+        if blockscale:
+            # fp8 payload and its 1x128 scales travel together; scales land in their own buffer
+            from .blockscale_gemm import blockscale_args
+            if seg % 128:
+                raise ValueError("block-scaled AG+GEMM needs M/W to be a multiple of 128")
+            args = blockscale_args(a, w, input_scale, weight_scale, bias, self.output_dtype, M,
+                                   status=self.status, keep=keep)
+            args.act = _dense.ACT[act]
+            if self.world > 1:
+                if self.scale_land is None:
+                    self.scale_land = SymmBuffer(self.full_m // 128 * (self.k_dim // 128) * 512, self.pg)
+                for r in range(self.world):
+                    args.ag_scale_land[r] = self.scale_land.ptr(r)
+        else:
+            args = _dense.base_args(a, w, bias, self.output_dtype, input_scale, weight_scale,
+                                    act=act, m=M, status=self.status, keep=keep)
         args.M = M
         args.d, args.ldd = out.data_ptr(), out.stride(0)
         args.mode, args.rank, args.world = _dense.ALLGATHER, self.rank, self.world

@@ -66,8 +66,15 @@ class GemmRS(FusedOpBase):
         a = input if input.stride(-1) == 1 else input.contiguous()
         out = torch.empty((M // self.world, N), dtype=self.output_dtype, device=input.device)
         keep: list = []
-        args = _dense.base_args(a, w, bias, self.output_dtype, input_scale, weight_scale,
-                                m=M, status=self.status, keep=keep)
+        if input_scale is not None and input_scale.dim() == 3:
+            from .blockscale_gemm import blockscale_args
+            if (M // self.world) % 128:
+                raise ValueError("block-scaled GEMM+RS needs M/W to be a multiple of 128")
+            args = blockscale_args(a, w, input_scale, weight_scale, bias, self.output_dtype, M,
+                                   status=self.status, keep=keep)
+        else:
+            args = _dense.base_args(a, w, bias, self.output_dtype, input_scale, weight_scale,
+                                    m=M, status=self.status, keep=keep)
         args.M = M
         args.mode, args.rank, args.world = _dense.REDUCE_SCATTER, self.rank, self.world
         args.epoch = self.epoch

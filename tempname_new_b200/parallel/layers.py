@@ -47,12 +47,13 @@ class _OpCache:
 
 class _ColumnParallelFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, cache: _OpCache, act):
+    def forward(ctx, x, weight, bias, cache: _OpCache, act, need_gathered=True):
         W = dist.get_world_size(cache.group)
         seg, K = x.shape
         M = seg * W
         op = cache.ag(M, weight.shape[0], K, x.dtype)
-        gathered = torch.empty((M, K), dtype=x.dtype, device=x.device)
+        # the gathered activations are only needed for the weight gradient
+        gathered = torch.empty((M, K), dtype=x.dtype, device=x.device) if need_gathered else None
         out = op.forward(x, weight, bias=bias, gathered_input=gathered, act=act)
         ctx.save_for_backward(gathered, weight)
         ctx.cache, ctx.has_bias, ctx.act = cache, bias is not None, act
@@ -68,9 +69,9 @@ class _ColumnParallelFn(torch.autograd.Function):
         # dgrad: [M, out/W] @ [out/W, in] summed over ranks and scattered over M
         op = cache.rs(g.shape[0], weight.shape[1], g.dtype)
         grad_x = op.forward(g, weight, None, transpose_weight_override=True)
-        grad_w = g.t().matmul(gathered)
+        grad_w = g.t().matmul(gathered) if gathered is not None else None
         grad_b = g.sum(0) if ctx.has_bias else None
-        return grad_x, grad_w, grad_b, None, None
+        return grad_x, grad_w, grad_b, None, None, None
 
 
 class _RowParallelFn(torch.autograd.Function):
@@ -114,7 +115,8 @@ class ColumnParallelLinear(nn.Module):
         self._cache = _OpCache(self.group)
 
     def forward(self, x: torch.Tensor, act: Optional[str] = None) -> torch.Tensor:
-        return _ColumnParallelFn.apply(x, self.weight, self.bias, self._cache, act)
+        need = torch.is_grad_enabled() and self.weight.requires_grad
+        return _ColumnParallelFn.apply(x, self.weight, self.bias, self._cache, act, need)
 
 
 class RowParallelLinear(nn.Module):
@@ -165,7 +167,8 @@ def patch_megatron_linears(model, tp_group=None, row: bool = True, column: bool 
             def fwd(self, input_, _cache=cache, **_):
                 s = input_.shape
                 b = None if self.skip_bias_add else self.bias
-                y = _ColumnParallelFn.apply(input_.reshape(-1, s[-1]).contiguous(), self.weight, b, _cache, None)
+                y = _ColumnParallelFn.apply(input_.reshape(-1, s[-1]).contiguous(), self.weight, b, _cache, None,
+                                            torch.is_grad_enabled() and self.weight.requires_grad)
                 y = y.reshape(s[0] * dist.get_world_size(_cache.group), *s[1:-1], self.weight.shape[0])
                 return y, (self.bias if self.skip_bias_add else None)
             mod.forward = fwd.__get__(mod)

@@ -1,0 +1,57 @@
+"""Block-scaled fp8 GEMM on the GPU against the PyTorch statement of the op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    return torch.device("cuda", 0)
+
+
+def _quantized(M, N, K, dev, seed=0):
+    import tempname_new_b200 as flux
+    g = torch.Generator(device=dev).manual_seed(seed)
+    x = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+    # make block scales differ a lot so that a wrong scale index shows
+    x[: M // 2] *= 8
+    w[:, K // 2:] *= 0.1
+    qz = flux.Quantization(torch.bfloat16, torch.float8_e4m3fn)
+    xq, sx, _, _ = qz.quantize_vector_blockwise(x, False)
+    wq, sw, _, _ = qz.quantize_square_blockwise(w, False)
+    return x, w, xq, sx, wq, sw
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (512, 1024, 2048), (1024, 3584, 8192)])
+def test_blockscale_gemm(dev, M, N, K):
+    import tempname_new_b200 as flux
+    x, w, xq, sx, wq, sw = _quantized(M, N, K, dev)
+    op = flux.BlockScaleGemm(torch.float8_e4m3fn, torch.float8_e4m3fn, torch.bfloat16)
+    out = op.forward(xq, wq, input_scale=sx, weight_scale=sw)
+    ref = flux.blockscale_gemm_torch(xq, wq, sx, sw, torch.float32)
+    full = x.float() @ w.float().t()
+    tol = 2e-2 * max(1.0, ref.abs().max().item())
+    assert (out.float() - ref).abs().max().item() <= tol
+    # and the quantised product tracks the unquantised one
+    rel = (out.float() - full).norm() / full.norm()
+    assert rel.item() < 0.06
+
+
+def test_blockscale_bias_and_grouped(dev):
+    import tempname_new_b200 as flux
+    M, N, K, E = 512, 256, 512, 2
+    x, w, xq, sx, wq, sw = _quantized(M, N * E, K, dev, seed=1)
+    op = flux.BlockScaleGemm()
+    bias = torch.randn(N * E, device=dev).bfloat16()
+    out = op.forward(xq, wq, bias=bias, input_scale=sx, weight_scale=sw)
+    ref = flux.blockscale_gemm_torch(xq, wq, sx, sw, torch.float32, bias)
+    assert (out.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    wq3, sw3 = wq.view(E, N, K), sw.view(E, N // 128, K // 128)
+    outg = op.forward_grouped(xq, torch.tensor([256, 256]), wq3, input_scale=sx, weight_scale=sw3)
+    for e in range(E):
+        r = flux.blockscale_gemm_torch(xq[e * 256:(e + 1) * 256], wq3[e], sx[e * 2:(e + 1) * 2], sw3[e], torch.float32)
+        assert (outg[e * 256:(e + 1) * 256].float() - r).abs().max().item() <= 2e-2 * max(1.0, r.abs().max().item())
