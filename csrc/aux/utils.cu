@@ -317,3 +317,49 @@ extern "C" int fluxb_moe_index_build(const int32_t* experts, int64_t n, int E, i
   g_launches.fetch_add(3, std::memory_order_relaxed);
   return kOk;
 }
+
+// ----------------------------------------------------------------------------------------
+// Routing-index build without any allocation (see moe_index_static.h). The per-block histogram
+// scratch is this fixed array. In host code `g_moe_index_static` only names the symbol; the
+// address a kernel can use comes from cudaGetSymbolAddress, looked up once per device.
+// ----------------------------------------------------------------------------------------
+#include "moe_index_static.h"
+
+static __device__ __align__(256) int32_t g_moe_index_static[FLUXB_MOE_INDEX_STATIC_ELEMS];
+
+extern "C" int fluxb_moe_index_build_static(const int32_t* experts, int64_t n, int E, int topk,
+                                            int32_t* splits, int32_t* offsets,
+                                            int32_t* scatter_index, int32_t* gather_index,
+                                            int32_t* topk_index, void* stream) {
+  FLUXB_REQUIRE(experts && offsets && scatter_index, "moe index arguments");
+  FLUXB_REQUIRE(E >= 1 && E <= kMaxExperts && topk >= 1 && n > 0, "moe index sizes");
+  const int64_t nblocks64 = (n + kIdxPerBlock - 1) / kIdxPerBlock;
+  if (nblocks64 * E > FLUXB_MOE_INDEX_STATIC_ELEMS)
+    return fail(kErrInvalid,
+                "fluxb_moe_index_build_static: ceil(n/4096)*E = " + std::to_string(nblocks64 * E) +
+                    " exceeds the built-in scratch of " + std::to_string(FLUXB_MOE_INDEX_STATIC_ELEMS) +
+                    " int32; use fluxb_moe_index_build with a caller-provided scratch buffer");
+  // set-up, once per device, with that device current
+  static int32_t* scratch_of_device[64] = {nullptr};
+  int dev = 0;
+  FLUXB_CUDA_OK(cudaGetDevice(&dev));
+  FLUXB_REQUIRE(dev >= 0 && dev < 64, "device ordinal out of range");
+  int32_t* scratch = scratch_of_device[dev];
+  if (scratch == nullptr) {
+    void* addr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&addr, g_moe_index_static);
+    if (e != cudaSuccess)
+      return fail(kErrCuda, std::string("cudaGetSymbolAddress(g_moe_index_static): ") + cudaGetErrorString(e));
+    scratch = static_cast<int32_t*>(addr);
+    scratch_of_device[dev] = scratch;
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int nblocks = static_cast<int>(nblocks64);
+  moe_hist_kernel<<<nblocks, kIdxThreads, E * sizeof(int32_t), s>>>(experts, n, E, scratch);
+  moe_scan_kernel<<<1, kMaxExperts, 0, s>>>(scratch, nblocks, E, splits, offsets);
+  moe_place_kernel<<<nblocks, kIdxThreads, E * sizeof(int32_t), s>>>(
+      experts, n, E, topk, scratch, scatter_index, gather_index, topk_index);
+  FLUXB_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(3, std::memory_order_relaxed);
+  return kOk;
+}
