@@ -18,7 +18,7 @@ const char* fluxb_last_error(void);
 /* element types */
 enum { FLUXB_BF16 = 0, FLUXB_FP8_E4M3 = 1, FLUXB_FP16 = 2, FLUXB_FP32 = 3, FLUXB_FP8_E5M2 = 4 };
 /* dense modes */
-enum { FLUXB_PLAIN = 0, FLUXB_ALLGATHER = 1, FLUXB_REDUCE_SCATTER = 2 };
+enum { FLUXB_PLAIN = 0, FLUXB_ALLGATHER = 1, FLUXB_REDUCE_SCATTER = 2, FLUXB_GEMM_A2A = 3, FLUXB_A2A_GEMM = 4 };
 
 /* Status record written by device code when a bounded wait gives up. 16 bytes. */
 typedef struct {
@@ -77,6 +77,30 @@ typedef struct {
 int fluxb_dense_gemm(const fluxb_dense_args_t* args);
 /* number of kernels libfluxb launched from this process so far */
 uint64_t fluxb_launch_count(void);
+
+/* ---- Ulysses sequence-parallel projections (base.mode = FLUXB_GEMM_A2A | FLUXB_A2A_GEMM) ----
+ * FLUXB_GEMM_A2A  (pre-attention): base.a = x [bs*local_seq, K], base.b = W [N, K] with
+ *   N = heads*hd laid out as `groups` head groups (1: plain heads; 3: q | k | v); each 64-column
+ *   piece of the product is stored by the GEMM epilogue straight into out[g][d], the buffer of
+ *   the rank d that owns the head: layout 0 = [bs, heads_g/W, seq, hd], 1 = [bs, seq, heads_g/W, hd].
+ *   The kernel returns when this rank's own buffers have received every rank's part.
+ * FLUXB_A2A_GEMM  (post-attention): attn = this rank's attention output, layout 0 =
+ *   [bs, heads/W, seq, hd], 1 = [bs, seq, heads/W, hd]; its slice for rank d's sequence range is
+ *   pushed into land[d] ([bs*local_seq, heads*hd]); base.d [bs*local_seq, N] = land[rank] * W^T
+ *   with the K loop gated slice by slice. base.a is ignored.
+ * a2a_flags[r]: W*ceil(M/128)+W uint32 per rank in symmetric memory, zero at first use. */
+typedef struct {
+  fluxb_dense_args_t base;
+  int32_t bs, local_seq, hd, groups;
+  int32_t group_heads[3];    /* global head count of each group */
+  int32_t layout;
+  void* out[3][FLUXB_MAX_RANKS];
+  const void* attn;
+  void* land[FLUXB_MAX_RANKS];
+  uint32_t* a2a_flags[FLUXB_MAX_RANKS];
+} fluxb_a2a_args_t;
+
+int fluxb_ulysses_gemm(const fluxb_a2a_args_t* args);
 
 /* ---- symmetric memory (CUDA IPC). `handle` is 64 bytes of host memory. ---- */
 int fluxb_symm_alloc(uint64_t bytes, void** ptr, void* handle);

@@ -52,7 +52,40 @@ using namespace fluxb;
 
 extern "C" uint64_t fluxb_launch_count(void) { return g_launches.load(); }
 
+static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x);
+
 extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
+  FLUXB_REQUIRE(a != nullptr, "null args");
+  FLUXB_REQUIRE(a->mode >= FLUXB_PLAIN && a->mode <= FLUXB_REDUCE_SCATTER, "mode");
+  return dense_impl(a, nullptr);
+}
+
+extern "C" int fluxb_ulysses_gemm(const fluxb_a2a_args_t* x) {
+  FLUXB_REQUIRE(x != nullptr, "null args");
+  FLUXB_REQUIRE(x->base.mode == FLUXB_GEMM_A2A || x->base.mode == FLUXB_A2A_GEMM, "mode");
+  return dense_impl(&x->base, x);
+}
+
+// (hd, seq, head, batch)-ordered 4-D map over a head-sharded activation buffer
+static int encode_heads_map(CUtensorMap* out, const void* base, int layout, int hd, int seq, int heads,
+                            int bs, uint32_t box_inner, Swz swz) {
+  const uint64_t e = 2;
+  uint64_t dims[4] = {static_cast<uint64_t>(hd), static_cast<uint64_t>(seq),
+                      static_cast<uint64_t>(heads), static_cast<uint64_t>(bs)};
+  uint64_t str[3];
+  if (layout == 0) {  // [bs, heads, seq, hd]
+    str[0] = hd * e;
+    str[1] = static_cast<uint64_t>(seq) * hd * e;
+  } else {            // [bs, seq, heads, hd]
+    str[0] = static_cast<uint64_t>(heads) * hd * e;
+    str[1] = hd * e;
+  }
+  str[2] = static_cast<uint64_t>(heads) * seq * hd * e;
+  uint32_t box[4] = {box_inner, 32, 1, 1};
+  return encode_tmap(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims, str, box, swz);
+}
+
+static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   FLUXB_REQUIRE(a != nullptr, "null args");
   FLUXB_REQUIRE(a->M > 0 && a->N > 0 && a->K > 0, "empty problem");
   FLUXB_REQUIRE(a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP8_E4M3 ||
@@ -64,9 +97,11 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   const bool in16 = a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP16;
   const int elt = in16 ? 2 : 1;
   const bool multi = a->world > 1 && a->mode != FLUXB_PLAIN;
+  const bool a2a = a->mode == FLUXB_GEMM_A2A || a->mode == FLUXB_A2A_GEMM;
+  const bool segmented = multi && !a2a;   // M is cut into one segment per rank
   FLUXB_REQUIRE((a->K * elt) % 16 == 0, "K row bytes must be a multiple of 16");
   FLUXB_REQUIRE(a->N % 8 == 0, "N must be a multiple of 8");
-  if (multi) FLUXB_REQUIRE(a->M % a->world == 0, "M must divide evenly over ranks");
+  if (segmented) FLUXB_REQUIRE(a->M % a->world == 0, "M must divide evenly over ranks");
 
   DenseGemmParams p;
   memset(&p, 0, sizeof(p));
@@ -75,8 +110,8 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   p.K = a->K;
   p.rank = a->rank;
   p.world = a->world;
-  p.mode = multi ? a->mode : kModePlain;
-  p.num_seg = multi ? a->world : 1;
+  p.mode = (multi || a2a) ? a->mode : kModePlain;
+  p.num_seg = segmented ? a->world : 1;
   p.seg_rows = a->M / p.num_seg;
   p.epoch = a->epoch;
   p.timeout_ns = a->timeout_ns ? a->timeout_ns : 2000000000ull;
@@ -104,6 +139,9 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
     FLUXB_REQUIRE((a->M / (multi ? a->world : 1)) % 128 == 0, "block-scaled GEMM needs rows per rank in multiples of 128");
     cg = 1;
     bn = 128;
+  } else if (a->mode == FLUXB_A2A_GEMM) {
+    if (cg == 2 && a->M >= 256) bn = 256;
+    else { cg = 1; bn = 128; }
   } else if (multi && a->mode == FLUXB_ALLGATHER) {
     // the all-gather variants exist for CTA pairs on 256-wide tiles and single CTAs on 128-wide
     if (cg == 2 && a->M / a->world >= 256) bn = 256;
@@ -119,10 +157,67 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   // ---- A
   {
     const uint64_t rows = (p.mode == kModeAllGather) ? p.seg_rows : a->M;
+    const void* a_base = a->a;
+    int64_t lda = a->lda;
+    if (p.mode == kModeA2AGemm) {
+      a_base = x->land[a->rank];
+      lda = a->K;
+    }
     uint64_t dims[2] = {static_cast<uint64_t>(a->K), rows};
-    uint64_t str[1] = {static_cast<uint64_t>(a->lda) * elt};
+    uint64_t str[1] = {static_cast<uint64_t>(lda) * elt};
     uint32_t box[2] = {static_cast<uint32_t>(bk), 128};
-    if ((rc = encode_tmap(&p.tm_a, in_dt, 2, a->a, dims, str, box, Swz::B128))) return rc;
+    if ((rc = encode_tmap(&p.tm_a, in_dt, 2, a_base, dims, str, box, Swz::B128))) return rc;
+  }
+  if (a2a) {
+    FLUXB_REQUIRE(in16, "the Ulysses projections run on bf16 / fp16");
+    FLUXB_REQUIRE(x->hd == 64 || x->hd == 128, "head_dim must be 64 or 128");
+    FLUXB_REQUIRE(x->local_seq % 32 == 0, "the local sequence length must be a multiple of 32");
+    FLUXB_REQUIRE(a->M == x->bs * x->local_seq, "M must equal bs * local_seq");
+    FLUXB_REQUIRE(a->local_cnt != nullptr, "local arrival scratch missing");
+    p.local_cnt = a->local_cnt;
+    p.a2a_hd = x->hd;
+    p.a2a_local_seq = x->local_seq;
+    p.a2a_bs = x->bs;
+    const int seq = x->local_seq * a->world;
+    for (int r = 0; r < a->world; ++r) {
+      FLUXB_REQUIRE(x->a2a_flags[r] != nullptr, "all-to-all flags missing");
+      p.a2a_flags[r] = x->a2a_flags[r];
+    }
+    if (p.mode == kModeGemmA2A) {
+      FLUXB_REQUIRE(x->groups >= 1 && x->groups <= kMaxHeadGroups, "1..3 head groups");
+      p.a2a_groups = x->groups;
+      int start = 0;
+      for (int g = 0; g < x->groups; ++g) {
+        FLUXB_REQUIRE(x->group_heads[g] > 0 && x->group_heads[g] % a->world == 0,
+                      "heads of every group must divide over the ranks");
+        p.a2a_group_start[g] = start;
+        start += x->group_heads[g];
+        for (int r = 0; r < a->world; ++r) {
+          FLUXB_REQUIRE(x->out[g][r] != nullptr, "output buffer missing");
+          if ((rc = encode_heads_map(&p.tm_a2a[g * kMaxRanks + r], x->out[g][r], x->layout, x->hd, seq,
+                                     x->group_heads[g] / a->world, x->bs, 64, Swz::B128)))
+            return rc;
+        }
+      }
+      p.a2a_group_start[x->groups] = start;
+      FLUXB_REQUIRE(start * x->hd == a->N, "N must equal total heads * head_dim");
+    } else {
+      FLUXB_REQUIRE(a->K % (a->world * x->hd) == 0, "K must equal heads * head_dim with heads divisible by W");
+      p.a2a_local_heads = a->K / x->hd / a->world;
+      FLUXB_REQUIRE(x->attn != nullptr, "attention output missing");
+      if ((rc = encode_heads_map(&p.tm_a2a_src, x->attn, x->layout, x->hd, seq, p.a2a_local_heads, x->bs,
+                                 static_cast<uint32_t>(x->hd), Swz::None)))
+        return rc;
+      for (int r = 0; r < a->world; ++r) {
+        FLUXB_REQUIRE(x->land[r] != nullptr, "landing buffer missing");
+        uint64_t dims[2] = {static_cast<uint64_t>(a->K), static_cast<uint64_t>(a->M)};
+        uint64_t str[1] = {static_cast<uint64_t>(a->K) * 2};
+        uint32_t box[2] = {static_cast<uint32_t>(x->hd), 32};
+        if ((rc = encode_tmap(&p.tm_a2a_land[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x->land[r], dims, str,
+                              box, Swz::None)))
+          return rc;
+      }
+    }
   }
   if (p.mode == kModeAllGather) {
     FLUXB_REQUIRE(a->ag_land[a->rank] != nullptr, "all-gather landing buffer missing");
@@ -171,7 +266,7 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
       p.rs_stage = a->rs_stage[a->rank];
       p.rs_out = a->rs_out;
       p.rs_work = a->rs_work;
-    } else {
+    } else if (p.mode != kModeGemmA2A) {
       void* out = a->d ? a->d : a->rs_out;
       const int64_t ldd = a->d ? a->ldd : a->N;
       FLUXB_REQUIRE(out != nullptr, "output missing");
@@ -206,7 +301,7 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   const int64_t tiles = static_cast<int64_t>(p.num_seg) * m_tiles_seg * ((a->N + bn - 1) / bn);
   int grid = sms;
   // every CTA of a multi-rank launch takes part in the flag protocol, so the grid stays full
-  if (!multi && tiles * cg < grid) grid = static_cast<int>(tiles) * cg;
+  if (!multi && !a2a && tiles * cg < grid) grid = static_cast<int>(tiles) * cg;
   if (cg == 2) grid &= ~1;
 
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
@@ -214,8 +309,8 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
     if (p.mode == kModeAllGather) return launch_dense<DenseCfg<128, 1, 4, 1, 32768, true>>(p, grid, stream);
     return launch_dense<DenseCfg<128, 1, 4, 1, 0, true>>(p, grid, stream);
   }
-  if (p.mode == kModeAllGather) {
-    // variants that carry the staging rings of the all-gather push
+  if (p.mode == kModeAllGather || p.mode == kModeA2AGemm) {
+    // variants that carry the staging rings of the all-gather / all-to-all push
     if (cg == 2 && bn == 256) {
       if (in16) return launch_dense<DenseCfg<256, 0, 5, 2, 32768>>(p, grid, stream);
       return launch_dense<DenseCfg<256, 1, 5, 2, 32768>>(p, grid, stream);

@@ -29,7 +29,14 @@ namespace fluxb {
 
 constexpr int kMaxRanks = 8;
 
-enum DenseMode : int32_t { kModePlain = 0, kModeAllGather = 1, kModeReduceScatter = 2 };
+enum DenseMode : int32_t {
+  kModePlain = 0,
+  kModeAllGather = 1,
+  kModeReduceScatter = 2,
+  kModeGemmA2A = 3,   // Ulysses pre-attention: GEMM, then seq->heads all-to-all in the epilogue
+  kModeA2AGemm = 4,   // Ulysses post-attention: heads->seq all-to-all feeding the GEMM's K loop
+};
+constexpr int kMaxHeadGroups = 3;  // q, k, v
 
 struct DenseGemmParams {
   CUtensorMap tm_a;              // A rows owned by this launch: [rows, K], box {BK, 128}
@@ -73,6 +80,19 @@ struct DenseGemmParams {
   const void* rs_stage;          // local staging [W][seg_rows][N] bf16
   void* rs_out;                  // [seg_rows, N] bf16
   uint32_t* rs_work;             // local work-claim counter, zero between calls
+  // ---- Ulysses all-to-all modes. Activations are [bs, local_seq, heads, hd] on the sequence-
+  // sharded side and [bs, heads/W, seq, hd] (or [bs, seq, heads/W, hd]) on the head-sharded side;
+  // every 4-D tensor map below is ordered (hd, seq, head, batch) whatever the memory order is.
+  CUtensorMap tm_a2a[kMaxHeadGroups * kMaxRanks];  // kModeGemmA2A: output of (group g, rank d),
+                                                   //   box {64, 32, 1, 1}
+  CUtensorMap tm_a2a_src;        // kModeA2AGemm: this rank's attention output, box {hd, 32, 1, 1}
+  CUtensorMap tm_a2a_land[kMaxRanks];  // kModeA2AGemm: rank d's GEMM input [bs*local_seq, heads*hd],
+                                       //   box {hd, 32}
+  int32_t a2a_hd, a2a_local_seq, a2a_bs, a2a_groups;
+  int32_t a2a_group_start[kMaxHeadGroups + 1];  // first global head of each group (q | k | v)
+  int32_t a2a_local_heads;       // kModeA2AGemm: heads per rank
+  uint32_t* a2a_flags[kMaxRanks];  // kModeGemmA2A: [W src] "all my tiles for you have landed";
+                                   // kModeA2AGemm: [W src][m_tiles] per tile row
 };
 
 // CG_ = 1: one CTA per 128 x BN tile. CG_ = 2: a pair of CTAs (one cluster) shares a 256 x BN
@@ -233,7 +253,22 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             ptx::fence_proxy_async_all();
           }
         }
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        // post-attention mode: the K range is W slices, one per source rank, landing
+        // independently; start with the own slice and gate each slice on its flag
+        const int kb_per_src = p.mode == kModeA2AGemm ? (p.a2a_local_heads * p.a2a_hd) / BK : k_blocks;
+        int cur_src = -1;
+        for (int ki = 0; ki < k_blocks; ++ki) {
+          int kb = ki;
+          if (p.mode == kModeA2AGemm) {
+            kb = ki + p.rank * kb_per_src;
+            if (kb >= k_blocks) kb -= k_blocks;
+            const int src = kb / kb_per_src;
+            if (src != cur_src) {
+              cur_src = src;
+              flag_wait_ge(wc, p.a2a_flags[p.rank] + src * m_tiles_seg + c.m_tile, p.epoch, kSiteA2AFlag);
+              ptx::fence_proxy_async_all();
+            }
+          }
           mbar_wait(wc, empty_bar(stage), phase ^ 1u, kSiteSmemEmpty);
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
           if constexpr (CG == 1) {
@@ -432,6 +467,85 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         }
       }
     }
+    if constexpr (Cfg::COMM_BYTES > 0) {
+      if (p.mode == kModeA2AGemm) {
+        // heads->seq all-to-all: every rank sends, for each destination d, the rows of its
+        // attention output that belong to d's sequence range, re-laid out so that they form
+        // columns [rank*local_heads*hd, +local_heads*hd) of d's GEMM input.
+        if (multi) {
+          if (lane < p.world) flag_wait_ge(wc, p.start_ctr[p.rank] + lane, p.epoch, kSiteStartBarrier);
+          __syncwarp();
+        }
+        if (lane == 0) {
+          constexpr int NSLOT = 2;
+          constexpr uint32_t SLOT = Cfg::COMM_BYTES / 2 / NSLOT;   // 8 KiB: 32 rows x hd <= 128 x 2 B
+          constexpr int LAG = 2;
+          const uint32_t ring = comm_base + (warp - 2) * (Cfg::COMM_BYTES / 2);
+          const uint32_t rbar = ring_bar_base + (warp - 2) * 4 * 8u;
+          const uint32_t cw = blockIdx.x * 2 + (warp - 2);
+          const uint32_t ncw = gridDim.x * 2;
+          const int hd = p.a2a_hd, lh = p.a2a_local_heads, ls = p.a2a_local_seq;
+          const uint32_t chunk_bytes = 32u * hd * Cfg::ELT;
+          const int groups_per_tile = BM / 32;                 // 32-row groups per tile row
+          const int rows_total = p.a2a_bs * ls;
+          auto step_chunks = [&](int mt) -> uint32_t {
+            const int rows = min(BM, rows_total - mt * BM);
+            const uint32_t nch = static_cast<uint32_t>(((rows + 31) / 32) * lh);
+            return nch > cw ? (nch - cw - 1) / ncw + 1 : 0u;
+          };
+          auto publish = [&](int d, int mt) {
+            int peer = p.rank + d;
+            if (peer >= p.world) peer -= p.world;
+            ptx::fence_proxy_async_all();
+            uint32_t* cnt = p.local_cnt + d * m_tiles_seg + mt;
+            if (ptx::atom_add_acq_rel_sys(cnt, 1u) == ncw - 1u) {
+              *cnt = 0;
+              ptx::st_release_sys(p.a2a_flags[peer] + p.rank * m_tiles_seg + mt, p.epoch);
+            }
+          };
+          uint32_t issued = 0;
+          int sig_d = 0, sig_mt = 0;
+          uint32_t sig_end = step_chunks(0);
+          // d = 0 is the local slice (every GEMM starts with it), then rank+1, rank+2, ...
+          for (int d = 0; d < p.world; ++d) {
+            int peer = p.rank + d;
+            if (peer >= p.world) peer -= p.world;
+            for (int mt = 0; mt < m_tiles_seg; ++mt) {
+              const int rows = min(BM, rows_total - mt * BM);
+              const uint32_t nch = static_cast<uint32_t>(((rows + 31) / 32) * lh);
+              for (uint32_t c = cw; c < nch; c += ncw) {
+                const int g = c / lh, h = c % lh;                  // 32-row group, local head
+                const int row0 = mt * BM + g * 32;                 // row of the peer's GEMM input
+                const int b = row0 / ls, s0 = row0 % ls;
+                const uint32_t slot = issued % NSLOT;
+                const uint32_t ph = (issued / NSLOT) & 1u;
+                ptx::bulk_wait_read<NSLOT - 1>();
+                ptx::mbar_arrive_expect_tx(rbar + 8u * slot, chunk_bytes);
+                ptx::tma_load_4d(ring + slot * SLOT, &p.tm_a2a_src, rbar + 8u * slot, 0,
+                                 peer * ls + s0, h, b);
+                mbar_wait(wc, rbar + 8u * slot, ph, kSiteSmemFull);
+                ptx::tma_store_2d(&p.tm_a2a_land[peer], ring + slot * SLOT, (p.rank * lh + h) * hd, row0);
+                ptx::bulk_commit();
+                ++issued;
+              }
+              ptx::bulk_wait<LAG>();
+              const uint32_t done = issued > LAG ? issued - LAG : 0u;
+              while ((sig_d < d || (sig_d == d && sig_mt <= mt)) && sig_end <= done) {
+                publish(sig_d, sig_mt);
+                if (++sig_mt == m_tiles_seg) { sig_mt = 0; ++sig_d; }
+                sig_end += step_chunks(sig_mt);
+              }
+            }
+          }
+          ptx::bulk_wait<0>();
+          while (sig_d < p.world) {
+            publish(sig_d, sig_mt);
+            if (++sig_mt == m_tiles_seg) { sig_mt = 0; ++sig_d; }
+          }
+          (void)groups_per_tile;
+        }
+      }
+    }
   } else {
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;              // TMEM lane quadrant this warp may read
@@ -446,7 +560,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     const bool scaled = p.scale_a != nullptr || p.scale_b != nullptr;
     int it = 0;
     uint32_t nstore = 0;
-    bool started = !(multi && p.mode == kModeReduceScatter);
+    bool started = !(multi && (p.mode == kModeReduceScatter || p.mode == kModeGemmA2A));
 
     // 32 rows x 64 columns of fp32 results (r0: columns 0..31, r1: 32..63 of the chunk, this
     // thread's row) -> scale, bias, activation -> 16-bit -> swizzled staging -> TMA store
@@ -502,8 +616,22 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       }
       ptx::fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0 && col0 < p.N && store_row0 < p.seg_rows)
-        ptx::tma_store_3d(tmd, my_epi_u32 + buf * Cfg::EPI_BUF_BYTES, col0, store_row0, z);
+      if (lane == 0 && col0 < p.N && store_row0 < p.seg_rows) {
+        if (p.mode == kModeGemmA2A) {
+          // 64 columns of one head, 32 consecutive sequence positions of one batch entry:
+          // goes to the rank that owns the head, at this rank's place in the full sequence
+          const int head = col0 / p.a2a_hd, e0 = col0 % p.a2a_hd;
+          int g = 0;
+          while (g + 1 < p.a2a_groups && head >= p.a2a_group_start[g + 1]) ++g;
+          const int hh = head - p.a2a_group_start[g];
+          const int lh = (p.a2a_group_start[g + 1] - p.a2a_group_start[g]) / p.world;
+          const int b = store_row0 / p.a2a_local_seq, s0 = store_row0 % p.a2a_local_seq;
+          ptx::tma_store_4d(&p.tm_a2a[g * kMaxRanks + hh / lh], my_epi_u32 + buf * Cfg::EPI_BUF_BYTES, e0,
+                            p.rank * p.a2a_local_seq + s0, hh % lh, b);
+        } else {
+          ptx::tma_store_3d(tmd, my_epi_u32 + buf * Cfg::EPI_BUF_BYTES, col0, store_row0, z);
+        }
+      }
       if (lane == 0) ptx::bulk_commit();
       ++nstore;
     };
@@ -513,6 +641,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       const int m_cta = c.m_in_seg + static_cast<int>(cta_rank) * Cfg::BM_CTA;
       const CUtensorMap* tmd = &p.tm_d[0];
       int z = c.seg;
+      if (p.mode == kModeGemmA2A && multi && !started) {
+        if (lane < p.world) flag_wait_ge(wc, p.start_ctr[p.rank] + lane, p.epoch, kSiteStartBarrier);
+        __syncwarp();
+        started = true;
+      }
       if (p.mode == kModeReduceScatter && multi) {
         tmd = &p.tm_d[c.seg];
         z = p.rank;
@@ -630,6 +763,21 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     }
     if (lane == 0) ptx::bulk_wait<0>();
     __syncwarp();
+    if (p.mode == kModeGemmA2A && multi) {
+      // all stores of this warp have landed; the last warp of the whole grid tells every rank,
+      // and everybody stays until all W sources have said so: when this kernel completes, the
+      // local head-sharded output is complete
+      if (lane == 0) {
+        ptx::fence_proxy_async_all();
+        if (ptx::atom_add_acq_rel_sys(p.local_cnt, 1u) == gridDim.x * Cfg::EPI_WARPS - 1u) {
+          *p.local_cnt = 0;
+          for (int d = 0; d < p.world; ++d) ptx::st_release_sys(p.a2a_flags[d] + p.rank, p.epoch);
+        }
+      }
+      __syncwarp();
+      if (lane < p.world) flag_wait_ge(wc, p.a2a_flags[p.rank] + lane, p.epoch, kSiteA2AFlag);
+      __syncwarp();
+    }
   }
 
   // -------------------------------------------------------------------- teardown of the GEMM

@@ -21,3 +21,4 @@ from .ops.quantization import Quantization  # noqa: F401
 from .ops.misc import (InplaceCast, bitwise_check, calc_scatter_index, inplace_cast_fp32_to_bf16,  # noqa: F401
                        moe_index_build, uniform_initialize)
 from .ops.blockscale_gemm import BlockScaleGemm, blockscale_gemm_torch  # noqa: F401
+from .ops.ulysses import AllToAllTransposeGemm, GemmAllToAllTranspose  # noqa: F401

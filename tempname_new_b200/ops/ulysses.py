@@ -1,0 +1,314 @@
+"""Ulysses sequence-parallel attention projections with the all-to-all fused into the GEMM.
+
+* ``GemmAllToAllTranspose`` (pre-attention): QKV projection on the local sequence shard; the GEMM
+  epilogue stores every (32 positions x 64 columns) piece directly into the rank that owns the
+  head, already in the head-sharded layout. Reference: ``flux.GemmAllToAllTranspose``
+  (``src/pybind/gemm_a2a_transpose.cc:30-140``, ``src/gemm_a2a_transpose/``), which writes a local
+  GEMM output, flags tiles and runs a separate pull kernel on carved-out SMs.
+* ``AllToAllTransposeGemm`` (post-attention): the head-sharded attention output is pushed into
+  the peers' GEMM-input buffers by two warps of every CTA while the out-projection GEMM of the
+  same kernel walks its K loop one source slice at a time, own slice first. Reference:
+  ``flux.AllToAllTransposeGemm`` (``src/pybind/a2a_transpose_gemm.cc:30-137``,
+  ``src/a2a_transpose_gemm/``): push kernel + flag-gated consumer GEMM.
+
+Layouts follow ``python/flux/testing/ulysses_sp_utils.py:21-166`` of the reference;
+``pre_attn_a2a_torch`` / ``post_attn_a2a_torch`` below restate them with ``all_to_all_single``
+and are the CPU path and the test oracle.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from . import _dense
+from ._fused_base import OFF_CTR, OFF_LOCAL, OFF_START, FusedOpBase
+from .gemm_only import _out_dtype, as_nk
+from .options import PreAttnAllToAllCommOp
+from ..parallel.symm import SymmBuffer, _ELEM
+
+_VP = ctypes.c_void_p
+
+
+class A2AArgs(ctypes.Structure):
+    _fields_ = [
+        ("base", _dense.DenseArgs),
+        ("bs", ctypes.c_int32), ("local_seq", ctypes.c_int32), ("hd", ctypes.c_int32),
+        ("groups", ctypes.c_int32),
+        ("group_heads", ctypes.c_int32 * 3),
+        ("layout", ctypes.c_int32),
+        ("out", (_VP * _dense.MAX_RANKS) * 3),
+        ("attn", _VP),
+        ("land", _VP * _dense.MAX_RANKS),
+        ("a2a_flags", _VP * _dense.MAX_RANKS),
+    ]
+
+
+# ------------------------------------------------------------------------------------------
+# PyTorch statements of the two all-to-alls (any backend)
+# ------------------------------------------------------------------------------------------
+def _a2a_heads(x: torch.Tensor, group, transpose: bool) -> torch.Tensor:
+    """x [bs, local_seq, heads, hd] -> [bs, heads/W, seq, hd] (transpose) or [bs, seq, heads/W, hd]."""
+    W = dist.get_world_size(group)
+    bs, ls, nh, hd = x.shape
+    send = x.reshape(bs, ls, W, nh // W, hd).permute(2, 0, 1, 3, 4).contiguous()   # [W, bs, ls, lh, hd]
+    recv = torch.empty_like(send)
+    if W > 1:
+        dist.all_to_all_single(recv, send, group=group)
+    else:
+        recv = send
+    out = recv.permute(1, 0, 2, 3, 4).reshape(bs, W * ls, nh // W, hd)             # [bs, seq, lh, hd]
+    return out.permute(0, 2, 1, 3).contiguous() if transpose else out.contiguous()
+
+
+def pre_attn_a2a_torch(x: torch.Tensor, group, bs: int, local_seq: int, nh: int, hd: int) -> List[torch.Tensor]:
+    return [_a2a_heads(x.reshape(bs, local_seq, nh, hd), group, True)]
+
+
+def pre_attn_qkv_pack_a2a_torch(x: torch.Tensor, group, bs: int, local_seq: int, nh: int, hd: int, gqa: int
+                                ) -> List[torch.Tensor]:
+    W = dist.get_world_size(group)
+    x = x.reshape(bs, local_seq, nh, hd)
+    local_nh = nh // W
+    lq, lk = local_nh // (gqa + 2) * gqa, local_nh // (gqa + 2)
+    q, k, v = x[:, :, :lq * W], x[:, :, lq * W:(lq + lk) * W], x[:, :, (lq + lk) * W:]
+    return [_a2a_heads(t.contiguous(), group, False) for t in (q, k, v)]
+
+
+def post_attn_a2a_torch(x: torch.Tensor, group, a2a_only: bool) -> torch.Tensor:
+    """x [bs, heads/W, seq, hd] (or [bs, seq, heads/W, hd] if a2a_only) -> [bs, seq/W, heads*hd]."""
+    W = dist.get_world_size(group)
+    if not a2a_only:
+        x = x.permute(0, 2, 1, 3)
+    bs, seq, lh, hd = x.shape
+    ls = seq // W
+    send = x.reshape(bs, W, ls, lh, hd).permute(1, 0, 2, 3, 4).contiguous()         # [W dst, bs, ls, lh, hd]
+    recv = torch.empty_like(send)
+    if W > 1:
+        dist.all_to_all_single(recv, send, group=group)
+    else:
+        recv = send
+    return recv.permute(1, 2, 0, 3, 4).reshape(bs, ls, W * lh * hd).contiguous()   # heads ordered by source
+
+
+def _check_sp(sp_size: int, world: int) -> None:
+    if sp_size != world:
+        raise NotImplementedError("sp_size must equal the size of the process group that is passed in; "
+                                  "build a sub-group for a smaller sequence-parallel degree")
+
+
+class GemmAllToAllTranspose(FusedOpBase):
+    def __init__(self, tp_group, nnodes: int, sp_size: int, bs: int, seq: int, hidden_dim: int,
+                 head_dim: int, n_dim: int, input_dtype: torch.dtype,
+                 output_dtype: Optional[torch.dtype] = None, transpose_weight: bool = False, gqa: int = 0,
+                 comm_op: PreAttnAllToAllCommOp = PreAttnAllToAllCommOp.A2ATranspose,
+                 max_num_comm_buf: int = 1, timeout_s: Optional[float] = None):
+        super().__init__(tp_group, nnodes, timeout_s)
+        _check_sp(sp_size, self.world)
+        self.bs, self.seq, self.hidden, self.hd, self.n_dim = bs, seq, hidden_dim, head_dim, n_dim
+        self.input_dtype = input_dtype
+        self.output_dtype = _out_dtype(input_dtype, output_dtype)
+        self.transpose_weight, self.gqa, self.comm_op = transpose_weight, gqa, PreAttnAllToAllCommOp(comm_op)
+        W = self.world
+        if seq % W or n_dim % head_dim or (n_dim // head_dim) % W:
+            raise ValueError("seq and the head count must divide over the group")
+        self.local_seq = seq // W
+        self.nh = n_dim // head_dim
+        local_nh = self.nh // W
+        if self.comm_op == PreAttnAllToAllCommOp.QKVPackA2A:
+            lq, lk = local_nh // (gqa + 2) * gqa, local_nh // (gqa + 2)
+            if lq + 2 * lk != local_nh or lk == 0:
+                raise ValueError("heads per rank must be a multiple of gqa + 2")
+            self.group_heads = [lq * W, lk * W, lk * W]
+            self.layout = 1     # [bs, seq, heads/W, hd]
+        else:
+            self.group_heads = [self.nh]
+            self.layout = 0     # [bs, heads/W, seq, hd]
+        # one symmetric block holds this rank's outputs of every group, back to back
+        self.out_elems = [bs * (g // W) * seq * head_dim for g in self.group_heads]
+        self.out_buf = SymmBuffer(sum(self.out_elems) * _ELEM[self.output_dtype], self.pg)
+
+    def _out_views(self) -> List[torch.Tensor]:
+        W, off, views = self.world, 0, []
+        for g, n in zip(self.group_heads, self.out_elems):
+            shape = (self.bs, g // W, self.seq, self.hd) if self.layout == 0 else (self.bs, self.seq, g // W, self.hd)
+            views.append(self.out_buf.view(self.rank, self.output_dtype, shape, off))
+            off += n * _ELEM[self.output_dtype]
+        return views
+
+    def forward(self, input: torch.Tensor, weight: torch.Tensor, seq_lens_cpu=None,
+                bias: Optional[torch.Tensor] = None, outputs: Optional[List[torch.Tensor]] = None,
+                input_scale=None, weight_scale=None, output_scale=None, fast_accum: bool = False,
+                num_comm_sm: int = -1, sm_margin: int = 0) -> List[torch.Tensor]:
+        """input [bs, seq/W, hidden] -> A2ATranspose: [out [bs, heads/W, seq, hd]];
+        QKVPackA2A: [q, k, v], each [bs, seq, heads_x/W, hd]. Without ``outputs`` the results are
+        views of the op's symmetric buffer and stay valid until the next call."""
+        if seq_lens_cpu is not None:
+            raise NotImplementedError("per-rank sequence lengths are not supported")
+        w = as_nk(weight, self.transpose_weight)
+        x2 = input.reshape(self.bs * self.local_seq, self.hidden)
+        self.epoch += 1
+        if not input.is_cuda:
+            res = self._forward_cpu(x2, w, bias)
+        else:
+            x2 = x2 if x2.is_contiguous() else x2.contiguous()
+            keep: list = []
+            args = A2AArgs()
+            base = _dense.base_args(x2, w, bias, self.output_dtype, m=x2.shape[0], status=self.status, keep=keep)
+            base.M = x2.shape[0]
+            base.mode, base.rank, base.world = 3, self.rank, self.world
+            base.epoch, base.timeout_ns = self.epoch, int(self.timeout_s * 1e9)
+            base.local_cnt = self.ctrl.ptr(self.rank, OFF_LOCAL)
+            for r in range(self.world):
+                base.start_ctr[r] = self.ctrl.ptr(r, OFF_START)
+                args.a2a_flags[r] = self.ctrl.ptr(r, OFF_CTR)
+            args.base = base
+            args.bs, args.local_seq, args.hd = self.bs, self.local_seq, self.hd
+            args.groups, args.layout = len(self.group_heads), self.layout
+            off = 0
+            for g, (heads, n) in enumerate(zip(self.group_heads, self.out_elems)):
+                args.group_heads[g] = heads
+                for r in range(self.world):
+                    args.out[g][r] = self.out_buf.ptr(r, off)
+                off += n * _ELEM[self.output_dtype]
+            _native.check(_native.lib().fluxb_ulysses_gemm(ctypes.byref(args)), "fluxb_ulysses_gemm")
+            self._after_launch()
+            res = self._out_views()
+        if outputs is not None:
+            for dst, src in zip(outputs, res):
+                dst.copy_(src)
+            return outputs
+        return res
+
+    __call__ = forward
+
+    def _forward_cpu(self, x2, w, bias):
+        y = x2.float() @ w.float().t()
+        if bias is not None:
+            y = y + bias.float()
+        y = y.to(self.output_dtype)
+        if self.comm_op == PreAttnAllToAllCommOp.QKVPackA2A:
+            return pre_attn_qkv_pack_a2a_torch(y, self.pg, self.bs, self.local_seq, self.nh, self.hd, self.gqa)
+        return pre_attn_a2a_torch(y, self.pg, self.bs, self.local_seq, self.nh, self.hd)
+
+    # a2a without the GEMM (input already projected): collective through the process group
+    def pre_attn_a2a(self, input, seq_lens_cpu=None, num_comm_sm: int = -1):
+        return pre_attn_a2a_torch(input, self.pg, self.bs, self.local_seq, self.nh, self.hd)[0]
+
+    def pre_attn_qkv_pack_a2a(self, qkv, seq_lens_cpu=None, num_comm_sm: int = -1):
+        return pre_attn_qkv_pack_a2a_torch(qkv, self.pg, self.bs, self.local_seq, self.nh, self.hd, self.gqa)
+
+    def pre_attn_a2a_no_cpy(self, input, seq_lens_cpu=None, num_comm_sm: int = -1, comm_buf_idx: int = 0):
+        return self.pre_attn_a2a(input, seq_lens_cpu, num_comm_sm)
+
+    def pre_attn_qkv_pack_a2a_no_cpy(self, qkv, seq_lens_cpu=None, num_comm_sm: int = -1, comm_buf_idx: int = 0):
+        return self.pre_attn_qkv_pack_a2a(qkv, seq_lens_cpu, num_comm_sm)
+
+    def get_input_comm_buf(self, input, comm_buf_idx: int = 0):
+        return input
+
+    def sp_group_barrier_all(self) -> None:
+        dist.barrier(group=self.pg)
+
+    def profiling(self, input, weight, bias=None, input_scale=None, weight_scale=None, output_scale=None,
+                  fast_accum=False, num_comm_sm=-1, sm_margin=0, prof_ctx=None):
+        from ..tuning.profiling import profile_call
+        return profile_call(self, "gemm_a2a_transpose", lambda: self.forward(input, weight, bias=bias), prof_ctx)
+
+
+class AllToAllTransposeGemm(FusedOpBase):
+    def __init__(self, tp_group, nnodes: int, sp_size: int, bs: int, num_head: int, seq: int, head_dim: int,
+                 input_dtype: torch.dtype, output_dtype: Optional[torch.dtype] = None,
+                 max_num_comm_buf: int = 1, a2a_only: bool = False, timeout_s: Optional[float] = None):
+        super().__init__(tp_group, nnodes, timeout_s)
+        _check_sp(sp_size, self.world)
+        W = self.world
+        if seq % W or num_head % W:
+            raise ValueError("seq and num_head must divide over the group")
+        self.bs, self.nh, self.seq, self.hd = bs, num_head, seq, head_dim
+        self.local_seq, self.local_nh = seq // W, num_head // W
+        self.hidden = num_head * head_dim
+        self.input_dtype = input_dtype
+        self.output_dtype = _out_dtype(input_dtype, output_dtype)
+        self.a2a_only = a2a_only
+        self.land = SymmBuffer(bs * self.local_seq * self.hidden * _ELEM[input_dtype], self.pg)
+
+    def forward(self, input: torch.Tensor, weight: torch.Tensor, seq_lens_cpu=None,
+                bias: Optional[torch.Tensor] = None, output: Optional[torch.Tensor] = None,
+                input_scale=None, weight_scale=None, output_scale=None, fast_accum: bool = False,
+                transpose_weight: bool = False, all_to_all_option=None,
+                a2a_transpose_output: Optional[torch.Tensor] = None, num_comm_sm: int = -1,
+                sm_margin: int = 0) -> torch.Tensor:
+        """input [bs, heads/W, seq, hd] (``a2a_only``: [bs, seq, heads/W, hd]) -> [bs, seq/W, N]."""
+        if seq_lens_cpu is not None:
+            raise NotImplementedError("per-rank sequence lengths are not supported")
+        w = as_nk(weight, transpose_weight)
+        N = w.shape[0]
+        M = self.bs * self.local_seq
+        self.epoch += 1
+        if not input.is_cuda:
+            gi = post_attn_a2a_torch(input, self.pg, self.a2a_only)
+            y = gi.reshape(M, self.hidden).float() @ w.float().t()
+            if bias is not None:
+                y = y + bias.float()
+            res = y.to(self.output_dtype).reshape(self.bs, self.local_seq, N)
+            if a2a_transpose_output is not None:
+                a2a_transpose_output.copy_(gi.reshape(a2a_transpose_output.shape))
+        else:
+            x = input if input.is_contiguous() else input.contiguous()
+            res = torch.empty((self.bs, self.local_seq, N), dtype=self.output_dtype, device=input.device)
+            keep: list = []
+            land_local = self.land.view(self.rank, self.input_dtype, (M, self.hidden))
+            args = A2AArgs()
+            base = _dense.base_args(land_local, w, bias, self.output_dtype, m=M, status=self.status, keep=keep)
+            base.M = M
+            base.d, base.ldd = res.data_ptr(), N
+            base.mode, base.rank, base.world = 4, self.rank, self.world
+            base.epoch, base.timeout_ns = self.epoch, int(self.timeout_s * 1e9)
+            base.local_cnt = self.ctrl.ptr(self.rank, OFF_LOCAL)
+            for r in range(self.world):
+                base.start_ctr[r] = self.ctrl.ptr(r, OFF_START)
+                args.a2a_flags[r] = self.ctrl.ptr(r, OFF_CTR)
+                args.land[r] = self.land.ptr(r)
+            args.base = base
+            args.bs, args.local_seq, args.hd = self.bs, self.local_seq, self.hd
+            args.layout = 1 if self.a2a_only else 0
+            args.attn = x.data_ptr()
+            _native.check(_native.lib().fluxb_ulysses_gemm(ctypes.byref(args)), "fluxb_ulysses_gemm")
+            self._after_launch()
+            if a2a_transpose_output is not None:
+                a2a_transpose_output.copy_(land_local.reshape(a2a_transpose_output.shape))
+        if output is not None:
+            output.copy_(res.reshape(output.shape))
+            return output
+        return res
+
+    __call__ = forward
+
+    def post_attn_a2a(self, input, seq_lens_cpu=None, all_to_all_option=None, num_comm_sm: int = -1):
+        return post_attn_a2a_torch(input, self.pg, self.a2a_only)
+
+    def post_attn_a2a_no_cpy(self, input, seq_lens_cpu=None, all_to_all_option=None, num_comm_sm: int = -1,
+                             comm_buf_idx: int = 0):
+        return self.post_attn_a2a(input, seq_lens_cpu)
+
+    def gemm_only(self, input, weight, bias=None, output=None, input_scale=None, weight_scale=None,
+                  output_scale=None, fast_accum=False, transpose_weight=False):
+        w = as_nk(weight, transpose_weight)
+        x2 = input.reshape(-1, input.shape[-1])
+        out = output if output is not None else torch.empty(
+            (x2.shape[0], w.shape[0]), dtype=self.output_dtype, device=input.device)
+        if not input.is_cuda:
+            out.copy_((x2.float() @ w.float().t()).to(self.output_dtype))
+            return out
+        return _dense.plain_gemm(x2 if x2.is_contiguous() else x2.contiguous(), w, out.view(x2.shape[0], -1), bias)
+
+    def sp_group_barrier_all(self) -> None:
+        dist.barrier(group=self.pg)
+
+    def profiling(self, input, weight, bias=None, output=None, prof_ctx=None, **kw):
+        from ..tuning.profiling import profile_call
+        return profile_call(self, "a2a_transpose_gemm", lambda: self.forward(input, weight, bias=bias), prof_ctx)

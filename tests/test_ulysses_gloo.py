@@ -1,0 +1,64 @@
+"""Ulysses projections on CPU ranks: the op layouts against an index-by-index statement."""
+import torch
+import torch.distributed as dist
+
+from conftest import run_gloo
+
+
+def _gather_full(t, world):
+    parts = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(parts, t.contiguous())
+    return parts
+
+
+def _pre_attn(rank, world):
+    import tempname_new_b200 as flux
+    bs, seq, hidden, hd, nh = 2, 8 * world, 32, 8, 4 * world
+    ls = seq // world
+    torch.manual_seed(0)
+    x_full = torch.randn(bs, seq, hidden)
+    w = torch.randn(nh * hd, hidden) * 0.2
+    x = x_full[:, rank * ls:(rank + 1) * ls].contiguous()
+    op = flux.GemmAllToAllTranspose(dist.group.WORLD, 1, world, bs, seq, hidden, hd, nh * hd, torch.float32)
+    (out,) = op.forward(x, w)
+    y = (x_full @ w.t()).reshape(bs, seq, nh, hd)                       # full projection
+    lh = nh // world
+    ref = y[:, :, rank * lh:(rank + 1) * lh].permute(0, 2, 1, 3)        # [bs, lh, seq, hd]
+    torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
+    # q/k/v packing with grouped-query attention: per rank 2 q heads + 1 k + 1 v
+    op2 = flux.GemmAllToAllTranspose(dist.group.WORLD, 1, world, bs, seq, hidden, hd, nh * hd, torch.float32,
+                                     gqa=2, comm_op=flux.PreAttnAllToAllCommOp.QKVPackA2A)
+    q, k, v = op2.forward(x, w)
+    lq, lk = 2, 1
+    yq, yk, yv = y[:, :, :lq * world], y[:, :, lq * world:(lq + lk) * world], y[:, :, (lq + lk) * world:]
+    torch.testing.assert_close(q, yq[:, :, rank * lq:(rank + 1) * lq], rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(k, yk[:, :, rank * lk:(rank + 1) * lk], rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(v, yv[:, :, rank * lk:(rank + 1) * lk], rtol=1e-5, atol=1e-5)
+
+
+def _post_attn(rank, world):
+    import tempname_new_b200 as flux
+    bs, seq, hd, nh, N = 2, 8 * world, 8, 2 * world, 24
+    ls, lh = seq // world, nh // world
+    torch.manual_seed(1)
+    attn_full = torch.randn(bs, nh, seq, hd)                            # all heads, full sequence
+    w = torch.randn(N, nh * hd) * 0.2
+    mine = attn_full[:, rank * lh:(rank + 1) * lh].contiguous()         # [bs, lh, seq, hd]
+    ref_in = attn_full.permute(0, 2, 1, 3).reshape(bs, seq, nh * hd)[:, rank * ls:(rank + 1) * ls]
+    ref = ref_in @ w.t()
+    for a2a_only in (False, True):
+        op = flux.AllToAllTransposeGemm(dist.group.WORLD, 1, world, bs, nh, seq, hd, torch.float32,
+                                        a2a_only=a2a_only)
+        inp = mine.permute(0, 2, 1, 3).contiguous() if a2a_only else mine
+        gi = torch.empty(bs, ls, nh * hd)
+        out = op.forward(inp, w, a2a_transpose_output=gi)
+        torch.testing.assert_close(gi, ref_in, rtol=0, atol=0)
+        torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_pre_attn_gemm_a2a_gloo():
+    run_gloo(_pre_attn, 2)
+
+
+def test_post_attn_a2a_gemm_gloo():
+    run_gloo(_post_attn, 2)
