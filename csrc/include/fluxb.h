@@ -102,6 +102,74 @@ typedef struct {
 
 int fluxb_ulysses_gemm(const fluxb_a2a_args_t* args);
 
+/* ---- MoE layers (csrc/ops/moe.cu) ---------------------------------------------------------
+ * Grouped GEMM over this rank's experts [e0, e0 + E_local) of E: D[rows_ep, N] = A_e * W_e^T.
+ * Rows live in the expert-sorted order defined by splits [E] (device, int32 counts).
+ *   gathered = 1 (layer 0): row r of that order is token gather_index[r] of a_tokens
+ *     ([world * tokens_per_rank, K]); gather_index is written by this call from scatter_index
+ *     ([n_entries] = tokens * topk, destination row of every (token, k)). With do_allgather the
+ *     kernel also gathers the token shards: ag_src = this rank's shard, ag_land[r] = rank r's
+ *     token matrix (a_tokens == ag_land[rank]).
+ *   gathered = 0 (layer 1): A = a [a_rows, K] holds this rank's rows contiguously.
+ * Epilogue: D = acc * scalar_scale[0] * expert_scale[e] * row_scale[row], any of them optional.
+ * scratch: fluxb_moe_schedule_scratch_bytes(E, world) bytes, kept by the caller between this call
+ * and fluxb_moe_combine (its header is the combine's `hdr`: scratch + fluxb_moe_hdr_offset). */
+typedef struct {
+  const int32_t* splits;
+  const int32_t* scatter_index;
+  int32_t* gather_index;
+  int64_t n_entries;
+  int32_t E, e0, E_local, topk;
+  int32_t tokens_per_rank, gathered, do_allgather, in_dtype;
+  int32_t N, K;
+  const void* a;
+  int64_t a_rows;
+  const void* a_tokens;
+  const void* weights;        /* [E_local, N, K] */
+  void* d;
+  int64_t ldd;
+  const float* expert_scale;
+  const float* scalar_scale;
+  const float* row_scale;
+  void* scratch;
+  int32_t rank, world;
+  uint32_t epoch, reserved;
+  uint64_t timeout_ns;
+  fluxb_status_t* status;
+  const void* ag_src;
+  void* ag_land[FLUXB_MAX_RANKS];
+  uint32_t* ag_flags[FLUXB_MAX_RANKS];
+  uint32_t* start_ctr[FLUXB_MAX_RANKS];
+  uint32_t* local_cnt;
+  void* stream;
+} fluxb_moe_gemm_args_t;
+
+int64_t fluxb_moe_schedule_scratch_bytes(int E, int world);
+int64_t fluxb_moe_hdr_offset(int E, int world);
+int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* args);
+
+/* Top-k combine + reduce-scatter: out[tokens_per_rank, H] = sum over ranks and over the top-k
+ * entries of each of this rank's tokens of y[routing_idx[token, k] - row_base]; rows that are not
+ * on a rank contribute nothing there. stage[r]: [world][tokens_per_rank][H] on rank r. */
+typedef struct {
+  const void* y;
+  const int32_t* hdr;         /* device: [0] row_base, [1] rows on this rank */
+  const int32_t* routing_idx; /* [world * tokens_per_rank * topk] */
+  int32_t topk, tokens_per_rank, H, dtype;
+  int32_t rank, world;
+  uint32_t epoch, reserved;
+  uint64_t timeout_ns;
+  fluxb_status_t* status;
+  void* stage[FLUXB_MAX_RANKS];
+  uint32_t* flags[FLUXB_MAX_RANKS];
+  uint32_t* start_ctr[FLUXB_MAX_RANKS];
+  uint32_t* local_cnt;
+  void* out;
+  void* stream;
+} fluxb_moe_combine_args_t;
+
+int fluxb_moe_combine(const fluxb_moe_combine_args_t* args);
+
 /* ---- symmetric memory (CUDA IPC). `handle` is 64 bytes of host memory. ---- */
 int fluxb_symm_alloc(uint64_t bytes, void** ptr, void* handle);
 int fluxb_symm_open(const void* handle, void** ptr);

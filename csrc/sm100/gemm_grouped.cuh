@@ -1,0 +1,362 @@
+// Grouped (per-expert) GEMM for MoE layers on sm_100a, same tcgen05/TMEM pipeline as the dense
+// kernel, with two things the dense kernel does not have:
+//   * a device-built schedule of sub-problems (expert, source rank, row range) walked by every
+//     CTA, so neither per-expert row counts nor pointer arrays ever visit the host;
+//   * optional gathered A: row r of the expert-sorted order is token gather_index[r] of the
+//     all-gathered token matrix. Four producer warps fetch those rows with 16-byte cp.async
+//     into the same 128-byte-swizzled layout TMA would produce; B (the expert's weight) comes
+//     by TMA from a 3-D map [expert][N][K].
+// In MoE layer 0 the kernel also performs the all-gather: warps 2-3 push this rank's token shard
+// into every peer's landing buffer (bulk-copy ring) and sub-problems of source rank s start
+// once s's shard has landed, own shard first.
+// Reference: src/moe_ag_scatter (GemmGroupedV3AGScatter, sort_util.cu, gather_tensor.hpp,
+// sm90_ag_scatter_fetcher.hpp) and src/moe_gather_rs (grouped GEMM part).
+#pragma once
+
+#include "gemm_dense.cuh"
+
+namespace fluxb {
+
+struct SubProblem {
+  int32_t row_begin, row_end;  // rows of the expert-sorted order
+  int32_t expert;              // local expert index (z coordinate of the weight map)
+  int32_t src;                 // source rank whose tokens these rows are (-1: no gating)
+};
+
+struct GroupedParams {
+  CUtensorMap tm_a;            // contiguous A [rows, K], box {BK, 128} (unused when gathered)
+  CUtensorMap tm_b;            // weights [E_local][N][K], box {BK, BN, 1}
+  const SubProblem* sp;        // [S]
+  const int32_t* tile_begin;   // [S + 1] prefix sums of (row tiles x column tiles)
+  int32_t S, N, K;
+  const int32_t* hdr;          // device: [0] row_base: sorted row r lives at row r - row_base of the
+                               // contiguous A and of D; [1] number of rows of this rank
+  int32_t gathered;            // 1: A rows are tokens picked by gather_index
+  int32_t tokens_per_rank;
+  const void* a_tokens;        // [W * tokens_per_rank, K] all-gathered tokens (landing buffer)
+  const int32_t* gather_index; // [total sorted rows] token of each sorted row
+  void* d;                     // [rows_out, N], 16-bit
+  int64_t ldd;
+  const float* expert_scale;   // [E_local] or null
+  const float* scalar_scale;   // [1] or null
+  const float* row_scale;      // [rows_out] or null (top-k gate weight of the row)
+  int32_t out_f16, ab_fmt;
+  // all-gather of the token shards (layer 0)
+  int32_t rank, world, do_allgather;
+  uint32_t epoch;
+  uint64_t timeout_ns;
+  Status* status;
+  const void* ag_src;          // this rank's shard [tokens_per_rank, K]
+  void* ag_land[kMaxRanks];
+  uint32_t* ag_flags[kMaxRanks];   // on every rank: [W src] last call whose shard landed
+  uint32_t* start_ctr[kMaxRanks];
+  uint32_t* local_cnt;             // [W]
+};
+
+template <int BN_, int KIND_, int STAGES_, bool GATHER_>
+struct GroupedCfg {
+  static constexpr int BM = 128, BN = BN_, KIND = KIND_, STAGES = STAGES_;
+  static constexpr bool GATHER = GATHER_;
+  static constexpr int ELT = KIND_ == 0 ? 2 : 1;
+  static constexpr int BK = 128 / ELT;
+  static constexpr int UMMA_K = 32 / ELT;
+  static constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128, STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int COMM_BYTES = GATHER_ ? 32768 : 0;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int THREADS = GATHER_ ? 384 : 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + COMM_BYTES + BAR_BYTES + 1024;
+  static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared memory limit");
+};
+
+struct GroupedTile {
+  int sp, row0, rows, n0, expert, src;
+};
+
+// Walks the schedule for increasing tile ids; `cursor` is the sub-problem of the previous tile.
+__device__ __forceinline__ GroupedTile grouped_decode(const GroupedParams& p, int t, int& cursor,
+                                                      int n_tiles, int BM, int BN) {
+  while (cursor + 1 < p.S && t >= p.tile_begin[cursor + 1]) ++cursor;
+  const SubProblem s = p.sp[cursor];
+  const int local = t - p.tile_begin[cursor];
+  const int m_tiles = (s.row_end - s.row_begin + BM - 1) / BM;
+  const int mt = local % m_tiles, nt = local / m_tiles;   // row tiles innermost: B tile reused
+  GroupedTile g;
+  g.sp = cursor;
+  g.row0 = s.row_begin + mt * BM;
+  g.rows = min(BM, s.row_end - g.row0);
+  g.n0 = nt * BN;
+  g.expert = s.expert;
+  g.src = s.src;
+  (void)n_tiles;
+  return g;
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __grid_constant__ GroupedParams p) {
+  constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t smem_base = raw_addr + pad;
+  const uint32_t comm_base = smem_base + STAGES * Cfg::STAGE_BYTES;
+  const uint32_t bar_base = comm_base + Cfg::COMM_BYTES;
+  uint8_t* bar_ptr = smem + STAGES * Cfg::STAGE_BYTES + Cfg::COMM_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * STAGES + 4));
+  volatile uint32_t* abort_word = tmem_slot + 1;
+  const uint32_t ring_bar_base = bar_base + 8u * (2 * STAGES + 4) + 16u;
+  static_assert(8 * (2 * STAGES + 4) + 16 + 64 <= Cfg::BAR_BYTES, "barrier block too small");
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      // B arrives by TMA (one arrival + bytes); gathered A adds one arrival per producer thread
+      ptx::mbar_init(full_bar(s), Cfg::GATHER ? 1 + 128 : 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 4);
+    }
+    for (int i = 0; i < 8; ++i) ptx::mbar_init(ring_bar_base + 8u * i, 1);
+    *abort_word = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tmap(&p.tm_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<1>(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    ptx::tmem_relinquish<1>();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  WaitCtx wc{p.status, abort_word, p.timeout_ns};
+
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int total_tiles = p.tile_begin[p.S];
+  const int k_blocks = (p.K + BK - 1) / BK;
+  const bool multi = p.world > 1 && p.do_allgather;
+  const int row_base = p.hdr[0];
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (B, and A if contiguous)
+    if (lane == 0) {
+      int stage = 0, cursor = 0, seen_src = -1;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        const GroupedTile g = grouped_decode(p, t, cursor, n_tiles, BM, BN);
+        (void)seen_src;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          mbar_wait(wc, empty_bar(stage), phase ^ 1u, kSiteSmemEmpty);
+          const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+          if constexpr (Cfg::GATHER) {
+            ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::B_BYTES);
+          } else {
+            ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+            ptx::tma_load_2d(sa, &p.tm_a, full_bar(stage), kb * BK, g.row0 - row_base);
+          }
+          ptx::tma_load_3d(sa + Cfg::A_BYTES, &p.tm_b, full_bar(stage), kb * BK, g.n0, g.expert);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = ptx::umma_idesc(p.ab_fmt, p.ab_fmt, BM, BN);
+      int stage = 0, it = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        mbar_wait(wc, tempty_bar(acc), (((it >> 1) & 1) ^ 1u), kSiteTmemEmpty);
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          mbar_wait(wc, full_bar(stage), phase, kSiteSmemFull);
+          // gathered A rows were written through the generic proxy (cp.async)
+          if constexpr (Cfg::GATHER) ptx::fence_proxy_async_smem();
+          ptx::tc_fence_after();
+          const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint64_t adesc = ptx::umma_desc_k_sw128(sa);
+          const uint64_t bdesc = ptx::umma_desc_k_sw128(sa + Cfg::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / Cfg::UMMA_K; ++k)
+            ptx::umma_ss<1, Cfg::KIND>(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          ptx::umma_commit(empty_bar(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        ptx::umma_commit(tfull_bar(acc));
+      }
+    }
+  } else if (warp == 2 || warp == 3) {
+    // ------------------------------------------------------------------ all-gather push of the token shard
+    if constexpr (Cfg::GATHER) {
+      if (multi && warp == 3 && blockIdx.x == 0 && lane < p.world)
+        ptx::st_release_sys(p.start_ctr[lane] + p.rank, p.epoch);
+      if (p.do_allgather) {
+        if (multi) {
+          if (lane < p.world) flag_wait_ge(wc, p.start_ctr[p.rank] + lane, p.epoch, kSiteStartBarrier);
+          __syncwarp();
+        }
+        if (lane == 0) {
+          constexpr int NSLOT = 4;
+          constexpr uint32_t CH = Cfg::COMM_BYTES / 2 / NSLOT;
+          const uint32_t ring = comm_base + (warp - 2) * (Cfg::COMM_BYTES / 2);
+          const uint32_t rbar = ring_bar_base + (warp - 2) * NSLOT * 8u;
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ag_src);
+          const int64_t bytes = static_cast<int64_t>(p.tokens_per_rank) * p.K * Cfg::ELT;
+          const int64_t slab_off = static_cast<int64_t>(p.rank) * bytes;
+          const uint32_t cw = blockIdx.x * 2 + (warp - 2), ncw = gridDim.x * 2;
+          const uint32_t nch = static_cast<uint32_t>((bytes + CH - 1) / CH);
+          uint32_t issued = 0;
+          // own landing slot first (the gather reads every token from the landing buffer), then
+          // the peer that consumes this shard first: rank-1, rank-2, ...
+          for (int d = 0; d < p.world; ++d) {
+            int peer = p.rank - d;
+            if (peer < 0) peer += p.world;
+            uint8_t* land = reinterpret_cast<uint8_t*>(p.ag_land[peer]) + slab_off;
+            for (uint32_t c = cw; c < nch; c += ncw) {
+              const int64_t off = static_cast<int64_t>(c) * CH;
+              const int64_t left = bytes - off;
+              const uint32_t sz = left < static_cast<int64_t>(CH) ? static_cast<uint32_t>(left) : CH;
+              const uint32_t slot = issued % NSLOT, ph = (issued / NSLOT) & 1u;
+              ptx::bulk_wait_read<NSLOT - 1>();
+              ptx::mbar_arrive_expect_tx(rbar + 8u * slot, sz);
+              ptx::bulk_load(ring + slot * CH, src + off, sz, rbar + 8u * slot);
+              mbar_wait(wc, rbar + 8u * slot, ph, kSiteSmemFull);
+              ptx::bulk_store(land + off, ring + slot * CH, sz);
+              ptx::bulk_commit();
+              ++issued;
+            }
+            // shard d is fully issued by this warp: wait for its stores, then count the arrival
+            ptx::bulk_wait<0>();
+            ptx::fence_proxy_async_all();
+            uint32_t* cnt = p.local_cnt + d;
+            if (ptx::atom_add_acq_rel_sys(cnt, 1u) == ncw - 1u) {
+              *cnt = 0;
+              ptx::st_release_sys(p.ag_flags[peer] + p.rank, p.epoch);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;
+    const bool f16 = p.out_f16 != 0;
+    const float sscale = p.scalar_scale ? *p.scalar_scale : 1.f;
+    int it = 0, cursor = 0;
+    uint16_t* dbase = reinterpret_cast<uint16_t*>(p.d);
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+      const GroupedTile g = grouped_decode(p, t, cursor, n_tiles, BM, BN);
+      const int acc = it & 1;
+      const uint32_t par = (it >> 1) & 1;
+      if (lane == 0) mbar_wait(wc, tfull_bar(acc), par, kSiteTmemFull);
+      __syncwarp();
+      mbar_wait(wc, tfull_bar(acc), par, kSiteTmemFull);
+      ptx::tc_fence_after();
+      const int r_in_tile = q * 32 + lane;
+      const bool row_ok = r_in_tile < g.rows;
+      const int64_t orow = static_cast<int64_t>(g.row0) - row_base + r_in_tile;
+      float scale = sscale;
+      if (p.expert_scale) scale *= p.expert_scale[g.expert];
+      if (p.row_scale && row_ok) scale *= p.row_scale[orow];
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 64; ++ch) {
+        uint32_t r0[32], r1[32];
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + ch * 64;
+        ptx::tmem_ld_32x32b_x32(taddr, r0);
+        ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
+        ptx::tmem_ld_wait();
+        if (ch == BN / 64 - 1) {
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+        }
+        const int col0 = g.n0 + ch * 64;
+        if (row_ok && col0 < p.N) {
+          uint16_t* drow = dbase + orow * p.ldd + col0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (col0 + 8 * j < p.N) {
+              uint4 v;
+              v.x = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 0]) * scale, __uint_as_float(r0[8 * j + 1]) * scale);
+              v.y = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 2]) * scale, __uint_as_float(r0[8 * j + 3]) * scale);
+              v.z = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 4]) * scale, __uint_as_float(r0[8 * j + 5]) * scale);
+              v.w = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 6]) * scale, __uint_as_float(r0[8 * j + 7]) * scale);
+              *reinterpret_cast<uint4*>(drow + 8 * j) = v;
+            }
+            if (col0 + 32 + 8 * j < p.N) {
+              uint4 v;
+              v.x = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 0]) * scale, __uint_as_float(r1[8 * j + 1]) * scale);
+              v.y = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 2]) * scale, __uint_as_float(r1[8 * j + 3]) * scale);
+              v.z = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 4]) * scale, __uint_as_float(r1[8 * j + 5]) * scale);
+              v.w = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 6]) * scale, __uint_as_float(r1[8 * j + 7]) * scale);
+              *reinterpret_cast<uint4*>(drow + 32 + 8 * j) = v;
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ gathered-A producers (warps 8..11)
+    if constexpr (Cfg::GATHER) {
+      const int i = threadIdx.x - 256;            // row of the tile this thread fetches
+      const uint8_t* tokens = reinterpret_cast<const uint8_t*>(p.a_tokens);
+      const int64_t row_bytes = static_cast<int64_t>(p.K) * Cfg::ELT;
+      int stage = 0, cursor = 0, ready_src = -1;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        const GroupedTile g = grouped_decode(p, t, cursor, n_tiles, BM, BN);
+        if (g.src >= 0 && g.src != ready_src) {
+          // tokens of this source must have landed (sub-problems are ordered by source, own first)
+          if (lane == 0) flag_wait_ge(wc, p.ag_flags[p.rank] + g.src, p.epoch, kSiteMoeFlag);
+          __syncwarp();
+          ready_src = g.src;
+        }
+        const bool valid = i < g.rows;
+        const uint8_t* src_row = tokens;
+        if (valid) src_row = tokens + static_cast<int64_t>(p.gather_index[g.row0 + i]) * row_bytes;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          mbar_wait(wc, empty_bar(stage), phase ^ 1u, kSiteSmemEmpty);
+          const uint32_t dst = smem_base + stage * Cfg::STAGE_BYTES + i * 128;
+          if (valid) {
+            const uint8_t* s = src_row + static_cast<int64_t>(kb) * 128;
+            const int64_t left = row_bytes - static_cast<int64_t>(kb) * 128;   // bytes of the row still in range
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const uint32_t n = left >= (c + 1) * 16 ? 16u : 0u;             // zero-fill past K
+              ptx::cp_async_16(dst + ((c ^ (i & 7)) << 4), s + c * 16, n);
+            }
+          }
+          ptx::cp_async_mbar_arrive_noinc(full_bar(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  }
+
+  __syncwarp();
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc<1>(tmem_base, 512);
+  }
+}
+
+}  // namespace fluxb

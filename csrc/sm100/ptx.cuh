@@ -229,6 +229,18 @@ __device__ __forceinline__ void bulk_store(void* gdst, uint32_t smem_src, uint32
                : "memory");
 }
 
+// 16-byte asynchronous copy global -> shared (generic proxy); bytes past src_size are zero-filled
+__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gsrc, uint32_t src_size) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst),
+               "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(src_size)
+               : "memory");
+}
+// the barrier receives one arrival (already counted in its init value) once all cp.async issued
+// so far by this thread have landed
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 // ----------------------------------------------------------------------------------------
 // tcgen05 / TMEM
 // ----------------------------------------------------------------------------------------

@@ -22,3 +22,5 @@ from .ops.misc import (InplaceCast, bitwise_check, calc_scatter_index, inplace_c
                        moe_index_build, uniform_initialize)
 from .ops.blockscale_gemm import BlockScaleGemm, blockscale_gemm_torch  # noqa: F401
 from .ops.ulysses import AllToAllTransposeGemm, GemmAllToAllTranspose  # noqa: F401
+from .ops.moe import (GemmGroupedV2, GemmGroupedV2AGScatterOp, GemmGroupedV2GatherRSOp, GemmGroupedV3,  # noqa: F401
+                      GemmGroupedV3AGScatter, GemmGroupedV3GatherRS, topk_scatter_reduce)

@@ -228,11 +228,12 @@ def check_ulysses():
 
 
 def check_moe():
-    try:
-        from tests_moe_checks import run as run_moe  # noqa: F401
-    except Exception:
-        p0("moe: no checks yet")
-        return
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from moe_common import run_moe_layer
+    for ep in sorted({W, 1, max(W // 2, 1)}):
+        run_moe_layer(rank, W, ep, torch.bfloat16, dev, tpr=256, H=512, ffn=768 * W // ep // max(W // ep, 1),
+                      E=8 * ep if ep > 1 else 8, topk=2, tol=3e-2)
+    p0(f"moe ok (W={W})")
 
 
 if "dense" in what:
