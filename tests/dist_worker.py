@@ -234,6 +234,68 @@ def check_moe():
         run_moe_layer(rank, W, ep, torch.bfloat16, dev, tpr=256, H=512, ffn=768 * W // ep // max(W // ep, 1),
                       E=8 * ep if ep > 1 else 8, topk=2, tol=3e-2)
     p0(f"moe ok (W={W})")
+    if perf:
+        moe_perf()
+
+
+def moe_perf(E=64, topk=8, H=4096, ffn=1536, tpr=8192):
+    """64 experts, top-8, hidden 4096, expert FFN 1536 (gate and up fused into one 3072-wide GEMM),
+    8192 tokens per rank, expert parallel over all ranks."""
+    from tempname_new_b200.testing import gen_moe_gating_args
+    tokens = tpr * W
+    g = gen_moe_gating_args(E, topk, tokens, device=dev, seed=1)
+    env = flux.DistEnvTPWithEP(pg, 1, None, ep_size=W)
+    E_loc, e0 = E // W, rank * (E // W)
+    x = (torch.randn(tpr, H, device=dev) * 0.5).bfloat16()
+    w1 = (torch.randn(E_loc, 2 * ffn, H, device=dev) * 0.02).bfloat16()
+    w2 = (torch.randn(E_loc, H, ffn, device=dev) * 0.02).bfloat16()
+    offs = torch.cat([torch.zeros(1, dtype=torch.long), g.splits_cpu.long().cumsum(0)])
+    lo, hi = int(offs[e0]), int(offs[e0 + E_loc])
+    rows = hi - lo
+    op0 = flux.GemmGroupedV3AGScatter(env, flux.MoeArguments(tokens, H, 2 * ffn, E, topk, torch.bfloat16))
+    op1 = flux.GemmGroupedV3GatherRS(E, tokens * topk, H, topk, rank, W, 1, W, tp_group=pg)
+    h = torch.empty(rows, 2 * ffn, device=dev, dtype=torch.bfloat16)
+    act = (torch.randn(rows, ffn, device=dev) * 0.5).bfloat16()
+    gate_rows = g.gate_weight.reshape(-1)[torch.argsort(g.choosed_experts.reshape(-1), stable=True)][lo:hi].contiguous()
+    t0 = timeit(lambda: op0.forward(x, w1, g.splits_gpu, g.scatter_index, outputs_buf=h), 5, 2)
+    t1 = timeit(lambda: op1.forward_gather_rs(act, w2, g.splits_gpu, g.scatter_index.reshape(-1),
+                                              output_vec_scale=gate_rows), 5, 2)
+    op0.check_status()
+    op1.check_status()
+    # torch statement of the same layers (all_gather + index_select + per-expert matmul; per-expert
+    # matmul + scatter + top-k sum + reduce_scatter)
+    full = torch.empty(tokens, H, device=dev, dtype=torch.bfloat16)
+    gidx = g.gather_index.long()
+    sl = g.splits_cpu.tolist()
+    ridx = g.scatter_index.reshape(-1).long()
+
+    def torch_l0():
+        dist.all_gather_into_tensor(full, x)
+        a = full[gidx[lo:hi]]
+        r = 0
+        for el in range(E_loc):
+            n = sl[e0 + el]
+            torch.matmul(a[r:r + n], w1[el].t(), out=h[r:r + n])
+            r += n
+
+    yrows = torch.empty(rows, H, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(tpr, H, device=dev, dtype=torch.bfloat16)
+
+    def torch_l1():
+        r = 0
+        for el in range(E_loc):
+            n = sl[e0 + el]
+            torch.matmul(act[r:r + n], w2[el].t(), out=yrows[r:r + n])
+            r += n
+        y = yrows * gate_rows[:, None].bfloat16()
+        fullrows = torch.zeros(tokens * topk, H, device=dev, dtype=torch.bfloat16)
+        fullrows[lo:hi] = y
+        red = fullrows[ridx].view(tokens, topk, H).sum(1)
+        dist.reduce_scatter_tensor(out, red)
+    tt0, tt1 = timeit(torch_l0, 3, 1), timeit(torch_l1, 3, 1)
+    f0, f1 = 2.0 * rows * H * 2 * ffn, 2.0 * rows * H * ffn
+    p0(f"MoE E={E} top{topk} H={H} ffn={ffn} {tpr} tok/rank EP{W}: layer0 fluxb {t0:.3f} ms ({f0 / t0 / 1e9:.0f} TF/GPU)"
+       f" | torch+nccl {tt0:.3f} ms ; layer1 fluxb {t1:.3f} ms ({f1 / t1 / 1e9:.0f} TF/GPU) | torch+nccl {tt1:.3f} ms")
 
 
 if "dense" in what:

@@ -1,0 +1,87 @@
+"""CPU checks of the host-side pieces: utilities, routing helpers, tuning table, roofline model."""
+import pytest
+import torch
+
+
+def test_torch_allclose_reports_offenders():
+    import tempname_new_b200 as flux
+    flux.torch_allclose(torch.ones(4, 4), torch.ones(4, 4) + 1e-6, 1e-3, 1e-3)
+    y = torch.ones(4, 4)
+    y[2, 3] = 5.0
+    with pytest.raises(AssertionError) as e:
+        flux.torch_allclose(torch.ones(4, 4), y, 1e-3, 1e-3)
+    assert "(2, 3)" in str(e.value) and "1 of 16" in str(e.value)
+
+
+def test_moe_routing_helpers_agree_with_device_free_index_build():
+    from tempname_new_b200.ops.misc import calc_scatter_index, moe_index_build
+    from tempname_new_b200.testing import gen_moe_gating_args, is_gather_index_stable
+    a = gen_moe_gating_args(16, 4, 200, device="cpu", seed=5)
+    assert int(a.splits_cpu.sum()) == 800
+    splits, offsets, scatter, gather, tki = moe_index_build(a.choosed_experts, 16)
+    assert torch.equal(splits, a.splits_gpu)
+    assert torch.equal(scatter, a.scatter_index)
+    assert torch.equal(gather, a.gather_index) and torch.equal(tki, a.topk_index)
+    assert is_gather_index_stable(gather, splits)
+    assert torch.equal(calc_scatter_index(a.choosed_experts, a.splits_gpu), a.scatter_index)
+    rr = gen_moe_gating_args(8, 2, 64, device="cpu", round_robin=True)
+    assert rr.splits_cpu.tolist() == [16] * 8
+
+
+def test_tuning_table_and_profiling_context(tmp_path, monkeypatch):
+    from tempname_new_b200.tuning import table
+    from tempname_new_b200.tuning.profiling import ProfilingContext, TuningRecord
+    k = table.lookup(8192, 6144, 12288)
+    assert k == {"cta_group": 2, "tile_n": 256, "group_m": 8}
+    h = table.lookup(333, 264, 72)
+    assert h["cta_group"] == 1 and h["tile_n"] in (128, 256)
+    assert table.heuristic(8192, 4096, 32768)["group_m"] == 2       # long K narrows the raster group
+    f = tmp_path / "extra.json"
+    f.write_text('[{"key": [1, 2, 3], "best": {"cta_group": 1, "tile_n": 128, "group_m": 4}}]')
+    monkeypatch.setenv("FLUXB_TUNE_FILE", str(f))
+    table._EXTRA = None
+    assert table.lookup(1, 2, 3)["group_m"] == 4
+    table._EXTRA = None
+    ctx = ProfilingContext("t")
+    ctx.add(TuningRecord("gemm_only", {"m": 1}, {"tile_n": 128}, 0.5))
+    assert "gemm_only" in ctx.get_latest_prof_result() and '"tile_n": 128' in ctx.get_code()
+    assert len(ctx.get_all_records()) == 1
+
+
+def test_perf_model_roofline_terms():
+    from tempname_new_b200.testing import (estimate_fused_sol_time_ms, estimate_gemm_sol_time_ms, get_nvlink_gbps,
+                                           get_tflops, roofline_fraction)
+    t = estimate_gemm_sol_time_ms(8192, 12288, 6144)
+    assert 0.5 < t < 1.2                                  # ~0.72-0.78 ms at 1.6-1.7 PFLOP/s
+    flops = 2.0 * 8192 * 12288 * 6144
+    comm = 7 / 8 * 8192 * 12288 * 2
+    sol = estimate_fused_sol_time_ms(flops, comm)
+    assert sol == pytest.approx(max(flops / (get_tflops() * 1e9), comm / (get_nvlink_gbps() * 1e6)))
+    assert roofline_fraction(2 * sol, flops, comm) == pytest.approx(0.5)
+    assert get_tflops(torch.float8_e4m3fn) == pytest.approx(2 * get_tflops(torch.bfloat16))
+
+
+def test_options_and_env_records():
+    import tempname_new_b200 as flux
+    o = flux.ReduceScatterOption()
+    o.use_1d_ring, o.ring_mode = True, flux.RingMode.Ring1D
+    assert flux.get_default_rs_ring_mode() == flux.RingMode.All2All
+    assert flux.AllGatherOption().mode is None and flux.AllToAllOption().skip_barrier is None
+    m = flux.MoeArguments(1024, 256, 512, 8, 2, torch.bfloat16)
+    assert m.output_dtype == torch.bfloat16
+    with flux.with_torch_deterministic(True):
+        assert torch.are_deterministic_algorithms_enabled()
+
+
+def test_cpu_fallbacks_of_small_ops():
+    import tempname_new_b200 as flux
+    a = torch.randn(10, 7)
+    assert flux.bitwise_check(a, a.clone()) and not flux.bitwise_check(a, a + 1)
+    t = torch.empty(1000)
+    flux.uniform_initialize(t, 3, -1.0, 1.0)
+    assert -1.0 <= float(t.min()) and float(t.max()) < 1.0
+    g = flux.GemmOnly(torch.float32, output_dtype=torch.float32)
+    x, w = torch.randn(5, 8), torch.randn(6, 8)
+    torch.testing.assert_close(g.forward(x, w), x @ w.t())
+    out = flux.GemmGroupedV3(torch.randn(2, 4, 8), 2).forward(torch.randn(5, 8), torch.tensor([2, 3]))
+    assert out.shape == (5, 4)
