@@ -170,6 +170,36 @@ typedef struct {
 
 int fluxb_moe_combine(const fluxb_moe_combine_args_t* args);
 
+/* ---- row exchange over peer memory (csrc/ops/a2a.cu) ----
+ * Variable-split all-to-all of rows (broadcast = 0: rows [sum(in_splits[:d]), +in_splits[d]) of
+ * `in` go to rank d) or all-gather (broadcast = 1: all rows_in rows go to every rank). In the
+ * destination, rows are ordered by source rank. out[r], table[r] (world*world int32) and
+ * flags[r] (2*world uint32) live in symmetric memory, zero at first use; out_splits [world] and
+ * out_offsets [world + 1] (optional, local) receive the row counts / start rows per source. */
+typedef struct {
+  const void* in;
+  const int32_t* in_splits;
+  int32_t rows_in, broadcast;
+  int64_t row_bytes;
+  int32_t rank, world;
+  uint32_t epoch;
+  int32_t num_ctas;
+  uint64_t timeout_ns;
+  fluxb_status_t* status;
+  void* out[FLUXB_MAX_RANKS];
+  int32_t* table[FLUXB_MAX_RANKS];
+  uint32_t* flags[FLUXB_MAX_RANKS];
+  uint32_t* local_cnt;
+  int32_t* out_splits;
+  int32_t* out_offsets;
+  int64_t out_capacity_rows;
+  void* stream;
+} fluxb_a2a_rows_args_t;
+
+int fluxb_a2a_rows(const fluxb_a2a_rows_args_t* args);
+/* *flag = value with system-scope release, stream ordered (flag may be peer memory) */
+int fluxb_set_flag(uint32_t* flag, uint32_t value, void* stream);
+
 /* ---- symmetric memory (CUDA IPC). `handle` is 64 bytes of host memory. ---- */
 int fluxb_symm_alloc(uint64_t bytes, void** ptr, void* handle);
 int fluxb_symm_open(const void* handle, void** ptr);

@@ -32,3 +32,4 @@ from .utils.dist_utils import exec_in_rank_order, get_dist_env  # noqa: F401
 from .tuning.profiling import ProfilingContext, TuningRecord  # noqa: F401
 from .parallel.layers import ColumnParallelLinear, RowParallelLinear, patch_megatron_linears  # noqa: F401
 from . import models, ops, parallel, testing, tuning, utils  # noqa: F401
+from .ops.coll import All2AllOp, All2AllSingle, AllGatherOp, AsyncSendRecv  # noqa: F401

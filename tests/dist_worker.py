@@ -24,7 +24,7 @@ dist.init_process_group("nccl", device_id=dev)
 pg = dist.group.WORLD
 flux.init_flux_shm(pg)
 torch.manual_seed(1234 + rank)
-what = [a for a in sys.argv[1:] if not a.startswith("--")] or ["dense", "blockscale", "ulysses", "moe"]
+what = [a for a in sys.argv[1:] if not a.startswith("--")] or ["dense", "blockscale", "ulysses", "moe", "coll"]
 perf = "--perf" in sys.argv
 
 
@@ -227,6 +227,40 @@ def check_ulysses():
     p0(f"ulysses ok (W={W})")
 
 
+def check_coll():
+    ag = flux.AllGatherOp(pg, 1, 1024 * W, 512, torch.bfloat16)
+    x = torch.randn(1024, 512, device=dev).bfloat16()
+    ref = torch.empty(1024 * W, 512, device=dev, dtype=torch.bfloat16)
+    dist.all_gather_into_tensor(ref, x)
+    for _ in range(2):
+        assert torch.equal(ag.run(x), ref)
+    ag.check_status()
+    a2a = flux.All2AllSingle(pg, 4096, 256, W, torch.bfloat16)
+    ins = torch.tensor([64 * (1 + (rank + d) % 3) for d in range(W)], device=dev, dtype=torch.int32)
+    inp = torch.randn(int(ins.sum()), 256, device=dev).bfloat16()
+    outs64 = torch.empty(W, dtype=torch.int64, device=dev)
+    dist.all_to_all_single(outs64, ins.long())
+    ref = torch.empty(int(outs64.sum()), 256, device=dev, dtype=torch.bfloat16)
+    dist.all_to_all_single(ref, inp, outs64.tolist(), ins.tolist())
+    osp = torch.empty(W, dtype=torch.int32, device=dev)
+    for _ in range(2):
+        res = a2a.forward(inp, None, ins, osp)
+        assert torch.equal(osp.long(), outs64)
+        assert torch.equal(res[: ref.shape[0]], ref)
+    a2a.check_status()
+    sr = flux.AsyncSendRecv(16, 64, rank, W, torch.bfloat16, duplicate=3, pg=pg)
+    sr.get_comm_buffer(0).fill_(float(rank + 1))
+    torch.cuda.synchronize()
+    dist.barrier()
+    nxt, prv = (rank + 1) % W, (rank - 1) % W
+    sr.write_comm_buffer(nxt, 0, 2)
+    sr.set_signal(nxt, 1, 7)
+    sr.wait_signal_eq(1, 7)
+    torch.cuda.synchronize()
+    assert float(sr.get_comm_buffer(2)[0, 0]) == float(prv + 1)
+    p0(f"coll ok (W={W})")
+
+
 def check_moe():
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     from moe_common import run_moe_layer
@@ -306,6 +340,8 @@ if "ulysses" in what:
     check_ulysses()
 if "moe" in what:
     check_moe()
+if "coll" in what:
+    check_coll()
 p0("ALL OK")
 dist.barrier()
 dist.destroy_process_group()

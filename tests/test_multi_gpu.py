@@ -25,4 +25,4 @@ def _run(world, what):
 def test_fused_ops_multi_gpu(world):
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    _run(world, ["dense", "blockscale", "ulysses", "moe"])
+    _run(world, ["dense", "blockscale", "ulysses", "moe", "coll"])
