@@ -125,6 +125,9 @@ typedef struct {
   const void* a;
   int64_t a_rows;
   const void* a_tokens;
+  void* a_sorted;             /* optional [a_sorted_rows, K] scratch for the expert-sorted copy of the
+                                 gathered rows (a_sorted_rows >= rows of this rank) */
+  int64_t a_sorted_rows;
   const void* weights;        /* [E_local, N, K] */
   void* d;
   int64_t ldd;

@@ -291,6 +291,17 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   if (p.mode == kModeAllGather) p.seg_first = a->rank;
   if (p.mode == kModeReduceScatter) p.seg_first = (a->rank + 1) % a->world;
 
+  // arrival flags of the pushes cover about 32 MB of a shard each (one flag per shard when it is
+  // smaller): few enough that counting the pushing warps stays cheap, fine enough for big shards
+  {
+    const int64_t row_b = p.mode == kModeA2AGemm ? static_cast<int64_t>(a->K / a->world) * elt
+                                                 : static_cast<int64_t>(a->K) * elt;
+    int64_t unit = (32ll << 20) / (row_b > 0 ? row_b : 1);
+    unit = (unit + bm - 1) / bm * bm;
+    const int64_t seg_round = (static_cast<int64_t>(p.seg_rows) + bm - 1) / bm * bm;
+    if (unit > seg_round || unit * 3 / 2 > seg_round) unit = seg_round;
+    p.flag_unit_rows = static_cast<int32_t>(unit);
+  }
   const int m_tiles_seg = (p.seg_rows + bm - 1) / bm;
   p.group_m = a->group_m > 0 ? a->group_m : 16 / cg;
   if (p.group_m > m_tiles_seg) p.group_m = m_tiles_seg;

@@ -11,6 +11,8 @@
 #include "../sm100/gemm_grouped.cuh"
 
 #include <atomic>
+#include <cstdlib>
+#include <string>
 
 namespace fluxb {
 extern std::atomic<uint64_t> g_launches;
@@ -294,9 +296,38 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
     if ((rc = encode_tmap(&p.tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a->weights, dims, str, box, Swz::B128)))
       return rc;
   }
+  // gathered rows: by default the communication warps copy them into a sorted buffer (when the
+  // caller provides one); FLUXB_MOE_GATHER=cpasync | gather4 selects the in-loader variants
+  static const int gather_mode = [] {
+    const char* e = getenv("FLUXB_MOE_GATHER");
+    if (e && std::string(e) == "cpasync") return 1;
+    if (e && std::string(e) == "gather4") return 2;
+    return 3;
+  }();
+  const bool pregather = a->gathered && gather_mode == 3 && a->a_sorted != nullptr;
+  const bool use_gather4 = a->gathered && gather_mode == 2;
+  p.E_local = a->E_local;
+  p.by_src = by_src ? 1 : 0;
   if (a->gathered) {
     FLUXB_REQUIRE(a->a_tokens != nullptr, "token matrix missing");
     p.a_tokens = a->a_tokens;
+    if (pregather) {
+      FLUXB_REQUIRE(a->a_sorted_rows > 0 && a->local_cnt != nullptr, "sorted buffer / local scratch");
+      p.a_sorted = a->a_sorted;
+      p.local_cnt = a->local_cnt;
+      uint64_t dims[2] = {static_cast<uint64_t>(a->K), static_cast<uint64_t>(a->a_sorted_rows)};
+      uint64_t str[1] = {static_cast<uint64_t>(a->K) * elt};
+      uint32_t box[2] = {64, 128};
+      if ((rc = encode_tmap(&p.tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->a_sorted, dims, str, box, Swz::B128)))
+        return rc;
+    } else if (use_gather4) {
+      uint64_t dims[2] = {static_cast<uint64_t>(a->K),
+                          static_cast<uint64_t>(a->tokens_per_rank) * (a->do_allgather || a->world > 1 ? a->world : 1)};
+      uint64_t str[1] = {static_cast<uint64_t>(a->K) * elt};
+      uint32_t box[2] = {64, 1};
+      if ((rc = encode_tmap(&p.tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->a_tokens, dims, str, box, Swz::B128)))
+        return rc;
+    }
     if (a->do_allgather) {
       FLUXB_REQUIRE(a->ag_src && a->local_cnt, "all-gather source / scratch missing");
       p.ag_src = a->ag_src;
@@ -318,12 +349,20 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
   }
   int sms = 0;
   if ((rc = device_sm_count(&sms))) return rc;
-  if (a->gathered) {
-    if (bn == 256) return launch_grouped<GroupedCfg<256, 0, 4, true>>(p, sms, stream);
-    return launch_grouped<GroupedCfg<128, 0, 5, true>>(p, sms, stream);
+  if (pregather) {
+    if (bn == 256) return launch_grouped<GroupedCfg<256, 0, 4, 3>>(p, sms, stream);
+    return launch_grouped<GroupedCfg<128, 0, 5, 3>>(p, sms, stream);
   }
-  if (bn == 256) return launch_grouped<GroupedCfg<256, 0, 4, false>>(p, sms, stream);
-  return launch_grouped<GroupedCfg<128, 0, 6, false>>(p, sms, stream);
+  if (a->gathered && use_gather4) {
+    if (bn == 256) return launch_grouped<GroupedCfg<256, 0, 4, 2>>(p, sms, stream);
+    return launch_grouped<GroupedCfg<128, 0, 5, 2>>(p, sms, stream);
+  }
+  if (a->gathered) {
+    if (bn == 256) return launch_grouped<GroupedCfg<256, 0, 4, 1>>(p, sms, stream);
+    return launch_grouped<GroupedCfg<128, 0, 5, 1>>(p, sms, stream);
+  }
+  if (bn == 256) return launch_grouped<GroupedCfg<256, 0, 4, 0>>(p, sms, stream);
+  return launch_grouped<GroupedCfg<128, 0, 6, 0>>(p, sms, stream);
 }
 
 extern "C" int fluxb_moe_combine(const fluxb_moe_combine_args_t* a) {

@@ -70,7 +70,10 @@ struct DenseGemmParams {
   // all-gather
   const void* ag_src;            // this rank's shard [seg_rows, K]
   void* ag_land[kMaxRanks];      // landing buffer of every rank, [W][seg_rows][K]
-  uint32_t* ag_flags[kMaxRanks]; // on every rank: [W src][m_tiles_seg] = last call whose rows landed
+  uint32_t* ag_flags[kMaxRanks]; // on every rank: [W src][units] = last call whose rows landed
+  int32_t flag_unit_rows;        // rows per arrival flag of the all-gather / all-to-all pushes
+                                 // (a multiple of the tile height; units = ceil(rows / this))
+  int32_t reserved4;
   // cross-rank start handshake
   uint32_t* start_ctr[kMaxRanks];  // on every rank: [W] last call number entered, by source
   // reduce-scatter
@@ -248,7 +251,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             a_row = m_cta;  // own shard straight from the caller's tensor
           } else {
             tma = &p.tm_a_land;
-            const uint32_t* f = p.ag_flags[p.rank] + c.seg * m_tiles_seg + c.m_tile;
+            const uint32_t* f = p.ag_flags[p.rank] + c.seg * ((p.seg_rows + p.flag_unit_rows - 1) / p.flag_unit_rows) +
+                                c.m_in_seg / p.flag_unit_rows;
             flag_wait_ge(wc, f, p.epoch, kSiteShardFlag);
             ptx::fence_proxy_async_all();
           }
@@ -265,7 +269,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             const int src = kb / kb_per_src;
             if (src != cur_src) {
               cur_src = src;
-              flag_wait_ge(wc, p.a2a_flags[p.rank] + src * m_tiles_seg + c.m_tile, p.epoch, kSiteA2AFlag);
+              flag_wait_ge(wc, p.a2a_flags[p.rank] + src * ((p.seg_rows + p.flag_unit_rows - 1) / p.flag_unit_rows) +
+                               c.m_in_seg / p.flag_unit_rows,
+                           p.epoch, kSiteA2AFlag);
               ptx::fence_proxy_async_all();
             }
           }
@@ -378,17 +384,19 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           const int64_t slab_off = static_cast<int64_t>(p.rank) * p.seg_rows * row_bytes;
           const uint32_t cw = blockIdx.x * 2 + (warp - 2);
           const uint32_t ncw = gridDim.x * 2;
+          const int UR = p.flag_unit_rows;
+          const int units = (p.seg_rows + UR - 1) / UR;
           // scales of a block-scaled shard ride along as a second byte range per tile row:
           // [rows/128][K/128][128] floats
           const int64_t srow_bytes = Cfg::BS ? static_cast<int64_t>(k_blocks) * 512 : 0;  // per 128 rows
           const int64_t sslab_off = static_cast<int64_t>(p.rank) * (p.seg_rows / 128) * srow_bytes;
           const uint8_t* ssrc = reinterpret_cast<const uint8_t*>(p.ag_scale_src);
           auto payload_chunks = [&](int mt) -> uint32_t {
-            const int rows = min(BM, p.seg_rows - mt * BM);
+            const int rows = min(UR, p.seg_rows - mt * UR);
             return static_cast<uint32_t>((rows * row_bytes + CH - 1) / CH);
           };
           auto scale_bytes = [&](int mt) -> int64_t {
-            const int rows = min(BM, p.seg_rows - mt * BM);
+            const int rows = min(UR, p.seg_rows - mt * UR);
             return static_cast<int64_t>((rows + 127) / 128) * srow_bytes;
           };
           auto step_chunks = [&](int mt) -> uint32_t {  // chunks of tile row mt that this warp moves
@@ -400,10 +408,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             if (peer < 0) peer += p.world;
             ptx::fence_proxy_async_all();
             // the last of the 2*gridDim.x pushing warps publishes the tile row to the peer
-            uint32_t* cnt = p.local_cnt + d * m_tiles_seg + mt;
+            uint32_t* cnt = p.local_cnt + d * units + mt;
             if (ptx::atom_add_acq_rel_sys(cnt, 1u) == ncw - 1u) {
               *cnt = 0;
-              ptx::st_release_sys(p.ag_flags[peer] + p.rank * m_tiles_seg + mt, p.epoch);
+              ptx::st_release_sys(p.ag_flags[peer] + p.rank * units + mt, p.epoch);
             }
           };
           uint32_t issued = 0;
@@ -414,12 +422,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             if (peer < 0) peer += p.world;
             uint8_t* land = reinterpret_cast<uint8_t*>(p.ag_land[peer]) + slab_off;
             uint8_t* sland = Cfg::BS ? reinterpret_cast<uint8_t*>(p.ag_scale_land[peer]) + sslab_off : nullptr;
-            for (int mt = 0; mt < m_tiles_seg; ++mt) {
-              const int rows = min(BM, p.seg_rows - mt * BM);
-              const int64_t first = static_cast<int64_t>(mt) * BM * row_bytes;
+            for (int mt = 0; mt < units; ++mt) {
+              const int rows = min(UR, p.seg_rows - mt * UR);
+              const int64_t first = static_cast<int64_t>(mt) * UR * row_bytes;
               const int64_t bytes = rows * row_bytes;
               const uint32_t nch_p = payload_chunks(mt);
-              const int64_t sfirst = static_cast<int64_t>(mt) * (BM / 128) * srow_bytes;
+              const int64_t sfirst = static_cast<int64_t>(mt) * (UR / 128) * srow_bytes;
               const int64_t sbytes = scale_bytes(mt);
               const uint32_t nch = nch_p + static_cast<uint32_t>((sbytes + CH - 1) / CH);
               for (uint32_t c = cw; c < nch; c += ncw) {
@@ -454,7 +462,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
               const uint32_t done = issued > LAG ? issued - LAG : 0u;
               while ((sig_d < d || (sig_d == d && sig_mt <= mt)) && sig_end <= done) {
                 publish(sig_d, sig_mt);
-                if (++sig_mt == m_tiles_seg) { sig_mt = 0; ++sig_d; }
+                if (++sig_mt == units) { sig_mt = 0; ++sig_d; }
                 sig_end += step_chunks(sig_mt);
               }
             }
@@ -462,7 +470,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           ptx::bulk_wait<0>();
           while (sig_d < p.world) {
             publish(sig_d, sig_mt);
-            if (++sig_mt == m_tiles_seg) { sig_mt = 0; ++sig_d; }
+            if (++sig_mt == units) { sig_mt = 0; ++sig_d; }
           }
         }
       }
@@ -486,10 +494,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           const uint32_t ncw = gridDim.x * 2;
           const int hd = p.a2a_hd, lh = p.a2a_local_heads, ls = p.a2a_local_seq;
           const uint32_t chunk_bytes = 32u * hd * Cfg::ELT;
-          const int groups_per_tile = BM / 32;                 // 32-row groups per tile row
+          const int UR = p.flag_unit_rows;
+          const int units = (p.a2a_bs * ls + UR - 1) / UR;
+          const int groups_per_tile = UR / 32;                 // 32-row groups per flag unit
           const int rows_total = p.a2a_bs * ls;
           auto step_chunks = [&](int mt) -> uint32_t {
-            const int rows = min(BM, rows_total - mt * BM);
+            const int rows = min(UR, rows_total - mt * UR);
             const uint32_t nch = static_cast<uint32_t>(((rows + 31) / 32) * lh);
             return nch > cw ? (nch - cw - 1) / ncw + 1 : 0u;
           };
@@ -497,10 +507,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             int peer = p.rank + d;
             if (peer >= p.world) peer -= p.world;
             ptx::fence_proxy_async_all();
-            uint32_t* cnt = p.local_cnt + d * m_tiles_seg + mt;
+            uint32_t* cnt = p.local_cnt + d * units + mt;
             if (ptx::atom_add_acq_rel_sys(cnt, 1u) == ncw - 1u) {
               *cnt = 0;
-              ptx::st_release_sys(p.a2a_flags[peer] + p.rank * m_tiles_seg + mt, p.epoch);
+              ptx::st_release_sys(p.a2a_flags[peer] + p.rank * units + mt, p.epoch);
             }
           };
           uint32_t issued = 0;
@@ -510,12 +520,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           for (int d = 0; d < p.world; ++d) {
             int peer = p.rank + d;
             if (peer >= p.world) peer -= p.world;
-            for (int mt = 0; mt < m_tiles_seg; ++mt) {
-              const int rows = min(BM, rows_total - mt * BM);
+            for (int mt = 0; mt < units; ++mt) {
+              const int rows = min(UR, rows_total - mt * UR);
               const uint32_t nch = static_cast<uint32_t>(((rows + 31) / 32) * lh);
               for (uint32_t c = cw; c < nch; c += ncw) {
                 const int g = c / lh, h = c % lh;                  // 32-row group, local head
-                const int row0 = mt * BM + g * 32;                 // row of the peer's GEMM input
+                const int row0 = mt * UR + g * 32;                 // row of the peer's GEMM input
                 const int b = row0 / ls, s0 = row0 % ls;
                 const uint32_t slot = issued % NSLOT;
                 const uint32_t ph = (issued / NSLOT) & 1u;
@@ -532,7 +542,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
               const uint32_t done = issued > LAG ? issued - LAG : 0u;
               while ((sig_d < d || (sig_d == d && sig_mt <= mt)) && sig_end <= done) {
                 publish(sig_d, sig_mt);
-                if (++sig_mt == m_tiles_seg) { sig_mt = 0; ++sig_d; }
+                if (++sig_mt == units) { sig_mt = 0; ++sig_d; }
                 sig_end += step_chunks(sig_mt);
               }
             }
@@ -540,7 +550,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           ptx::bulk_wait<0>();
           while (sig_d < p.world) {
             publish(sig_d, sig_mt);
-            if (++sig_mt == m_tiles_seg) { sig_mt = 0; ++sig_d; }
+            if (++sig_mt == units) { sig_mt = 0; ++sig_d; }
           }
           (void)groups_per_tile;
         }
@@ -636,6 +646,17 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       ++nstore;
     };
 
+    // the tile row's slab has fully landed at the owner: the last of the warps that store into
+    // it tells the owner
+    auto rs_arrive = [&](int seg, int mt) {
+      ptx::fence_proxy_async_all();
+      uint32_t* cnt = p.local_cnt + seg * m_tiles_seg + mt;
+      if (ptx::atom_add_acq_rel_sys(cnt, 1u) == static_cast<uint32_t>(n_tiles) * Cfg::EPI_WARPS * CG - 1u) {
+        *cnt = 0;
+        ptx::st_release_sys(p.rs_ctr[seg] + mt * kMaxRanks + p.rank, p.epoch);
+      }
+    };
+    int pend_seg = -1, pend_mt = 0;
     for (int t = tile_slot; t < total_tiles; t += tile_stride, ++it) {
       const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
       const int m_cta = c.m_in_seg + static_cast<int>(cta_rank) * Cfg::BM_CTA;
@@ -672,7 +693,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           } else {
             sa_rows = p.sa_land;
             // the scales travelled with the shard: make this thread's reads follow the flag
-            const uint32_t* f = p.ag_flags[p.rank] + c.seg * m_tiles_seg + c.m_tile;
+            const uint32_t* f = p.ag_flags[p.rank] + c.seg * ((p.seg_rows + p.flag_unit_rows - 1) / p.flag_unit_rows) +
+                                c.m_in_seg / p.flag_unit_rows;
             if (lane == 0) flag_wait_ge(wc, f, p.epoch, kSiteShardFlag);
             __syncwarp();
           }
@@ -746,22 +768,21 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         }
       }
       if (p.mode == kModeReduceScatter && multi) {
-        // the tile's slab rows have fully landed at the owner -> count this warp's arrival
+        // Arrival counting runs one tile behind: waiting for this tile's stores to land would
+        // stall the warp for an NVLink round trip, so wait only for the previous tile's (all but
+        // the store groups committed for this tile) and count that one.
         if (lane == 0) {
-          ptx::bulk_wait<0>();
-          ptx::fence_proxy_async_all();
-          // the last of the warps that store into this tile row tells the owner
-          uint32_t* cnt = p.local_cnt + c.seg * m_tiles_seg + c.m_tile;
-          if (ptx::atom_add_acq_rel_sys(cnt, 1u) ==
-              static_cast<uint32_t>(n_tiles) * Cfg::EPI_WARPS * CG - 1u) {
-            *cnt = 0;
-            ptx::st_release_sys(p.rs_ctr[c.seg] + c.m_tile * kMaxRanks + p.rank, p.epoch);
-          }
+          constexpr int kGroupsPerTile = Cfg::BS ? 1 : BN / 64;
+          ptx::bulk_wait<kGroupsPerTile>();
+          if (pend_seg >= 0) rs_arrive(pend_seg, pend_mt);
         }
+        pend_seg = c.seg;
+        pend_mt = c.m_tile;
         __syncwarp();
       }
     }
     if (lane == 0) ptx::bulk_wait<0>();
+    if (p.mode == kModeReduceScatter && multi && lane == 0 && pend_seg >= 0) rs_arrive(pend_seg, pend_mt);
     __syncwarp();
     if (p.mode == kModeGemmA2A && multi) {
       // all stores of this warp have landed; the last warp of the whole grid tells every rank,

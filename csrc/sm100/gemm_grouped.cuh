@@ -24,7 +24,7 @@ struct SubProblem {
 };
 
 struct GroupedParams {
-  CUtensorMap tm_a;            // contiguous A [rows, K], box {BK, 128} (unused when gathered)
+  CUtensorMap tm_a;            // contiguous A [rows, K], box {BK, 128}; gather4: tokens [T, K], box {BK, 1}
   CUtensorMap tm_b;            // weights [E_local][N][K], box {BK, BN, 1}
   const SubProblem* sp;        // [S]
   const int32_t* tile_begin;   // [S + 1] prefix sums of (row tiles x column tiles)
@@ -34,6 +34,8 @@ struct GroupedParams {
   int32_t gathered;            // 1: A rows are tokens picked by gather_index
   int32_t tokens_per_rank;
   const void* a_tokens;        // [W * tokens_per_rank, K] all-gathered tokens (landing buffer)
+  void* a_sorted;              // pre-gather mode: [rows of this rank, K] expert-sorted copy of the rows
+  int32_t E_local, by_src;     // schedule shape: S = E_local * (by_src ? world : 1)
   const int32_t* gather_index; // [total sorted rows] token of each sorted row
   void* d;                     // [rows_out, N], 16-bit
   int64_t ldd;
@@ -53,17 +55,24 @@ struct GroupedParams {
   uint32_t* local_cnt;             // [W]
 };
 
-template <int BN_, int KIND_, int STAGES_, bool GATHER_>
+// GATHER_: 0 = contiguous A by TMA; 1 = gathered A rows by cp.async from four producer warps;
+// 2 = gathered A rows by TMA tile::gather4 (four indexed rows per instruction) from the producer lane;
+// 3 = the communication warps copy the gathered rows, whole rows at a time, into an expert-sorted
+//     buffer as soon as their source shard has landed, and the GEMM reads that buffer by TMA.
+template <int BN_, int KIND_, int STAGES_, int GATHER_>
 struct GroupedCfg {
   static constexpr int BM = 128, BN = BN_, KIND = KIND_, STAGES = STAGES_;
-  static constexpr bool GATHER = GATHER_;
+  static constexpr bool GATHER = GATHER_ == 1;     // cp.async producers
+  static constexpr bool GATHER4 = GATHER_ == 2;    // TMA gather4
+  static constexpr bool PREGATHER = GATHER_ == 3;  // rows copied into a sorted buffer by the comm warps
+  static constexpr bool ANY_GATHER = GATHER_ != 0;
   static constexpr int ELT = KIND_ == 0 ? 2 : 1;
   static constexpr int BK = 128 / ELT;
   static constexpr int UMMA_K = 32 / ELT;
   static constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128, STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int COMM_BYTES = GATHER_ ? 32768 : 0;
-  static constexpr int BAR_BYTES = 256;
-  static constexpr int THREADS = GATHER_ ? 384 : 256;
+  static constexpr int COMM_BYTES = GATHER_ != 0 ? 32768 : 0;
+  static constexpr int BAR_BYTES = 256 + 1024;     // barriers, then two 128-entry row-index buffers
+  static constexpr int THREADS = GATHER_ == 1 ? 384 : 256;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + COMM_BYTES + BAR_BYTES + 1024;
   static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared memory limit");
 };
@@ -144,18 +153,53 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
   const int row_base = p.hdr[0];
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer (B, and A if contiguous)
-    if (lane == 0) {
-      int stage = 0, cursor = 0, seen_src = -1;
-      uint32_t phase = 0;
-      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-        const GroupedTile g = grouped_decode(p, t, cursor, n_tiles, BM, BN);
-        (void)seen_src;
+    // ------------------------------------------------------------------ TMA producer (B, and A unless cp.async gathers it)
+    int stage = 0, cursor = 0, ready_src = -1, nt = 0;
+    uint32_t phase = 0;
+    int32_t* idx_buf = reinterpret_cast<int32_t*>(bar_ptr + 256);
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
+      const GroupedTile g = grouped_decode(p, t, cursor, n_tiles, BM, BN);
+      int32_t* idx = idx_buf + (nt & 1) * 128;
+      if constexpr (Cfg::GATHER4) {
+        if (g.src >= 0 && g.src != ready_src) {
+          // tokens of this source must have landed (sub-problems are ordered by source, own first)
+          if (lane == 0) {
+            flag_wait_ge(wc, p.ag_flags[p.rank] + g.src, p.epoch, kSiteMoeFlag);
+            ptx::fence_proxy_async_all();
+          }
+          ready_src = g.src;
+        }
+        // the 128 token ids of this tile (rows past the end of the sub-problem read token 0; their
+        // results are never stored)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = lane * 4 + j;
+          idx[r] = r < g.rows ? p.gather_index[g.row0 + r] : 0;
+        }
+        __syncwarp();
+      }
+      if constexpr (Cfg::PREGATHER) {
+        const int step = g.sp / p.E_local;       // source step (0 when the schedule is not by source)
+        if (step != ready_src) {
+          if (lane == 0) {
+            flag_wait_ge(wc, p.local_cnt + 32 + step, p.epoch, kSiteMoeFlag);
+            ptx::fence_proxy_async_all();
+          }
+          ready_src = step;
+        }
+      }
+      if (lane == 0) {
         for (int kb = 0; kb < k_blocks; ++kb) {
           mbar_wait(wc, empty_bar(stage), phase ^ 1u, kSiteSmemEmpty);
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
           if constexpr (Cfg::GATHER) {
             ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::B_BYTES);
+          } else if constexpr (Cfg::GATHER4) {
+            ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+#pragma unroll 4
+            for (int i = 0; i < 32; ++i)
+              ptx::tma_gather4_2d(sa + i * 512, &p.tm_a, full_bar(stage), kb * BK, idx[4 * i], idx[4 * i + 1],
+                                  idx[4 * i + 2], idx[4 * i + 3]);
           } else {
             ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
             ptx::tma_load_2d(sa, &p.tm_a, full_bar(stage), kb * BK, g.row0 - row_base);
@@ -167,6 +211,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
           }
         }
       }
+      __syncwarp();
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -201,51 +246,87 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
     }
   } else if (warp == 2 || warp == 3) {
     // ------------------------------------------------------------------ all-gather push of the token shard
-    if constexpr (Cfg::GATHER) {
+    if constexpr (Cfg::ANY_GATHER) {
       if (multi && warp == 3 && blockIdx.x == 0 && lane < p.world)
         ptx::st_release_sys(p.start_ctr[lane] + p.rank, p.epoch);
-      if (p.do_allgather) {
-        if (multi) {
-          if (lane < p.world) flag_wait_ge(wc, p.start_ctr[p.rank] + lane, p.epoch, kSiteStartBarrier);
-          __syncwarp();
-        }
-        if (lane == 0) {
-          constexpr int NSLOT = 4;
-          constexpr uint32_t CH = Cfg::COMM_BYTES / 2 / NSLOT;
-          const uint32_t ring = comm_base + (warp - 2) * (Cfg::COMM_BYTES / 2);
-          const uint32_t rbar = ring_bar_base + (warp - 2) * NSLOT * 8u;
-          const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ag_src);
-          const int64_t bytes = static_cast<int64_t>(p.tokens_per_rank) * p.K * Cfg::ELT;
-          const int64_t slab_off = static_cast<int64_t>(p.rank) * bytes;
-          const uint32_t cw = blockIdx.x * 2 + (warp - 2), ncw = gridDim.x * 2;
-          const uint32_t nch = static_cast<uint32_t>((bytes + CH - 1) / CH);
-          uint32_t issued = 0;
-          // own landing slot first (the gather reads every token from the landing buffer), then
-          // the peer that consumes this shard first: rank-1, rank-2, ...
-          for (int d = 0; d < p.world; ++d) {
+      if (multi) {
+        if (lane < p.world) flag_wait_ge(wc, p.start_ctr[p.rank] + lane, p.epoch, kSiteStartBarrier);
+        __syncwarp();
+      }
+      if (lane == 0 && (p.do_allgather || Cfg::PREGATHER)) {
+        // One lane per warp drives a ring of staging slots (bulk load -> bulk store). Per step d:
+        // push this rank's shard to peer rank-d (d = 0: the own landing slot), then - in pre-gather
+        // mode - copy the rows that come from source rank+d, which arrives during the same step
+        // because every rank walks the same rotation, into the expert-sorted buffer.
+        const uint32_t ring = comm_base + (warp - 2) * (Cfg::COMM_BYTES / 2);
+        const uint32_t rbar = ring_bar_base + (warp - 2) * 4 * 8u;
+        const uint32_t cw = blockIdx.x * 2 + (warp - 2), ncw = gridDim.x * 2;
+        const int64_t row_bytes = static_cast<int64_t>(p.K) * Cfg::ELT;
+        uint32_t used[4] = {0u, 0u, 0u, 0u};   // loads seen by each ring barrier (their phase)
+        auto move = [&](const uint8_t* from, uint8_t* to, uint32_t sz, uint32_t slot_off, uint32_t bar_id) {
+          const uint32_t ph = used[bar_id] & 1u;
+          ++used[bar_id];
+          ptx::mbar_arrive_expect_tx(rbar + 8u * bar_id, sz);
+          ptx::bulk_load(ring + slot_off, from, sz, rbar + 8u * bar_id);
+          mbar_wait(wc, rbar + 8u * bar_id, ph, kSiteSmemFull);
+          ptx::bulk_store(to, ring + slot_off, sz);
+          ptx::bulk_commit();
+        };
+        const int steps = p.do_allgather ? p.world : 1;
+        uint32_t n_push = 0, n_gath = 0;
+        for (int d = 0; d < steps; ++d) {
+          if (p.do_allgather) {
+            constexpr uint32_t CH = Cfg::COMM_BYTES / 2 / 4;   // 4 slots of 4 KiB
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ag_src);
+            const int64_t bytes = static_cast<int64_t>(p.tokens_per_rank) * row_bytes;
+            const uint32_t nch = static_cast<uint32_t>((bytes + CH - 1) / CH);
             int peer = p.rank - d;
             if (peer < 0) peer += p.world;
-            uint8_t* land = reinterpret_cast<uint8_t*>(p.ag_land[peer]) + slab_off;
-            for (uint32_t c = cw; c < nch; c += ncw) {
+            uint8_t* land = reinterpret_cast<uint8_t*>(p.ag_land[peer]) + static_cast<int64_t>(p.rank) * bytes;
+            for (uint32_t c = cw; c < nch; c += ncw, ++n_push) {
               const int64_t off = static_cast<int64_t>(c) * CH;
               const int64_t left = bytes - off;
               const uint32_t sz = left < static_cast<int64_t>(CH) ? static_cast<uint32_t>(left) : CH;
-              const uint32_t slot = issued % NSLOT, ph = (issued / NSLOT) & 1u;
-              ptx::bulk_wait_read<NSLOT - 1>();
-              ptx::mbar_arrive_expect_tx(rbar + 8u * slot, sz);
-              ptx::bulk_load(ring + slot * CH, src + off, sz, rbar + 8u * slot);
-              mbar_wait(wc, rbar + 8u * slot, ph, kSiteSmemFull);
-              ptx::bulk_store(land + off, ring + slot * CH, sz);
-              ptx::bulk_commit();
-              ++issued;
+              ptx::bulk_wait_read<3>();
+              move(src + off, land + off, sz, (n_push % 4) * CH, n_push % 4);
             }
-            // shard d is fully issued by this warp: wait for its stores, then count the arrival
             ptx::bulk_wait<0>();
             ptx::fence_proxy_async_all();
             uint32_t* cnt = p.local_cnt + d;
             if (ptx::atom_add_acq_rel_sys(cnt, 1u) == ncw - 1u) {
               *cnt = 0;
               ptx::st_release_sys(p.ag_flags[peer] + p.rank, p.epoch);
+            }
+          }
+          if constexpr (Cfg::PREGATHER) {
+            constexpr uint32_t SLOT = Cfg::COMM_BYTES / 2 / 2;  // 2 slots of 8 KiB (over ring slots {0,1}, {2,3})
+            const uint8_t* tokens = reinterpret_cast<const uint8_t*>(p.a_tokens);
+            uint8_t* sorted = reinterpret_cast<uint8_t*>(p.a_sorted);
+            if (p.by_src) {
+              int src = p.rank + d;
+              if (src >= p.world) src -= p.world;
+              flag_wait_ge(wc, p.ag_flags[p.rank] + src, p.epoch, kSiteMoeFlag);
+              ptx::fence_proxy_async_all();
+            }
+            for (int el = 0; el < p.E_local; ++el) {
+              const SubProblem sp = p.sp[d * p.E_local + el];
+              for (int r = sp.row_begin + static_cast<int>(cw); r < sp.row_end; r += static_cast<int>(ncw)) {
+                const uint8_t* from = tokens + static_cast<int64_t>(p.gather_index[r]) * row_bytes;
+                uint8_t* to = sorted + static_cast<int64_t>(r - row_base) * row_bytes;
+                for (int64_t off = 0; off < row_bytes; off += SLOT, ++n_gath) {
+                  const int64_t left = row_bytes - off;
+                  const uint32_t sz = left < static_cast<int64_t>(SLOT) ? static_cast<uint32_t>(left) : SLOT;
+                  ptx::bulk_wait_read<1>();
+                  move(from + off, to + off, sz, (n_gath % 2) * SLOT, (n_gath % 2) * 2);
+                }
+              }
+            }
+            ptx::bulk_wait<0>();
+            ptx::fence_proxy_async_all();
+            uint32_t* cnt = p.local_cnt + 16 + d;
+            if (ptx::atom_add_acq_rel_sys(cnt, 1u) == ncw - 1u) {
+              *cnt = 0;
+              ptx::st_release_sys(p.local_cnt + 32 + d, p.epoch);
             }
           }
         }

@@ -175,6 +175,16 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t smem
       "r"(smem_src), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
+// Four rows of a 2-D tensor picked by index (y0..y3), `box` columns starting at x, written as four
+// consecutive rows at smem_dst. The tensor map's box is {columns, 1}.
+__device__ __forceinline__ void tma_gather4_2d(uint32_t smem_dst, const CUtensorMap* m, uint32_t bar,
+                                               int32_t x, int32_t y0, int32_t y1, int32_t y2, int32_t y3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(smem_dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3)
+      : "memory");
+}
 // 2-D tiled store shared -> global (local or peer memory), bulk-group completion.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t smem_src, int32_t x,
                                              int32_t y) {

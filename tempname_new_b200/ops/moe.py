@@ -43,7 +43,8 @@ class MoeGemmArgs(ctypes.Structure):
         ("tokens_per_rank", ctypes.c_int32), ("gathered", ctypes.c_int32), ("do_allgather", ctypes.c_int32),
         ("in_dtype", ctypes.c_int32),
         ("N", ctypes.c_int32), ("K", ctypes.c_int32),
-        ("a", _VP), ("a_rows", ctypes.c_int64), ("a_tokens", _VP), ("weights", _VP),
+        ("a", _VP), ("a_rows", ctypes.c_int64), ("a_tokens", _VP), ("a_sorted", _VP),
+        ("a_sorted_rows", ctypes.c_int64), ("weights", _VP),
         ("d", _VP), ("ldd", ctypes.c_int64),
         ("expert_scale", _VP), ("scalar_scale", _VP), ("row_scale", _VP), ("scratch", _VP),
         ("rank", ctypes.c_int32), ("world", ctypes.c_int32),
@@ -152,6 +153,7 @@ class GemmGroupedV3AGScatter(FusedOpBase):
             if self.world > 1 else None
         self._scratch = None
         self._gather = None
+        self._sorted = None
 
     def clear_buffers(self) -> None:
         """Kept for API compatibility: flags carry the call number, nothing needs clearing."""
@@ -211,13 +213,19 @@ class GemmGroupedV3AGScatter(FusedOpBase):
             a.rank, a.world = self.rank, self.world
             a.timeout_ns, a.status = int(self.timeout_s * 1e9), self.status.data_ptr()
             a.stream = _dense.current_stream_ptr(dev)
+            # expert-sorted copy of this rank's rows, filled by the kernel's communication warps
+            rows_cap = out.shape[0]
+            if self._sorted is None or self._sorted.shape[0] < rows_cap or self._sorted.shape[1] != H:
+                self._sorted = torch.empty((max(rows_cap, 128), H), dtype=x.dtype, device=dev)
+            a.a_sorted, a.a_sorted_rows = self._sorted.data_ptr(), self._sorted.shape[0]
+            a.local_cnt = self.ctrl.ptr(self.rank, OFF_LOCAL)
+            self.epoch += 1
+            a.epoch = self.epoch
             if self.world > 1:
                 a.a_tokens = self.land.ptr(self.rank)
                 if g == 0:
-                    self.epoch += 1
-                    a.do_allgather, a.epoch = 1, self.epoch
+                    a.do_allgather = 1
                     a.ag_src = x.data_ptr()
-                    a.local_cnt = self.ctrl.ptr(self.rank, OFF_LOCAL)
                     for r in range(self.world):
                         a.ag_land[r] = self.land.ptr(r)
                         a.ag_flags[r] = self.ctrl.ptr(r, OFF_CTR)

@@ -83,6 +83,55 @@ def cmd_quant(a):
                       "gbs": gbs, "frac_of_hbm_peak": gbs / pk, "peak": src}))
 
 
+def cmd_blockscale(a):
+    import tempname_new_b200 as flux
+    dev = torch.device("cuda")
+    x = torch.randn(a.m, a.k, device=dev).bfloat16()
+    w = (torch.randn(a.n, a.k, device=dev) * 0.05).bfloat16()
+    qz = flux.Quantization(torch.bfloat16, torch.float8_e4m3fn)
+    xq, sx, _, _ = qz.quantize_vector_blockwise(x, False)
+    wq, sw, _, _ = qz.quantize_square_blockwise(w, False)
+    op = flux.BlockScaleGemm()
+    out = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+    ms = timed(lambda: op.forward(xq, wq, output=out, input_scale=sx, weight_scale=sw), a.iters, a.warmup,
+               not a.no_flush)
+    tf = 2.0 * a.m * a.n * a.k / ms / 1e9
+    pk, _, src = peaks()
+    print(json.dumps({"op": "blockscale_gemm", "m": a.m, "n": a.n, "k": a.k, "ms": ms, "tflops": tf,
+                      "frac_of_bf16_peak": tf / pk, "peak": src}))
+
+
+def cmd_grouped(a):
+    """Per-expert GEMM over `rows` expert-sorted rows, contiguous or gathered from a token matrix."""
+    import os
+    import torch.distributed as dist
+    import tempname_new_b200 as flux
+    dev = torch.device("cuda", torch.cuda.current_device())
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29561")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    E, topk = a.experts, a.topk
+    tokens = a.rows // topk
+    g = flux.testing.gen_moe_gating_args(E, topk, tokens, device=dev, seed=1)
+    w = (torch.randn(E, a.n, a.k, device=dev) * 0.02).bfloat16()
+    out = torch.empty(a.rows, a.n, device=dev, dtype=torch.bfloat16)
+    if a.gathered:
+        x = torch.randn(tokens, a.k, device=dev).bfloat16()
+        env = flux.DistEnvTPWithEP(dist.group.WORLD, 1, None, ep_size=1)
+        op = flux.GemmGroupedV3AGScatter(env, flux.MoeArguments(tokens, a.k, a.n, E, topk, torch.bfloat16))
+        fn = lambda: op.forward(x, w, g.splits_gpu, g.scatter_index, outputs_buf=out)  # noqa: E731
+    else:
+        x = torch.randn(a.rows, a.k, device=dev).bfloat16()
+        op = flux.GemmGroupedV3(w, E)
+        fn = lambda: op.forward(x, g.splits_gpu)  # noqa: E731
+    ms = timed(fn, a.iters, a.warmup, not a.no_flush)
+    tf = 2.0 * a.rows * a.n * a.k / ms / 1e9
+    pk, _, src = peaks()
+    print(json.dumps({"op": "grouped_gemm", "gathered": bool(a.gathered), "rows": a.rows, "n": a.n, "k": a.k,
+                      "experts": E, "ms": ms, "tflops": tf, "frac_of_bf16_peak": tf / pk, "peak": src}))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -102,7 +151,20 @@ def main(argv=None):
     q.add_argument("--kind", default="1x128", choices=["1x128", "128x128"])
     q.add_argument("--transpose", action="store_true")
     q.set_defaults(fn=cmd_quant)
-    for p in (g, q):
+    b = sub.add_parser("blockscale")
+    b.add_argument("--m", type=int, default=8192)
+    b.add_argument("--n", type=int, default=8192)
+    b.add_argument("--k", type=int, default=8192)
+    b.set_defaults(fn=cmd_blockscale)
+    gg = sub.add_parser("grouped")
+    gg.add_argument("--rows", type=int, default=65536)
+    gg.add_argument("--n", type=int, default=3072)
+    gg.add_argument("--k", type=int, default=4096)
+    gg.add_argument("--experts", type=int, default=8)
+    gg.add_argument("--topk", type=int, default=8)
+    gg.add_argument("--gathered", action="store_true")
+    gg.set_defaults(fn=cmd_grouped)
+    for p in (g, q, b, gg):
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--no-flush", action="store_true")
