@@ -111,7 +111,7 @@ struct DenseCfg {
   static constexpr bool BS = BS_;
   static constexpr int EPI_WARPS = BS_ ? 8 : 4;
   static constexpr int THREADS = 128 + 32 * EPI_WARPS;
-  static constexpr int ACC_BUFS = BS_ ? 4 : 2;
+  static constexpr int ACC_BUFS = BS_ ? 3 : 2;   // block-scaled: 3 k-block buffers + 1 exchange region
   static_assert(!BS_ || (KIND_ == 1 && BN_ == 128 && CG_ == 1), "block-scaled variant: fp8, 128x128 tiles");
   static constexpr int CG = CG_;
   static constexpr int BM_CTA = 128;                       // rows of A / D per CTA
@@ -132,7 +132,7 @@ struct DenseCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + COMM_BYTES + BAR_BYTES + 1024;
   static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared memory limit");
   static constexpr int TMEM_COLS = 512;
-  static_assert(ACC_BUFS * BN <= TMEM_COLS, "accumulators must fit TMEM");
+  static_assert((ACC_BUFS + (BS_ ? 1 : 0)) * BN <= TMEM_COLS, "accumulators must fit TMEM");
 };
 
 struct TileCoord {
@@ -191,7 +191,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
   volatile uint32_t* abort_word = tmem_slot + 1;
   volatile uint32_t* claim_slot = tmem_slot + 2;
   const uint32_t ring_bar_base = bar_base + 8u * (2 * STAGES + 2 * NACC) + 16u;
-  static_assert(8 * (2 * STAGES + 2 * NACC) + 16 + 64 <= Cfg::BAR_BYTES, "barrier block too small");
+  const uint32_t xfull_bar = ring_bar_base + 64u, xempty_bar = ring_bar_base + 72u;  // block-scaled exchange
+  static_assert(8 * (2 * STAGES + 2 * NACC) + 16 + 64 + 16 <= Cfg::BAR_BYTES, "barrier block too small");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -210,8 +211,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     }
     for (int a = 0; a < NACC; ++a) {
       ptx::mbar_init(tfull_bar(a), 1);
-      ptx::mbar_init(tempty_bar(a), Cfg::EPI_WARPS * CG);
+      ptx::mbar_init(tempty_bar(a), 4 * CG);   // one epilogue warp per TMEM lane quadrant reads a buffer
     }
+    ptx::mbar_init(xfull_bar, 4);
+    ptx::mbar_init(xempty_bar, 4);
     for (int i = 0; i < 8; ++i) ptx::mbar_init(ring_bar_base + 8u * i, 1);
     *abort_word = 0;
     ptx::fence_mbar_init();
@@ -235,6 +238,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
   const int k_blocks = (p.K + BK - 1) / BK;
   const bool multi = p.world > 1 && p.mode != kModePlain;
 
+  if (warp < 4) {
+  // (block-scaled variant) producer, issuer and communication warps give registers to the
+  // promotion warps; all four warps of the group execute the same instruction here
+  if constexpr (Cfg::BS) ptx::setmaxnreg_dec<88>();
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -556,7 +563,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         }
       }
     }
+  }
   } else {
+    if constexpr (Cfg::BS) ptx::setmaxnreg_inc<208>();  // 128 fp32 accumulators per thread
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;              // TMEM lane quadrant this warp may read
     const int ew = warp - 4;             // epilogue warp index
@@ -651,12 +660,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     auto rs_arrive = [&](int seg, int mt) {
       ptx::fence_proxy_async_all();
       uint32_t* cnt = p.local_cnt + seg * m_tiles_seg + mt;
-      if (ptx::atom_add_acq_rel_sys(cnt, 1u) == static_cast<uint32_t>(n_tiles) * Cfg::EPI_WARPS * CG - 1u) {
+      if (ptx::atom_add_acq_rel_sys(cnt, 1u) == static_cast<uint32_t>(n_tiles) * 4u * CG - 1u) {
         *cnt = 0;
         ptx::st_release_sys(p.rs_ctr[seg] + mt * kMaxRanks + p.rank, p.epoch);
       }
     };
     int pend_seg = -1, pend_mt = 0;
+    uint64_t bs_acc[Cfg::BS ? 64 : 1];
     for (int t = tile_slot; t < total_tiles; t += tile_stride, ++it) {
       const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
       const int m_cta = c.m_in_seg + static_cast<int>(cta_rank) * Cfg::BM_CTA;
@@ -682,8 +692,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
 
       if constexpr (Cfg::BS) {
         // ---- block-scaled: promote every k-block's partial product into fp32 registers.
-        // This warp owns 64 of the tile's 128 columns (warps 4..7: 0..63, warps 8..11: 64..127).
-        const int half = ew >> 2;
+        // The eight epilogue warps form two sets (warps 4..7 and 8..11, one warp per TMEM lane
+        // quadrant each). The sets take alternate k-blocks, each over all 128 columns, so that
+        // one set's TMEM read latency hides behind the other's FMAs. At the end of a tile the
+        // sets' partial sums are added through a spare 128-column TMEM region; the sets take
+        // turns (by tile parity) at being the one that adds, converts and stores.
+        const int set = ew >> 2;
         const int kbs = k_blocks;                               // scale blocks along K (BK == 128)
         const float* sa_rows = p.sa;
         int64_t srow = grow;                                    // row in the scale tensor's frame
@@ -701,45 +715,92 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         }
         const float* sa_ptr = sa_rows + (srow >> 7) * static_cast<int64_t>(kbs) * 128 + (srow & 127);
         const float* sb_ptr = p.sb + static_cast<int64_t>(c.n0 >> 7) * kbs;
-        uint64_t acc2[32];
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc2[j] = 0ull;
-        float s_next = sa_ptr[0] * sb_ptr[0];
-        for (int kb = 0; kb < kbs; ++kb) {
-          const float sc = s_next;
-          if (kb + 1 < kbs) s_next = sa_ptr[static_cast<int64_t>(kb + 1) * 128] * sb_ptr[kb + 1];
-          const uint32_t n = static_cast<uint32_t>(it) * kbs + kb;
+        for (int j = 0; j < 64; ++j) bs_acc[j] = 0ull;
+        const uint32_t n0 = static_cast<uint32_t>(it) * kbs;
+        for (int kb = ((n0 & 1u) == static_cast<uint32_t>(set)) ? 0 : 1; kb < kbs; kb += 2) {
+          const uint32_t n = n0 + kb;
           const int buf = n % NACC;
           const uint32_t par = (n / NACC) & 1u;
+          const float sc = sa_ptr[static_cast<int64_t>(kb) * 128] * sb_ptr[kb];
+          const uint64_t sc2 = ptx::pack_f32x2(sc, sc);
           if (lane == 0) mbar_wait(wc, tfull_bar(buf), par, kSiteTmemFull);
           __syncwarp();
           mbar_wait(wc, tfull_bar(buf), par, kSiteTmemFull);
           ptx::tc_fence_after();
-          uint32_t r0[32], r1[32];
-          const uint32_t taddr =
-              tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + half * 64;
-          ptx::tmem_ld_32x32b_x32(taddr, r0);
-          ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
-          ptx::tmem_ld_wait();
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
-          const uint64_t sc2 = ptx::pack_f32x2(sc, sc);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            acc2[j] = ptx::ffma2(ptx::pack_b32x2(r0[2 * j], r0[2 * j + 1]), sc2, acc2[j]);
-            acc2[16 + j] = ptx::ffma2(ptx::pack_b32x2(r1[2 * j], r1[2 * j + 1]), sc2, acc2[16 + j]);
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r0[32], r1[32];
+            const uint32_t taddr = lane_base + buf * BN + h * 64;
+            ptx::tmem_ld_32x32b_x32(taddr, r0);
+            ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
+            ptx::tmem_ld_wait();
+            if (h == 1) {
+              ptx::tc_fence_before();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              bs_acc[h * 32 + j] = ptx::ffma2(ptx::pack_b32x2(r0[2 * j], r0[2 * j + 1]), sc2, bs_acc[h * 32 + j]);
+              bs_acc[h * 32 + 16 + j] =
+                  ptx::ffma2(ptx::pack_b32x2(r1[2 * j], r1[2 * j + 1]), sc2, bs_acc[h * 32 + 16 + j]);
+            }
           }
         }
-        uint32_t o0[32], o1[32];
+        // ---- add the two sets' partial sums through the spare TMEM columns
+        const uint32_t xaddr = lane_base + NACC * BN;
+        const bool emitter = (it & 1) == set;
+        if (!emitter) {
+          if (lane == 0) mbar_wait(wc, xempty_bar, ((it & 1) ^ 1u), kSiteTmemEmpty);
+          __syncwarp();
+          mbar_wait(wc, xempty_bar, ((it & 1) ^ 1u), kSiteTmemEmpty);
+          ptx::tc_fence_after();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          o0[2 * j] = static_cast<uint32_t>(acc2[j]);
-          o0[2 * j + 1] = static_cast<uint32_t>(acc2[j] >> 32);
-          o1[2 * j] = static_cast<uint32_t>(acc2[16 + j]);
-          o1[2 * j + 1] = static_cast<uint32_t>(acc2[16 + j] >> 32);
+          for (int g = 0; g < 4; ++g) {
+            uint32_t r[32];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              r[2 * j] = static_cast<uint32_t>(bs_acc[g * 16 + j]);
+              r[2 * j + 1] = static_cast<uint32_t>(bs_acc[g * 16 + j] >> 32);
+            }
+            ptx::tmem_st_32x32b_x32(xaddr + g * 32, r);
+          }
+          ptx::tmem_st_wait();
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(xfull_bar);
+        } else {
+          if (lane == 0) mbar_wait(wc, xfull_bar, (it & 1), kSiteTmemFull);
+          __syncwarp();
+          mbar_wait(wc, xfull_bar, (it & 1), kSiteTmemFull);
+          ptx::tc_fence_after();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r0[32], r1[32];
+            ptx::tmem_ld_32x32b_x32(xaddr + h * 64, r0);
+            ptx::tmem_ld_32x32b_x32(xaddr + h * 64 + 32, r1);
+            ptx::tmem_ld_wait();
+            if (h == 1) {
+              ptx::tc_fence_before();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive(xempty_bar);
+            }
+            const uint64_t one2 = ptx::pack_f32x2(1.f, 1.f);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const uint64_t a0 = ptx::ffma2(ptx::pack_b32x2(r0[2 * j], r0[2 * j + 1]), one2, bs_acc[h * 32 + j]);
+              const uint64_t a1 =
+                  ptx::ffma2(ptx::pack_b32x2(r1[2 * j], r1[2 * j + 1]), one2, bs_acc[h * 32 + 16 + j]);
+              r0[2 * j] = static_cast<uint32_t>(a0);
+              r0[2 * j + 1] = static_cast<uint32_t>(a0 >> 32);
+              r1[2 * j] = static_cast<uint32_t>(a1);
+              r1[2 * j + 1] = static_cast<uint32_t>(a1 >> 32);
+            }
+            emit_chunk(r0, r1, c.n0 + h * 64, row, grow, m_cta + q * 32, tmd, z);
+          }
         }
-        emit_chunk(o0, o1, c.n0 + half * 64, row, grow, m_cta + q * 32, tmd, z);
       } else {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
@@ -771,13 +832,17 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         // Arrival counting runs one tile behind: waiting for this tile's stores to land would
         // stall the warp for an NVLink round trip, so wait only for the previous tile's (all but
         // the store groups committed for this tile) and count that one.
-        if (lane == 0) {
-          constexpr int kGroupsPerTile = Cfg::BS ? 1 : BN / 64;
-          ptx::bulk_wait<kGroupsPerTile>();
-          if (pend_seg >= 0) rs_arrive(pend_seg, pend_mt);
+        // (block-scaled variant: only the set that stored this tile takes part)
+        const bool stored = !Cfg::BS || ((it & 1) == (ew >> 2));
+        if (stored) {
+          if (lane == 0) {
+            constexpr int kGroupsPerTile = Cfg::BS ? 2 : BN / 64;
+            ptx::bulk_wait<kGroupsPerTile>();
+            if (pend_seg >= 0) rs_arrive(pend_seg, pend_mt);
+          }
+          pend_seg = c.seg;
+          pend_mt = c.m_tile;
         }
-        pend_seg = c.seg;
-        pend_mt = c.m_tile;
         __syncwarp();
       }
     }
