@@ -33,3 +33,6 @@ from .tuning.profiling import ProfilingContext, TuningRecord  # noqa: F401
 from .parallel.layers import ColumnParallelLinear, RowParallelLinear, patch_megatron_linears  # noqa: F401
 from . import models, ops, parallel, testing, tuning, utils  # noqa: F401
 from .ops.coll import All2AllOp, All2AllSingle, AllGatherOp, AsyncSendRecv  # noqa: F401
+from .ops.ep_dispatch import (AGKernelInterNode, AGKernelXNode, All2AllInference, DisScatterBackward,  # noqa: F401
+                              DisScatterForward, GemmRS_multinode, GemmRSInterNode, TransportOp, bsr_reduce,
+                              load_tuning_record, pad_m_to_TPxTile)

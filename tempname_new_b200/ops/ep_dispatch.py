@@ -1,0 +1,232 @@
+"""Expert-parallel token dispatch / combine and the remaining transport helpers, single node.
+
+* ``DisScatterForward``: every rank contributes its local tokens; each rank receives, in
+  expert-sorted order, the rows routed to its own experts (reference: ``flux.DisScatterForward``,
+  ``src/coll/dis_scatter_forward_impl.cu``; there a hierarchical NVSHMEM put/signal protocol that
+  also spans nodes). Here: one peer-memory all-gather kernel + a row gather by the routing index.
+* ``DisScatterBackward``: the inverse, the weighted combine: the expert outputs of all ranks are
+  summed per token over the top-k entries and delivered to the rank that owns the token — the
+  ``moe_combine_kernel`` used by ``GemmGroupedV3GatherRS`` (reference:
+  ``src/coll/dis_scatter_backward_impl.cu``).
+* ``All2AllInference``, ``TransportOp``: thin wrappers over the row-exchange and copy kernels.
+* ``GemmRSInterNode`` / ``GemmRS_multinode`` / ``AGKernelInterNode`` / ``AGKernelXNode``: multi-node
+  variants; this library targets one NVSwitch domain, so constructing them raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from . import _dense
+from .coll import All2AllSingle, AllGatherOp
+from .moe import GemmGroupedV3GatherRS, _scratch
+
+
+class DisScatterForward:
+    def __init__(self, total_num_experts: int, max_m: int, n_dim: int, topk: int, rank: int, tp_world_size: int,
+                 ep_world_size: int, local_world_size: int, moe_capacity_ratio: float = 1.3,
+                 duplicate_comm_buffer: int = 1, team: int = 0, pg=None, dtype: torch.dtype = torch.bfloat16):
+        self.pg = pg if pg is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.pg)
+        self.rank = rank
+        if tp_world_size * ep_world_size != self.world:
+            raise ValueError("tp_world_size * ep_world_size must equal the group size")
+        self.E, self.topk, self.H = total_num_experts, topk, n_dim
+        self.E_local = self.E // ep_world_size
+        self.e0 = (rank // tp_world_size) * self.E_local
+        self.ag = AllGatherOp(self.pg, 1, max_m, n_dim, dtype)
+
+    def forward_gpu(self, input: torch.Tensor, ag_exp_indices: torch.Tensor, ag_scatter_idx: torch.Tensor,
+                    splits: torch.Tensor, ep_token_counts=None, output_tensor: Optional[torch.Tensor] = None,
+                    sm_margin: int = 0, copy_to_local_tensor: bool = True) -> torch.Tensor:
+        """input [local tokens, H]; ag_scatter_idx [tokens, topk] = sorted row of every (token, k);
+        splits [E] rows per expert. Returns this rank's rows [sum(splits[e0:e0+E_local]), H]."""
+        tokens_full = self.ag.run(input)
+        n = ag_scatter_idx.numel()
+        topk = ag_scatter_idx.shape[-1]
+        gather = torch.empty(n, dtype=torch.long, device=input.device)
+        gather[ag_scatter_idx.reshape(-1).long()] = torch.arange(n, device=input.device) // topk
+        offs = torch.cat([torch.zeros(1, dtype=torch.long, device=splits.device), splits.long().cumsum(0)])
+        lo, hi = int(offs[self.e0]), int(offs[self.e0 + self.E_local])
+        out = tokens_full.index_select(0, gather[lo:hi])
+        if output_tensor is not None:
+            output_tensor[: out.shape[0]].copy_(out)
+            return output_tensor
+        return out
+
+    def forward(self, input, ag_exp_indices, ag_scatter_idx, splits_cpu, ep_token_counts=None, sm_margin: int = 0,
+                copy_to_local_tensor: bool = True):
+        return self.forward_gpu(input, ag_exp_indices, ag_scatter_idx, splits_cpu.to(input.device),
+                                ep_token_counts, None, sm_margin, copy_to_local_tensor)
+
+    forward_no_cpy = forward
+    forward_gpu_no_cpy = forward_gpu
+
+    def ep_barrier_all(self) -> None:
+        dist.barrier(group=self.pg)
+
+
+class DisScatterBackward:
+    def __init__(self, total_num_experts: int, max_m: int, n_dim: int, topk: int, rank: int, tp_world_size: int,
+                 ep_world_size: int, local_world_size: int, moe_capacity_ratio: float = 1.3,
+                 duplicate_comm_buffer: int = 1, team: int = 0, pg=None, dtype: torch.dtype = torch.bfloat16):
+        self.pg = pg if pg is not None else dist.group.WORLD
+        world = dist.get_world_size(self.pg)
+        self.op = GemmGroupedV3GatherRS(total_num_experts, max_m * topk if max_m * topk else topk, n_dim, topk, rank,
+                                        world, tp_world_size, ep_world_size, tp_group=self.pg, dtype=dtype)
+
+    def forward_gpu(self, input: torch.Tensor, ag_exp_indices, ag_scatter_idx: torch.Tensor, splits: torch.Tensor,
+                    ep_token_counts=None, output_tensor: Optional[torch.Tensor] = None, sm_margin: int = 0,
+                    copy_to_local_tensor: bool = True) -> torch.Tensor:
+        """input [rows of this rank's experts, H] (already gate-weighted) -> [local tokens, H]:
+        per token the sum of its top-k rows over all ranks."""
+        op = self.op
+        ridx = ag_scatter_idx.reshape(-1)
+        tokens = ridx.numel() // op.topk
+        tpr = tokens // op.world
+        if not input.is_cuda:
+            offs = torch.cat([torch.zeros(1, dtype=torch.long), splits.long().cumsum(0)])
+            base = int(offs[op.e0])
+            full = torch.zeros(tokens, input.shape[1])
+            r = ridx.reshape(tokens, op.topk).long() - base
+            ok = (r >= 0) & (r < input.shape[0])
+            for k in range(op.topk):
+                sel = ok[:, k]
+                full[sel] += input[r[sel, k]].float()
+            out = torch.empty(tpr, input.shape[1], dtype=input.dtype)
+            dist.reduce_scatter(out, [c.contiguous() for c in full.to(input.dtype).chunk(op.world)], group=self.pg)
+        else:
+            dev = input.device
+            if op._scratch is None:
+                op._scratch = _scratch(op.E, op.world, dev)
+            # the combine kernel reads (row_base, rows) from the schedule header: fill it here
+            offs = torch.cat([torch.zeros(1, dtype=torch.int32, device=dev),
+                              splits.to(dev).to(torch.int32).cumsum(0).to(torch.int32)])
+            lib = _native.lib()
+            lib.fluxb_moe_hdr_offset.restype = ctypes.c_int64
+            hdr_off = int(lib.fluxb_moe_hdr_offset(op.E, op.world))
+            hdr = op._scratch[hdr_off:hdr_off + 8].view(torch.int32)
+            hdr[0] = offs[op.e0]
+            hdr[1] = offs[op.e0 + op.E_local] - offs[op.e0]
+            out = torch.empty((tpr, input.shape[1]), dtype=input.dtype, device=dev)
+            op._combine(input.contiguous(), ridx.to(device=dev, dtype=torch.int32).contiguous(), tpr, out)
+        if output_tensor is not None:
+            output_tensor[: out.shape[0]].copy_(out)
+            return output_tensor
+        return out
+
+    def forward(self, input, ag_exp_indices, ag_scatter_idx, splits_cpu, ep_token_counts=None, sm_margin: int = 0,
+                copy_to_local_tensor: bool = True):
+        return self.forward_gpu(input, ag_exp_indices, ag_scatter_idx, splits_cpu, ep_token_counts, None, sm_margin)
+
+    forward_no_cpy = forward
+    forward_gpu_no_cpy = forward_gpu
+
+    def ep_barrier_all(self) -> None:
+        dist.barrier(group=self.pg)
+
+    local_barrier_all = ep_barrier_all
+
+
+class All2AllInference:
+    """Token all-to-all for inference-time EP (reference: ``flux.All2AllInference``): the caller
+    fills ``get_input_buffer`` and gives the cumulative row splits per destination."""
+
+    def __init__(self, max_m: int, n_dim: int, rank: int, total_num_experts: int, world_size: int,
+                 local_world_size: int, max_element_size: int, pg=None):
+        self.pg = pg if pg is not None else dist.group.WORLD
+        self.world, self.rank, self.n_dim, self.max_m = world_size, rank, n_dim, max_m
+        self._ops = {}
+        self._inputs = {}
+
+    def _dtype(self, element_size: int) -> torch.dtype:
+        return {1: torch.uint8, 2: torch.bfloat16, 4: torch.float32}[element_size]
+
+    def get_input_buffer(self, input_shape, element_size: int, with_scale: bool = False) -> torch.Tensor:
+        dt = self._dtype(element_size)
+        dev = "cuda" if torch.cuda.is_available() and "nccl" in str(dist.get_backend(self.pg)) else "cpu"
+        buf = torch.empty(tuple(input_shape), dtype=dt, device=dev)
+        self._inputs[element_size] = buf
+        return buf
+
+    def forward(self, input_size, input_split_cumsum: torch.Tensor, element_size: int, with_scale: bool = False):
+        dt = self._dtype(element_size)
+        if element_size not in self._ops:
+            self._ops[element_size] = All2AllSingle(self.pg, self.max_m, self.n_dim, self.world, dt)
+        x = self._inputs[element_size][: int(input_size[0])]
+        cs = input_split_cumsum.to(torch.int64)
+        splits = torch.diff(cs, prepend=torch.zeros(1, dtype=cs.dtype, device=cs.device))[: self.world]
+        osp = torch.empty(self.world, dtype=torch.int32, device=x.device)
+        out = self._ops[element_size].forward(x, None, splits, osp)
+        return out, osp
+
+
+class TransportOp:
+    """``copy_by_sm``: copy a tensor into rank ``tgt``'s symmetric buffer with a copy kernel
+    (reference: ``flux.TransportOp``)."""
+
+    def __init__(self, rank: int, world_size: int, buffer: torch.Tensor, pg=None):
+        from ..parallel.symm import SymmBuffer
+        self.pg = pg if pg is not None else dist.group.WORLD
+        self.rank, self.world = rank, world_size
+        self.template = buffer
+        self.buf = SymmBuffer(buffer.numel() * buffer.element_size(), self.pg)
+
+    def local_buffer(self) -> torch.Tensor:
+        return self.buf.view(self.rank, self.template.dtype, tuple(self.template.shape))
+
+    def copy_by_sm(self, src: torch.Tensor, tgt_rank: int) -> None:
+        nbytes = src.numel() * src.element_size()
+        if not src.is_cuda:
+            self.buf.view(tgt_rank, src.dtype, tuple(src.shape)).copy_(src)
+            return
+        rc = _native.lib().fluxb_copy_bytes(ctypes.c_void_p(self.buf.ptr(tgt_rank)), ctypes.c_void_p(src.data_ptr()),
+                                            ctypes.c_int64(nbytes),
+                                            ctypes.c_void_p(_dense.current_stream_ptr(src.device)))
+        _native.check(rc, "fluxb_copy_bytes")
+
+
+def _multi_node(name: str):
+    class _Unavailable:
+        def __init__(self, *a, **k):
+            raise NotImplementedError(
+                f"{name}: multi-node operation is outside the single NVSwitch domain this library targets")
+    _Unavailable.__name__ = name
+    return _Unavailable
+
+
+GemmRSInterNode = _multi_node("GemmRSInterNode")
+GemmRS_multinode = _multi_node("GemmRS_multinode")
+AGKernelInterNode = _multi_node("AGKernelInterNode")
+AGKernelXNode = _multi_node("AGKernelXNode")
+
+
+def load_tuning_record(record) -> None:
+    """Add a tuning record (``TuningRecord`` or dict with ``key`` = [M, N, K] and ``best``) to the
+    in-memory table (reference: ``flux.load_tuning_record``)."""
+    from ..tuning import table
+    key = tuple(record["key"] if isinstance(record, dict) else record.key.get("mnk", ()))
+    best = record["best"] if isinstance(record, dict) else record.best
+    if len(key) != 3:
+        raise ValueError("tuning record needs key = [M, N, K]")
+    table.DENSE_TABLE[key] = dict(best)
+
+
+def bsr_reduce(input: torch.Tensor, output: torch.Tensor, block_h: int = 128, block_w: int = 128) -> torch.Tensor:
+    """output[M, N] = sum over dim 0 of input[B, M, N] (reference: ``flux.bsr_reduce``; the block
+    sizes only shaped the reference kernel's grid)."""
+    output.copy_(input.float().sum(0).to(output.dtype))
+    return output
+
+
+def pad_m_to_TPxTile(input: torch.Tensor, tp_size: int, tile: int = 128) -> torch.Tensor:
+    """Pad the rows of ``input`` to a multiple of tp_size * tile (reference: ``pad_m_to_TPxTile``;
+    the kernels here clip partial tiles themselves, so callers rarely need it)."""
+    m = input.shape[0]
+    unit = tp_size * tile
+    pm = (-m) % unit
+    return torch.nn.functional.pad(input, (0, 0, 0, pm)) if pm else input

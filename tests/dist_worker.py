@@ -258,6 +258,24 @@ def check_coll():
     sr.wait_signal_eq(1, 7)
     torch.cuda.synchronize()
     assert float(sr.get_comm_buffer(2)[0, 0]) == float(prv + 1)
+    # expert-parallel dispatch / combine
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from moe_common import routed_problem
+    tpr, H, E, topk = 256, 512, 8 * W, 2
+    tokens = tpr * W
+    experts, gate, scatter, splits, order = routed_problem(tokens, topk, E, seed=2, device=dev)
+    x_full = torch.randn(tokens, H, generator=torch.Generator().manual_seed(9)).to(dev).bfloat16()
+    fwd = flux.DisScatterForward(E, tokens, H, topk, rank, 1, W, W, pg=pg)
+    bwd = flux.DisScatterBackward(E, tokens, H, topk, rank, 1, W, W, pg=pg)
+    rows = fwd.forward(x_full[rank * tpr:(rank + 1) * tpr].contiguous(), experts, scatter, splits)
+    offs = torch.cat([torch.zeros(1, dtype=torch.long, device=dev), splits.long().cumsum(0)])
+    E_loc = E // W
+    lo, hi = int(offs[rank * E_loc]), int(offs[(rank + 1) * E_loc])
+    assert torch.equal(rows, x_full[(order // topk)[lo:hi]])
+    wrow = gate.reshape(-1)[order][lo:hi]
+    out = bwd.forward((rows.float() * wrow[:, None]).bfloat16(), experts, scatter, splits)
+    close(out, (x_full.float() * gate.sum(1, keepdim=True))[rank * tpr:(rank + 1) * tpr], "ep combine")
+    bwd.op.check_status()
     p0(f"coll ok (W={W})")
 
 
