@@ -5,12 +5,30 @@
 #include "../sm100/gemm_dense.cuh"
 
 #include <atomic>
+#include <cstdlib>
 
 namespace fluxb {
 
 std::atomic<uint64_t> g_launches{0};
 
 namespace {
+
+// Wave counters: a small pool per device, zeroed once; a launch takes the next slot and leaves
+// it at zero again when it finishes.
+static uint32_t* next_wave_counter() {
+  constexpr int kSlots = 64;
+  static uint32_t* pool[64] = {nullptr};
+  static std::atomic<unsigned> next{0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (pool[dev] == nullptr) {
+    uint32_t* p = nullptr;
+    if (cudaMalloc(&p, kSlots * 128) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, kSlots * 128);
+    pool[dev] = p;
+  }
+  return pool[dev] + (next.fetch_add(1) % kSlots) * 32;
+}
 
 template <class Cfg>
 int launch_dense(const DenseGemmParams& p, int grid, cudaStream_t stream) {
@@ -316,6 +334,17 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   if (cg == 2) grid &= ~1;
 
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
+  {
+    // wave-synchronous tile starts pay off when a wave's operands do not fit L2 together
+    static const int wave_env = [] {
+      const char* e = getenv("FLUXB_WAVE_SYNC");
+      return e ? atoi(e) : -1;
+    }();
+    // (tiles long enough that the bubble at a wave boundary is noise, and more than two waves)
+    const int kblocks = (a->K + bk - 1) / bk;
+    const bool want = wave_env >= 0 ? wave_env != 0 : kblocks >= 48;
+    if (want && tiles > 2 * (grid / cg)) p.wave_ctr = next_wave_counter();
+  }
   if (a->blockscale) {
     if (p.mode == kModeAllGather) return launch_dense<DenseCfg<128, 1, 4, 1, 32768, true>>(p, grid, stream);
     return launch_dense<DenseCfg<128, 1, 4, 1, 0, true>>(p, grid, stream);

@@ -83,6 +83,9 @@ struct DenseGemmParams {
   const void* rs_stage;          // local staging [W][seg_rows][N] bf16
   void* rs_out;                  // [seg_rows, N] bf16
   uint32_t* rs_work;             // local work-claim counter, zero between calls
+  uint32_t* wave_ctr;            // optional, zero between launches: number of tiles whose loads have been
+                                 // issued. CTAs start wave i only after all of wave i-1 has been issued, so
+                                 // the whole grid walks K together and shared tiles are read while in L2.
   // ---- Ulysses all-to-all modes. Activations are [bs, local_seq, heads, hd] on the sequence-
   // sharded side and [bs, heads/W, seq, hd] (or [bs, seq, heads/W, hd]) on the head-sharded side;
   // every 4-D tensor map below is ordered (hd, seq, head, batch) whatever the memory order is.
@@ -248,8 +251,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       int stage = 0;
       uint32_t phase = 0;
       const uint32_t full_owner0 = CG == 2 ? ptx::mapa_u32(full_bar(0), 0) : full_bar(0);
-      for (int t = tile_slot; t < total_tiles; t += tile_stride) {
+      int wave = 0;
+      for (int t = tile_slot; t < total_tiles; t += tile_stride, ++wave) {
         const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
+        if (p.wave_ctr != nullptr && leader && wave > 0) {
+          const uint32_t need = min(static_cast<uint32_t>(wave) * tile_stride, static_cast<uint32_t>(total_tiles));
+          flag_wait_ge(wc, p.wave_ctr, need, kSiteStartBarrier);
+        }
         const CUtensorMap* tma = &p.tm_a;
         const int m_cta = c.m_in_seg + static_cast<int>(cta_rank) * Cfg::BM_CTA;
         int a_row = c.seg * p.seg_rows + m_cta;
@@ -300,6 +308,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             stage = 0;
             phase ^= 1u;
           }
+        }
+        if (p.wave_ctr != nullptr && leader) {
+          // this tile's loads are all issued; whoever issues the last tile of the launch puts the
+          // counter back to zero (every wait of the launch is for a smaller value)
+          if (atomicAdd(p.wave_ctr, 1u) == static_cast<uint32_t>(total_tiles) - 1u) atomicExch(p.wave_ctr, 0u);
         }
       }
     }

@@ -35,7 +35,7 @@ def test_tuning_table_and_profiling_context(tmp_path, monkeypatch):
     assert k == {"cta_group": 2, "tile_n": 256, "group_m": 8}
     h = table.lookup(333, 264, 72)
     assert h["cta_group"] == 1 and h["tile_n"] in (128, 256)
-    assert table.heuristic(8192, 4096, 32768)["group_m"] == 2       # long K narrows the raster group
+    assert table.heuristic(8192, 4096, 32768) == {"cta_group": 2, "tile_n": 256, "group_m": 8}
     f = tmp_path / "extra.json"
     f.write_text('[{"key": [1, 2, 3], "best": {"cta_group": 1, "tile_n": 128, "group_m": 4}}]')
     monkeypatch.setenv("FLUXB_TUNE_FILE", str(f))
