@@ -31,13 +31,39 @@ class TPMLP(nn.Module):
 
     @torch.no_grad()
     def forward_host(self, x_pinned: torch.Tensor, result_pinned: Optional[torch.Tensor] = None):
-        """End-to-end step for a host-resident batch: copy the shard from pinned host memory,
-        run the block, and bring a per-step result (mean |y| and the first output row) back."""
+        """End-to-end step for a host-resident batch: copy the shard from pinned host memory, run the
+        block, and bring a per-step result (mean |y| and the first output row) back.
+
+        The copies run on a side stream into one of two device buffers, so the upload of this
+        step overlaps the kernels of the previous step that are still in flight; the returned
+        pinned tensor is complete once ``torch.cuda.current_stream().synchronize()`` (or the
+        event in ``self.last_result_event``) has passed."""
         dev = self.fc1.weight.device
-        x = x_pinned.to(dev, non_blocking=True)
-        y = self.forward(x)
+        st = self.__dict__.setdefault("_host_state", {})
+        if not st or st["shape"] != tuple(x_pinned.shape) or st["dtype"] != x_pinned.dtype:
+            st.update(shape=tuple(x_pinned.shape), dtype=x_pinned.dtype, step=0,
+                      copy_stream=torch.cuda.Stream(device=dev),
+                      bufs=[torch.empty(x_pinned.shape, dtype=x_pinned.dtype, device=dev) for _ in range(2)],
+                      used=[None, None])
+        main = torch.cuda.current_stream(dev)
+        k = st["step"] & 1
+        st["step"] += 1
+        cs = st["copy_stream"]
+        if st["used"][k] is not None:
+            cs.wait_event(st["used"][k])          # the step that last read this buffer is done with it
+        with torch.cuda.stream(cs):
+            st["bufs"][k].copy_(x_pinned, non_blocking=True)
+            up = torch.cuda.Event()
+            up.record(cs)
+        main.wait_event(up)
+        y = self.forward(st["bufs"][k])
         res = torch.cat([y.float().abs().mean().reshape(1), y[0].float()])
+        done = torch.cuda.Event()
+        done.record(main)
+        st["used"][k] = done
         if result_pinned is None:
             return res.cpu()
         result_pinned.copy_(res, non_blocking=True)
+        self.last_result_event = torch.cuda.Event()
+        self.last_result_event.record(main)
         return result_pinned

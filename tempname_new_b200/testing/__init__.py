@@ -11,3 +11,4 @@ from ..ops.ulysses import (post_attn_a2a_torch as torch_post_attn_all_to_all_tra
                            pre_attn_qkv_pack_a2a_torch as torch_pre_attn_qkv_pack_a2a)
 from ..ops.moe import moe_layer0_torch, moe_layer1_partial_torch  # noqa: F401
 from ..ops.blockscale_gemm import blockscale_gemm_torch  # noqa: F401
+from .perf_log import PerfResult, log_perf  # noqa: F401

@@ -1,0 +1,42 @@
+"""Benchmark records as JSON lines (reference: ``python/flux/testing/perf_db_helper.py``, which
+prints a ``PerfResult`` or uploads it to a MySQL database; the upload has no counterpart here)."""
+from __future__ import annotations
+
+import json
+import os
+import sys
+import time
+from dataclasses import asdict, dataclass, field
+from typing import Dict, Optional
+
+import torch
+
+
+@dataclass
+class PerfResult:
+    name: str
+    output: Optional[torch.Tensor] = None
+    total_ms: float = 0.0
+    gemm_time_ms: float = 0.0
+    comm_time_ms: float = 0.0
+    extra: Dict = field(default_factory=dict)
+
+    def __repr__(self) -> str:
+        return (f"{self.name}: total {self.total_ms:.3f} ms, gemm {self.gemm_time_ms:.3f} ms, "
+                f"comm {self.comm_time_ms:.3f} ms")
+
+
+def log_perf(result: PerfResult, file=None) -> None:
+    """One JSON line per result: to ``file``, else to ``$FLUXB_PERF_LOG`` when set, else stdout."""
+    rec = {k: v for k, v in asdict(result).items() if k != "output"}
+    rec["time"] = time.time()
+    rec["device"] = torch.cuda.get_device_name() if torch.cuda.is_available() else "cpu"
+    line = json.dumps(rec)
+    path = os.environ.get("FLUXB_PERF_LOG")
+    if file is not None:
+        file.write(line + "\n")
+    elif path:
+        with open(path, "a") as f:
+            f.write(line + "\n")
+    else:
+        sys.stdout.write(line + "\n")

@@ -350,6 +350,37 @@ def moe_perf(E=64, topk=8, H=4096, ffn=1536, tpr=8192):
        f" | torch+nccl {tt0:.3f} ms ; layer1 fluxb {t1:.3f} ms ({f1 / t1 / 1e9:.0f} TF/GPU) | torch+nccl {tt1:.3f} ms")
 
 
+def check_failure():
+    """A rank that stops taking part between steps: the others' device waits give up after their
+    limit, the status record says where, and the context stays usable. Runs with plain peer
+    stores (no multicast objects are in use anywhere in the library)."""
+    M, N, K = 256 * W, 256, 128 * W
+    a = (torch.randn(M, K // W, device=dev) * 0.5).bfloat16()
+    w = (torch.randn(N, K // W, device=dev) * 0.05).bfloat16()
+    op = flux.GemmRS(pg, 1, M, N, torch.bfloat16, timeout_s=1.0)
+    ref32 = torch.empty(M // W, N, device=dev)
+    dist.reduce_scatter_tensor(ref32, a.float() @ w.float().t())
+    close(op.forward(a, w), ref32, "GemmRS before the failure")
+    op.check_status()
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank == W - 1:
+        p0("")                                  # the last rank leaves between steps: no launch
+    else:
+        op.forward(a, w)                        # peers wait for the missing rank, bounded
+        try:
+            op.check_status()
+            raise AssertionError("the missing rank went unnoticed")
+        except flux.FluxTimeoutError as e:
+            assert "start handshake" in str(e) or "tile counter" in str(e), str(e)
+        # the device still works
+        x = torch.randn(512, 512, device=dev).bfloat16()
+        g = flux.GemmOnly(torch.bfloat16).forward(x, x)
+        close(g, x.float() @ x.float().t(), "GemmOnly after the timeout")
+    torch.cuda.synchronize()
+    print(f"[rank {rank}] failure ok", flush=True)
+
+
 if "dense" in what:
     check_dense()
 if "blockscale" in what:
@@ -360,6 +391,8 @@ if "moe" in what:
     check_moe()
 if "coll" in what:
     check_coll()
+if "failure" in what:
+    check_failure()
 p0("ALL OK")
 dist.barrier()
 dist.destroy_process_group()

@@ -12,8 +12,9 @@ from conftest import ROOT, free_port
 pytestmark = pytest.mark.gpu
 
 
-def _run(world, what):
+def _run(world, what, extra_env=None):
     env = dict(os.environ, NCCL_DEBUG="WARN", FLUXB_WAIT_TIMEOUT_S="20")
+    env.update(extra_env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
            os.path.join(ROOT, "tests", "dist_worker.py"), *what]
@@ -26,3 +27,11 @@ def test_fused_ops_multi_gpu(world):
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     _run(world, ["dense", "blockscale", "ulysses", "moe", "coll"])
+
+
+def test_rank_leaving_between_steps_is_detected():
+    """Failure detection on the GPU without a fault: a rank stops launching, the others' bounded
+    waits time out and report it. NVLS off in NCCL, plain peer stores in our kernels."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    _run(2, ["failure"], {"NCCL_NVLS_ENABLE": "0"})
