@@ -135,23 +135,42 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __grid_constant_
         const int r = p.routing_idx[t * p.topk + k] - row_base;
         if (r >= 0 && r < rows_ep) rows[nloc++] = r;
       }
-      for (int c = lane; c < chunks; c += 32) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int j = 0; j < nloc; ++j) {
-          const uint4 v = *reinterpret_cast<const uint4*>(p.y + static_cast<int64_t>(rows[j]) * p.H + c * 8);
-          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      // four 16-byte chunks per lane per trip, all loads of a trip issued before the first add
+      for (int c0 = lane; c0 < chunks; c0 += 128) {
+        float acc[4][8];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            acc[2 * e] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] & 0xFFFFu), f16);
-            acc[2 * e + 1] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] >> 16), f16);
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+        for (int j = 0; j < nloc; ++j) {
+          const uint16_t* yrow = p.y + static_cast<int64_t>(rows[j]) * p.H;
+          uint4 v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (c0 + 32 * u < chunks) v[u] = *reinterpret_cast<const uint4*>(yrow + (c0 + 32 * u) * 8);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (c0 + 32 * u < chunks) {
+              const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                acc[u][2 * e] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] & 0xFFFFu), f16);
+                acc[u][2 * e + 1] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] >> 16), f16);
+              }
+            }
           }
         }
-        uint4 o;
-        o.x = ptx::pack_half2(f16, acc[0], acc[1]);
-        o.y = ptx::pack_half2(f16, acc[2], acc[3]);
-        o.z = ptx::pack_half2(f16, acc[4], acc[5]);
-        o.w = ptx::pack_half2(f16, acc[6], acc[7]);
-        ptx::st_global_v4(slab + static_cast<int64_t>(tl) * p.H + c * 8, o);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (c0 + 32 * u < chunks) {
+            uint4 o;
+            o.x = ptx::pack_half2(f16, acc[u][0], acc[u][1]);
+            o.y = ptx::pack_half2(f16, acc[u][2], acc[u][3]);
+            o.z = ptx::pack_half2(f16, acc[u][4], acc[u][5]);
+            o.w = ptx::pack_half2(f16, acc[u][6], acc[u][7]);
+            ptx::st_global_v4(slab + static_cast<int64_t>(tl) * p.H + (c0 + 32 * u) * 8, o);
+          }
+        }
       }
     }
     // everything this CTA had for `owner` is written: the last CTA tells the owner

@@ -85,3 +85,31 @@ def test_cpu_fallbacks_of_small_ops():
     torch.testing.assert_close(g.forward(x, w), x @ w.t())
     out = flux.GemmGroupedV3(torch.randn(2, 4, 8), 2).forward(torch.randn(5, 8), torch.tensor([2, 3]))
     assert out.shape == (5, 4)
+
+
+def test_topology_probe_with_fake_nvml():
+    from tempname_new_b200.parallel import topo
+
+    class FakeNvml:
+        def __init__(self, links, switch):
+            self.links, self.switch = links, switch
+
+        def nvmlInit(self): pass
+        def nvmlShutdown(self): pass
+        def nvmlDeviceGetCount(self): return len(self.links)
+        def nvmlDeviceGetHandleByIndex(self, i): return i
+        def nvmlDeviceGetName(self, h): return b"NVIDIA B200"
+        def nvmlDeviceGetNvLinkState(self, h, link): return 1 if link < self.links[h] else 0
+        def nvmlDeviceGetNvLinkRemoteDeviceType(self, h, link): return 2 if self.switch else 0
+        def nvmlDeviceGetCurrPcieLinkGeneration(self, h): return 5
+
+        def nvmlDeviceGetPciInfo(self, h):
+            class P:
+                busId = b"00000000:1B:00.0"
+            return P()
+
+    t = topo.probe(FakeNvml([18] * 8, True))
+    assert t.num_gpus == 8 and t.has_nvlink and t.has_nvswitch and not t.has_heterogeneous_nvlink
+    assert t.numa_local_world_size == 8 and t.pcie_gen == [5] * 8
+    t = topo.probe(FakeNvml([18, 12, 0, 18], False))
+    assert not t.has_nvlink and not t.has_nvswitch and t.has_heterogeneous_nvlink
