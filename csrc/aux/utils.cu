@@ -21,8 +21,9 @@ namespace {
 // from a counter; "chunk read" is published as flag[c] = epoch; the wait on flag[c/2] is bounded.
 // ----------------------------------------------------------------------------------------
 constexpr int kCastThreads = 256;
-constexpr int kCastPerThread = 8;
-constexpr int kChunk = kCastThreads * kCastPerThread;  // 2048 elements
+constexpr int kCastVec = 8;                               // floats per 32-byte piece
+constexpr int kCastPieces = 4;                            // pieces per thread, 2048 elements apart
+constexpr int kChunk = kCastThreads * kCastVec * kCastPieces;  // 8192 elements
 
 __global__ void __launch_bounds__(kCastThreads) inplace_cast_kernel(
     float* data, int64_t n, uint32_t* flags, uint32_t* claim, uint32_t epoch, uint64_t timeout_ns,
@@ -43,16 +44,19 @@ __global__ void __launch_bounds__(kCastThreads) inplace_cast_kernel(
     __syncthreads();
     const uint32_t c = chunk_slot;
     if (c >= chunks) break;
-    const int64_t base = static_cast<int64_t>(c) * kChunk + threadIdx.x * kCastPerThread;
-    float v[kCastPerThread];
-    if (base + kCastPerThread <= n) {
-      const float4 a = *reinterpret_cast<const float4*>(data + base);
-      const float4 b = *reinterpret_cast<const float4*>(data + base + 4);
-      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-      v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    } else {
+    float v[kCastPieces][kCastVec];
 #pragma unroll
-      for (int j = 0; j < kCastPerThread; ++j) v[j] = base + j < n ? data[base + j] : 0.f;
+    for (int p = 0; p < kCastPieces; ++p) {
+      const int64_t base = static_cast<int64_t>(c) * kChunk + (p * kCastThreads + threadIdx.x) * kCastVec;
+      if (base + kCastVec <= n) {
+        const float4 a = *reinterpret_cast<const float4*>(data + base);
+        const float4 b = *reinterpret_cast<const float4*>(data + base + 4);
+        v[p][0] = a.x; v[p][1] = a.y; v[p][2] = a.z; v[p][3] = a.w;
+        v[p][4] = b.x; v[p][5] = b.y; v[p][6] = b.z; v[p][7] = b.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < kCastVec; ++j) v[p][j] = base + j < n ? data[base + j] : 0.f;
+      }
     }
     __syncthreads();  // every thread of the CTA holds its part of chunk c in registers
     if (threadIdx.x == 0) {
@@ -61,17 +65,21 @@ __global__ void __launch_bounds__(kCastThreads) inplace_cast_kernel(
       flag_wait_ge(wc, flags + (c >> 1), epoch, kSiteInplaceCast);
     }
     __syncthreads();
-    if (base + kCastPerThread <= n) {
-      uint4 o;
-      o.x = ptx::pack_bf16x2(v[0], v[1]);
-      o.y = ptx::pack_bf16x2(v[2], v[3]);
-      o.z = ptx::pack_bf16x2(v[4], v[5]);
-      o.w = ptx::pack_bf16x2(v[6], v[7]);
-      *reinterpret_cast<uint4*>(out + base) = o;
-    } else {
 #pragma unroll
-      for (int j = 0; j < kCastPerThread; ++j)
-        if (base + j < n) out[base + j] = __float2bfloat16_rn(v[j]);
+    for (int p = 0; p < kCastPieces; ++p) {
+      const int64_t base = static_cast<int64_t>(c) * kChunk + (p * kCastThreads + threadIdx.x) * kCastVec;
+      if (base + kCastVec <= n) {
+        uint4 o;
+        o.x = ptx::pack_bf16x2(v[p][0], v[p][1]);
+        o.y = ptx::pack_bf16x2(v[p][2], v[p][3]);
+        o.z = ptx::pack_bf16x2(v[p][4], v[p][5]);
+        o.w = ptx::pack_bf16x2(v[p][6], v[p][7]);
+        *reinterpret_cast<uint4*>(out + base) = o;
+      } else {
+#pragma unroll
+        for (int j = 0; j < kCastVec; ++j)
+          if (base + j < n) out[base + j] = __float2bfloat16_rn(v[p][j]);
+      }
     }
   }
 }

@@ -72,6 +72,12 @@ typedef struct {
   int32_t blockscale;
   int32_t reserved3;
   void* stream;
+  /* optional timeline: [CTAs][16] uint64 of device memory receiving %globaltimer stamps (ns):
+   * 0 roles start, 1 start handshake done, 2 pushes of communication warp 2 published, 3 loads of
+   * the CTA's first tile issued, 4 loads of its last tile issued, 5 first epilogue store, 6 epilogue
+   * done, 7 total ns the producer spent waiting for arrival flags, 8 + j: K slice j of the first tile
+   * became readable (post-attention mode). Null = off. */
+  uint64_t* trace;
 } fluxb_dense_args_t;
 
 int fluxb_dense_gemm(const fluxb_dense_args_t* args);
@@ -86,8 +92,10 @@ uint64_t fluxb_launch_count(void);
  *   The kernel returns when this rank's own buffers have received every rank's part.
  * FLUXB_A2A_GEMM  (post-attention): attn = this rank's attention output, layout 0 =
  *   [bs, heads/W, seq, hd], 1 = [bs, seq, heads/W, hd]; its slice for rank d's sequence range is
- *   pushed into land[d] ([bs*local_seq, heads*hd]); base.d [bs*local_seq, N] = land[rank] * W^T
- *   with the K loop gated slice by slice. base.a is ignored.
+ *   pushed into slab `rank` of land[d], which keeps the source's layout ([W][heads/W][M][hd] for
+ *   layout 0, [W][M][heads/W][hd] for layout 1, M = bs*local_seq) so that every piece moves as one
+ *   contiguous run; base.d [M, N] = (the W slabs side by side along K) * W^T with the K loop gated
+ *   slab by slab. base.a is ignored.
  * a2a_flags[r]: W*ceil(M/128)+W uint32 per rank in symmetric memory, zero at first use. */
 typedef struct {
   fluxb_dense_args_t base;
@@ -98,6 +106,9 @@ typedef struct {
   const void* attn;
   void* land[FLUXB_MAX_RANKS];
   uint32_t* a2a_flags[FLUXB_MAX_RANKS];
+  int32_t copy_local;        /* FLUXB_A2A_GEMM: 1 = land[rank] also receives this rank's own slice (the
+                                whole GEMM input is then readable there); 0 = the own slice is read in
+                                place from attn */
 } fluxb_a2a_args_t;
 
 int fluxb_ulysses_gemm(const fluxb_a2a_args_t* args);
@@ -227,7 +238,7 @@ int fluxb_quantize_blockwise(const void* x, int64_t ldx, int in_dtype, void* q, 
 
 /* ---- small utilities (csrc/aux/utils.cu) ---- */
 /* In-place fp32 -> bf16 compaction of data[0..n): results are packed at the front of the buffer.
- * flags: ceil(n/2048) uint32 of scratch, claim: one uint32; both zero at first use and owned by
+ * flags: ceil(n/8192) uint32 of scratch, claim: one uint32; both zero at first use and owned by
  * the caller across calls; epoch grows by one per call. */
 int fluxb_inplace_cast_fp32_to_bf16(float* data, int64_t n, uint32_t* flags, uint32_t* claim,
                                     uint32_t epoch, uint64_t timeout_ns, fluxb_status_t* status,

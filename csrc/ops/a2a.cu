@@ -146,7 +146,7 @@ extern "C" int fluxb_a2a_rows(const fluxb_a2a_rows_args_t* a) {
   }
   int sms = 0, rc;
   if ((rc = device_sm_count(&sms))) return rc;
-  int grid = a->num_ctas > 0 ? a->num_ctas : 32;
+  int grid = a->num_ctas > 0 ? a->num_ctas : 64;
   if (grid > sms) grid = sms;  // all CTAs must be resident: they count arrivals together
   a2a_rows_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(a->stream)>>>(p);
   FLUXB_CUDA_OK(cudaGetLastError());

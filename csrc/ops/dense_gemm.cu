@@ -135,6 +135,7 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   p.timeout_ns = a->timeout_ns ? a->timeout_ns : 2000000000ull;
   p.status = reinterpret_cast<Status*>(a->status);
   p.bias = a->bias;
+  p.trace = a->trace;
   p.bias_row_stride = a->bias_row_stride;
   p.scale_a = a->scale_a;
   p.scale_b = a->scale_b;
@@ -223,16 +224,51 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
       FLUXB_REQUIRE(a->K % (a->world * x->hd) == 0, "K must equal heads * head_dim with heads divisible by W");
       p.a2a_local_heads = a->K / x->hd / a->world;
       FLUXB_REQUIRE(x->attn != nullptr, "attention output missing");
-      if ((rc = encode_heads_map(&p.tm_a2a_src, x->attn, x->layout, x->hd, seq, p.a2a_local_heads, x->bs,
-                                 static_cast<uint32_t>(x->hd), Swz::None)))
-        return rc;
+      p.a2a_attn = x->attn;
+      p.a2a_layout = x->layout;
+      // the own slice is read in place when a 128-row tile never straddles two batches
+      p.a2a_copy_local = (x->copy_local || !(x->bs == 1 || x->local_seq % 128 == 0)) ? 1 : 0;
+      {
+        const uint64_t e = 2;
+        const uint64_t lh = static_cast<uint64_t>(p.a2a_local_heads);
+        uint64_t dims[4] = {static_cast<uint64_t>(x->hd), static_cast<uint64_t>(seq), lh,
+                            static_cast<uint64_t>(x->bs)};
+        uint64_t str[3];
+        if (x->layout == 0) {
+          str[0] = x->hd * e;
+          str[1] = static_cast<uint64_t>(seq) * x->hd * e;
+        } else {
+          str[0] = lh * x->hd * e;
+          str[1] = x->hd * e;
+        }
+        str[2] = lh * seq * x->hd * e;
+        uint32_t box[4] = {64, 128, 1, 1};
+        if ((rc = encode_tmap(&p.tm_a_own, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, x->attn, dims, str, box,
+                              Swz::B128)))
+          return rc;
+      }
       for (int r = 0; r < a->world; ++r) {
         FLUXB_REQUIRE(x->land[r] != nullptr, "landing buffer missing");
-        uint64_t dims[2] = {static_cast<uint64_t>(a->K), static_cast<uint64_t>(a->M)};
-        uint64_t str[1] = {static_cast<uint64_t>(a->K) * 2};
-        uint32_t box[2] = {static_cast<uint32_t>(x->hd), 32};
-        if ((rc = encode_tmap(&p.tm_a2a_land[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x->land[r], dims, str,
-                              box, Swz::None)))
+        p.a2a_land[r] = x->land[r];
+      }
+      {
+        // own landing buffer, one slab per source: (hd, M, head, source)
+        const uint64_t e = 2;
+        const uint64_t lh = static_cast<uint64_t>(p.a2a_local_heads);
+        const uint64_t Mr = static_cast<uint64_t>(a->M);
+        uint64_t dims[4] = {static_cast<uint64_t>(x->hd), Mr, lh, static_cast<uint64_t>(a->world)};
+        uint64_t str[3];
+        if (x->layout == 0) {
+          str[0] = x->hd * e;
+          str[1] = Mr * x->hd * e;
+        } else {
+          str[0] = lh * x->hd * e;
+          str[1] = x->hd * e;
+        }
+        str[2] = lh * Mr * x->hd * e;
+        uint32_t box[4] = {64, 128, 1, 1};
+        if ((rc = encode_tmap(&p.tm_a_land4, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, x->land[a->rank], dims, str,
+                              box, Swz::B128)))
           return rc;
       }
     }
@@ -318,10 +354,15 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     unit = (unit + bm - 1) / bm * bm;
     const int64_t seg_round = (static_cast<int64_t>(p.seg_rows) + bm - 1) / bm * bm;
     if (unit > seg_round || unit * 3 / 2 > seg_round) unit = seg_round;
+    // the post-attention exchange is short next to its GEMM: 1024-row units let the first wave of
+    // tiles start on the first quarter of what arrives
+    if (p.mode == kModeA2AGemm && seg_round >= 2048) unit = 1024;
     p.flag_unit_rows = static_cast<int32_t>(unit);
   }
   const int m_tiles_seg = (p.seg_rows + bm - 1) / bm;
   p.group_m = a->group_m > 0 ? a->group_m : 16 / cg;
+  // post-attention: the first wave of tiles should need as few rows of the exchange as possible
+  if (p.mode == kModeA2AGemm && a->world > 1 && p.group_m > 4) p.group_m = 4;
   if (p.group_m > m_tiles_seg) p.group_m = m_tiles_seg;
 
   int sms = 0;

@@ -414,7 +414,7 @@ extern "C" int fluxb_moe_combine(const fluxb_moe_combine_args_t* a) {
   int sms = 0, rc;
   if ((rc = device_sm_count(&sms))) return rc;
   // every CTA takes part in the arrival counting, so all of them must be resident
-  moe_combine_kernel<<<sms * 2, 256, 0, reinterpret_cast<cudaStream_t>(a->stream)>>>(p);
+  moe_combine_kernel<<<sms * 3, 256, 0, reinterpret_cast<cudaStream_t>(a->stream)>>>(p);
   FLUXB_CUDA_OK(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return kOk;

@@ -36,6 +36,20 @@ enum DenseMode : int32_t {
   kModeGemmA2A = 3,   // Ulysses pre-attention: GEMM, then seq->heads all-to-all in the epilogue
   kModeA2AGemm = 4,   // Ulysses post-attention: heads->seq all-to-all feeding the GEMM's K loop
 };
+
+// slots of the optional per-CTA timeline (DenseGemmParams::trace)
+enum TraceSlot : int {
+  kTraceEntry = 0,        // roles start
+  kTraceHandshake = 1,    // communication warp 2: every peer has entered the call
+  kTracePushDone = 2,     // communication warp 2: its last push is published
+  kTraceFirstLoads = 3,   // producer: all loads of the CTA's first tile issued
+  kTraceLastLoads = 4,    // producer: all loads of its last tile issued
+  kTraceFirstStore = 5,   // epilogue warp 4: first tile handed to the TMA store
+  kTraceEnd = 6,          // epilogue warp 4: done
+  kTraceFlagWait = 7,     // producer: total time spent waiting for arrival flags
+  kTraceSlice0 = 8,       // producer, first tile: 8 + j = K slice j (post-attention) became readable
+};
+constexpr int kTraceWords = 16;  // words per CTA
 constexpr int kMaxHeadGroups = 3;  // q, k, v
 
 struct DenseGemmParams {
@@ -52,6 +66,7 @@ struct DenseGemmParams {
   uint32_t reserved0;
   uint64_t timeout_ns;
   Status* status;
+  uint64_t* trace;               // optional [gridDim.x][kTraceWords] globaltimer stamps (ns), see kTrace*
   const void* bias;              // output dtype, may be null
   int64_t bias_row_stride;       // elements between bias rows; 0 = one row broadcast over M
   const float* scale_a;          // optional per-tensor scales (fp8): D = (A*B^T) * sa * sb
@@ -91,12 +106,19 @@ struct DenseGemmParams {
   // every 4-D tensor map below is ordered (hd, seq, head, batch) whatever the memory order is.
   CUtensorMap tm_a2a[kMaxHeadGroups * kMaxRanks];  // kModeGemmA2A: output of (group g, rank d),
                                                    //   box {64, 32, 1, 1}
-  CUtensorMap tm_a2a_src;        // kModeA2AGemm: this rank's attention output, box {hd, 32, 1, 1}
-  CUtensorMap tm_a2a_land[kMaxRanks];  // kModeA2AGemm: rank d's GEMM input [bs*local_seq, heads*hd],
-                                       //   box {hd, 32}
+  const void* a2a_attn;          // kModeA2AGemm: this rank's attention output
+  void* a2a_land[kMaxRanks];     // kModeA2AGemm: rank d's landing buffer, one slab per source rank laid
+                                 // out like the source: [W][heads/W][M][hd] (layout 0) or
+                                 // [W][M][heads/W][hd] (layout 1), so every 32-row piece of a head is
+                                 // one contiguous run on both sides of the copy
+  CUtensorMap tm_a_land4;        // kModeA2AGemm: own landing buffer as (hd, M, head, source), box {64, 128, 1, 1}
+  int32_t a2a_layout;
   int32_t a2a_hd, a2a_local_seq, a2a_bs, a2a_groups;
   int32_t a2a_group_start[kMaxHeadGroups + 1];  // first global head of each group (q | k | v)
   int32_t a2a_local_heads;       // kModeA2AGemm: heads per rank
+  int32_t a2a_copy_local;        // kModeA2AGemm: 1 = the own slice is copied into the landing buffer too;
+                                 // 0 = the K loop reads it in place through tm_a_own
+  CUtensorMap tm_a_own;          // kModeA2AGemm: the attention output as (hd, seq, head, batch), box {64, 128, 1, 1}
   uint32_t* a2a_flags[kMaxRanks];  // kModeGemmA2A: [W src] "all my tiles for you have landed";
                                    // kModeA2AGemm: [W src][m_tiles] per tile row
 };
@@ -234,6 +256,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
   const uint32_t tmem_base = *tmem_slot;
 
   WaitCtx wc{p.status, abort_word, p.timeout_ns};
+  auto stamp = [&](int slot) {
+    if (p.trace != nullptr) p.trace[blockIdx.x * kTraceWords + slot] = ptx::globaltimer_ns();
+  };
 
   const int m_tiles_seg = (p.seg_rows + BM - 1) / BM;
   const int n_tiles = (p.N + BN - 1) / BN;
@@ -252,6 +277,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       uint32_t phase = 0;
       const uint32_t full_owner0 = CG == 2 ? ptx::mapa_u32(full_bar(0), 0) : full_bar(0);
       int wave = 0;
+      uint64_t flag_ns = 0;
+      stamp(kTraceEntry);
       for (int t = tile_slot; t < total_tiles; t += tile_stride, ++wave) {
         const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
         if (p.wave_ctr != nullptr && leader && wave > 0) {
@@ -268,39 +295,70 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             tma = &p.tm_a_land;
             const uint32_t* f = p.ag_flags[p.rank] + c.seg * ((p.seg_rows + p.flag_unit_rows - 1) / p.flag_unit_rows) +
                                 c.m_in_seg / p.flag_unit_rows;
+            const uint64_t w0 = p.trace != nullptr ? ptx::globaltimer_ns() : 0;
             flag_wait_ge(wc, f, p.epoch, kSiteShardFlag);
             ptx::fence_proxy_async_all();
+            if (p.trace != nullptr) flag_ns += ptx::globaltimer_ns() - w0;
           }
         }
         // post-attention mode: the K range is W slices, one per source rank, landing
         // independently; start with the own slice and gate each slice on its flag
         const int kb_per_src = p.mode == kModeA2AGemm ? (p.a2a_local_heads * p.a2a_hd) / BK : k_blocks;
-        int cur_src = -1;
+        // (no division in the k loop: one thread issues every load of the CTA, and a few dozen
+        // dependent integer instructions per k-block are enough to starve the tensor pipe)
+        const bool a2a_in = p.mode == kModeA2AGemm;
+        const bool own_in_place = a2a_in && p.a2a_copy_local == 0;
+        const int hd_shift = p.a2a_hd == 128 ? 7 : 6;
+        const int own_b = own_in_place ? m_cta / p.a2a_local_seq : 0;
+        const int own_s = own_in_place ? p.rank * p.a2a_local_seq + m_cta % p.a2a_local_seq : 0;
+        const uint32_t* a2a_flag_row =
+            a2a_in ? p.a2a_flags[p.rank] + c.m_in_seg / p.flag_unit_rows : nullptr;
+        const int a2a_units = a2a_in ? (p.seg_rows + p.flag_unit_rows - 1) / p.flag_unit_rows : 0;
+        int src = p.rank, kin = 0;   // source rank of the current K slice, k-block within the slice
         for (int ki = 0; ki < k_blocks; ++ki) {
           int kb = ki;
-          if (p.mode == kModeA2AGemm) {
-            kb = ki + p.rank * kb_per_src;
-            if (kb >= k_blocks) kb -= k_blocks;
-            const int src = kb / kb_per_src;
-            if (src != cur_src) {
-              cur_src = src;
-              flag_wait_ge(wc, p.a2a_flags[p.rank] + src * ((p.seg_rows + p.flag_unit_rows - 1) / p.flag_unit_rows) +
-                               c.m_in_seg / p.flag_unit_rows,
-                           p.epoch, kSiteA2AFlag);
+          bool in_place = false;
+          if (a2a_in) {
+            // slice j of the K loop is the one that source rank-j pushed at its step j
+            kb = src * kb_per_src + kin;
+            in_place = own_in_place && src == p.rank;
+            if (kin == 0 && !in_place) {
+              const uint64_t w0 = p.trace != nullptr ? ptx::globaltimer_ns() : 0;
+              flag_wait_ge(wc, a2a_flag_row + src * a2a_units, p.epoch, kSiteA2AFlag);
               ptx::fence_proxy_async_all();
+              if (p.trace != nullptr) {
+                flag_ns += ptx::globaltimer_ns() - w0;
+                int j = p.rank - src;
+                if (j < 0) j += p.world;
+                if (wave == 0) stamp(kTraceSlice0 + j);
+              }
             }
           }
           mbar_wait(wc, empty_bar(stage), phase ^ 1u, kSiteSmemEmpty);
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+          // post-attention input: (column in head, head of the slice, source); the own slice comes
+          // straight from the attention output
+          const int own_k = kin * BK;
+          const int own_head = own_k >> hd_shift;
+          const int own_col = own_k & (p.a2a_hd - 1);
+          const int ld_src = src;
+          if (a2a_in && ++kin == kb_per_src) {
+            kin = 0;
+            src = src == 0 ? p.world - 1 : src - 1;
+          }
           if constexpr (CG == 1) {
             ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
-            ptx::tma_load_2d(sa, tma, full_bar(stage), kb * BK, a_row);
+            if (in_place) ptx::tma_load_4d(sa, &p.tm_a_own, full_bar(stage), own_col, own_s, own_head, own_b);
+            else if (a2a_in) ptx::tma_load_4d(sa, &p.tm_a_land4, full_bar(stage), own_col, m_cta, own_head, ld_src);
+            else ptx::tma_load_2d(sa, tma, full_bar(stage), kb * BK, a_row);
             ptx::tma_load_2d(sa + Cfg::A_BYTES, &p.tm_b, full_bar(stage), kb * BK, c.n0);
           } else {
             // both CTAs' bytes are counted on the leader's barrier
             const uint32_t fb = full_owner0 + 8u * stage;
             if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * Cfg::STAGE_BYTES);
-            ptx::tma_load_2d_cg2(sa, tma, fb, kb * BK, a_row);
+            if (in_place) ptx::tma_load_4d_cg2(sa, &p.tm_a_own, fb, own_col, own_s, own_head, own_b);
+            else if (a2a_in) ptx::tma_load_4d_cg2(sa, &p.tm_a_land4, fb, own_col, m_cta, own_head, ld_src);
+            else ptx::tma_load_2d_cg2(sa, tma, fb, kb * BK, a_row);
             ptx::tma_load_2d_cg2(sa + Cfg::A_BYTES, &p.tm_b, fb, kb * BK,
                                  c.n0 + static_cast<int>(cta_rank) * Cfg::B_ROWS_CTA);
           }
@@ -314,7 +372,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           // counter back to zero (every wait of the launch is for a smaller value)
           if (atomicAdd(p.wave_ctr, 1u) == static_cast<uint32_t>(total_tiles) - 1u) atomicExch(p.wave_ctr, 0u);
         }
+        if (wave == 0) stamp(kTraceFirstLoads);
       }
+      stamp(kTraceLastLoads);
+      if (p.trace != nullptr) p.trace[blockIdx.x * kTraceWords + kTraceFlagWait] = flag_ns;
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -388,6 +449,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       if (p.mode == kModeAllGather && multi) {
         if (lane < p.world) flag_wait_ge(wc, p.start_ctr[p.rank] + lane, p.epoch, kSiteStartBarrier);
         __syncwarp();
+        if (lane == 0 && warp == 2) stamp(kTraceHandshake);
         if (lane == 0) {
           // One lane per warp drives a ring of NSLOT staging slots: bulk-load a chunk of the local
           // shard into a slot, bulk-store it into the peer's landing slab, reuse the slot once
@@ -492,6 +554,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             publish(sig_d, sig_mt);
             if (++sig_mt == units) { sig_mt = 0; ++sig_d; }
           }
+          if (warp == 2) stamp(kTracePushDone);
         }
       }
     }
@@ -504,75 +567,149 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           if (lane < p.world) flag_wait_ge(wc, p.start_ctr[p.rank] + lane, p.epoch, kSiteStartBarrier);
           __syncwarp();
         }
+        if (lane == 0 && warp == 2) stamp(kTraceHandshake);
         if (lane == 0) {
-          constexpr int NSLOT = 2;
-          constexpr uint32_t SLOT = Cfg::COMM_BYTES / 2 / NSLOT;   // 8 KiB: 32 rows x hd <= 128 x 2 B
+          // One lane per warp: bulk-load a 4 KiB piece of the attention output (RG rows of one head,
+          // one contiguous run) into one of four staging slots, three loads ahead of the stores,
+          // and bulk-store it into the peer's landing slab for this source. The pieces of the whole
+          // exchange are numbered in the order (row unit, destination step, piece) and claimed in
+          // that order by the pushing warps, so every rank fills the first row unit of all its
+          // peers first - the rows that the first wave of tiles reads. Small pieces keep the time
+          // between a piece landing and its step being published short.
+          constexpr int NSLOT = 4;
+          constexpr int PF = NSLOT - 1;                            // loads in flight ahead of the store
+          constexpr uint32_t SLOT = Cfg::COMM_BYTES / 2 / NSLOT;   // 4 KiB
+          // stores that may still be on their way to the peer when a step is published (a deeper
+          // lag did not move more bytes per second and delays the flags)
           constexpr int LAG = 2;
           const uint32_t ring = comm_base + (warp - 2) * (Cfg::COMM_BYTES / 2);
           const uint32_t rbar = ring_bar_base + (warp - 2) * 4 * 8u;
-          const uint32_t cw = blockIdx.x * 2 + (warp - 2);
           const uint32_t ncw = gridDim.x * 2;
           const int hd = p.a2a_hd, lh = p.a2a_local_heads, ls = p.a2a_local_seq;
-          const uint32_t chunk_bytes = 32u * hd * Cfg::ELT;
+          const int RG = static_cast<int>(SLOT) / (hd * 2);         // rows per piece: 16 (hd 128) or 32 (hd 64)
+          const uint32_t chunk_bytes = static_cast<uint32_t>(RG) * hd * 2u;
           const int UR = p.flag_unit_rows;
-          const int units = (p.a2a_bs * ls + UR - 1) / UR;
-          const int groups_per_tile = UR / 32;                 // 32-row groups per flag unit
           const int rows_total = p.a2a_bs * ls;
-          auto step_chunks = [&](int mt) -> uint32_t {
+          const int units = (rows_total + UR - 1) / UR;
+          const int d0 = p.a2a_copy_local ? 0 : 1;             // step 0 is the local slice
+          const int nd = p.world - d0;
+          const int nsteps = units * nd;
+          auto step_nch = [&](int s) -> uint32_t {             // pieces of step s
+            const int mt = s / nd;
             const int rows = min(UR, rows_total - mt * UR);
-            const uint32_t nch = static_cast<uint32_t>(((rows + 31) / 32) * lh);
-            return nch > cw ? (nch - cw - 1) / ncw + 1 : 0u;
+            return static_cast<uint32_t>(((rows + RG - 1) / RG) * lh);
           };
-          auto publish = [&](int d, int mt) {
+          uint32_t total = 0;
+          for (int s = 0; s < nsteps; ++s) total += step_nch(s);
+          struct Walk { int s; uint32_t first, n; };
+          auto locate = [&](Walk& w, uint32_t g) {
+            while (g >= w.first + w.n) {
+              w.first += w.n;
+              ++w.s;
+              w.n = step_nch(w.s);
+            }
+          };
+          const uint8_t* attn = reinterpret_cast<const uint8_t*>(p.a2a_attn);
+          const int64_t seq = static_cast<int64_t>(ls) * p.world;
+          // piece g: destination rank, byte offset in the attention output, byte offset in the
+          // destination's landing buffer (slab `rank`)
+          auto coords = [&](const Walk& w, uint32_t g, int& peer, int64_t& soff, int64_t& doff) {
+            const uint32_t c = g - w.first;
+            const int mt = w.s / nd, d = d0 + w.s % nd;
+            peer = p.rank + d;
+            if (peer >= p.world) peer -= p.world;
+            const int i = static_cast<int>(c % lh);                    // head (layout 0) / part of the row group
+            const int row0 = mt * UR + static_cast<int>(c / lh) * RG;  // row of the peer's GEMM input
+            const int b = row0 / ls, s0 = row0 % ls;
+            if (p.a2a_layout == 0) {
+              soff = ((static_cast<int64_t>(b) * lh + i) * seq + static_cast<int64_t>(peer) * ls + s0) * hd * 2;
+              doff = ((static_cast<int64_t>(p.rank) * lh + i) * rows_total + row0) * hd * 2;
+            } else {
+              // RG rows of all heads are one run of lh pieces
+              soff = ((static_cast<int64_t>(b) * seq + static_cast<int64_t>(peer) * ls + s0) * lh + i * RG) * hd * 2;
+              doff = ((static_cast<int64_t>(p.rank) * rows_total + row0) * lh + i * RG) * hd * 2;
+            }
+          };
+          // a piece of step s has landed (its bulk group is complete: the bytes are visible to this
+          // thread, and the release below carries them); whoever lands the last piece of the step
+          // tells the peer
+          auto arrive = [&](int s) {
+            const int mt = s / nd, d = d0 + s % nd;
             int peer = p.rank + d;
             if (peer >= p.world) peer -= p.world;
-            ptx::fence_proxy_async_all();
-            uint32_t* cnt = p.local_cnt + d * units + mt;
-            if (ptx::atom_add_acq_rel_sys(cnt, 1u) == ncw - 1u) {
+            uint32_t* cnt = p.local_cnt + s;
+            if (ptx::atom_add_acq_rel_gpu(cnt, 1u) == step_nch(s) - 1u) {
               *cnt = 0;
               ptx::st_release_sys(p.a2a_flags[peer] + p.rank * units + mt, p.epoch);
             }
           };
-          uint32_t issued = 0;
-          int sig_d = 0, sig_mt = 0;
-          uint32_t sig_end = step_chunks(0);
-          // d = 0 is the local slice (every GEMM starts with it), then rank+1, rank+2, ...
-          for (int d = 0; d < p.world; ++d) {
-            int peer = p.rank + d;
-            if (peer >= p.world) peer -= p.world;
-            for (int mt = 0; mt < units; ++mt) {
-              const int rows = min(UR, rows_total - mt * UR);
-              const uint32_t nch = static_cast<uint32_t>(((rows + 31) / 32) * lh);
-              for (uint32_t c = cw; c < nch; c += ncw) {
-                const int g = c / lh, h = c % lh;                  // 32-row group, local head
-                const int row0 = mt * UR + g * 32;                 // row of the peer's GEMM input
-                const int b = row0 / ls, s0 = row0 % ls;
-                const uint32_t slot = issued % NSLOT;
-                const uint32_t ph = (issued / NSLOT) & 1u;
-                ptx::bulk_wait_read<NSLOT - 1>();
-                ptx::mbar_arrive_expect_tx(rbar + 8u * slot, chunk_bytes);
-                ptx::tma_load_4d(ring + slot * SLOT, &p.tm_a2a_src, rbar + 8u * slot, 0,
-                                 peer * ls + s0, h, b);
-                mbar_wait(wc, rbar + 8u * slot, ph, kSiteSmemFull);
-                ptx::tma_store_2d(&p.tm_a2a_land[peer], ring + slot * SLOT, (p.rank * lh + h) * hd, row0);
-                ptx::bulk_commit();
-                ++issued;
-              }
-              ptx::bulk_wait<LAG>();
-              const uint32_t done = issued > LAG ? issued - LAG : 0u;
-              while ((sig_d < d || (sig_d == d && sig_mt <= mt)) && sig_end <= done) {
-                publish(sig_d, sig_mt);
-                if (++sig_mt == units) { sig_mt = 0; ++sig_d; }
-                sig_end += step_chunks(sig_mt);
-              }
+          // pieces are claimed in order from one counter, so warps on SMs that get more of the
+          // link take more pieces and the early steps finish early; the ncw failed claims that
+          // end the launch put the counter back to zero
+          uint32_t* claim = p.local_cnt + 1024;
+          bool exhausted = false;
+          constexpr uint32_t NONE = 0xffffffffu;
+          auto claim_next = [&]() -> uint32_t {
+            if (exhausted) return NONE;
+            const uint32_t g = atomicAdd(claim, 1u);
+            if (g < total) return g;
+            exhausted = true;
+            if (g == total + ncw - 1u) atomicExch(claim, 0u);
+            return NONE;
+          };
+          Walk wl{0, 0u, nsteps > 0 ? step_nch(0) : 0u};   // walker of the loads
+          Walk ws = wl;                                     // walker of the stores
+          auto issue_load = [&](uint32_t g, uint32_t idx) {
+            int peer;
+            int64_t soff, doff;
+            locate(wl, g);
+            coords(wl, g, peer, soff, doff);
+            const uint32_t slot = idx % NSLOT;
+            ptx::mbar_arrive_expect_tx(rbar + 8u * slot, chunk_bytes);
+            ptx::bulk_load(ring + slot * SLOT, attn + soff, chunk_bytes, rbar + 8u * slot);
+          };
+          uint32_t gbuf[NSLOT];   // piece in each slot
+          int stepq[8];           // step of the last eight stored pieces
+          uint32_t nload = 0, nstore = 0, counted = 0;
+          for (int k = 0; k < PF; ++k) {
+            const uint32_t g = claim_next();
+            if (g == NONE) break;
+            gbuf[nload % NSLOT] = g;
+            issue_load(g, nload);
+            ++nload;
+          }
+          while (nstore < nload) {
+            const uint32_t gn = claim_next();
+            if (gn != NONE) {
+              ptx::bulk_wait_read<0>();   // the store that last used the slot (piece nload - NSLOT) has read it
+              gbuf[nload % NSLOT] = gn;
+              issue_load(gn, nload);
+              ++nload;
+            }
+            const uint32_t g = gbuf[nstore % NSLOT];
+            int peer;
+            int64_t soff, doff;
+            locate(ws, g);
+            coords(ws, g, peer, soff, doff);
+            const uint32_t slot = nstore % NSLOT;
+            mbar_wait(wc, rbar + 8u * slot, (nstore / NSLOT) & 1u, kSiteSmemFull);
+            ptx::bulk_store(reinterpret_cast<uint8_t*>(p.a2a_land[peer]) + doff, ring + slot * SLOT, chunk_bytes);
+            ptx::bulk_commit();
+            stepq[nstore & 7u] = ws.s;
+            ++nstore;
+            // all but the LAG most recent stores have landed
+            ptx::bulk_wait<LAG>();
+            while (counted + LAG < nstore) {
+              arrive(stepq[counted & 7u]);
+              ++counted;
             }
           }
           ptx::bulk_wait<0>();
-          while (sig_d < p.world) {
-            publish(sig_d, sig_mt);
-            if (++sig_mt == units) { sig_mt = 0; ++sig_d; }
+          while (counted < nstore) {
+            arrive(stepq[counted & 7u]);
+            ++counted;
           }
-          (void)groups_per_tile;
+          if (warp == 2) stamp(kTracePushDone);
         }
       }
     }
@@ -665,6 +802,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         }
       }
       if (lane == 0) ptx::bulk_commit();
+      if (nstore == 0 && ew == 0 && lane == 0) stamp(kTraceFirstStore);
       ++nstore;
     };
 
@@ -877,6 +1015,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       if (lane < p.world) flag_wait_ge(wc, p.a2a_flags[p.rank] + lane, p.epoch, kSiteA2AFlag);
       __syncwarp();
     }
+    if (ew == 0 && lane == 0) stamp(kTraceEnd);
   }
 
   // -------------------------------------------------------------------- teardown of the GEMM

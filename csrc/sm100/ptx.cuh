@@ -167,6 +167,15 @@ __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap
       "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d_cg2(uint32_t smem_dst, const CUtensorMap* m,
+                                                uint32_t bar_cluster_addr, int32_t x, int32_t y,
+                                                int32_t z, int32_t w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t smem_src, int32_t x,
                                              int32_t y, int32_t z, int32_t w) {
   asm volatile(
@@ -437,6 +446,12 @@ __device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
 }
 __device__ __forceinline__ void red_add_release_gpu(uint32_t* p, uint32_t v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// gpu-scope arrival counting between CTAs of this GPU (the flag that follows carries sys scope)
+__device__ __forceinline__ uint32_t atom_add_acq_rel_gpu(uint32_t* p, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
 }
 __device__ __forceinline__ uint32_t atom_add_acq_rel_sys(uint32_t* p, uint32_t v) {
   uint32_t old;

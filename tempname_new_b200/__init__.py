@@ -15,6 +15,7 @@ from .parallel.symm import (FluxTimeoutError, GroupBarrier, SymmBuffer, create_t
                             init_flux_shm)
 from .parallel.dist_env import DistEnvTP, DistEnvTPWithEP, MoeArguments  # noqa: F401
 from .ops.gemm_only import GemmOnly  # noqa: F401
+from .ops._dense import KernelTimeline  # noqa: F401
 from .ops.gemm_rs import GemmRS  # noqa: F401
 from .ops.ag_gemm import AGKernel  # noqa: F401
 from .ops.quantization import Quantization  # noqa: F401

@@ -38,6 +38,7 @@ class DenseArgs(ctypes.Structure):
         ("sa", _VP), ("sb", _VP), ("ag_scale_land", _VP * MAX_RANKS),
         ("blockscale", ctypes.c_int32), ("reserved3", ctypes.c_int32),
         ("stream", _VP),
+        ("trace", _VP),
     ]
 
 
@@ -79,6 +80,53 @@ def _as_scale(t: Optional[torch.Tensor], dev) -> Optional[torch.Tensor]:
     return t.reshape(-1)[:1].contiguous()
 
 
+_TIMELINE: Optional[torch.Tensor] = None
+
+TRACE_SLOTS = ("entry", "handshake", "push_done", "first_tile_loads", "last_tile_loads", "first_store",
+               "epilogue_done", "flag_wait_total") + tuple(f"slice{j}_ready" for j in range(8))
+
+
+class KernelTimeline:
+    """While active, every dense-kernel launch of this process writes a per-CTA timeline
+    (``%globaltimer`` stamps) that ``summary()`` reduces to microseconds since the first CTA started:
+    when the start handshake completed, when the pushes of the communication warps were published,
+    when the loads of the first / last tile were issued, when the epilogue stored first / finished,
+    and how long the producers waited for arrival flags in total. Only the latest launch is kept.
+    The reference exposes per-op ``profiling()`` context hooks (python/flux/cpp_mod.pyi); this is the
+    device-side counterpart for the fused kernels here."""
+
+    def __init__(self, device=None, ctas: int = 160):
+        self.buf = torch.zeros(ctas, 16, dtype=torch.int64, device=device if device is not None else "cuda")
+
+    def __enter__(self):
+        global _TIMELINE
+        _TIMELINE = self.buf
+        return self
+
+    def __exit__(self, *exc):
+        global _TIMELINE
+        _TIMELINE = None
+        return False
+
+    def summary(self) -> dict:
+        t = self.buf.cpu()
+        t = t[t[:, 0] > 0]
+        if t.numel() == 0:
+            return {}
+        t0 = int(t[:, 0].min())
+        out = {}
+        for i, name in enumerate(TRACE_SLOTS):
+            col = t[:, i]
+            if i == 7:
+                out[name + "_us"] = {"median": float(col.median()) / 1e3, "max": float(col.max()) / 1e3}
+                continue
+            col = col[col > 0]
+            if col.numel():
+                out[name + "_us"] = {"min": (int(col.min()) - t0) / 1e3, "median": (int(col.median()) - t0) / 1e3,
+                                     "max": (int(col.max()) - t0) / 1e3}
+        return out
+
+
 def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
               scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None, *,
               tile_n: int = 0, group_m: int = 0, num_sms: int = 0, act: Optional[str] = None,
@@ -95,6 +143,9 @@ def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], ou
     if a.dtype != b.dtype:
         raise TypeError("A and B must share a dtype")
     args = DenseArgs()
+    if _TIMELINE is not None:
+        _TIMELINE.zero_()
+        args.trace = _TIMELINE.data_ptr()
     args.a, args.b = a.data_ptr(), b.data_ptr()
     args.lda, args.ldb = a.stride(0), b.stride(0)
     args.N, args.K = b.shape[0], a.shape[1]

@@ -13,7 +13,7 @@ from .. import _native
 from ..parallel.symm import FluxTimeoutError
 from ._dense import current_stream_ptr, dtype_code
 
-_CHUNK = 2048
+_CHUNK = 8192
 
 
 class InplaceCast:

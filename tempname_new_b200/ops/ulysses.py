@@ -44,6 +44,7 @@ class A2AArgs(ctypes.Structure):
         ("attn", _VP),
         ("land", _VP * _dense.MAX_RANKS),
         ("a2a_flags", _VP * _dense.MAX_RANKS),
+        ("copy_local", ctypes.c_int32),
     ]
 
 
@@ -277,10 +278,17 @@ class AllToAllTransposeGemm(FusedOpBase):
             args.bs, args.local_seq, args.hd = self.bs, self.local_seq, self.hd
             args.layout = 1 if self.a2a_only else 0
             args.attn = x.data_ptr()
+            args.copy_local = 1 if a2a_transpose_output is not None else 0
             _native.check(_native.lib().fluxb_ulysses_gemm(ctypes.byref(args)), "fluxb_ulysses_gemm")
             self._after_launch()
             if a2a_transpose_output is not None:
-                a2a_transpose_output.copy_(land_local.reshape(a2a_transpose_output.shape))
+                # the landing buffer holds one slab per source rank in the source's own layout
+                W, lh = self.world, self.local_nh
+                if self.a2a_only:
+                    gi = self.land.view(self.rank, self.input_dtype, (W, M, lh, self.hd)).permute(1, 0, 2, 3)
+                else:
+                    gi = self.land.view(self.rank, self.input_dtype, (W, lh, M, self.hd)).permute(2, 0, 1, 3)
+                a2a_transpose_output.copy_(gi.reshape(a2a_transpose_output.shape))
         if output is not None:
             output.copy_(res.reshape(output.shape))
             return output

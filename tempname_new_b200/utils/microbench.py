@@ -132,6 +132,77 @@ def cmd_grouped(a):
                       "experts": E, "ms": ms, "tflops": tf, "frac_of_bf16_peak": tf / pk, "peak": src}))
 
 
+def _single_rank_group():
+    import os
+    import torch.distributed as dist
+    dev = torch.device("cuda", torch.cuda.current_device())
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29561")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    return dist.group.WORLD, dev
+
+
+def cmd_ulysses(a):
+    """World-size-1 run of the Ulysses kernels: the GEMM plus the layout change done by the
+    epilogue (pre) or by the communication warps feeding the K loop (post)."""
+    import tempname_new_b200 as flux
+    pg, dev = _single_rank_group()
+    hidden = a.heads * a.head_dim
+    if a.which == "pre":
+        op = flux.GemmAllToAllTranspose(pg, 1, 1, 1, a.seq, hidden, a.head_dim, hidden, torch.bfloat16)
+        x = torch.randn(1, a.seq, hidden, device=dev).bfloat16()
+        w = (torch.randn(hidden, hidden, device=dev) * 0.02).bfloat16()
+        fn = lambda: op.forward(x, w)  # noqa: E731
+    else:
+        op = flux.AllToAllTransposeGemm(pg, 1, 1, 1, a.heads, a.seq, a.head_dim, torch.bfloat16)
+        x = torch.randn(1, a.heads, a.seq, a.head_dim, device=dev).bfloat16()
+        w = (torch.randn(hidden, hidden, device=dev) * 0.02).bfloat16()
+        fn = lambda: op.forward(x, w)  # noqa: E731
+    ms = timed(fn, a.iters, a.warmup, not a.no_flush)
+    tf = 2.0 * a.seq * hidden * hidden / ms / 1e9
+    pk, _, src = peaks()
+    print(json.dumps({"op": "ulysses_" + a.which, "seq": a.seq, "heads": a.heads, "head_dim": a.head_dim, "ms": ms,
+                      "tflops": tf, "frac_of_bf16_peak": tf / pk, "peak": src}))
+
+
+def cmd_combine(a):
+    """World-size-1 run of the MoE top-k combine kernel (grouped GEMM excluded)."""
+    import tempname_new_b200 as flux
+    pg, dev = _single_rank_group()
+    E, topk, H = a.experts, a.topk, a.hidden
+    g = flux.testing.gen_moe_gating_args(E, topk, a.tokens, device=dev, seed=1)
+    op = flux.DisScatterBackward(E, a.tokens, H, topk, 0, 1, 1, 1, pg=pg)
+    rows = torch.randn(a.tokens * topk, H, device=dev).bfloat16()
+    fn = lambda: op.forward_gpu(rows, None, g.scatter_index, g.splits_gpu)  # noqa: E731
+    ms = timed(fn, a.iters, a.warmup, not a.no_flush)
+    nbytes = a.tokens * H * 2 * (topk + 1 + 1 + 1)   # rows read, partial written, partial read, output written
+    _, pk, src = peaks()
+    print(json.dumps({"op": "moe_combine", "tokens": a.tokens, "topk": topk, "hidden": H, "ms": ms,
+                      "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / pk, "peak": src}))
+
+
+def cmd_small(a):
+    """In-place cast, routing-index build and row all-gather (world size 1) in one go."""
+    import tempname_new_b200 as flux
+    pg, dev = _single_rank_group()
+    _, pk, src = peaks()
+    n = a.elems
+    t = torch.rand(n, device=dev)
+    op = flux.InplaceCast(n, dev)
+    ms = timed(lambda: op.from_fp32_to_bf16(t), a.iters, a.warmup, not a.no_flush)
+    print(json.dumps({"op": "inplace_cast", "elems": n, "ms": ms, "gbs": n * 6 / ms / 1e6,
+                      "frac_of_hbm_peak": n * 6 / ms / 1e6 / pk, "peak": src}))
+    ce = torch.randint(0, 64, (65536, 8), device=dev, dtype=torch.int32)
+    ms = timed(lambda: flux.moe_index_build(ce, 64), a.iters, a.warmup, not a.no_flush)
+    print(json.dumps({"op": "moe_index_build", "entries": ce.numel(), "experts": 64, "ms": ms}))
+    ag = flux.AllGatherOp(pg, 1, 16384, 4096, torch.bfloat16)
+    x = torch.randn(16384, 4096, device=dev).bfloat16()
+    ms = timed(lambda: ag.run(x), a.iters, a.warmup, not a.no_flush)
+    print(json.dumps({"op": "a2a_rows(all-gather, W=1)", "bytes": x.numel() * 2, "ms": ms,
+                      "gbs": x.numel() * 4 / ms / 1e6, "frac_of_hbm_peak": x.numel() * 4 / ms / 1e6 / pk, "peak": src}))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -164,7 +235,22 @@ def main(argv=None):
     gg.add_argument("--topk", type=int, default=8)
     gg.add_argument("--gathered", action="store_true")
     gg.set_defaults(fn=cmd_grouped)
-    for p in (g, q, b, gg):
+    u = sub.add_parser("ulysses")
+    u.add_argument("--which", default="pre", choices=["pre", "post"])
+    u.add_argument("--seq", type=int, default=4096)
+    u.add_argument("--heads", type=int, default=32)
+    u.add_argument("--head-dim", type=int, default=128)
+    u.set_defaults(fn=cmd_ulysses)
+    c = sub.add_parser("combine")
+    c.add_argument("--tokens", type=int, default=8192)
+    c.add_argument("--topk", type=int, default=8)
+    c.add_argument("--experts", type=int, default=64)
+    c.add_argument("--hidden", type=int, default=4096)
+    c.set_defaults(fn=cmd_combine)
+    sm = sub.add_parser("small")
+    sm.add_argument("--elems", type=int, default=1 << 26)
+    sm.set_defaults(fn=cmd_small)
+    for p in (g, q, b, gg, u, c, sm):
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--no-flush", action="store_true")

@@ -205,6 +205,9 @@ def check_ulysses():
                 out = op3.forward(inp, wo, a2a_transpose_output=gi)
                 assert torch.equal(gi, gi_ref), f"[rank {rank}] a2a_transpose_gemm gathered input differs"
                 close(out.reshape(-1, N), ref, f"a2a_transpose_gemm bs{bs} seq{seq} a2a_only={a2a_only}")
+            for _ in range(2):   # own slice read in place from the attention output
+                out = op3.forward(inp, wo)
+                close(out.reshape(-1, N), ref, f"a2a_transpose_gemm (in place) bs{bs} seq{seq} a2a_only={a2a_only}")
             op3.check_status()
         if perf and seq >= 8192:
             full_flops = 2.0 * bs * ls * hidden * nh * hd
@@ -224,6 +227,12 @@ def check_ulysses():
                 torch.matmul(g.reshape(-1, nh * hd), wo.t())
             t_t = timeit(torch_post)
             p0(f"a2a_transpose_gemm seq={seq} W={W}: fluxb {t_f:.3f} ms | torch+nccl {t_t:.3f} ms")
+            if "--timeline" in sys.argv:
+                with flux.KernelTimeline(dev) as tl:
+                    dist.barrier(pg)
+                    op3.forward(attn, wo)
+                    torch.cuda.synchronize()
+                p0(f"a2a_transpose_gemm timeline (us): {tl.summary()}")
     p0(f"ulysses ok (W={W})")
 
 

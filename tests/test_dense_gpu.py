@@ -103,6 +103,44 @@ def test_single_rank_fused_ops_match_matmul(dev):
     rs.check_status()
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("a2a_only", [False, True])
+def test_single_rank_ulysses_projections(dev, a2a_only):
+    """World size 1: the pre-attention epilogue store and the post-attention input read (in place,
+    and through the landing buffer when the re-laid-out input is asked for) against fp32 matmul."""
+    import os
+    import torch.distributed as dist
+    import tempname_new_b200 as flux
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29541")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    pg = dist.group.WORLD
+    bs, seq, nh, hd = 2, 384, 4, 128
+    hidden = nh * hd
+    x = (torch.randn(bs, seq, hidden, device=dev) * 0.5).bfloat16()
+    w = (torch.randn(hidden, hidden, device=dev) * 0.05).bfloat16()
+    y = (x.reshape(-1, hidden).float() @ w.float().t())
+    pre = flux.GemmAllToAllTranspose(pg, 1, 1, bs, seq, hidden, hd, hidden, torch.bfloat16)
+    (q,) = pre.forward(x, w)
+    ref_q = y.reshape(bs, seq, nh, hd).permute(0, 2, 1, 3)
+    assert (q.float() - ref_q).abs().max().item() <= _tol(ref_q)
+    pre.check_status()
+    attn = (torch.randn(bs, nh, seq, hd, device=dev) * 0.5).bfloat16()
+    inp = attn.permute(0, 2, 1, 3).contiguous() if a2a_only else attn
+    gi_ref = attn.permute(0, 2, 1, 3).reshape(bs, seq, hidden)
+    ref = gi_ref.reshape(-1, hidden).float() @ w.float().t()
+    post = flux.AllToAllTransposeGemm(pg, 1, 1, bs, nh, seq, hd, torch.bfloat16, a2a_only=a2a_only)
+    for _ in range(2):
+        out = post.forward(inp, w)
+        assert (out.reshape(-1, hidden).float() - ref).abs().max().item() <= _tol(ref)
+    gi = torch.empty(bs, seq, hidden, device=dev, dtype=torch.bfloat16)
+    out = post.forward(inp, w, a2a_transpose_output=gi)
+    assert torch.equal(gi, gi_ref)
+    assert (out.reshape(-1, hidden).float() - ref).abs().max().item() <= _tol(ref)
+    post.check_status()
+
+
 def test_bounded_wait_reports_timeout(dev):
     """A device wait on a flag that nothing sets gives up after its limit and reports it in the
     status record; the context stays usable."""
