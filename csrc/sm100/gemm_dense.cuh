@@ -47,7 +47,8 @@ enum TraceSlot : int {
   kTraceFirstStore = 5,   // epilogue warp 4: first tile handed to the TMA store
   kTraceEnd = 6,          // epilogue warp 4: done
   kTraceFlagWait = 7,     // producer: total time spent waiting for arrival flags
-  kTraceSlice0 = 8,       // producer, first tile: 8 + j = K slice j (post-attention) became readable
+  kTraceSlice0 = 8,       // producer, first tile: 8 + j = K slice j (post-attention) became readable;
+                          // reduce-scatter: 8 = reduce tail entered, 9 = reduce tail left
 };
 constexpr int kTraceWords = 16;  // words per CTA
 constexpr int kMaxHeadGroups = 3;  // q, k, v
@@ -1044,6 +1045,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     const int64_t slab_chunks = total_chunks;
     int verified_mt = -1;
     const bool tail_f16 = p.out_f16 != 0;
+    if (threadIdx.x == 0) stamp(kTraceSlice0);      // reduce tail entered
     while (true) {
       __syncthreads();
       if (threadIdx.x == 0) {
@@ -1108,6 +1110,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         }
       }
     }
+    if (threadIdx.x == 0) stamp(kTraceSlice0 + 1);  // reduce tail left
   }
 }
 

@@ -95,6 +95,49 @@ def post_attn_a2a_torch(x: torch.Tensor, group, a2a_only: bool) -> torch.Tensor:
     return recv.permute(1, 2, 0, 3, 4).reshape(bs, ls, W * lh * hd).contiguous()   # heads ordered by source
 
 
+def _seq_lens_list(seq_lens_cpu, world: int) -> List[int]:
+    lens = [int(v) for v in (seq_lens_cpu.tolist() if hasattr(seq_lens_cpu, "tolist") else seq_lens_cpu)]
+    if len(lens) != world:
+        raise ValueError("seq_lens_cpu needs one length per rank")
+    return lens
+
+
+def pre_attn_a2a_varlen_torch(x: torch.Tensor, group, seq_lens: List[int]) -> torch.Tensor:
+    """Ranks hold different sequence lengths (reference: the ``seq_lens_cpu`` / "dp" form of
+    python/flux/testing/ulysses_sp_utils.py:46-116). x [bs, seq_lens[rank], heads, hd] ->
+    [bs, sum(seq_lens), heads/W, hd], sources in rank order."""
+    W, rank = dist.get_world_size(group), dist.get_rank(group)
+    bs, ls, nh, hd = x.shape
+    lh = nh // W
+    send = x.reshape(bs, ls, W, lh, hd).permute(2, 1, 0, 3, 4).contiguous().reshape(W * ls, bs, lh, hd)
+    recv = torch.empty((sum(seq_lens), bs, lh, hd), dtype=x.dtype, device=x.device)
+    if W > 1:
+        dist.all_to_all_single(recv, send, output_split_sizes=list(seq_lens), input_split_sizes=[ls] * W,
+                               group=group)
+    else:
+        recv = send
+    assert ls == seq_lens[rank]
+    return recv.permute(1, 0, 2, 3).contiguous()
+
+
+def post_attn_a2a_varlen_torch(x: torch.Tensor, group, a2a_only: bool, seq_lens: List[int]) -> torch.Tensor:
+    """x [bs, heads/W, sum(seq_lens), hd] (or [bs, sum, heads/W, hd] if a2a_only) ->
+    [bs, seq_lens[rank], heads*hd] (reference: ulysses_sp_utils.py:119-150, ``is_dp``)."""
+    W, rank = dist.get_world_size(group), dist.get_rank(group)
+    if not a2a_only:
+        x = x.permute(0, 2, 1, 3)
+    bs, total, lh, hd = x.shape
+    ls = seq_lens[rank]
+    send = x.permute(1, 0, 2, 3).contiguous()                                      # [sum, bs, lh, hd]
+    recv = torch.empty((W * ls, bs, lh, hd), dtype=x.dtype, device=x.device)
+    if W > 1:
+        dist.all_to_all_single(recv, send, output_split_sizes=[ls] * W, input_split_sizes=list(seq_lens),
+                               group=group)
+    else:
+        recv = send
+    return recv.reshape(W, ls, bs, lh, hd).permute(2, 1, 0, 3, 4).reshape(bs, ls, W * lh * hd).contiguous()
+
+
 def _check_sp(sp_size: int, world: int) -> None:
     if sp_size != world:
         raise NotImplementedError("sp_size must equal the size of the process group that is passed in; "
@@ -148,7 +191,7 @@ class GemmAllToAllTranspose(FusedOpBase):
         QKVPackA2A: [q, k, v], each [bs, seq, heads_x/W, hd]. Without ``outputs`` the results are
         views of the op's symmetric buffer and stay valid until the next call."""
         if seq_lens_cpu is not None:
-            raise NotImplementedError("per-rank sequence lengths are not supported")
+            return self._forward_varlen(input, weight, _seq_lens_list(seq_lens_cpu, self.world), bias, outputs)
         w = as_nk(weight, self.transpose_weight)
         x2 = input.reshape(self.bs * self.local_seq, self.hidden)
         self.epoch += 1
@@ -185,6 +228,35 @@ class GemmAllToAllTranspose(FusedOpBase):
         return res
 
     __call__ = forward
+
+    def _forward_varlen(self, input, weight, seq_lens, bias, outputs):
+        """Ranks with different sequence lengths: the projection runs on the GEMM kernel, the
+        exchange as one variable-split collective of the process group (not fused)."""
+        if self.comm_op != PreAttnAllToAllCommOp.QKVPackA2A:
+            raise NotImplementedError("per-rank sequence lengths exist for QKVPackA2A only, as in the reference "
+                                      "(python/flux/testing/ulysses_sp_utils.py:24-25)")
+        w = as_nk(weight, self.transpose_weight)
+        ls = seq_lens[self.rank]
+        x2 = input.reshape(self.bs * ls, self.hidden)
+        if x2.is_cuda:
+            x2 = x2 if x2.is_contiguous() else x2.contiguous()
+            y = torch.empty((x2.shape[0], w.shape[0]), dtype=self.output_dtype, device=x2.device)
+            _dense.plain_gemm(x2, w, y, bias)
+        else:
+            y = x2.float() @ w.float().t()
+            if bias is not None:
+                y = y + bias.float()
+            y = y.to(self.output_dtype)
+        y = y.reshape(self.bs, ls, self.nh, self.hd)
+        W = self.world
+        lq, lk = self.group_heads[0] // W, self.group_heads[1] // W
+        parts = (y[:, :, :lq * W], y[:, :, lq * W:(lq + lk) * W], y[:, :, (lq + lk) * W:])
+        res = [pre_attn_a2a_varlen_torch(t.contiguous(), self.pg, seq_lens) for t in parts]
+        if outputs is not None:
+            for dst, src in zip(outputs, res):
+                dst.copy_(src)
+            return outputs
+        return res
 
     def _forward_cpu(self, x2, w, bias):
         y = x2.float() @ w.float().t()
@@ -245,7 +317,12 @@ class AllToAllTransposeGemm(FusedOpBase):
                 sm_margin: int = 0) -> torch.Tensor:
         """input [bs, heads/W, seq, hd] (``a2a_only``: [bs, seq, heads/W, hd]) -> [bs, seq/W, N]."""
         if seq_lens_cpu is not None:
-            raise NotImplementedError("per-rank sequence lengths are not supported")
+            # ranks with different sequence lengths: variable-split collective, then the GEMM kernel
+            gi = post_attn_a2a_varlen_torch(input, self.pg, self.a2a_only, _seq_lens_list(seq_lens_cpu, self.world))
+            if a2a_transpose_output is not None:
+                a2a_transpose_output.copy_(gi.reshape(a2a_transpose_output.shape))
+            res = self.gemm_only(gi, weight, bias=bias, output=output, transpose_weight=transpose_weight)
+            return res if output is not None else res.reshape(self.bs, gi.shape[1], -1)
         w = as_nk(weight, transpose_weight)
         N = w.shape[0]
         M = self.bs * self.local_seq
@@ -297,6 +374,8 @@ class AllToAllTransposeGemm(FusedOpBase):
     __call__ = forward
 
     def post_attn_a2a(self, input, seq_lens_cpu=None, all_to_all_option=None, num_comm_sm: int = -1):
+        if seq_lens_cpu is not None:
+            return post_attn_a2a_varlen_torch(input, self.pg, self.a2a_only, _seq_lens_list(seq_lens_cpu, self.world))
         return post_attn_a2a_torch(input, self.pg, self.a2a_only)
 
     def post_attn_a2a_no_cpy(self, input, seq_lens_cpu=None, all_to_all_option=None, num_comm_sm: int = -1,
@@ -310,7 +389,10 @@ class AllToAllTransposeGemm(FusedOpBase):
         out = output if output is not None else torch.empty(
             (x2.shape[0], w.shape[0]), dtype=self.output_dtype, device=input.device)
         if not input.is_cuda:
-            out.copy_((x2.float() @ w.float().t()).to(self.output_dtype))
+            y = x2.float() @ w.float().t()
+            if bias is not None:
+                y = y + bias.float()
+            out.copy_(y.to(self.output_dtype).reshape(out.shape))
             return out
         return _dense.plain_gemm(x2 if x2.is_contiguous() else x2.contiguous(), w, out.view(x2.shape[0], -1), bias)
 

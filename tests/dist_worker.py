@@ -96,7 +96,15 @@ def check_dense():
         def torch_rs():
             dist.reduce_scatter_tensor(ref, torch.matmul(a, w.t()))
         t_f, t_t, t_g = timeit(lambda: op.forward(a, w)), timeit(torch_rs), timeit(lambda: torch.matmul(a, w.t()))
-        p0(f"GEMM-RS M={M} N={N} K={K} W={W}: fluxb {t_f:.3f} ms | torch+nccl {t_t:.3f} ms | matmul {t_g:.3f} ms")
+        t_p = timeit(lambda: flux.GemmOnly(torch.bfloat16, torch.bfloat16).forward(a, w))
+        p0(f"GEMM-RS M={M} N={N} K={K} W={W}: fluxb {t_f:.3f} ms | torch+nccl {t_t:.3f} ms | matmul {t_g:.3f} ms"
+           f" | fluxb plain GEMM {t_p:.3f} ms")
+        if "--timeline" in sys.argv:
+            with flux.KernelTimeline(dev) as tl:
+                dist.barrier(pg)
+                op.forward(a, w)
+                torch.cuda.synchronize()
+            p0(f"GEMM-RS timeline (us; slice0 = reduce tail entered, slice1 = left): {tl.summary()}")
         op.check_status()
         M, N, K = 8192, 49152, 12288
         a = (torch.randn(M // W, K, device=dev) * 0.5).bfloat16()
@@ -110,7 +118,15 @@ def check_dense():
             torch.matmul(full, w.t(), out=out)
         t_f, t_t = timeit(lambda: op.forward(a, w, output=out)), timeit(torch_ag)
         t_g = timeit(lambda: torch.matmul(full, w.t(), out=out))
-        p0(f"AG-GEMM M={M} N={N} K={K} W={W}: fluxb {t_f:.3f} ms | torch+nccl {t_t:.3f} ms | matmul {t_g:.3f} ms")
+        t_p = timeit(lambda: flux.GemmOnly(torch.bfloat16, torch.bfloat16).forward(full, w, output=out))
+        p0(f"AG-GEMM M={M} N={N} K={K} W={W}: fluxb {t_f:.3f} ms | torch+nccl {t_t:.3f} ms | matmul {t_g:.3f} ms"
+           f" | fluxb plain GEMM {t_p:.3f} ms")
+        if "--timeline" in sys.argv:
+            with flux.KernelTimeline(dev) as tl:
+                dist.barrier(pg)
+                op.forward(a, w, output=out)
+                torch.cuda.synchronize()
+            p0(f"AG-GEMM timeline (us): {tl.summary()}")
         op.check_status()
 
 

@@ -168,3 +168,26 @@ def test_bounded_wait_reports_timeout(dev):
 def test_smoke_entry(dev):
     import __graft_entry__ as g
     g.smoke()
+
+
+@pytest.mark.gpu
+def test_kernel_timeline_records_stamps(dev):
+    """The optional per-CTA timeline: stamps are ordered and cover every CTA that ran."""
+    import tempname_new_b200 as flux
+    a, b = _ab(1024, 1024, 512, dev)
+    op = flux.GemmOnly(torch.bfloat16)
+    with flux.KernelTimeline(dev) as tl:
+        out = op.forward(a, b)
+        torch.cuda.synchronize()
+    ref = a.float() @ b.float().t()
+    assert (out.float() - ref).abs().max().item() <= _tol(ref)
+    s = tl.summary()
+    assert s["entry_us"]["min"] == 0.0
+    assert s["first_tile_loads_us"]["min"] > 0.0
+    assert s["epilogue_done_us"]["max"] >= s["last_tile_loads_us"]["max"]
+    # off again: the buffer stays as it is
+    before = tl.buf.clone()
+    op.forward(a, b)
+    torch.cuda.synchronize()
+    assert torch.equal(before, tl.buf)
+

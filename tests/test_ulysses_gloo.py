@@ -62,3 +62,46 @@ def test_pre_attn_gemm_a2a_gloo():
 
 def test_post_attn_a2a_gemm_gloo():
     run_gloo(_post_attn, 2)
+
+
+def _varlen(rank, world):
+    """Ranks with different sequence lengths (``seq_lens_cpu``): q/k/v packing before attention and
+    the out-projection after it, against index-by-index statements over the concatenated sequence."""
+    import tempname_new_b200 as flux
+    bs, hidden, hd, nh, N = 2, 32, 8, 4 * world, 24
+    lens = [5 + 3 * r for r in range(world)]
+    offs = [sum(lens[:r]) for r in range(world)]
+    total = sum(lens)
+    seq_lens_cpu = torch.tensor(lens, dtype=torch.int32)
+    torch.manual_seed(2)
+    x_full = torch.randn(bs, total, hidden)
+    w = torch.randn(nh * hd, hidden) * 0.2
+    x = x_full[:, offs[rank]:offs[rank] + lens[rank]].contiguous()
+    op = flux.GemmAllToAllTranspose(dist.group.WORLD, 1, world, bs, 8 * world, hidden, hd, nh * hd, torch.float32,
+                                    gqa=2, comm_op=flux.PreAttnAllToAllCommOp.QKVPackA2A)
+    q, k, v = op.forward(x, w, seq_lens_cpu=seq_lens_cpu)
+    y = (x_full @ w.t()).reshape(bs, total, nh, hd)
+    lq, lk = 2, 1
+    yq, yk, yv = y[:, :, :lq * world], y[:, :, lq * world:(lq + lk) * world], y[:, :, (lq + lk) * world:]
+    torch.testing.assert_close(q, yq[:, :, rank * lq:(rank + 1) * lq], rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(k, yk[:, :, rank * lk:(rank + 1) * lk], rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(v, yv[:, :, rank * lk:(rank + 1) * lk], rtol=1e-5, atol=1e-5)
+    # post-attention
+    nh2 = 2 * world
+    lh = nh2 // world
+    attn_full = torch.randn(bs, nh2, total, hd)
+    wo = torch.randn(N, nh2 * hd) * 0.2
+    mine = attn_full[:, rank * lh:(rank + 1) * lh].contiguous()
+    ref_in = attn_full.permute(0, 2, 1, 3).reshape(bs, total, nh2 * hd)[:, offs[rank]:offs[rank] + lens[rank]]
+    ref = ref_in @ wo.t()
+    for a2a_only in (False, True):
+        op2 = flux.AllToAllTransposeGemm(dist.group.WORLD, 1, world, bs, nh2, 8 * world, hd, torch.float32,
+                                         a2a_only=a2a_only)
+        inp = mine.permute(0, 2, 1, 3).contiguous() if a2a_only else mine
+        out = op2.forward(inp, wo, seq_lens_cpu=seq_lens_cpu)
+        torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(op2.post_attn_a2a(inp, seq_lens_cpu=seq_lens_cpu), ref_in, rtol=0, atol=0)
+
+
+def test_per_rank_sequence_lengths_gloo():
+    run_gloo(_varlen, 2)
