@@ -11,11 +11,9 @@ namespace fluxb {
 
 std::atomic<uint64_t> g_launches{0};
 
-namespace {
-
 // Wave counters: a small pool per device, zeroed once; a launch takes the next slot and leaves
 // it at zero again when it finishes.
-static uint32_t* next_wave_counter() {
+uint32_t* next_wave_counter() {
   constexpr int kSlots = 64;
   static uint32_t* pool[64] = {nullptr};
   static std::atomic<unsigned> next{0};
@@ -29,6 +27,8 @@ static uint32_t* next_wave_counter() {
   }
   return pool[dev] + (next.fetch_add(1) % kSlots) * 32;
 }
+
+namespace {
 
 template <class Cfg>
 int launch_dense(const DenseGemmParams& p, int grid, cudaStream_t stream) {
@@ -393,12 +393,12 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   if (p.mode == kModeAllGather || p.mode == kModeA2AGemm) {
     // variants that carry the staging rings of the all-gather / all-to-all push
     if (cg == 2 && bn == 256) {
-      if (in16) return launch_dense<DenseCfg<256, 0, 5, 2, 32768>>(p, grid, stream);
-      return launch_dense<DenseCfg<256, 1, 5, 2, 32768>>(p, grid, stream);
+      if (in16) return launch_dense<DenseCfg<256, 0, 6, 2, 16384>>(p, grid, stream);
+      return launch_dense<DenseCfg<256, 1, 6, 2, 16384>>(p, grid, stream);
     }
     FLUXB_REQUIRE(cg == 1 && bn == 128, "all-gather GEMM runs as CTA pairs on 256-wide tiles or single CTAs on 128-wide tiles");
-    if (in16) return launch_dense<DenseCfg<128, 0, 5, 1, 32768>>(p, grid, stream);
-    return launch_dense<DenseCfg<128, 1, 5, 1, 32768>>(p, grid, stream);
+    if (in16) return launch_dense<DenseCfg<128, 0, 6, 1, 16384>>(p, grid, stream);
+    return launch_dense<DenseCfg<128, 1, 6, 1, 16384>>(p, grid, stream);
   }
   if (cg == 2) {
     if (in16) {

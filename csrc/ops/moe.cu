@@ -323,6 +323,10 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
     if (e && std::string(e) == "gather4") return 2;
     return 3;
   }();
+  static const int wave_env = [] {
+    const char* e = getenv("FLUXB_MOE_WAVE_SYNC");
+    return e ? atoi(e) : 0;
+  }();
   const bool pregather = a->gathered && gather_mode == 3 && a->a_sorted != nullptr;
   const bool use_gather4 = a->gathered && gather_mode == 2;
   p.E_local = a->E_local;
@@ -368,6 +372,8 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
   }
   int sms = 0;
   if ((rc = device_sm_count(&sms))) return rc;
+  // (the cp.async variant keeps its own producer warps per tile and is left alone)
+  if (wave_env != 0 && !(a->gathered && gather_mode == 1)) p.wave_ctr = next_wave_counter();
   if (pregather) {
     if (bn == 256) return launch_grouped<GroupedCfg<256, 0, 4, 3>>(p, sms, stream);
     return launch_grouped<GroupedCfg<128, 0, 5, 3>>(p, sms, stream);

@@ -46,5 +46,8 @@ int encode_tmap(CUtensorMap* out, CUtensorMapDataType dt, int nd, const void* ba
                 const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box, Swz swz);
 
 int device_sm_count(int* out);
+// A zeroed device word from a small per-device pool, for launches that keep their CTAs in step wave
+// by wave; the launch leaves it at zero again (csrc/ops/dense_gemm.cu).
+uint32_t* next_wave_counter();
 
 }  // namespace fluxb

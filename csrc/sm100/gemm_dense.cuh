@@ -153,7 +153,10 @@ struct DenseCfg {
   static constexpr int B_BYTES = B_ROWS_CTA * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_BUF_BYTES = 32 * 128;           // 32 rows x 64 bf16
-  static constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_BUF_BYTES;
+  // staging buffers per epilogue warp: the variants with a communication ring give one of the two
+  // to a sixth pipeline stage (the epilogue of a tile hides behind the next tile's main loop anyway)
+  static constexpr int EPI_BUFS = (COMM_ > 0 && !BS_) ? 1 : 2;
+  static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUFS * EPI_BUF_BYTES;
   static constexpr int BAR_BYTES = 256;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + COMM_BYTES + BAR_BYTES + 1024;
   static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared memory limit");
@@ -720,8 +723,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;              // TMEM lane quadrant this warp may read
     const int ew = warp - 4;             // epilogue warp index
-    uint8_t* my_epi = epi_ptr + ew * 2 * Cfg::EPI_BUF_BYTES;
-    const uint32_t my_epi_u32 = epi_base + ew * 2 * Cfg::EPI_BUF_BYTES;
+    uint8_t* my_epi = epi_ptr + ew * Cfg::EPI_BUFS * Cfg::EPI_BUF_BYTES;
+    const uint32_t my_epi_u32 = epi_base + ew * Cfg::EPI_BUFS * Cfg::EPI_BUF_BYTES;
     const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.bias);
     const bool f16 = p.out_f16 != 0;
     float alpha = 1.f;
@@ -762,8 +765,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           r1[j] = __float_as_uint(ptx::activate(__uint_as_float(r1[j]), p.act));
         }
       }
-      const uint32_t buf = nstore & 1u;
-      if (lane == 0) ptx::bulk_wait_read<1>();
+      const uint32_t buf = Cfg::EPI_BUFS == 2 ? (nstore & 1u) : 0u;
+      if (lane == 0) ptx::bulk_wait_read<Cfg::EPI_BUFS - 1>();
       __syncwarp();
       uint8_t* dst = my_epi + buf * Cfg::EPI_BUF_BYTES + lane * 128;
 #pragma unroll

@@ -53,6 +53,7 @@ struct GroupedParams {
   uint32_t* ag_flags[kMaxRanks];   // on every rank: [W src] last call whose shard landed
   uint32_t* start_ctr[kMaxRanks];
   uint32_t* local_cnt;             // [W]
+  uint32_t* wave_ctr;              // optional: tiles whose loads are all issued (wave-synchronous starts)
 };
 
 // GATHER_: 0 = contiguous A by TMA; 1 = gathered A rows by cp.async from four producer warps;
@@ -189,6 +190,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
         }
       }
       if (lane == 0) {
+        // wave-synchronous starts: tile nt of this CTA waits until every CTA has issued the loads
+        // of its tile nt - 1, which keeps the CTAs on neighbouring tiles and k ranges (L2 reuse)
+        if (p.wave_ctr != nullptr && nt > 0) {
+          const uint32_t need = min(static_cast<uint32_t>(nt) * gridDim.x, static_cast<uint32_t>(total_tiles));
+          flag_wait_ge(wc, p.wave_ctr, need, kSiteStartBarrier);
+        }
         for (int kb = 0; kb < k_blocks; ++kb) {
           mbar_wait(wc, empty_bar(stage), phase ^ 1u, kSiteSmemEmpty);
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
@@ -210,6 +217,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
             phase ^= 1u;
           }
         }
+        if (p.wave_ctr != nullptr &&
+            atomicAdd(p.wave_ctr, 1u) == static_cast<uint32_t>(total_tiles) - 1u)
+          atomicExch(p.wave_ctr, 0u);   // last tile of the launch: every wait was for a smaller value
       }
       __syncwarp();
     }

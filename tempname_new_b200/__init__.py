@@ -16,7 +16,8 @@ from .parallel.symm import (FluxTimeoutError, GroupBarrier, SymmBuffer, create_t
 from .parallel.dist_env import DistEnvTP, DistEnvTPWithEP, MoeArguments  # noqa: F401
 from .ops.gemm_only import GemmOnly  # noqa: F401
 from .ops._dense import KernelTimeline  # noqa: F401
-from .ops.gemm_rs import GemmRS  # noqa: F401
+from .ops.gemm_rs import (GemmRS, SegmentInfo, calc_gemm_rs_threadblock_segments_info,  # noqa: F401
+                          get_gemm_rs_threadblock_segments_info)
 from .ops.ag_gemm import AGKernel  # noqa: F401
 from .ops.quantization import Quantization  # noqa: F401
 from .ops.misc import (InplaceCast, bitwise_check, calc_scatter_index, inplace_cast_fp32_to_bf16,  # noqa: F401
@@ -35,5 +36,6 @@ from .parallel.layers import ColumnParallelLinear, RowParallelLinear, patch_mega
 from . import models, ops, parallel, testing, tuning, utils  # noqa: F401
 from .ops.coll import All2AllOp, All2AllSingle, AllGatherOp, AsyncSendRecv  # noqa: F401
 from .ops.ep_dispatch import (AGKernelInterNode, AGKernelXNode, All2AllInference, DisScatterBackward,  # noqa: F401
-                              DisScatterForward, GemmRS_multinode, GemmRSInterNode, TransportOp, bsr_reduce,
+                              DisScatterForward, GemmRS_multinode, GemmRSInterNode, TopkReduceScatterOp, TransportOp,
+                              bsr_reduce,
                               load_tuning_record, pad_m_to_TPxTile)

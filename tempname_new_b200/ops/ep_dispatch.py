@@ -132,6 +132,50 @@ class DisScatterBackward:
     local_barrier_all = ep_barrier_all
 
 
+class TopkReduceScatterOp:
+    """The communication half of MoE layer 1 on its own: expert outputs (already computed, one
+    tensor per weight group) -> per token the gate-weighted sum of its top-k rows over all ranks,
+    delivered to the token's owner (reference: ``TopkReduceScatterOp``,
+    src/pybind/gemm_grouped_v2_gather_rs.cc:166-215, src/moe_gather_rs/topk_gather_rs.cu). Runs on
+    ``moe_combine_kernel``; ``barriers``, ``n_split`` and ``use_read_mode`` select protocols that do
+    not exist here and are accepted for signature compatibility."""
+
+    def __init__(self, tp_group, max_m: int, n_dim: int, topk: int, output_dtype: torch.dtype,
+                 num_experts: int, ep_world_size: int, barriers=None, n_split: int = 4,
+                 do_all_reduce: bool = False, use_read_mode: bool = False):
+        self.pg = tp_group if tp_group is not None else dist.group.WORLD
+        world, rank = dist.get_world_size(self.pg), dist.get_rank(self.pg)
+        if world % ep_world_size:
+            raise ValueError("ep_world_size must divide the group")
+        self.do_all_reduce = do_all_reduce
+        self.inner = DisScatterBackward(num_experts, max_m // max(topk, 1), n_dim, topk, rank, world // ep_world_size,
+                                        ep_world_size, world, pg=self.pg, dtype=output_dtype)
+
+    def run(self, gemm_outs, output: Optional[torch.Tensor], ep_start: int, ep_nexperts: int, splits: torch.Tensor,
+            routing_idx: torch.Tensor, output_vec_scales=None, num_thread_blocks: int = 0, stream=None) -> torch.Tensor:
+        op = self.inner.op
+        if ep_start != op.e0 or ep_nexperts != op.E_local:
+            raise ValueError("ep_start / ep_nexperts must describe this rank's experts")
+        y = None
+        for g, t in enumerate(gemm_outs):
+            part = t
+            if output_vec_scales is not None and output_vec_scales[g] is not None:
+                part = (t.float() * output_vec_scales[g].float().reshape(-1, 1)).to(t.dtype)
+            y = part if y is None else y + part
+        out = self.inner.forward_gpu(y, None, routing_idx, splits)
+        if self.do_all_reduce:
+            parts = [torch.empty_like(out) for _ in range(op.world)]
+            dist.all_gather(parts, out, group=self.pg)
+            out = torch.cat(parts)
+        if output is not None:
+            output[: out.shape[0]].copy_(out)
+            return output
+        return out
+
+    def reset_buffer(self) -> None:
+        """Nothing to reset: flags carry the call number."""
+
+
 class All2AllInference:
     """Token all-to-all for inference-time EP (reference: ``flux.All2AllInference``): the caller
     fills ``get_input_buffer`` and gives the cumulative row splits per destination."""

@@ -13,6 +13,8 @@ a ``[W, M/W, N]`` buffer and a separate kernel reduces it.
 """
 from __future__ import annotations
 
+import dataclasses
+
 from typing import Optional
 
 import torch
@@ -131,3 +133,49 @@ class GemmRS(FusedOpBase):
         self._cpu_wait(self._cpu_words(r, OFF_CTR, 8)[:W], self.epoch, "reduce-scatter arrivals")
         mine = self.stage.view(r, self.output_dtype, (W, seg, N))
         return mine.float().sum(0).to(self.output_dtype)
+
+
+@dataclasses.dataclass
+class SegmentInfo:
+    """One run of consecutive tile rows that keeps its order when the GEMM re-orders its tile
+    rows for the reduce-scatter (reference: ``SegmentInfo``, src/pybind/gemm_rs.cc:104-108)."""
+    segment_origin: int        # owner rank of the rows
+    size: int                  # tile rows in the run
+    tile_m_start_origin: int   # first tile row in the output's own order
+    tile_m_start_new: int      # first tile row in the order the kernel visits them
+
+
+def get_gemm_rs_threadblock_segments_info(problem_shape, tiled_shape, rank: int, world_size: int,
+                                          sub_world_size: int = 0, nnodes: int = 1, use_2d_ring: bool = False,
+                                          per_tile_flags: bool = False):
+    """The order in which the reduce-scatter GEMM of this library visits the output: the segment
+    of rank+1 first, its own segment last, so that every owner receives its partial tiles spread
+    over the whole run and computes its own contribution when the others have arrived. The
+    reference computes the analogous table for its PCIe / 2-D ring orders
+    (src/pybind/gemm_rs.cc:110-140, ``ThreadBlockSwizzleSegmentUtils``); ``sub_world_size``,
+    ``use_2d_ring`` and ``per_tile_flags`` select orders that one NVSwitch domain does not need."""
+    if nnodes != 1:
+        raise NotImplementedError("one NVSwitch node")
+    M, tile_m = int(problem_shape[0]), int(tiled_shape[0])
+    if M % world_size:
+        raise ValueError("M must divide over the ranks")
+    per_seg = -(-(M // world_size) // tile_m)
+    out = []
+    for i in range(world_size):
+        seg = (rank + 1 + i) % world_size
+        out.append(SegmentInfo(seg, per_seg, seg * per_seg, i * per_seg))
+    return out
+
+
+def calc_gemm_rs_threadblock_segments_info(segments: torch.Tensor, problem_shape, tiled_shape, rank: int,
+                                           world_size: int, sub_world_size: int = 0, nnodes: int = 1,
+                                           use_2d_ring: bool = False, per_tile_flags: bool = False) -> int:
+    """Writes the table above into ``segments`` ([>= world_size, 4] int32) and returns its length."""
+    info = get_gemm_rs_threadblock_segments_info(problem_shape, tiled_shape, rank, world_size, sub_world_size,
+                                                 nnodes, use_2d_ring, per_tile_flags)
+    flat = segments.view(-1, 4)
+    for i, s in enumerate(info):
+        flat[i] = torch.tensor([s.segment_origin, s.size, s.tile_m_start_origin, s.tile_m_start_new],
+                               dtype=flat.dtype)
+    return len(info)
+

@@ -25,6 +25,16 @@ def _ep(rank, world):
     out = bwd.forward(rows * w[:, None], experts, scatter, splits)
     ref = (x_full * gate.sum(1, keepdim=True))[rank * tpr:(rank + 1) * tpr]
     torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
+    # the same combine through the stand-alone op, gate weights given as the per-row scale
+    tr = flux.TopkReduceScatterOp(dist.group.WORLD, tokens * topk, H, topk, torch.float32, E, world)
+    out2 = tr.run([rows], None, rank * E_loc, E_loc, splits, scatter, [w])
+    torch.testing.assert_close(out2, ref, rtol=1e-5, atol=1e-5)
+    seg = flux.get_gemm_rs_threadblock_segments_info((64 * world, 32), (16, 16), rank, world)
+    assert [s.segment_origin for s in seg] == [(rank + 1 + i) % world for i in range(world)]
+    assert seg[-1].segment_origin == rank and seg[0].tile_m_start_new == 0 and seg[0].size == 4
+    table = torch.zeros(world, 4, dtype=torch.int32)
+    assert flux.calc_gemm_rs_threadblock_segments_info(table, (64 * world, 32), (16, 16), rank, world) == world
+    assert table[:, 3].tolist() == [4 * i for i in range(world)]
     import pytest
     with pytest.raises(NotImplementedError):
         flux.AGKernelXNode()
