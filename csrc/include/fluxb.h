@@ -16,7 +16,7 @@ extern "C" {
 const char* fluxb_last_error(void);
 
 /* element types */
-enum { FLUXB_BF16 = 0, FLUXB_FP8_E4M3 = 1, FLUXB_FP16 = 2, FLUXB_FP32 = 3, FLUXB_FP8_E5M2 = 4 };
+enum { FLUXB_BF16 = 0, FLUXB_FP8_E4M3 = 1, FLUXB_FP16 = 2, FLUXB_FP32 = 3, FLUXB_FP8_E5M2 = 4, FLUXB_INT8 = 5 };
 /* dense modes */
 enum { FLUXB_PLAIN = 0, FLUXB_ALLGATHER = 1, FLUXB_REDUCE_SCATTER = 2, FLUXB_GEMM_A2A = 3, FLUXB_A2A_GEMM = 4 };
 
@@ -40,7 +40,7 @@ typedef struct {
   int64_t lda, ldb, ldd;     /* elements */
   int64_t bias_row_stride;   /* 0: bias is one row of N */
   int32_t M, N, K;
-  int32_t in_dtype;          /* FLUXB_BF16 | FLUXB_FP16 | FLUXB_FP8_E4M3 | FLUXB_FP8_E5M2 */
+  int32_t in_dtype;          /* FLUXB_BF16 | FLUXB_FP16 | FLUXB_FP8_E4M3 | FLUXB_FP8_E5M2 | FLUXB_INT8 (signed) */
   int32_t out_dtype;         /* FLUXB_BF16 | FLUXB_FP16 (also the dtype of bias and rs_stage) */
   const float* scale_a;      /* optional device scalars: D = (A*B^T) * scale_a * scale_b */
   const float* scale_b;

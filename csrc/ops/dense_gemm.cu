@@ -107,7 +107,7 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   FLUXB_REQUIRE(a != nullptr, "null args");
   FLUXB_REQUIRE(a->M > 0 && a->N > 0 && a->K > 0, "empty problem");
   FLUXB_REQUIRE(a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP8_E4M3 ||
-                    a->in_dtype == FLUXB_FP16 || a->in_dtype == FLUXB_FP8_E5M2,
+                    a->in_dtype == FLUXB_FP16 || a->in_dtype == FLUXB_FP8_E5M2 || a->in_dtype == FLUXB_INT8,
                 "input dtype");
   FLUXB_REQUIRE(a->out_dtype == FLUXB_BF16 || a->out_dtype == FLUXB_FP16, "output dtype");
   FLUXB_REQUIRE(a->world >= 1 && a->world <= FLUXB_MAX_RANKS, "world size 1..8");
@@ -141,7 +141,7 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   p.scale_b = a->scale_b;
   p.sa = a->sa;
   p.sb = a->sb;
-  p.ab_fmt = (a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP8_E5M2) ? 1 : 0;
+  p.ab_fmt = (a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP8_E5M2 || a->in_dtype == FLUXB_INT8) ? 1 : 0;
   p.out_f16 = a->out_dtype == FLUXB_FP16 ? 1 : 0;
   p.act = a->act;
 
@@ -363,7 +363,20 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   p.group_m = a->group_m > 0 ? a->group_m : 16 / cg;
   // post-attention: the first wave of tiles should need as few rows of the exchange as possible
   if (p.mode == kModeA2AGemm && a->world > 1 && p.group_m > 4) p.group_m = 4;
-  if (p.group_m > m_tiles_seg) p.group_m = m_tiles_seg;
+  // segmented modes: a raster band may span two consecutive segments when one segment has fewer
+  // tile rows than the band (the own shard of the all-gather stays alone: it is all there is at first)
+  p.seg_span = 1;
+  {
+    static const int pair_env = [] {
+      const char* e = getenv("FLUXB_SEG_PAIR");
+      return e ? atoi(e) : 1;
+    }();
+    if (segmented && pair_env != 0 && p.num_seg >= 3 && p.group_m > m_tiles_seg) {
+      p.seg_span = 2;
+      p.seg_solo_first = p.mode == kModeAllGather ? 1 : 0;
+    }
+  }
+  if (p.group_m > p.seg_span * m_tiles_seg) p.group_m = p.seg_span * m_tiles_seg;
 
   int sms = 0;
   if ((rc = device_sm_count(&sms))) return rc;
@@ -394,11 +407,20 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     // variants that carry the staging rings of the all-gather / all-to-all push
     if (cg == 2 && bn == 256) {
       if (in16) return launch_dense<DenseCfg<256, 0, 6, 2, 16384>>(p, grid, stream);
+      if (a->in_dtype == FLUXB_INT8) return launch_dense<DenseCfg<256, 2, 6, 2, 16384>>(p, grid, stream);
       return launch_dense<DenseCfg<256, 1, 6, 2, 16384>>(p, grid, stream);
     }
     FLUXB_REQUIRE(cg == 1 && bn == 128, "all-gather GEMM runs as CTA pairs on 256-wide tiles or single CTAs on 128-wide tiles");
     if (in16) return launch_dense<DenseCfg<128, 0, 6, 1, 16384>>(p, grid, stream);
+    if (a->in_dtype == FLUXB_INT8) return launch_dense<DenseCfg<128, 2, 6, 1, 16384>>(p, grid, stream);
     return launch_dense<DenseCfg<128, 1, 6, 1, 16384>>(p, grid, stream);
+  }
+  if (a->in_dtype == FLUXB_INT8) {
+    // signed 8-bit operands, s32 accumulation (tcgen05 kind::i8)
+    if (cg == 2 && bn == 256) return launch_dense<DenseCfg<256, 2, 6, 2>>(p, grid, stream);
+    FLUXB_REQUIRE(bn == 128, "int8 runs on 256-wide CTA-pair tiles or 128-wide single-CTA tiles");
+    if (cg == 2) return launch_dense<DenseCfg<128, 2, 8, 2>>(p, grid, stream);
+    return launch_dense<DenseCfg<128, 2, 6>>(p, grid, stream);
   }
   if (cg == 2) {
     if (in16) {

@@ -63,6 +63,7 @@ struct DenseGemmParams {
   int32_t rank, world;
   int32_t mode;
   int32_t group_m;
+  int32_t seg_span, seg_solo_first;  // raster groups of visited segments, see decode_tile
   uint32_t epoch;                // call number of the owning op object, starts at 1
   uint32_t reserved0;
   uint64_t timeout_ns;
@@ -143,7 +144,7 @@ struct DenseCfg {
   static constexpr int BM_CTA = 128;                       // rows of A / D per CTA
   static constexpr int BM = 128 * CG_;                     // rows per tile
   static constexpr int BN = BN_;
-  static constexpr int KIND = KIND_;                       // 0 = bf16, 1 = fp8 e4m3
+  static constexpr int KIND = KIND_;                       // 0 = bf16 / fp16, 1 = fp8, 2 = int8 (s32 accumulators)
   static constexpr int ELT = KIND_ == 0 ? 2 : 1;
   static constexpr int BK = 128 / ELT;                     // one 128-byte swizzle row
   static constexpr int UMMA_K = 32 / ELT;
@@ -173,19 +174,43 @@ struct TileCoord {
 
 __device__ __forceinline__ TileCoord decode_tile(const DenseGemmParams& p, int t, int m_tiles_seg,
                                                  int n_tiles, int BM, int BN) {
+  // Segments are visited in the order seg_first, seg_first + 1, ... and rastered in groups of
+  // seg_span consecutive segments (1 or 2; seg_solo_first: the first visited segment is a group
+  // of its own), so that a band of group_m tile rows can span two segments.
   const int per_seg = m_tiles_seg * n_tiles;
-  const int si = t / per_seg;
-  int r = t - si * per_seg;
-  int seg = p.seg_first + si;
-  if (seg >= p.num_seg) seg -= p.num_seg;
+  int v0, span, r;
+  if (p.seg_span <= 1) {
+    v0 = t / per_seg;
+    span = 1;
+    r = t - v0 * per_seg;
+  } else if (p.seg_solo_first && t < per_seg) {
+    v0 = 0;
+    span = 1;
+    r = t;
+  } else {
+    const int lead = p.seg_solo_first ? 1 : 0;
+    const int tt = t - lead * per_seg;
+    const int gi = tt / (2 * per_seg);
+    v0 = lead + 2 * gi;
+    span = min(2, p.num_seg - v0);
+    r = tt - gi * 2 * per_seg;
+  }
+  const int m_tiles_g = span * m_tiles_seg;
   const int G = p.group_m;
   const int per_group = G * n_tiles;
   const int gid = r / per_group;
   const int first_m = gid * G;
-  const int gsz = min(G, m_tiles_seg - first_m);
+  const int gsz = min(G, m_tiles_g - first_m);
   r -= gid * per_group;
-  const int mt = first_m + r % gsz;
+  int mt = first_m + r % gsz;
   const int nt = r / gsz;
+  int v = v0;
+  if (mt >= m_tiles_seg) {
+    mt -= m_tiles_seg;
+    ++v;
+  }
+  int seg = p.seg_first + v;
+  if (seg >= p.num_seg) seg -= p.num_seg;
   TileCoord c;
   c.seg = seg;
   c.m_tile = mt;
@@ -384,7 +409,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && leader) {
-      const uint32_t idesc = ptx::umma_idesc(p.ab_fmt, p.ab_fmt, BM, BN);
+      const uint32_t idesc = ptx::umma_idesc(p.ab_fmt, p.ab_fmt, BM, BN, 0, 0, Cfg::KIND == 2 ? 2u : 1u);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -739,6 +764,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     // thread's row) -> scale, bias, activation -> 16-bit -> swizzled staging -> TMA store
     auto emit_chunk = [&](uint32_t (&r0)[32], uint32_t (&r1)[32], int col0, int row, int64_t grow,
                           int store_row0, const CUtensorMap* tmd, int z) {
+      if constexpr (Cfg::KIND == 2) {   // s32 accumulators of the int8 kind
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          r0[j] = __float_as_uint(__int2float_rn(static_cast<int32_t>(r0[j])));
+          r1[j] = __float_as_uint(__int2float_rn(static_cast<int32_t>(r1[j])));
+        }
+      }
       if (scaled) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {

@@ -12,7 +12,7 @@ from .. import _native
 MAX_RANKS = 8
 PLAIN, ALLGATHER, REDUCE_SCATTER = 0, 1, 2
 ACT = {None: 0, "none": 0, "gelu": 1, "gelu_tanh": 1, "relu": 2, "silu": 3}
-BF16, FP8_E4M3, FP16, FP32, FP8_E5M2 = 0, 1, 2, 3, 4
+BF16, FP8_E4M3, FP16, FP32, FP8_E5M2, INT8 = 0, 1, 2, 3, 4, 5
 
 _VP = ctypes.c_void_p
 
@@ -53,6 +53,8 @@ def dtype_code(dt: torch.dtype) -> int:
         return FP32
     if dt == torch.float8_e5m2:
         return FP8_E5M2
+    if dt == torch.int8:
+        return INT8
     raise TypeError(f"unsupported dtype {dt}")
 
 

@@ -8,13 +8,13 @@ import torch
 
 from . import _dense
 
-_IN_DTYPES = (torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float8_e5m2)
+_IN_DTYPES = (torch.bfloat16, torch.float16, torch.float8_e4m3fn, torch.float8_e5m2, torch.int8)
 
 
 def _out_dtype(input_dtype: torch.dtype, output_dtype: Optional[torch.dtype]) -> torch.dtype:
     if output_dtype is not None:
         return output_dtype
-    return torch.bfloat16 if input_dtype in (torch.float8_e4m3fn, torch.float8_e5m2) else input_dtype
+    return torch.bfloat16 if input_dtype in (torch.float8_e4m3fn, torch.float8_e5m2, torch.int8) else input_dtype
 
 
 def as_nk(weight: torch.Tensor, transpose_weight: bool) -> torch.Tensor:

@@ -80,6 +80,21 @@ def test_gemm_only_fp8_per_tensor_scale(dev, dtype):
     assert (out.float() - ref).abs().max().item() <= 3e-2 * max(1.0, ref.abs().max().item())
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (1024, 768, 512)])
+def test_gemm_only_int8(dev, M, N, K):
+    """Signed 8-bit operands, s32 accumulation, dequantised by the two per-tensor scales."""
+    import tempname_new_b200 as flux
+    g = torch.Generator(device="cpu").manual_seed(5)
+    a8 = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8).to(dev)
+    b8 = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8).to(dev)
+    sa = torch.tensor([0.01], device=dev)
+    sb = torch.tensor([0.02], device=dev)
+    op = flux.GemmOnly(torch.int8, output_dtype=torch.bfloat16)
+    out = op.forward(a8, b8, input_scale=sa, weight_scale=sb)
+    ref = (a8.double() @ b8.double().t()).float() * 2e-4
+    assert (out.float() - ref).abs().max().item() <= 1e-2 * max(1.0, ref.abs().max().item())
+
+
 def test_single_rank_fused_ops_match_matmul(dev):
     """World size 1: AGKernel and GemmRS reduce to the plain kernel and must agree with it."""
     import os
