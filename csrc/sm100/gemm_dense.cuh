@@ -599,18 +599,18 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         if (lane == 0 && warp == 2) stamp(kTraceHandshake);
         if (lane == 0) {
           // One lane per warp: bulk-load a 4 KiB piece of the attention output (RG rows of one head,
-          // one contiguous run) into one of four staging slots, three loads ahead of the stores,
-          // and bulk-store it into the peer's landing slab for this source. The pieces of the whole
+          // one contiguous run) into one of two staging slots, one load ahead of the stores, and
+          // bulk-store it into the peer's landing slab for this source. The pieces of the whole
           // exchange are numbered in the order (row unit, destination step, piece) and claimed in
-          // that order by the pushing warps, so every rank fills the first row unit of all its
-          // peers first - the rows that the first wave of tiles reads. Small pieces keep the time
-          // between a piece landing and its step being published short.
-          constexpr int NSLOT = 4;
+          // that order, four at a time, by the pushing warps: warps on SMs that get more of the
+          // link take more pieces, and every rank fills the first row unit of all its peers first -
+          // the rows that the first wave of tiles reads. Small pieces keep the time between a piece
+          // landing and its step being published short.
+          constexpr int NSLOT = 2;
           constexpr int PF = NSLOT - 1;                            // loads in flight ahead of the store
           constexpr uint32_t SLOT = Cfg::COMM_BYTES / 2 / NSLOT;   // 4 KiB
-          // stores that may still be on their way to the peer when a step is published (a deeper
-          // lag did not move more bytes per second and delays the flags)
-          constexpr int LAG = 2;
+          constexpr int LAG = 2;        // stores that may still be on their way when arrivals are counted
+          constexpr uint32_t BATCH = 4; // pieces per claim
           const uint32_t ring = comm_base + (warp - 2) * (Cfg::COMM_BYTES / 2);
           const uint32_t rbar = ring_bar_base + (warp - 2) * 4 * 8u;
           const uint32_t ncw = gridDim.x * 2;
@@ -630,114 +630,127 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           };
           uint32_t total = 0;
           for (int s = 0; s < nsteps; ++s) total += step_nch(s);
-          struct Walk { int s; uint32_t first, n; };
-          auto locate = [&](Walk& w, uint32_t g) {
-            while (g >= w.first + w.n) {
-              w.first += w.n;
-              ++w.s;
-              w.n = step_nch(w.s);
-            }
-          };
+          const uint32_t nbatch = (total + BATCH - 1) / BATCH;
           const uint8_t* attn = reinterpret_cast<const uint8_t*>(p.a2a_attn);
           const int64_t seq = static_cast<int64_t>(ls) * p.world;
-          // piece g: destination rank, byte offset in the attention output, byte offset in the
-          // destination's landing buffer (slab `rank`)
-          auto coords = [&](const Walk& w, uint32_t g, int& peer, int64_t& soff, int64_t& doff) {
-            const uint32_t c = g - w.first;
-            const int mt = w.s / nd, d = d0 + w.s % nd;
-            peer = p.rank + d;
-            if (peer >= p.world) peer -= p.world;
-            const int i = static_cast<int>(c % lh);                    // head (layout 0) / part of the row group
-            const int row0 = mt * UR + static_cast<int>(c / lh) * RG;  // row of the peer's GEMM input
+          // walker over the steps (this warp's pieces come in increasing order)
+          int w_s = 0, w_mt = 0, w_peer = 0;
+          uint32_t w_first = 0, w_n = nsteps > 0 ? step_nch(0) : 0u;
+          auto enter_step = [&]() {
+            w_mt = w_s / nd;
+            w_peer = p.rank + d0 + w_s % nd;
+            if (w_peer >= p.world) w_peer -= p.world;
+          };
+          enter_step();
+          // what is in each staging slot: destination, offset there, step
+          int q_peer[NSLOT], q_step[NSLOT];
+          int64_t q_doff[NSLOT];
+          auto issue_load = [&](uint32_t g, uint32_t idx) {
+            while (g >= w_first + w_n) {
+              w_first += w_n;
+              ++w_s;
+              w_n = step_nch(w_s);
+              enter_step();
+            }
+            const uint32_t c = g - w_first;
+            const int i = static_cast<int>(c % lh);                      // head (layout 0) / part of the row group
+            const int row0 = w_mt * UR + static_cast<int>(c / lh) * RG;  // row of the peer's GEMM input
             const int b = row0 / ls, s0 = row0 % ls;
+            int64_t soff, doff;
             if (p.a2a_layout == 0) {
-              soff = ((static_cast<int64_t>(b) * lh + i) * seq + static_cast<int64_t>(peer) * ls + s0) * hd * 2;
+              soff = ((static_cast<int64_t>(b) * lh + i) * seq + static_cast<int64_t>(w_peer) * ls + s0) * hd * 2;
               doff = ((static_cast<int64_t>(p.rank) * lh + i) * rows_total + row0) * hd * 2;
             } else {
               // RG rows of all heads are one run of lh pieces
-              soff = ((static_cast<int64_t>(b) * seq + static_cast<int64_t>(peer) * ls + s0) * lh + i * RG) * hd * 2;
+              soff = ((static_cast<int64_t>(b) * seq + static_cast<int64_t>(w_peer) * ls + s0) * lh + i * RG) * hd * 2;
               doff = ((static_cast<int64_t>(p.rank) * rows_total + row0) * lh + i * RG) * hd * 2;
             }
-          };
-          // a piece of step s has landed (its bulk group is complete: the bytes are visible to this
-          // thread, and the release below carries them); whoever lands the last piece of the step
-          // tells the peer
-          auto arrive = [&](int s) {
-            const int mt = s / nd, d = d0 + s % nd;
-            int peer = p.rank + d;
-            if (peer >= p.world) peer -= p.world;
-            uint32_t* cnt = p.local_cnt + s;
-            if (ptx::atom_add_acq_rel_gpu(cnt, 1u) == step_nch(s) - 1u) {
-              *cnt = 0;
-              ptx::st_release_sys(p.a2a_flags[peer] + p.rank * units + mt, p.epoch);
-            }
-          };
-          // pieces are claimed in order from one counter, so warps on SMs that get more of the
-          // link take more pieces and the early steps finish early; the ncw failed claims that
-          // end the launch put the counter back to zero
-          uint32_t* claim = p.local_cnt + 1024;
-          bool exhausted = false;
-          constexpr uint32_t NONE = 0xffffffffu;
-          auto claim_next = [&]() -> uint32_t {
-            if (exhausted) return NONE;
-            const uint32_t g = atomicAdd(claim, 1u);
-            if (g < total) return g;
-            exhausted = true;
-            if (g == total + ncw - 1u) atomicExch(claim, 0u);
-            return NONE;
-          };
-          Walk wl{0, 0u, nsteps > 0 ? step_nch(0) : 0u};   // walker of the loads
-          Walk ws = wl;                                     // walker of the stores
-          auto issue_load = [&](uint32_t g, uint32_t idx) {
-            int peer;
-            int64_t soff, doff;
-            locate(wl, g);
-            coords(wl, g, peer, soff, doff);
             const uint32_t slot = idx % NSLOT;
+            q_peer[slot] = w_peer;
+            q_step[slot] = w_s;
+            q_doff[slot] = doff;
             ptx::mbar_arrive_expect_tx(rbar + 8u * slot, chunk_bytes);
             ptx::bulk_load(ring + slot * SLOT, attn + soff, chunk_bytes, rbar + 8u * slot);
           };
-          uint32_t gbuf[NSLOT];   // piece in each slot
+          // Pieces of step s have landed (their bulk groups are complete: the bytes are visible to
+          // this thread, and the release below carries them); whoever lands the last piece of the
+          // step tells the peer. Arrivals of the same step are counted together, up to BATCH.
+          int pend_s = -1;
+          uint32_t pend_n = 0;
+          auto flush = [&]() {
+            if (pend_n == 0) return;
+            const int mt = pend_s / nd;
+            int peer = p.rank + d0 + pend_s % nd;
+            if (peer >= p.world) peer -= p.world;
+            uint32_t* cnt = p.local_cnt + pend_s;
+            if (ptx::atom_add_acq_rel_gpu(cnt, pend_n) + pend_n == step_nch(pend_s)) {
+              *cnt = 0;
+              ptx::st_release_sys(p.a2a_flags[peer] + p.rank * units + mt, p.epoch);
+            }
+            pend_n = 0;
+          };
+          auto landed = [&](int s) {
+            if (s != pend_s) {
+              flush();
+              pend_s = s;
+            }
+            if (++pend_n == BATCH) flush();
+          };
+          // claims: batch b is pieces [b * BATCH, (b + 1) * BATCH); every warp ends with one failed
+          // claim, and the last of those puts the counter back to zero
+          uint32_t* claim = p.local_cnt + 1024;
+          bool exhausted = false;
+          uint32_t cur = 0, cur_end = 0;
+          constexpr uint32_t NONE = 0xffffffffu;
+          auto next_piece = [&]() -> uint32_t {
+            if (cur == cur_end) {
+              if (exhausted) return NONE;
+              const uint32_t b = atomicAdd(claim, 1u);
+              if (b >= nbatch) {
+                exhausted = true;
+                if (b == nbatch + ncw - 1u) atomicExch(claim, 0u);
+                return NONE;
+              }
+              cur = b * BATCH;
+              cur_end = min(cur + BATCH, total);
+            }
+            return cur++;
+          };
           int stepq[8];           // step of the last eight stored pieces
           uint32_t nload = 0, nstore = 0, counted = 0;
           for (int k = 0; k < PF; ++k) {
-            const uint32_t g = claim_next();
+            const uint32_t g = next_piece();
             if (g == NONE) break;
-            gbuf[nload % NSLOT] = g;
             issue_load(g, nload);
             ++nload;
           }
           while (nstore < nload) {
-            const uint32_t gn = claim_next();
+            const uint32_t slot = nstore % NSLOT;
+            mbar_wait(wc, rbar + 8u * slot, (nstore / NSLOT) & 1u, kSiteSmemFull);
+            ptx::bulk_store(reinterpret_cast<uint8_t*>(p.a2a_land[q_peer[slot]]) + q_doff[slot], ring + slot * SLOT,
+                            chunk_bytes);
+            ptx::bulk_commit();
+            stepq[nstore & 7u] = q_step[slot];
+            ++nstore;
+            const uint32_t gn = next_piece();
             if (gn != NONE) {
-              ptx::bulk_wait_read<0>();   // the store that last used the slot (piece nload - NSLOT) has read it
-              gbuf[nload % NSLOT] = gn;
+              ptx::bulk_wait_read<NSLOT - 1>();   // the store that last used the slot (piece nload - NSLOT) has read it
               issue_load(gn, nload);
               ++nload;
             }
-            const uint32_t g = gbuf[nstore % NSLOT];
-            int peer;
-            int64_t soff, doff;
-            locate(ws, g);
-            coords(ws, g, peer, soff, doff);
-            const uint32_t slot = nstore % NSLOT;
-            mbar_wait(wc, rbar + 8u * slot, (nstore / NSLOT) & 1u, kSiteSmemFull);
-            ptx::bulk_store(reinterpret_cast<uint8_t*>(p.a2a_land[peer]) + doff, ring + slot * SLOT, chunk_bytes);
-            ptx::bulk_commit();
-            stepq[nstore & 7u] = ws.s;
-            ++nstore;
             // all but the LAG most recent stores have landed
             ptx::bulk_wait<LAG>();
             while (counted + LAG < nstore) {
-              arrive(stepq[counted & 7u]);
+              landed(stepq[counted & 7u]);
               ++counted;
             }
           }
           ptx::bulk_wait<0>();
           while (counted < nstore) {
-            arrive(stepq[counted & 7u]);
+            landed(stepq[counted & 7u]);
             ++counted;
           }
+          flush();
           if (warp == 2) stamp(kTracePushDone);
         }
       }

@@ -118,7 +118,7 @@ def check_dense():
             torch.matmul(full, w.t(), out=out)
         t_f, t_t = timeit(lambda: op.forward(a, w, output=out)), timeit(torch_ag)
         t_g = timeit(lambda: torch.matmul(full, w.t(), out=out))
-        t_p = timeit(lambda: flux.GemmOnly(torch.bfloat16, torch.bfloat16).forward(full, w, output=out))
+        t_p = timeit(lambda: flux.GemmOnly(torch.bfloat16, torch.bfloat16).forward(full, w, output_buf=out))
         p0(f"AG-GEMM M={M} N={N} K={K} W={W}: fluxb {t_f:.3f} ms | torch+nccl {t_t:.3f} ms | matmul {t_g:.3f} ms"
            f" | fluxb plain GEMM {t_p:.3f} ms")
         if "--timeline" in sys.argv:
