@@ -29,7 +29,7 @@ if ROOT not in sys.path:
 TOKENS, HIDDEN, FFN = 8192, 12288, 49152
 METRIC = "fused-op TFLOPS (AG-GEMM + GEMM-RS, GPT-3-175B TP MLP shapes)"
 REFERENCE_UNAVAILABLE = (
-    "reference (Flux 1.1.2 fork) cannot be installed offline: pip install --no-index of /root/reference "
+    "reference (Flux 1.1.2 fork) cannot be installed offline: pip install --no-index of the reference tree "
     "fails (setup.py tries to download a cached wheel, then builds with no sources because 3rdparty/cutlass, "
     "3rdparty/nccl are empty submodules and NVSHMEM is absent); it also has no sm_100 kernels")
 

@@ -80,6 +80,26 @@ def check_dense():
             close(op.forward(a, w, gathered_input=gi), full.float() @ w.float().t(), f"AGKernel {M}x{Nn}x{K}")
             assert torch.equal(gi, full)
         op.check_status()
+    # signed 8-bit operands (s32 accumulation), dequantised by two per-tensor scales
+    M, Nn, K = 256 * W, 512, 256 * W
+    g = torch.Generator(device="cpu").manual_seed(7 + rank)
+    a8 = torch.randint(-127, 128, (M, K // W), generator=g, dtype=torch.int8).to(dev)
+    w8 = torch.randint(-127, 128, (Nn, K // W), generator=g, dtype=torch.int8).to(dev)
+    sa, sb = torch.tensor([0.02], device=dev), torch.tensor([0.01], device=dev)
+    op = flux.GemmRS(pg, 1, M, Nn, torch.int8, output_dtype=torch.bfloat16)
+    part = (a8.float() @ w8.float().t()) * 2e-4          # exact in fp32: |sum| < 2^24
+    ref32 = torch.empty(M // W, Nn, device=dev)
+    dist.reduce_scatter_tensor(ref32, part.bfloat16().float())
+    close(op.forward(a8, w8, input_scale=sa, weight_scale=sb), ref32, "GemmRS int8")
+    op.check_status()
+    a8 = torch.randint(-127, 128, (M // W, K), generator=g, dtype=torch.int8).to(dev)
+    w8 = torch.randint(-127, 128, (Nn, K), generator=g, dtype=torch.int8).to(dev)
+    op = flux.AGKernel(pg, 1, M, Nn, K, torch.int8, output_dtype=torch.bfloat16)
+    full8 = torch.empty(M, K, device=dev, dtype=torch.int8)
+    dist.all_gather_into_tensor(full8, a8)
+    close(op.forward(a8, w8, input_scale=sa, weight_scale=sb), (full8.float() @ w8.float().t()) * 2e-4,
+          "AGKernel int8")
+    op.check_status()
     gb = flux.GroupBarrier(pg)
     for _ in range(3):
         gb.barrier_all()

@@ -113,3 +113,23 @@ def test_topology_probe_with_fake_nvml():
     assert t.numa_local_world_size == 8 and t.pcie_gen == [5] * 8
     t = topo.probe(FakeNvml([18, 12, 0, 18], False))
     assert not t.has_nvlink and not t.has_nvswitch and t.has_heterogeneous_nvlink
+
+
+def test_kernel_timeline_summary_from_stamps():
+    """summary() turns raw per-CTA stamps into microseconds since the first CTA started."""
+    import torch
+    from tempname_new_b200.ops._dense import KernelTimeline, TRACE_SLOTS
+    tl = KernelTimeline(device="cpu", ctas=4)
+    base = 1_000_000
+    for cta in range(3):                      # CTA 3 never ran: all zero
+        tl.buf[cta, 0] = base + 100 * cta     # entry
+        tl.buf[cta, 3] = base + 5_000 + cta   # first tile loads
+        tl.buf[cta, 6] = base + 9_000         # end
+        tl.buf[cta, 7] = 2_000 * (cta + 1)    # a duration, not a stamp
+    s = tl.summary()
+    assert s["entry_us"] == {"min": 0.0, "median": 0.1, "max": 0.2}
+    assert s["first_tile_loads_us"]["min"] == 5.0
+    assert s["epilogue_done_us"]["max"] == 9.0
+    assert s["flag_wait_total_us"] == {"median": 4.0, "max": 6.0}
+    assert "handshake_us" not in s and len(TRACE_SLOTS) == 16
+    assert KernelTimeline(device="cpu", ctas=2).summary() == {}
