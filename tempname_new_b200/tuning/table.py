@@ -62,6 +62,27 @@ def _load_extra() -> Dict[Key, Dict[str, int]]:
 
 
 _EXTRA = None
+_OVERRIDE: Dict[Key, Dict[str, int]] = {}
+
+
+class override:
+    """``with override((m, n, k), knobs):`` pins the knobs of one shape for the calls inside the
+    block - how the tuners try candidates through the public ops."""
+
+    def __init__(self, key: Key, knobs: Dict[str, int]):
+        self.key, self.knobs = tuple(key), dict(knobs)
+
+    def __enter__(self):
+        self.prev = _OVERRIDE.get(self.key)
+        _OVERRIDE[self.key] = self.knobs
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev is None:
+            _OVERRIDE.pop(self.key, None)
+        else:
+            _OVERRIDE[self.key] = self.prev
+        return False
 
 
 def lookup(m: int, n: int, k: int, elt: int = 2) -> Dict[str, int]:
@@ -69,6 +90,8 @@ def lookup(m: int, n: int, k: int, elt: int = 2) -> Dict[str, int]:
     if _EXTRA is None:
         _EXTRA = _load_extra()
     key = (m, n, k)
+    if key in _OVERRIDE:
+        return dict(_OVERRIDE[key])
     if key in _EXTRA:
         return dict(_EXTRA[key])
     if key in DENSE_TABLE:

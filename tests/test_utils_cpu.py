@@ -133,3 +133,15 @@ def test_kernel_timeline_summary_from_stamps():
     assert s["flag_wait_total_us"] == {"median": 4.0, "max": 6.0}
     assert "handshake_us" not in s and len(TRACE_SLOTS) == 16
     assert KernelTimeline(device="cpu", ctas=2).summary() == {}
+
+
+def test_tuning_override_pins_knobs_inside_block():
+    from tempname_new_b200.tuning.table import lookup, override
+    key = (8192, 6144, 12288)
+    before = lookup(*key)
+    with override(key, {"cta_group": 1, "tile_n": 128, "group_m": 16}):
+        assert lookup(*key) == {"cta_group": 1, "tile_n": 128, "group_m": 16}
+        with override(key, {"cta_group": 2, "tile_n": 256, "group_m": 2}):
+            assert lookup(*key)["group_m"] == 2
+        assert lookup(*key)["tile_n"] == 128
+    assert lookup(*key) == before
