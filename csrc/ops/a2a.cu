@@ -81,15 +81,17 @@ __global__ void __launch_bounds__(256) a2a_rows_kernel(const __grid_constant__ A
     const uint4* src = reinterpret_cast<const uint4*>(p.in + src_row * p.row_bytes);
     uint4* dst = reinterpret_cast<uint4*>(p.out[d] + dst_row * p.row_bytes);
     const int64_t n = rows * chunks_per_row;
-    for (int64_t i = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) * 4; i < n;
-         i += static_cast<int64_t>(gridDim.x) * 256 * 4) {
-      uint4 v[4];
+    // eight 16-byte pieces per thread in flight, a warp's pieces of one round contiguous (512 B)
+    constexpr int kU = 8;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 * kU + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * 256 * kU) {
+      uint4 v[kU];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (i + u < n) v[u] = ptx::ld_global_v4(src + i + u);
+      for (int u = 0; u < kU; ++u)
+        if (i + u * 256 < n) v[u] = ptx::ld_global_v4(src + i + u * 256);
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (i + u < n) ptx::st_global_v4(dst + i + u, v[u]);
+      for (int u = 0; u < kU; ++u)
+        if (i + u * 256 < n) ptx::st_global_v4(dst + i + u * 256, v[u]);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -146,7 +148,7 @@ extern "C" int fluxb_a2a_rows(const fluxb_a2a_rows_args_t* a) {
   }
   int sms = 0, rc;
   if ((rc = device_sm_count(&sms))) return rc;
-  int grid = a->num_ctas > 0 ? a->num_ctas : 64;
+  int grid = a->num_ctas > 0 ? a->num_ctas : 128;
   if (grid > sms) grid = sms;  // all CTAs must be resident: they count arrivals together
   a2a_rows_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(a->stream)>>>(p);
   FLUXB_CUDA_OK(cudaGetLastError());

@@ -166,6 +166,8 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     if (cg == 2 && a->M / a->world >= 256) bn = 256;
     else { cg = 1; bn = 128; }
   }
+  // int8 is built for 256-wide CTA-pair tiles and 128-wide tiles only
+  if (a->in_dtype == FLUXB_INT8 && !a->blockscale && !(cg == 2 && bn == 256)) bn = 128;
   const int bm = 128 * cg;
   const int bk = 128 / elt;
   const CUtensorMapDataType in_dt =

@@ -322,6 +322,17 @@ def check_coll():
     close(out, (x_full.float() * gate.sum(1, keepdim=True))[rank * tpr:(rank + 1) * tpr], "ep combine")
     bwd.op.check_status()
     p0(f"coll ok (W={W})")
+    if perf:
+        rows_, K_ = 1024, 12288          # the activation shard of the TP-MLP step
+        agp = flux.AllGatherOp(pg, 1, rows_ * W, K_, torch.bfloat16)
+        xs = torch.randn(rows_, K_, device=dev).bfloat16()
+        full_ = torch.empty(rows_ * W, K_, device=dev, dtype=torch.bfloat16)
+        t_f = timeit(lambda: agp.run(xs))
+        t_t = timeit(lambda: dist.all_gather_into_tensor(full_, xs))
+        recv = (W - 1) * xs.numel() * 2 / 1e6
+        p0(f"AllGatherOp {rows_}x{K_} bf16 per rank, W={W}: fluxb {t_f:.3f} ms ({recv / t_f:.0f} GB/s in per GPU) | "
+           f"nccl {t_t:.3f} ms ({recv / t_t:.0f} GB/s)")
+        agp.check_status()
 
 
 def check_moe():
