@@ -307,6 +307,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       const uint32_t full_owner0 = CG == 2 ? ptx::mapa_u32(full_bar(0), 0) : full_bar(0);
       int wave = 0;
       uint64_t flag_ns = 0;
+      uint64_t ag_seen = 0;               // all-gather: shard units seen to have arrived
+      uint32_t a2a_seen[kMaxRanks] = {};  // post-attention: row units seen, per source
       stamp(kTraceEntry);
       for (int t = tile_slot; t < total_tiles; t += tile_stride, ++wave) {
         const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
@@ -322,12 +324,17 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             a_row = m_cta;  // own shard straight from the caller's tensor
           } else {
             tma = &p.tm_a_land;
-            const uint32_t* f = p.ag_flags[p.rank] + c.seg * ((p.seg_rows + p.flag_unit_rows - 1) / p.flag_unit_rows) +
-                                c.m_in_seg / p.flag_unit_rows;
-            const uint64_t w0 = p.trace != nullptr ? ptx::globaltimer_ns() : 0;
-            flag_wait_ge(wc, f, p.epoch, kSiteShardFlag);
-            ptx::fence_proxy_async_all();
-            if (p.trace != nullptr) flag_ns += ptx::globaltimer_ns() - w0;
+            // a shard unit that this thread has seen arrive needs neither the acquire nor the
+            // proxy fence again (a few microseconds per tile otherwise)
+            const int ag_units = (p.seg_rows + p.flag_unit_rows - 1) / p.flag_unit_rows;
+            const int fi = c.seg * ag_units + c.m_in_seg / p.flag_unit_rows;
+            if (fi >= 64 || ((ag_seen >> fi) & 1ull) == 0ull) {
+              const uint64_t w0 = p.trace != nullptr ? ptx::globaltimer_ns() : 0;
+              flag_wait_ge(wc, p.ag_flags[p.rank] + fi, p.epoch, kSiteShardFlag);
+              ptx::fence_proxy_async_all();
+              if (fi < 64) ag_seen |= 1ull << fi;
+              if (p.trace != nullptr) flag_ns += ptx::globaltimer_ns() - w0;
+            }
           }
         }
         // post-attention mode: the K range is W slices, one per source rank, landing
@@ -340,8 +347,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         const int hd_shift = p.a2a_hd == 128 ? 7 : 6;
         const int own_b = own_in_place ? m_cta / p.a2a_local_seq : 0;
         const int own_s = own_in_place ? p.rank * p.a2a_local_seq + m_cta % p.a2a_local_seq : 0;
-        const uint32_t* a2a_flag_row =
-            a2a_in ? p.a2a_flags[p.rank] + c.m_in_seg / p.flag_unit_rows : nullptr;
+        const int a2a_unit = a2a_in ? c.m_in_seg / p.flag_unit_rows : 0;
+        const uint32_t* a2a_flag_row = a2a_in ? p.a2a_flags[p.rank] + a2a_unit : nullptr;
         const int a2a_units = a2a_in ? (p.seg_rows + p.flag_unit_rows - 1) / p.flag_unit_rows : 0;
         int src = p.rank, kin = 0;   // source rank of the current K slice, k-block within the slice
         for (int ki = 0; ki < k_blocks; ++ki) {
@@ -351,10 +358,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             // slice j of the K loop is the one that source rank-j pushed at its step j
             kb = src * kb_per_src + kin;
             in_place = own_in_place && src == p.rank;
-            if (kin == 0 && !in_place) {
+            if (kin == 0 && !in_place && (a2a_unit >= 32 || ((a2a_seen[src] >> a2a_unit) & 1u) == 0u)) {
               const uint64_t w0 = p.trace != nullptr ? ptx::globaltimer_ns() : 0;
               flag_wait_ge(wc, a2a_flag_row + src * a2a_units, p.epoch, kSiteA2AFlag);
               ptx::fence_proxy_async_all();
+              if (a2a_unit < 32) a2a_seen[src] |= 1u << a2a_unit;
               if (p.trace != nullptr) {
                 flag_ns += ptx::globaltimer_ns() - w0;
                 int j = p.rank - src;
@@ -1091,7 +1099,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     const uint4* stage = reinterpret_cast<const uint4*>(p.rs_stage);
     uint4* out = reinterpret_cast<uint4*>(p.rs_out);
     const int64_t slab_chunks = total_chunks;
-    int verified_mt = -1;
     const bool tail_f16 = p.out_f16 != 0;
     if (threadIdx.x == 0) stamp(kTraceSlice0);      // reduce tail entered
     while (true) {
@@ -1104,6 +1111,18 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       __syncthreads();
       const uint32_t u = *claim_slot;
       if (u >= units) break;
+      {
+        // every source's slab rows of this unit must have landed: one thread per source looks at
+        // the flags of the tile rows the unit touches (usually one), the block barrier passes it on
+        const int64_t c0 = static_cast<int64_t>(u) * kUnit;
+        const int64_t c1 = (c0 + kUnit < total_chunks ? c0 + kUnit : total_chunks) - 1;
+        const int mt0 = static_cast<int>((c0 / chunks_per_row) / BM);
+        const int mt1 = static_cast<int>((c1 / chunks_per_row) / BM);
+        if (static_cast<int>(threadIdx.x) < p.world)
+          for (int mt = mt0; mt <= mt1; ++mt)
+            flag_wait_ge(wc, p.rs_ctr[p.rank] + mt * kMaxRanks + threadIdx.x, p.epoch, kSiteTileCounter);
+        __syncthreads();
+      }
       if (threadIdx.x >= 256) continue;  // (block-scaled variant runs 384 threads)
 #pragma unroll 1
       for (int rep = 0; rep < kUnit / 256; rep += 2) {
@@ -1113,14 +1132,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         for (int h = 0; h < 2; ++h) {
           idx[h] = static_cast<int64_t>(u) * kUnit + (rep + h) * 256 + threadIdx.x;
           ok[h] = idx[h] < total_chunks;
-          if (ok[h]) {
-            const int mt = static_cast<int>((idx[h] / chunks_per_row) / BM);
-            if (mt != verified_mt) {
-              for (int src = 0; src < p.world; ++src)
-                flag_wait_ge(wc, p.rs_ctr[p.rank] + mt * kMaxRanks + src, p.epoch, kSiteTileCounter);
-              verified_mt = mt;
-            }
-          }
+
         }
         float accv[2][8];
 #pragma unroll
