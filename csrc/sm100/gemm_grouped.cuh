@@ -273,17 +273,46 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
         const uint32_t cw = blockIdx.x * 2 + (warp - 2), ncw = gridDim.x * 2;
         const int64_t row_bytes = static_cast<int64_t>(p.K) * Cfg::ELT;
         uint32_t used[4] = {0u, 0u, 0u, 0u};   // loads seen by each ring barrier (their phase)
-        auto move = [&](const uint8_t* from, uint8_t* to, uint32_t sz, uint32_t slot_off, uint32_t bar_id) {
-          const uint32_t ph = used[bar_id] & 1u;
-          ++used[bar_id];
-          ptx::mbar_arrive_expect_tx(rbar + 8u * bar_id, sz);
-          ptx::bulk_load(ring + slot_off, from, sz, rbar + 8u * bar_id);
-          mbar_wait(wc, rbar + 8u * bar_id, ph, kSiteSmemFull);
-          ptx::bulk_store(to, ring + slot_off, sz);
-          ptx::bulk_commit();
+        struct Item {
+          const uint8_t* from;
+          uint8_t* to;
+          uint32_t sz;
+        };
+        // Copies the pieces that `gen` hands out through NS staging slots of SZ bytes (barrier of
+        // slot i: i * bar_stride): NS - 1 loads are in flight ahead of the store that is being
+        // issued, so neither the load latency nor the store latency is paid per piece. Every slot
+        // is free when this starts (each step ends with a full bulk wait).
+        auto pipe = [&](auto&& gen, const uint32_t NS, const uint32_t SZ, const uint32_t bar_stride) {
+          Item q[4];
+          uint32_t qph[4];
+          uint32_t head = 0, tail = 0;
+          auto issue = [&](const Item& it) {
+            const uint32_t slot = tail % NS, bar = slot * bar_stride;
+            qph[slot] = used[bar] & 1u;
+            ++used[bar];
+            q[slot] = it;
+            ptx::mbar_arrive_expect_tx(rbar + 8u * bar, it.sz);
+            ptx::bulk_load(ring + slot * SZ, it.from, it.sz, rbar + 8u * bar);
+            ++tail;
+          };
+          Item it;
+          for (uint32_t k = 0; k + 1 < NS; ++k) {
+            if (!gen(it)) break;
+            issue(it);
+          }
+          while (head < tail) {
+            const uint32_t slot = head % NS, bar = slot * bar_stride;
+            mbar_wait(wc, rbar + 8u * bar, qph[slot], kSiteSmemFull);
+            ptx::bulk_store(q[slot].to, ring + slot * SZ, q[slot].sz);
+            ptx::bulk_commit();
+            ++head;
+            if (gen(it)) {
+              ptx::bulk_wait_read<1>();   // the slot's last store (two stores back) has read it
+              issue(it);
+            }
+          }
         };
         const int steps = p.do_allgather ? p.world : 1;
-        uint32_t n_push = 0, n_gath = 0;
         for (int d = 0; d < steps; ++d) {
           if (p.do_allgather) {
             constexpr uint32_t CH = Cfg::COMM_BYTES / 2 / 4;   // 4 slots of 4 KiB
@@ -293,13 +322,19 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
             int peer = p.rank - d;
             if (peer < 0) peer += p.world;
             uint8_t* land = reinterpret_cast<uint8_t*>(p.ag_land[peer]) + static_cast<int64_t>(p.rank) * bytes;
-            for (uint32_t c = cw; c < nch; c += ncw, ++n_push) {
-              const int64_t off = static_cast<int64_t>(c) * CH;
-              const int64_t left = bytes - off;
-              const uint32_t sz = left < static_cast<int64_t>(CH) ? static_cast<uint32_t>(left) : CH;
-              ptx::bulk_wait_read<3>();
-              move(src + off, land + off, sz, (n_push % 4) * CH, n_push % 4);
-            }
+            uint32_t c = cw;
+            pipe(
+                [&](Item& it) -> bool {
+                  if (c >= nch) return false;
+                  const int64_t off = static_cast<int64_t>(c) * CH;
+                  const int64_t left = bytes - off;
+                  it.from = src + off;
+                  it.to = land + off;
+                  it.sz = left < static_cast<int64_t>(CH) ? static_cast<uint32_t>(left) : CH;
+                  c += ncw;
+                  return true;
+                },
+                4u, CH, 1u);
             ptx::bulk_wait<0>();
             ptx::fence_proxy_async_all();
             uint32_t* cnt = p.local_cnt + d;
@@ -318,19 +353,45 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
               flag_wait_ge(wc, p.ag_flags[p.rank] + src, p.epoch, kSiteMoeFlag);
               ptx::fence_proxy_async_all();
             }
-            for (int el = 0; el < p.E_local; ++el) {
-              const SubProblem sp = p.sp[d * p.E_local + el];
-              for (int r = sp.row_begin + static_cast<int>(cw); r < sp.row_end; r += static_cast<int>(ncw)) {
-                const uint8_t* from = tokens + static_cast<int64_t>(p.gather_index[r]) * row_bytes;
-                uint8_t* to = sorted + static_cast<int64_t>(r - row_base) * row_bytes;
-                for (int64_t off = 0; off < row_bytes; off += SLOT, ++n_gath) {
-                  const int64_t left = row_bytes - off;
-                  const uint32_t sz = left < static_cast<int64_t>(SLOT) ? static_cast<uint32_t>(left) : SLOT;
-                  ptx::bulk_wait_read<1>();
-                  move(from + off, to + off, sz, (n_gath % 2) * SLOT, (n_gath % 2) * 2);
-                }
-              }
-            }
+            // rows of the sub-problems of this step, every ncw-th row, each in pieces of SLOT bytes
+            int el = 0, r = 0, row_end = 0;
+            bool in_expert = false, have_row = false;
+            int64_t off = 0;
+            const uint8_t* from_row = nullptr;
+            uint8_t* to_row = nullptr;
+            pipe(
+                [&](Item& it) -> bool {
+                  for (;;) {
+                    if (have_row && off < row_bytes) {
+                      const int64_t left = row_bytes - off;
+                      it.from = from_row + off;
+                      it.to = to_row + off;
+                      it.sz = left < static_cast<int64_t>(SLOT) ? static_cast<uint32_t>(left) : SLOT;
+                      off += SLOT;
+                      return true;
+                    }
+                    have_row = false;
+                    if (!in_expert) {
+                      if (el >= p.E_local) return false;
+                      const SubProblem sp = p.sp[d * p.E_local + el];
+                      r = sp.row_begin + static_cast<int>(cw);
+                      row_end = sp.row_end;
+                      in_expert = true;
+                    } else {
+                      r += static_cast<int>(ncw);
+                    }
+                    if (r >= row_end) {
+                      ++el;
+                      in_expert = false;
+                      continue;
+                    }
+                    from_row = tokens + static_cast<int64_t>(p.gather_index[r]) * row_bytes;
+                    to_row = sorted + static_cast<int64_t>(r - row_base) * row_bytes;
+                    off = 0;
+                    have_row = true;
+                  }
+                },
+                2u, SLOT, 2u);
             ptx::bulk_wait<0>();
             ptx::fence_proxy_async_all();
             uint32_t* cnt = p.local_cnt + 16 + d;
