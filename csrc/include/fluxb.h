@@ -154,7 +154,8 @@ typedef struct {
   void* ag_land[FLUXB_MAX_RANKS];
   uint32_t* ag_flags[FLUXB_MAX_RANKS];
   uint32_t* start_ctr[FLUXB_MAX_RANKS];
-  uint32_t* local_cnt;
+  uint32_t* local_cnt;       /* local scratch, 1152 uint32, zero at first use: push-step counters, then
+                                one arrival counter and one flag per (expert, source) sub-problem */
   void* stream;
 } fluxb_moe_gemm_args_t;
 

@@ -365,6 +365,13 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   p.group_m = a->group_m > 0 ? a->group_m : 16 / cg;
   // post-attention: the first wave of tiles should need as few rows of the exchange as possible
   if (p.mode == kModeA2AGemm && a->world > 1 && p.group_m > 4) p.group_m = 4;
+  {
+    static const int inflight_env = [] {
+      const char* e = getenv("FLUXB_AG_INFLIGHT");
+      return e ? atoi(e) : 3;
+    }();
+    p.ag_inflight = inflight_env;
+  }
   // segmented modes: a raster band may span two consecutive segments when one segment has fewer
   // tile rows than the band (the own shard of the all-gather stays alone: it is all there is at first)
   p.seg_span = 1;

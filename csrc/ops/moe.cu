@@ -327,7 +327,8 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
     const char* e = getenv("FLUXB_MOE_WAVE_SYNC");
     return e ? atoi(e) : 0;
   }();
-  const bool pregather = a->gathered && gather_mode == 3 && a->a_sorted != nullptr;
+  // (the sorted buffer's per-sub-problem flags have room for 512 sub-problems)
+  const bool pregather = a->gathered && gather_mode == 3 && a->a_sorted != nullptr && S <= 512;
   const bool use_gather4 = a->gathered && gather_mode == 2;
   p.E_local = a->E_local;
   p.by_src = by_src ? 1 : 0;

@@ -64,6 +64,7 @@ struct DenseGemmParams {
   int32_t mode;
   int32_t group_m;
   int32_t seg_span, seg_solo_first;  // raster groups of visited segments, see decode_tile
+  int32_t ag_inflight;           // all-gather push: loads in flight ahead of the stores (1..3)
   uint32_t epoch;                // call number of the owning op object, starts at 1
   uint32_t reserved0;
   uint64_t timeout_ns;
@@ -533,57 +534,85 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
               ptx::st_release_sys(p.ag_flags[peer] + p.rank * units + mt, p.epoch);
             }
           };
-          uint32_t issued = 0;
-          int sig_d = 1, sig_mt = 0;           // next step to publish
-          uint32_t sig_end = step_chunks(0);   // chunk count at which that step is fully issued
-          for (int d = 1; d < p.world; ++d) {
-            int peer = p.rank - d;
-            if (peer < 0) peer += p.world;
-            uint8_t* land = reinterpret_cast<uint8_t*>(p.ag_land[peer]) + slab_off;
-            uint8_t* sland = Cfg::BS ? reinterpret_cast<uint8_t*>(p.ag_scale_land[peer]) + sslab_off : nullptr;
-            for (int mt = 0; mt < units; ++mt) {
-              const int rows = min(UR, p.seg_rows - mt * UR);
-              const int64_t first = static_cast<int64_t>(mt) * UR * row_bytes;
-              const int64_t bytes = rows * row_bytes;
-              const uint32_t nch_p = payload_chunks(mt);
-              const int64_t sfirst = static_cast<int64_t>(mt) * (UR / 128) * srow_bytes;
-              const int64_t sbytes = scale_bytes(mt);
+          // this warp's chunks, step by step (destination, then row unit); chunk c of a step
+          // belongs to warp c % ncw
+          int g_d = 1, g_mt = 0;
+          uint32_t g_c = cw;
+          auto gen = [&](const uint8_t*& from, uint8_t*& to, uint32_t& sz) -> bool {
+            for (;;) {
+              if (g_d >= p.world) return false;
+              const int rows = min(UR, p.seg_rows - g_mt * UR);
+              const uint32_t nch_p = payload_chunks(g_mt);
+              const int64_t sbytes = scale_bytes(g_mt);
               const uint32_t nch = nch_p + static_cast<uint32_t>((sbytes + CH - 1) / CH);
-              for (uint32_t c = cw; c < nch; c += ncw) {
-                const uint8_t* from;
-                uint8_t* to;
+              if (g_c < nch) {
+                int peer = p.rank - g_d;
+                if (peer < 0) peer += p.world;
                 int64_t left;
-                if (c < nch_p) {
-                  const int64_t off = first + static_cast<int64_t>(c) * CH;
+                if (g_c < nch_p) {
+                  const int64_t off = static_cast<int64_t>(g_mt) * UR * row_bytes + static_cast<int64_t>(g_c) * CH;
                   from = src + off;
-                  to = land + off;
-                  left = bytes - static_cast<int64_t>(c) * CH;
+                  to = reinterpret_cast<uint8_t*>(p.ag_land[peer]) + slab_off + off;
+                  left = rows * row_bytes - static_cast<int64_t>(g_c) * CH;
                 } else {
-                  const int64_t off = sfirst + static_cast<int64_t>(c - nch_p) * CH;
+                  const int64_t off = static_cast<int64_t>(g_mt) * (UR / 128) * srow_bytes +
+                                      static_cast<int64_t>(g_c - nch_p) * CH;
                   from = ssrc + off;
-                  to = sland + off;
-                  left = sbytes - static_cast<int64_t>(c - nch_p) * CH;
+                  to = reinterpret_cast<uint8_t*>(p.ag_scale_land[peer]) + sslab_off + off;
+                  left = sbytes - static_cast<int64_t>(g_c - nch_p) * CH;
                 }
-                const uint32_t sz = left < static_cast<int64_t>(CH) ? static_cast<uint32_t>(left) : CH;
-                const uint32_t slot = issued % NSLOT;
-                const uint32_t ph = (issued / NSLOT) & 1u;
-                ptx::bulk_wait_read<NSLOT - 1>();  // the store that last used this slot has read it
-                ptx::mbar_arrive_expect_tx(rbar + 8u * slot, sz);
-                ptx::bulk_load(ring + slot * CH, from, sz, rbar + 8u * slot);
-                mbar_wait(wc, rbar + 8u * slot, ph, kSiteSmemFull);
-                ptx::bulk_store(to, ring + slot * CH, sz);
-                ptx::bulk_commit();
-                ++issued;
+                sz = left < static_cast<int64_t>(CH) ? static_cast<uint32_t>(left) : CH;
+                g_c += ncw;
+                return true;
               }
-              // everything but the LAG most recent chunk stores has landed: publish the steps
-              // that lie entirely before that point
-              ptx::bulk_wait<LAG>();
-              const uint32_t done = issued > LAG ? issued - LAG : 0u;
-              while ((sig_d < d || (sig_d == d && sig_mt <= mt)) && sig_end <= done) {
-                publish(sig_d, sig_mt);
-                if (++sig_mt == units) { sig_mt = 0; ++sig_d; }
-                sig_end += step_chunks(sig_mt);
+              g_c = cw;
+              if (++g_mt == units) {
+                g_mt = 0;
+                ++g_d;
               }
+            }
+          };
+          // NSLOT - 1 loads are in flight ahead of the store being issued
+          uint8_t* q_to[NSLOT];
+          uint32_t q_sz[NSLOT];
+          uint32_t head = 0, tail = 0;   // stores issued, loads issued
+          auto issue = [&]() -> bool {
+            const uint8_t* from;
+            uint8_t* to;
+            uint32_t sz;
+            if (!gen(from, to, sz)) return false;
+            const uint32_t slot = tail % NSLOT;
+            q_to[slot] = to;
+            q_sz[slot] = sz;
+            ptx::mbar_arrive_expect_tx(rbar + 8u * slot, sz);
+            ptx::bulk_load(ring + slot * CH, from, sz, rbar + 8u * slot);
+            ++tail;
+            return true;
+          };
+          int sig_d = 1, sig_mt = 0;           // next step to publish
+          uint32_t sig_end = step_chunks(0);   // own chunks through that step
+          const int inflight = p.ag_inflight >= 1 && p.ag_inflight <= NSLOT - 1 ? p.ag_inflight : NSLOT - 1;
+          for (int k = 0; k < inflight; ++k)
+            if (!issue()) break;
+          while (head < tail) {
+            const uint32_t slot = head % NSLOT;
+            mbar_wait(wc, rbar + 8u * slot, (head / NSLOT) & 1u, kSiteSmemFull);
+            ptx::bulk_store(q_to[slot], ring + slot * CH, q_sz[slot]);
+            ptx::bulk_commit();
+            ++head;
+            // the slot of the next load was last read by the store NSLOT - inflight + 1 back
+            if (inflight == 3) ptx::bulk_wait_read<1>();
+            else if (inflight == 2) ptx::bulk_wait_read<2>();
+            else ptx::bulk_wait_read<3>();
+            issue();
+            // everything but the LAG most recent chunk stores has landed: publish the steps
+            // that lie entirely before that point
+            ptx::bulk_wait<LAG>();
+            const uint32_t done = head > LAG ? head - LAG : 0u;
+            while (sig_d < p.world && sig_end <= done) {
+              publish(sig_d, sig_mt);
+              if (++sig_mt == units) { sig_mt = 0; ++sig_d; }
+              if (sig_d < p.world) sig_end += step_chunks(sig_mt);
             }
           }
           ptx::bulk_wait<0>();

@@ -78,6 +78,11 @@ struct GroupedCfg {
   static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared memory limit");
 };
 
+// words of GroupedParams::local_cnt: [0, 16) arrival counters of the push steps, then one arrival
+// counter and one "rows are in the sorted buffer" flag per sub-problem (at most 512)
+constexpr int kGatherCountBase = 64;
+constexpr int kGatherFlagBase = 64 + 512;
+
 struct GroupedTile {
   int sp, row0, rows, n0, expert, src;
 };
@@ -180,13 +185,14 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
         __syncwarp();
       }
       if constexpr (Cfg::PREGATHER) {
-        const int step = g.sp / p.E_local;       // source step (0 when the schedule is not by source)
-        if (step != ready_src) {
+        // the rows of this sub-problem must be in the sorted buffer (one flag per sub-problem, so
+        // the GEMM follows the gather expert by expert instead of source by source)
+        if (g.sp != ready_src) {
           if (lane == 0) {
-            flag_wait_ge(wc, p.local_cnt + 32 + step, p.epoch, kSiteMoeFlag);
+            flag_wait_ge(wc, p.local_cnt + kGatherFlagBase + g.sp, p.epoch, kSiteMoeFlag);
             ptx::fence_proxy_async_all();
           }
-          ready_src = step;
+          ready_src = g.sp;
         }
       }
       if (lane == 0) {
@@ -353,51 +359,43 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
               flag_wait_ge(wc, p.ag_flags[p.rank] + src, p.epoch, kSiteMoeFlag);
               ptx::fence_proxy_async_all();
             }
-            // rows of the sub-problems of this step, every ncw-th row, each in pieces of SLOT bytes
-            int el = 0, r = 0, row_end = 0;
-            bool in_expert = false, have_row = false;
-            int64_t off = 0;
-            const uint8_t* from_row = nullptr;
-            uint8_t* to_row = nullptr;
-            pipe(
-                [&](Item& it) -> bool {
-                  for (;;) {
-                    if (have_row && off < row_bytes) {
-                      const int64_t left = row_bytes - off;
-                      it.from = from_row + off;
-                      it.to = to_row + off;
-                      it.sz = left < static_cast<int64_t>(SLOT) ? static_cast<uint32_t>(left) : SLOT;
-                      off += SLOT;
-                      return true;
-                    }
-                    have_row = false;
-                    if (!in_expert) {
-                      if (el >= p.E_local) return false;
-                      const SubProblem sp = p.sp[d * p.E_local + el];
-                      r = sp.row_begin + static_cast<int>(cw);
-                      row_end = sp.row_end;
-                      in_expert = true;
-                    } else {
+            // rows of the sub-problems of this step, every ncw-th row, each in pieces of SLOT bytes;
+            // each sub-problem is published on its own
+            for (int el = 0; el < p.E_local; ++el) {
+              const int spi = d * p.E_local + el;
+              const SubProblem sp = p.sp[spi];
+              int r = sp.row_begin + static_cast<int>(cw) - static_cast<int>(ncw);
+              bool have_row = false;
+              int64_t off = 0;
+              const uint8_t* from_row = nullptr;
+              uint8_t* to_row = nullptr;
+              pipe(
+                  [&](Item& it) -> bool {
+                    for (;;) {
+                      if (have_row && off < row_bytes) {
+                        const int64_t left = row_bytes - off;
+                        it.from = from_row + off;
+                        it.to = to_row + off;
+                        it.sz = left < static_cast<int64_t>(SLOT) ? static_cast<uint32_t>(left) : SLOT;
+                        off += SLOT;
+                        return true;
+                      }
                       r += static_cast<int>(ncw);
+                      if (r >= sp.row_end) return false;
+                      from_row = tokens + static_cast<int64_t>(p.gather_index[r]) * row_bytes;
+                      to_row = sorted + static_cast<int64_t>(r - row_base) * row_bytes;
+                      off = 0;
+                      have_row = true;
                     }
-                    if (r >= row_end) {
-                      ++el;
-                      in_expert = false;
-                      continue;
-                    }
-                    from_row = tokens + static_cast<int64_t>(p.gather_index[r]) * row_bytes;
-                    to_row = sorted + static_cast<int64_t>(r - row_base) * row_bytes;
-                    off = 0;
-                    have_row = true;
-                  }
-                },
-                2u, SLOT, 2u);
-            ptx::bulk_wait<0>();
-            ptx::fence_proxy_async_all();
-            uint32_t* cnt = p.local_cnt + 16 + d;
-            if (ptx::atom_add_acq_rel_sys(cnt, 1u) == ncw - 1u) {
-              *cnt = 0;
-              ptx::st_release_sys(p.local_cnt + 32 + d, p.epoch);
+                  },
+                  2u, SLOT, 2u);
+              ptx::bulk_wait<0>();
+              ptx::fence_proxy_async_all();
+              uint32_t* cnt = p.local_cnt + kGatherCountBase + spi;
+              if (ptx::atom_add_acq_rel_sys(cnt, 1u) == ncw - 1u) {
+                *cnt = 0;
+                ptx::st_release_sys(p.local_cnt + kGatherFlagBase + spi, p.epoch);
+              }
             }
           }
         }
