@@ -373,6 +373,13 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
   }
   int sms = 0;
   if ((rc = device_sm_count(&sms))) return rc;
+  {
+    static const int inflight_env = [] {
+      const char* e = getenv("FLUXB_MOE_INFLIGHT");
+      return e ? atoi(e) : 0;
+    }();
+    p.ring_inflight = inflight_env;
+  }
   // (the cp.async variant keeps its own producer warps per tile and is left alone)
   if (wave_env != 0 && !(a->gathered && gather_mode == 1)) p.wave_ctr = next_wave_counter();
   if (pregather) {

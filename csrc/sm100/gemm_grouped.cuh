@@ -54,6 +54,7 @@ struct GroupedParams {
   uint32_t* start_ctr[kMaxRanks];
   uint32_t* local_cnt;             // [W]
   uint32_t* wave_ctr;              // optional: tiles whose loads are all issued (wave-synchronous starts)
+  int32_t ring_inflight;           // loads in flight ahead of the stores in the push / gather rings (0 = all slots but one)
 };
 
 // GATHER_: 0 = contiguous A by TMA; 1 = gathered A rows by cp.async from four producer warps;
@@ -302,7 +303,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
             ++tail;
           };
           Item it;
-          for (uint32_t k = 0; k + 1 < NS; ++k) {
+          const uint32_t depth = p.ring_inflight >= 1 && static_cast<uint32_t>(p.ring_inflight) < NS
+                                     ? static_cast<uint32_t>(p.ring_inflight) : NS - 1;
+          for (uint32_t k = 0; k < depth; ++k) {
             if (!gen(it)) break;
             issue(it);
           }
@@ -313,7 +316,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
             ptx::bulk_commit();
             ++head;
             if (gen(it)) {
-              ptx::bulk_wait_read<1>();   // the slot's last store (two stores back) has read it
+              // the slot's last store (NS - depth + 1 stores back) has read it
+              if (NS - depth == 1) ptx::bulk_wait_read<1>();
+              else if (NS - depth == 2) ptx::bulk_wait_read<2>();
+              else ptx::bulk_wait_read<3>();
               issue(it);
             }
           }
