@@ -368,9 +368,13 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   {
     static const int inflight_env = [] {
       const char* e = getenv("FLUXB_AG_INFLIGHT");
-      return e ? atoi(e) : 3;
+      return e ? atoi(e) : 0;
     }();
-    p.ag_inflight = inflight_env;
+    // Three loads ahead move the shards fastest, but tiles that run while 7/8 of A is arriving are
+    // slowed by it; with many ranks a paced push (one load at a time, 176 MB in ~520 us instead
+    // of ~300 us at 8 ranks) gave the shorter kernel (0.958 against 1.043 ms), with two ranks the
+    // fast one did (3.94-4.02 against 4.10-4.12 ms).
+    p.ag_inflight = inflight_env > 0 ? inflight_env : (a->world > 2 ? 1 : 3);
   }
   // segmented modes: a raster band may span two consecutive segments when one segment has fewer
   // tile rows than the band (the own shard of the all-gather stays alone: it is all there is at first)

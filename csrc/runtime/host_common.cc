@@ -1,3 +1,4 @@
+#include <cstdlib>
 #include "host_common.h"
 
 #include <mutex>
@@ -36,6 +37,15 @@ int encode_tmap(CUtensorMap* out, CUtensorMapDataType dt, int nd, const void* ba
   if (fn == nullptr) return fail(kErrCuda, "cuTensorMapEncodeTiled is not available (no driver?)");
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
     return fail(kErrInvalid, "tensor base address must be 16-byte aligned for TMA");
+  // L2 promotion of the tiled loads: 256 B unless FLUXB_TMAP_L2PROMO says 0 (none), 64 or 128
+  static const CUtensorMapL2promotion l2promo = [] {
+    const char* e = getenv("FLUXB_TMAP_L2PROMO");
+    const int v = e ? atoi(e) : 256;
+    if (v == 0) return CU_TENSOR_MAP_L2_PROMOTION_NONE;
+    if (v == 64) return CU_TENSOR_MAP_L2_PROMOTION_L2_64B;
+    if (v == 128) return CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
+    return CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+  }();
   cuuint64_t gdim[5];
   cuuint64_t gstr[5];
   cuuint32_t bdim[5];
@@ -53,7 +63,7 @@ int encode_tmap(CUtensorMap* out, CUtensorMapDataType dt, int nd, const void* ba
   CUresult r = fn(out, dt, static_cast<cuuint32_t>(nd), const_cast<void*>(base), gdim, gstr, bdim,
                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   swz == Swz::B128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  l2promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(kErrCuda, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(int(r)));
   return kOk;
