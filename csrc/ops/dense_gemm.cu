@@ -376,6 +376,13 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     // fast one did (3.94-4.02 against 4.10-4.12 ms).
     p.ag_inflight = inflight_env > 0 ? inflight_env : (a->world > 2 ? 1 : 3);
   }
+  {
+    static const int hints_env = [] {
+      const char* e = getenv("FLUXB_L2_HINTS");
+      return e ? atoi(e) : 0;
+    }();
+    p.l2_hints = hints_env;
+  }
   // segmented modes: a raster band may span two consecutive segments when one segment has fewer
   // tile rows than the band (the own shard of the all-gather stays alone: it is all there is at first)
   p.seg_span = 1;

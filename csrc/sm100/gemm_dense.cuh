@@ -65,6 +65,8 @@ struct DenseGemmParams {
   int32_t group_m;
   int32_t seg_span, seg_solo_first;  // raster groups of visited segments, see decode_tile
   int32_t ag_inflight;           // all-gather push: loads in flight ahead of the stores (1..3)
+  int32_t l2_hints;              // 1: A tiles are loaded evict_last (the band is reused by the next waves),
+                                 // B tiles evict_first (streamed once per wave)
   uint32_t epoch;                // call number of the owning op object, starts at 1
   uint32_t reserved0;
   uint64_t timeout_ns;
@@ -308,6 +310,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       const uint32_t full_owner0 = CG == 2 ? ptx::mapa_u32(full_bar(0), 0) : full_bar(0);
       int wave = 0;
       uint64_t flag_ns = 0;
+      const uint64_t pol_a = ptx::l2_policy_evict_last(), pol_b = ptx::l2_policy_evict_first();
       uint64_t ag_seen = 0;               // all-gather: shard units seen to have arrived
       uint32_t a2a_seen[kMaxRanks] = {};  // post-attention: row units seen, per source
       stamp(kTraceEntry);
@@ -388,17 +391,24 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
             if (in_place) ptx::tma_load_4d(sa, &p.tm_a_own, full_bar(stage), own_col, own_s, own_head, own_b);
             else if (a2a_in) ptx::tma_load_4d(sa, &p.tm_a_land4, full_bar(stage), own_col, m_cta, own_head, ld_src);
+            else if (p.l2_hints) ptx::tma_load_2d_hint(sa, tma, full_bar(stage), kb * BK, a_row, pol_a);
             else ptx::tma_load_2d(sa, tma, full_bar(stage), kb * BK, a_row);
-            ptx::tma_load_2d(sa + Cfg::A_BYTES, &p.tm_b, full_bar(stage), kb * BK, c.n0);
+            if (p.l2_hints) ptx::tma_load_2d_hint(sa + Cfg::A_BYTES, &p.tm_b, full_bar(stage), kb * BK, c.n0, pol_b);
+            else ptx::tma_load_2d(sa + Cfg::A_BYTES, &p.tm_b, full_bar(stage), kb * BK, c.n0);
           } else {
             // both CTAs' bytes are counted on the leader's barrier
             const uint32_t fb = full_owner0 + 8u * stage;
             if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * Cfg::STAGE_BYTES);
             if (in_place) ptx::tma_load_4d_cg2(sa, &p.tm_a_own, fb, own_col, own_s, own_head, own_b);
             else if (a2a_in) ptx::tma_load_4d_cg2(sa, &p.tm_a_land4, fb, own_col, m_cta, own_head, ld_src);
+            else if (p.l2_hints) ptx::tma_load_2d_cg2_hint(sa, tma, fb, kb * BK, a_row, pol_a);
             else ptx::tma_load_2d_cg2(sa, tma, fb, kb * BK, a_row);
-            ptx::tma_load_2d_cg2(sa + Cfg::A_BYTES, &p.tm_b, fb, kb * BK,
-                                 c.n0 + static_cast<int>(cta_rank) * Cfg::B_ROWS_CTA);
+            if (p.l2_hints)
+              ptx::tma_load_2d_cg2_hint(sa + Cfg::A_BYTES, &p.tm_b, fb, kb * BK,
+                                        c.n0 + static_cast<int>(cta_rank) * Cfg::B_ROWS_CTA, pol_b);
+            else
+              ptx::tma_load_2d_cg2(sa + Cfg::A_BYTES, &p.tm_b, fb, kb * BK,
+                                   c.n0 + static_cast<int>(cta_rank) * Cfg::B_ROWS_CTA);
           }
           if (++stage == STAGES) {
             stage = 0;
