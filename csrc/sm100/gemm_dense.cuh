@@ -316,6 +316,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       stamp(kTraceEntry);
       for (int t = tile_slot; t < total_tiles; t += tile_stride, ++wave) {
         const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
+        if (!dcheck(wc, c.seg >= 0 && c.seg < p.num_seg && c.m_in_seg >= 0 && c.m_in_seg < p.seg_rows &&
+                            c.n0 >= 0 && c.n0 < p.N,
+                    kCheckTileDecode, static_cast<uint32_t>(t), static_cast<uint32_t>(c.seg)))
+          break;
         if (p.wave_ctr != nullptr && leader && wave > 0) {
           const uint32_t need = min(static_cast<uint32_t>(wave) * tile_stride, static_cast<uint32_t>(total_tiles));
           flag_wait_ge(wc, p.wave_ctr, need, kSiteStartBarrier);
@@ -573,6 +577,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
                 }
                 sz = left < static_cast<int64_t>(CH) ? static_cast<uint32_t>(left) : CH;
                 g_c += ncw;
+                if (!dcheck(wc, left > 0 && (sz & 15u) == 0u && (reinterpret_cast<uintptr_t>(from) & 15u) == 0u &&
+                                    (reinterpret_cast<uintptr_t>(to) & 15u) == 0u,
+                            kCheckAgPush, static_cast<uint32_t>(g_d * units + g_mt), sz))
+                  return false;
                 return true;
               }
               g_c = cw;
@@ -713,6 +721,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
               doff = ((static_cast<int64_t>(p.rank) * rows_total + row0) * lh + i * RG) * hd * 2;
             }
             const uint32_t slot = idx % NSLOT;
+            {
+              const int64_t src_bytes = static_cast<int64_t>(p.a2a_bs) * lh * seq * hd * 2;
+              const int64_t land_bytes = static_cast<int64_t>(p.world) * lh * rows_total * hd * 2;
+              dcheck(wc, soff >= 0 && soff + chunk_bytes <= src_bytes && doff >= 0 &&
+                             doff + chunk_bytes <= land_bytes && ((soff | doff) & 15) == 0,
+                     kCheckA2APush, g, static_cast<uint32_t>(w_s));
+            }
             q_peer[slot] = w_peer;
             q_step[slot] = w_s;
             q_doff[slot] = doff;
@@ -881,7 +896,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       }
       ptx::fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0 && col0 < p.N && store_row0 < p.seg_rows) {
+      if (lane == 0 && col0 < p.N && store_row0 < p.seg_rows &&
+          dcheck(wc, store_row0 >= 0 && col0 >= 0 && (col0 & 7) == 0 && z >= 0 && z < kMaxRanks, kCheckStore,
+                 static_cast<uint32_t>(col0), static_cast<uint32_t>(store_row0))) {
         if (p.mode == kModeGemmA2A) {
           // 64 columns of one head, 32 consecutive sequence positions of one batch entry:
           // goes to the rank that owns the head, at this rank's place in the full sequence

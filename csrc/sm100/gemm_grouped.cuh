@@ -388,7 +388,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
                       }
                       r += static_cast<int>(ncw);
                       if (r >= sp.row_end) return false;
-                      from_row = tokens + static_cast<int64_t>(p.gather_index[r]) * row_bytes;
+                      const int tok = p.gather_index[r];
+                      const int tok_limit = p.tokens_per_rank * (p.world > 1 ? p.world : 1);
+                      if (!dcheck(wc, tok >= 0 && tok < tok_limit && r >= row_base, kCheckMoeGather,
+                                  static_cast<uint32_t>(r), static_cast<uint32_t>(tok)))
+                        return false;
+                      from_row = tokens + static_cast<int64_t>(tok) * row_bytes;
                       to_row = sorted + static_cast<int64_t>(r - row_base) * row_bytes;
                       off = 0;
                       have_row = true;

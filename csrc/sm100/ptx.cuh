@@ -618,6 +618,29 @@ __device__ __forceinline__ void wait_give_up(const WaitCtx& w, uint32_t site, ui
   }
 }
 
+// Self-checks of the kernels, compiled in with -DFLUXB_DEBUG_CHECKS (the debug build of the
+// library): a failed check records its site (100 + id) and two details in the status record,
+// raises the CTA's abort word and tells the caller to skip the access it guards. In the normal
+// build dcheck() is the constant true and the checks cost nothing.
+enum CheckSite : uint32_t {
+  kCheckTileDecode = 101,   // tile coordinates outside the problem
+  kCheckAgPush = 102,       // all-gather push: piece outside the shard / misaligned
+  kCheckA2APush = 103,      // post-attention push: piece outside the source or the landing slab
+  kCheckMoeGather = 104,    // MoE row gather: token index outside the token matrix
+  kCheckFlagEpoch = 105,    // a flag carries a call number far ahead of the current call
+  kCheckStore = 106,        // epilogue store outside the output
+};
+#ifdef FLUXB_DEBUG_CHECKS
+__device__ __forceinline__ bool dcheck(const WaitCtx& w, bool ok, uint32_t site, uint32_t d0, uint32_t d1) {
+  if (!ok) wait_give_up(w, site, d0, d1);
+  return ok;
+}
+#else
+__device__ __forceinline__ constexpr bool dcheck(const WaitCtx&, bool, uint32_t, uint32_t, uint32_t) {
+  return true;
+}
+#endif
+
 // Wait for the mbarrier phase with the given parity. Returns false if it gave up.
 __device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint32_t bar, uint32_t parity,
                                           uint32_t site) {
@@ -641,13 +664,15 @@ __device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint32_t bar, uint32
 __device__ __forceinline__ bool flag_wait_ge(const WaitCtx& w, const uint32_t* flag,
                                              uint32_t expected, uint32_t site) {
   uint32_t v = ptx::ld_acquire_sys(flag);
-  if (static_cast<int32_t>(v - expected) >= 0) return true;
+  if (static_cast<int32_t>(v - expected) >= 0)
+    return dcheck(w, v - expected < (1u << 24), kCheckFlagEpoch, v, expected);
   if (*w.abort) return false;
   const uint64_t t0 = ptx::globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
     v = ptx::ld_acquire_sys(flag);
-    if (static_cast<int32_t>(v - expected) >= 0) return true;
+    if (static_cast<int32_t>(v - expected) >= 0)
+      return dcheck(w, v - expected < (1u << 24), kCheckFlagEpoch, v, expected);
     if ((++spins & 31u) == 0u) {
       if (*w.abort) return false;
       if (ptx::globaltimer_ns() - t0 > w.timeout_ns) {

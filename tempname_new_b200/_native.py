@@ -23,6 +23,10 @@ _CSRC = _ROOT / "csrc"
 _LIBDIR = _PKG / "_lib"
 _LIB = _LIBDIR / "libfluxb.so"
 _OBJDIR = _ROOT / "build" / "obj"
+# the self-checking build (FLUXB_DEBUG=1): same sources with -DFLUXB_DEBUG_CHECKS, see
+# csrc/sm100/ptx.cuh::dcheck
+_LIB_DEBUG = _LIBDIR / "libfluxb_debug.so"
+_OBJDIR_DEBUG = _ROOT / "build" / "obj_debug"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -53,29 +57,37 @@ def sources() -> list[Path]:
     return out
 
 
-def _headers_digest() -> str:
+def debug_enabled() -> bool:
+    return os.environ.get("FLUXB_DEBUG", "0") not in ("", "0")
+
+
+def _headers_digest(flags) -> str:
     h = hashlib.sha1()
     for pat in ("**/*.cuh", "**/*.h"):
         for f in sorted(_CSRC.glob(pat)):
             h.update(f.read_bytes())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(flags).encode())
     return h.hexdigest()
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every source under ``csrc/`` for sm_100a and link ``_lib/libfluxb.so``.
+def build(force: bool = False, verbose: bool = False, debug: bool = False) -> Path:
+    """Compile every source under ``csrc/`` for sm_100a and link ``_lib/libfluxb.so``
+    (``debug``: ``_lib/libfluxb_debug.so`` with the device-side self-checks compiled in).
 
     Incremental: an object is rebuilt when its source, any header or the flags changed.
     """
     nvcc = _nvcc()
-    _OBJDIR.mkdir(parents=True, exist_ok=True)
+    objdir = _OBJDIR_DEBUG if debug else _OBJDIR
+    target = _LIB_DEBUG if debug else _LIB
+    flags = NVCC_FLAGS + (["-DFLUXB_DEBUG_CHECKS=1"] if debug else [])
+    objdir.mkdir(parents=True, exist_ok=True)
     _LIBDIR.mkdir(parents=True, exist_ok=True)
-    hdig = _headers_digest()
+    hdig = _headers_digest(flags)
     jobs = []
     objs = []
     for src in sources():
         rel = src.relative_to(_CSRC)
-        obj = _OBJDIR / (str(rel).replace("/", "__") + ".o")
+        obj = objdir / (str(rel).replace("/", "__") + ".o")
         stamp = obj.with_suffix(".stamp")
         dig = hashlib.sha1(src.read_bytes() + hdig.encode()).hexdigest()
         objs.append(obj)
@@ -85,7 +97,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     def compile_one(job):
         src, obj, stamp, dig = job
-        cmd = [nvcc, *NVCC_FLAGS, "-I", str(_CSRC / "include"), "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *flags, "-I", str(_CSRC / "include"), "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise NativeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
@@ -96,15 +108,15 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(compile_one, jobs))
-    if jobs or not _LIB.exists() or force:
-        tmp = _LIB.with_suffix(".so.tmp%d" % os.getpid())
+    if jobs or not target.exists() or force:
+        tmp = target.with_suffix(".so.tmp%d" % os.getpid())
         cmd = [nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-cudart", "static",
                "-Xcompiler", "-fPIC", "-lrt", "-lpthread", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise NativeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-        os.replace(tmp, _LIB)
-    return _LIB
+        os.replace(tmp, target)
+    return target
 
 
 def lib() -> ctypes.CDLL:
@@ -114,9 +126,11 @@ def lib() -> ctypes.CDLL:
         return _handle
     with _lock:
         if _handle is None:
-            if not _LIB.exists():
-                build()
-            h = ctypes.CDLL(str(_LIB))
+            dbg = debug_enabled()
+            path = _LIB_DEBUG if dbg else _LIB
+            if not path.exists():
+                build(debug=dbg)
+            h = ctypes.CDLL(str(path))
             h.fluxb_last_error.restype = ctypes.c_char_p
             h.fluxb_launch_count.restype = ctypes.c_uint64
             _handle = h

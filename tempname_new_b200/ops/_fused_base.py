@@ -25,6 +25,16 @@ SITE_NAMES = {
     5: "start handshake", 6: "all-gather shard flag", 7: "reduce-scatter tile counter",
     8: "barrier_all", 9: "inplace cast", 10: "all-to-all flag", 11: "MoE flag", 12: "test wait",
 }
+# self-checks of the debug build (FLUXB_DEBUG=1), csrc/sm100/ptx.cuh::CheckSite
+CHECK_NAMES = {
+    101: "tile coordinates outside the problem", 102: "all-gather push outside the shard or misaligned",
+    103: "post-attention push outside its buffers", 104: "MoE gather index outside the token matrix",
+    105: "flag carries a call number far ahead of the current call", 106: "epilogue store outside the output",
+}
+
+
+class FluxDeviceCheckError(RuntimeError):
+    """A device-side self-check of the debug build failed."""
 
 
 class FusedOpBase:
@@ -52,6 +62,11 @@ class FusedOpBase:
         if self.status is None:
             return
         st = self.status.tolist()
+        if st[0] >= 100:
+            self.status.zero_()
+            raise FluxDeviceCheckError(
+                f"{type(self).__name__}: device check '{CHECK_NAMES.get(st[0], st[0])}' failed in block {st[1]} "
+                f"(details {st[2] & 0xFFFFFFFF}, {st[3] & 0xFFFFFFFF})")
         if st[0] != 0:
             self.status.zero_()
             raise FluxTimeoutError(
