@@ -24,6 +24,26 @@ def test_debug_build_runs_the_dense_and_moe_checks_clean():
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
 
 
+@pytest.mark.gpu
+def test_debug_build_reports_a_flag_from_a_far_future_call():
+    """The call-number check is a comparison of two values the kernel already holds: a flag that is
+    2^26 calls ahead of the expected one is reported through the status word (site 105), and the
+    same wait in the normal build passes silently."""
+    code = (
+        "import ctypes, torch; from tempname_new_b200 import _native; dev = torch.device('cuda', 0); "
+        "flag = torch.full((1,), 1 << 26, dtype=torch.int32, device=dev); "
+        "status = torch.zeros(4, dtype=torch.int32, device=dev); "
+        "rc = _native.lib().fluxb_wait_flag(ctypes.c_void_p(flag.data_ptr()), ctypes.c_uint32(1), "
+        "ctypes.c_uint64(200000000), ctypes.c_void_p(status.data_ptr()), "
+        "ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)); "
+        "torch.cuda.synchronize(); print('STATUS', rc, status.tolist()[0])"
+    )
+    for debug, expect in (("1", "STATUS 0 105"), ("0", "STATUS 0 0")):
+        r = subprocess.run([sys.executable, "-c", code], cwd=ROOT, env=dict(os.environ, FLUXB_DEBUG=debug),
+                           capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0 and expect in r.stdout, r.stdout[-1000:] + r.stderr[-2000:]
+
+
 def test_debug_switch_selects_the_library(monkeypatch):
     from tempname_new_b200 import _native
     monkeypatch.setenv("FLUXB_DEBUG", "1")
