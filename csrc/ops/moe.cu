@@ -106,7 +106,7 @@ struct CombineParams {
   uint16_t* out;                // [tokens_per_rank, H]
 };
 
-__global__ void __launch_bounds__(256) moe_combine_kernel(const __grid_constant__ CombineParams p) {
+__global__ void __launch_bounds__(256, 4) moe_combine_kernel(const __grid_constant__ CombineParams p) {
   __shared__ uint32_t abort_word;
   if (threadIdx.x == 0) abort_word = 0;
   __syncthreads();
@@ -428,7 +428,13 @@ extern "C" int fluxb_moe_combine(const fluxb_moe_combine_args_t* a) {
   int sms = 0, rc;
   if ((rc = device_sm_count(&sms))) return rc;
   // every CTA takes part in the arrival counting, so all of them must be resident
-  moe_combine_kernel<<<sms * 3, 256, 0, reinterpret_cast<cudaStream_t>(a->stream)>>>(p);
+  // latency-bound streaming kernel: four CTAs per SM (64 registers) keep more rows in flight
+  static const int per_sm = [] {
+    const char* e = getenv("FLUXB_COMBINE_CTAS_PER_SM");
+    const int v = e ? atoi(e) : 4;
+    return v >= 1 && v <= 4 ? v : 4;
+  }();
+  moe_combine_kernel<<<sms * per_sm, 256, 0, reinterpret_cast<cudaStream_t>(a->stream)>>>(p);
   FLUXB_CUDA_OK(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return kOk;
