@@ -52,6 +52,34 @@ def _ag_gemm(rank, world):
     torch.testing.assert_close(out_t, out, rtol=1e-6, atol=1e-6)
 
 
+def _int8(rank, world):
+    """Signed 8-bit operands with two per-tensor scales through both fused ops (CPU statement of
+    what the kind::i8 kernels compute: exact integer products, scaled, rounded to bf16)."""
+    import tempname_new_b200 as flux
+    flux.init_flux_shm()
+    M, Kl, N = 64, 32, 48
+    g = torch.Generator().manual_seed(3 + rank)
+    a = torch.randint(-127, 128, (M, Kl), generator=g, dtype=torch.int8)
+    w = torch.randint(-127, 128, (N, Kl), generator=g, dtype=torch.int8)
+    sa, sb = torch.tensor([0.02]), torch.tensor([0.01])
+    op = flux.GemmRS(dist.group.WORLD, 1, M, N, torch.int8, output_dtype=torch.bfloat16)
+    out = op.forward(a, w, input_scale=sa, weight_scale=sb)
+    full = (a.float() @ w.float().t()) * 2e-4
+    ref = torch.empty(M // world, N)
+    dist.reduce_scatter(ref, list(full.chunk(world)))
+    assert out.dtype == torch.bfloat16
+    assert (out.float() - ref).abs().max() <= 2e-2 * ref.abs().max()     # bf16 rounding of the result
+    seg = M // world
+    w2 = torch.randint(-127, 128, (N, Kl * 2), generator=torch.Generator().manual_seed(11), dtype=torch.int8)
+    a2 = torch.randint(-127, 128, (seg, Kl * 2), generator=g, dtype=torch.int8)
+    ag = flux.AGKernel(dist.group.WORLD, 1, M, N, Kl * 2, torch.int8, output_dtype=torch.bfloat16)
+    out = ag.forward(a2, w2, input_scale=sa, weight_scale=sb)
+    parts = [torch.empty_like(a2) for _ in range(world)]
+    dist.all_gather(parts, a2)
+    ref = (torch.cat(parts).float() @ w2.float().t()) * 2e-4
+    assert (out.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
+
+
 def _symm(rank, world):
     import tempname_new_b200 as flux
     ts = flux.create_tensor_list((4, 8), torch.float32)
@@ -81,3 +109,8 @@ def test_gemm_rs_gloo_w4():
 
 def test_symmetric_memory_and_barrier_gloo():
     run_gloo(_symm, 3)
+
+
+def test_int8_operands_gloo():
+    run_gloo(_int8, 2)
+
