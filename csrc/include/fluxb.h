@@ -81,6 +81,11 @@ typedef struct {
 } fluxb_dense_args_t;
 
 int fluxb_dense_gemm(const fluxb_dense_args_t* args);
+/* Host evaluation of the dense kernel's tile order (the function the kernel itself calls):
+ * out[3t..3t+2] = (segment, tile row in the segment, first column) of tile t, t < n. No GPU needed. */
+int fluxb_decode_tiles(int32_t num_seg, int32_t seg_first, int32_t m_tiles_seg, int32_t n_tiles,
+                       int32_t group_m, int32_t seg_span, int32_t seg_solo_first, int32_t bm, int32_t bn,
+                       int32_t* out, int32_t n);
 /* number of kernels libfluxb launched from this process so far */
 uint64_t fluxb_launch_count(void);
 

@@ -78,6 +78,29 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   return dense_impl(a, nullptr);
 }
 
+// The tile order of the dense kernel, evaluated on the host by the same function the kernel
+// calls: out[3 * t .. 3 * t + 2] = (segment, tile row inside the segment, first column) of tile t.
+extern "C" int fluxb_decode_tiles(int32_t num_seg, int32_t seg_first, int32_t m_tiles_seg, int32_t n_tiles,
+                                  int32_t group_m, int32_t seg_span, int32_t seg_solo_first, int32_t bm,
+                                  int32_t bn, int32_t* out, int32_t n) {
+  FLUXB_REQUIRE(out != nullptr && num_seg >= 1 && m_tiles_seg >= 1 && n_tiles >= 1 && group_m >= 1, "tile grid");
+  FLUXB_REQUIRE(n <= num_seg * m_tiles_seg * n_tiles, "more tiles asked for than the grid has");
+  DenseGemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.num_seg = num_seg;
+  p.seg_first = seg_first;
+  p.group_m = group_m;
+  p.seg_span = seg_span;
+  p.seg_solo_first = seg_solo_first;
+  for (int t = 0; t < n; ++t) {
+    const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, bm, bn);
+    out[3 * t] = c.seg;
+    out[3 * t + 1] = c.m_tile;
+    out[3 * t + 2] = c.n0;
+  }
+  return kOk;
+}
+
 extern "C" int fluxb_ulysses_gemm(const fluxb_a2a_args_t* x) {
   FLUXB_REQUIRE(x != nullptr, "null args");
   FLUXB_REQUIRE(x->base.mode == FLUXB_GEMM_A2A || x->base.mode == FLUXB_A2A_GEMM, "mode");

@@ -175,7 +175,7 @@ struct TileCoord {
   int n0;        // first output column
 };
 
-__device__ __forceinline__ TileCoord decode_tile(const DenseGemmParams& p, int t, int m_tiles_seg,
+__host__ __device__ __forceinline__ TileCoord decode_tile(const DenseGemmParams& p, int t, int m_tiles_seg,
                                                  int n_tiles, int BM, int BN) {
   // Segments are visited in the order seg_first, seg_first + 1, ... and rastered in groups of
   // seg_span consecutive segments (1 or 2; seg_solo_first: the first visited segment is a group

@@ -1,0 +1,58 @@
+"""The tile order of the dense kernel, evaluated on the host by the very function the kernel
+calls (``decode_tile`` in csrc/sm100/gemm_dense.cuh, exported as ``fluxb_decode_tiles``): every
+tile exactly once, segments entered in the promised order, raster bands of ``group_m`` tile rows
+that may span two segments."""
+import ctypes
+
+import numpy as np
+import pytest
+
+
+def _decode(num_seg, seg_first, m_tiles_seg, n_tiles, group_m, seg_span, solo, bm=256, bn=256):
+    from tempname_new_b200 import _native
+    n = num_seg * m_tiles_seg * n_tiles
+    out = np.zeros(3 * n, dtype=np.int32)
+    rc = _native.lib().fluxb_decode_tiles(num_seg, seg_first, m_tiles_seg, n_tiles, group_m, seg_span, solo, bm, bn,
+                                          out.ctypes.data_as(ctypes.c_void_p), n)
+    _native.check(rc, "fluxb_decode_tiles")
+    return out.reshape(n, 3)
+
+
+@pytest.mark.parametrize("W,mts,nt,G,span,solo", [
+    (8, 4, 24, 8, 2, 1),    # all-gather GEMM of the TP-MLP step at 8 ranks
+    (8, 4, 48, 8, 2, 0),    # GEMM + reduce-scatter of the same step
+    (4, 8, 12, 8, 1, 0), (3, 4, 5, 8, 2, 0), (8, 2, 6, 4, 2, 1), (5, 3, 7, 6, 2, 0), (1, 16, 16, 8, 1, 0),
+    (2, 1, 3, 2, 1, 0),
+])
+def test_every_tile_once_and_segments_in_order(W, mts, nt, G, span, solo):
+    first = 3 % W
+    t = _decode(W, first, mts, nt, min(G, span * mts), span, solo)
+    assert len({tuple(r) for r in t.tolist()}) == W * mts * nt
+    assert t[:, 0].min() >= 0 and t[:, 0].max() < W
+    assert t[:, 1].min() >= 0 and t[:, 1].max() < mts
+    assert set(t[:, 2].tolist()) == {256 * j for j in range(nt)}
+    order = []
+    for seg in t[:, 0].tolist():
+        if seg not in order:
+            order.append(seg)
+    assert order == [(first + i) % W for i in range(W)]
+
+
+def test_bands_span_two_segments_but_the_own_shard_stays_alone():
+    W, mts, nt, G = 8, 4, 24, 8
+    t = _decode(W, 2, mts, nt, G, 2, 1)
+    per_seg = mts * nt
+    assert set(t[:per_seg, 0].tolist()) == {2}                 # first group: the own shard only
+    band = t[per_seg:per_seg + G * nt]                          # first band of the next group
+    assert set(band[:, 0].tolist()) == {3, 4}                   # eight tile rows = two segments
+    assert band[:G, 2].tolist() == [0] * G                      # rows innermost: B tile reused
+    # without pairing a band never leaves its segment
+    t1 = _decode(W, 2, mts, nt, mts, 1, 0)
+    for s in range(W):
+        assert len(set(t1[s * per_seg:(s + 1) * per_seg, 0].tolist())) == 1
+
+
+def test_decode_rejects_a_bad_grid():
+    from tempname_new_b200 import _native
+    out = np.zeros(3, dtype=np.int32)
+    assert _native.lib().fluxb_decode_tiles(0, 0, 1, 1, 1, 1, 0, 256, 256, out.ctypes.data_as(ctypes.c_void_p), 1) != 0
