@@ -25,7 +25,8 @@ from .ops.misc import (InplaceCast, bitwise_check, calc_scatter_index, inplace_c
 from .ops.blockscale_gemm import BlockScaleGemm, blockscale_gemm_torch  # noqa: F401
 from .ops.ulysses import AllToAllTransposeGemm, GemmAllToAllTranspose  # noqa: F401
 from .ops.moe import (GemmGroupedV2, GemmGroupedV2AGScatterOp, GemmGroupedV2GatherRSOp, GemmGroupedV3,  # noqa: F401
-                      GemmGroupedV3AGScatter, GemmGroupedV3GatherRS, topk_scatter_reduce)
+                      GemmGroupedV3AGScatter, GemmGroupedV3GatherRS, calc_moe_triton_blocked_gather_a,
+                      prepare_moe_ag_scatter_args, topk_scatter_reduce)
 from .utils.util import (bench_func, get_arch, get_torch_prof_ctx, group_profile, is_fp8_dtype,  # noqa: F401
                          torch_allclose, with_torch_deterministic)
 from .utils import util  # noqa: F401

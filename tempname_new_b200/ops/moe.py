@@ -457,3 +457,69 @@ def topk_scatter_reduce(inputs: torch.Tensor, scatter_idx: torch.Tensor, topk: i
     """out[t] = sum_k inputs[scatter_idx[t * topk + k]] (reference: ``flux.topk_scatter_reduce``)."""
     idx = scatter_idx.reshape(-1, topk).long()
     return inputs[idx].float().sum(1).to(inputs.dtype)
+
+
+_PAD_ROW = 2 ** 31 - 1    # marks padding rows of a blocked index (INT32_MAX, as in the reference)
+
+
+def calc_moe_triton_blocked_gather_a(splits: torch.Tensor, ep_start: int, ep_nexperts: int, block_size_m: int,
+                                     gather_a_index: torch.Tensor, expert_index: torch.Tensor, stream=None) -> None:
+    """Blocked row index of a grouped GEMM whose row tiles never straddle two experts: the rows of
+    every expert in [ep_start, ep_start + ep_nexperts) are padded to a multiple of ``block_size_m``;
+    ``gather_a_index[padded row]`` = row inside this rank's expert-sorted rows (INT32_MAX on padding),
+    ``expert_index[tile]`` = local expert of the tile. The outputs are written in place, as by the
+    reference's kernel of the same name (src/moe_gather_rs/moe_utils.cu:762-793)."""
+    sp = splits[ep_start:ep_start + ep_nexperts].to(torch.int64)
+    dev = sp.device
+    tiles = (sp + block_size_m - 1) // block_size_m
+    n_tiles = int(tiles.sum())
+    m_start = torch.cumsum(sp, 0) - sp
+    tile_start = torch.cumsum(tiles, 0) - tiles
+    tile_expert = torch.repeat_interleave(torch.arange(ep_nexperts, device=dev), tiles)
+    expert_index[:n_tiles] = tile_expert.to(expert_index.dtype)
+    pos = torch.arange(n_tiles * block_size_m, device=dev)
+    e = tile_expert[pos // block_size_m]
+    i = pos - tile_start[e] * block_size_m                    # row inside the expert, padding included
+    rows = torch.where(i < sp[e], m_start[e] + i, torch.full_like(i, _PAD_ROW))
+    gather_a_index[:pos.numel()] = rows.to(gather_a_index.dtype)
+
+
+def prepare_moe_ag_scatter_args(splits_gpu: torch.Tensor, scatter_index: torch.Tensor, ntokens: int, topk: int,
+                                num_weight_groups: int, ep_start: int, ep_experts: int, rank: int,
+                                world_size: int, tile_size_m: int, cp_stream=None):
+    """Index tensors for a tile-blocked MoE layer-0 GEMM over this rank's experts (the arguments the
+    reference prepares for its Triton kernel, src/pybind/gemm_grouped_v2_ag_scatter.cc:30). Returns
+    ``(M_this_ep, M_this_ep_pad, gather_A_index, scatter_D_index, expert_index, rank_start_index,
+    rank_end_index)``: per padded row the token to read (INT32_MAX on padding) and the output row to
+    write; per row tile its local expert and the first / last source rank whose tokens it reads, so
+    that a consumer can wait for exactly those shards of the all-gather. The kernels of this library
+    build the equivalent schedule on the device (``moe_schedule_kernel``); this is the same
+    information as tensors."""
+    dev = splits_gpu.device
+    sp_all = splits_gpu.to(torch.int64)
+    base = int(sp_all[:ep_start].sum())
+    sp = sp_all[ep_start:ep_start + ep_experts]
+    M = int(sp.sum())
+    tiles = (sp + tile_size_m - 1) // tile_size_m
+    n_tiles = int(tiles.sum())
+    M_pad = n_tiles * tile_size_m
+    gather_rows = torch.empty(M_pad, dtype=torch.int32, device=dev)
+    expert_index = torch.empty(n_tiles, dtype=torch.int32, device=dev)
+    calc_moe_triton_blocked_gather_a(splits_gpu, ep_start, ep_experts, tile_size_m, gather_rows, expert_index)
+    # sorted row -> token: scatter_index[token, k] is the sorted row of (token, k)
+    flat = scatter_index.reshape(-1).to(torch.int64)
+    token_of_row = torch.empty(flat.numel(), dtype=torch.int64, device=dev)
+    token_of_row[flat] = torch.arange(flat.numel(), device=dev) // topk
+    pad = gather_rows == _PAD_ROW
+    rows = gather_rows.to(torch.int64).clamp(max=max(M - 1, 0))
+    tok = token_of_row[base + rows]
+    gather_a = torch.where(pad, torch.full_like(tok, _PAD_ROW), tok).to(torch.int32)
+    scatter_d = torch.where(pad, torch.full_like(rows, _PAD_ROW), rows).to(torch.int32)
+    tpr = max(ntokens // world_size, 1)
+    src = (tok // tpr).reshape(n_tiles, tile_size_m)
+    padm = pad.reshape(n_tiles, tile_size_m)
+    rank_start = torch.where(padm, torch.full_like(src, world_size), src).min(1).values.to(torch.int32)
+    rank_end = torch.where(padm, torch.full_like(src, -1), src).max(1).values.to(torch.int32)
+    m_pad_t = torch.tensor([M_pad], dtype=torch.int32, device=dev)
+    rep = lambda t: t.repeat(num_weight_groups) if num_weight_groups > 1 else t  # noqa: E731
+    return M, m_pad_t, rep(gather_a), rep(scatter_d), rep(expert_index), rep(rank_start), rep(rank_end)

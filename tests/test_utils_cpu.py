@@ -145,3 +145,45 @@ def test_tuning_override_pins_knobs_inside_block():
             assert lookup(*key)["group_m"] == 2
         assert lookup(*key)["tile_n"] == 128
     assert lookup(*key) == before
+
+
+def test_blocked_moe_index_helpers():
+    """calc_moe_triton_blocked_gather_a / prepare_moe_ag_scatter_args against a loop statement."""
+    import sys, os
+    import torch
+    import tempname_new_b200 as flux
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from moe_common import routed_problem
+    tokens, topk, E, W, tile = 48, 2, 8, 4, 8
+    experts, gate, scatter, splits, order = routed_problem(tokens, topk, E, seed=5)
+    ep_start, ep_n = 2, 4
+    PAD = 2 ** 31 - 1
+    sp = splits[ep_start:ep_start + ep_n].tolist()
+    n_tiles = sum(-(-s // tile) for s in sp)
+    ga = torch.empty(n_tiles * tile, dtype=torch.int32)
+    ei = torch.empty(n_tiles, dtype=torch.int32)
+    flux.calc_moe_triton_blocked_gather_a(splits, ep_start, ep_n, tile, ga, ei)
+    exp_rows, exp_e, m = [], [], 0
+    for e, s in enumerate(sp):
+        t = -(-s // tile)
+        exp_e += [e] * t
+        exp_rows += [m + i if i < s else PAD for i in range(t * tile)]
+        m += s
+    assert ga.tolist() == exp_rows and ei.tolist() == exp_e
+    M, M_pad, gA, sD, eidx, r0, r1 = flux.prepare_moe_ag_scatter_args(
+        splits, scatter, tokens, topk, 1, ep_start, ep_n, 0, W, tile)
+    assert M == sum(sp) and int(M_pad) == n_tiles * tile and eidx.tolist() == exp_e
+    base = int(splits[:ep_start].sum())
+    token_of_row = (order // topk).tolist()            # sorted row -> token
+    tpr = tokens // W
+    for pos, row in enumerate(exp_rows):
+        if row == PAD:
+            assert gA[pos] == PAD and sD[pos] == PAD
+        else:
+            assert gA[pos] == token_of_row[base + row] and sD[pos] == row
+    for t in range(n_tiles):
+        srcs = [token_of_row[base + r] // tpr for r in exp_rows[t * tile:(t + 1) * tile] if r != PAD]
+        assert r0[t] == min(srcs) and r1[t] == max(srcs)
+    # several weight groups repeat the per-group tensors
+    out2 = flux.prepare_moe_ag_scatter_args(splits, scatter, tokens, topk, 2, ep_start, ep_n, 0, W, tile)
+    assert out2[2].numel() == 2 * gA.numel() and out2[4].tolist() == exp_e * 2
