@@ -40,3 +40,8 @@ from .ops.ep_dispatch import (AGKernelInterNode, AGKernelXNode, All2AllInference
                               DisScatterForward, GemmRS_multinode, GemmRSInterNode, TopkReduceScatterOp, TransportOp,
                               bsr_reduce,
                               load_tuning_record, pad_m_to_TPxTile)
+from .parallel.teams import (TEAM_INVALID, TEAM_WORLD, TeamConfig, _nvshmem_team_destroy,  # noqa: F401,E402
+                             _nvshmem_team_get_config, _nvshmem_team_my_pe, _nvshmem_team_npes,
+                             _nvshmem_team_split_2d, _nvshmem_team_split_strided, _nvshmem_team_translate_pe,
+                             team_group)
+
