@@ -80,6 +80,32 @@ def _int8(rank, world):
     assert (out.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
 
 
+def _varying_shapes(rank, world):
+    """One op object, calls with different row counts in a row (the call-number flags must not
+    depend on the shape of the previous call), ranks entering the calls at different times."""
+    import time
+    import tempname_new_b200 as flux
+    flux.init_flux_shm()
+    N, Kl = 48, 32
+    rs = flux.GemmRS(dist.group.WORLD, 1, 256, N, torch.float32)
+    ag = flux.AGKernel(dist.group.WORLD, 1, 256, N, Kl, torch.float32)
+    for i, M in enumerate([256, 64, 128, 32, 256, 64]):
+        if (i + rank) % 2:
+            time.sleep(0.02)                      # skew the ranks
+        a = _data(M, Kl, Kl * world, 10 * i + rank)
+        w = _data(N, Kl, Kl * world, 100 + rank)
+        out = rs.forward(a, w)
+        ref = torch.empty(M // world, N)
+        dist.reduce_scatter(ref, list((a @ w.t()).chunk(world)))
+        torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
+        seg = M // world
+        a2 = _data(seg, Kl, Kl, 20 * i + rank)
+        out2 = ag.forward(a2, w)
+        parts = [torch.empty_like(a2) for _ in range(world)]
+        dist.all_gather(parts, a2)
+        torch.testing.assert_close(out2, torch.cat(parts) @ w.t(), rtol=1e-5, atol=1e-5)
+
+
 def _symm(rank, world):
     import tempname_new_b200 as flux
     ts = flux.create_tensor_list((4, 8), torch.float32)
@@ -113,4 +139,8 @@ def test_symmetric_memory_and_barrier_gloo():
 
 def test_int8_operands_gloo():
     run_gloo(_int8, 2)
+
+
+def test_calls_with_varying_shapes_gloo():
+    run_gloo(_varying_shapes, 2)
 
