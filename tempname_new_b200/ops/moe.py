@@ -416,12 +416,22 @@ class GemmGroupedV3:
         self._scratch = None
         self._status = None
 
-    def forward(self, input: torch.Tensor, splits_cpu: torch.Tensor) -> torch.Tensor:
+    def forward(self, input: torch.Tensor, splits_cpu: torch.Tensor, input_scale: Optional[torch.Tensor] = None,
+                weight_scale: Optional[torch.Tensor] = None, output_scale: Optional[torch.Tensor] = None,
+                fast_accum: bool = False, sm_margin: int = 0) -> torch.Tensor:
+        """``input_scale`` [1] and ``weight_scale`` [E] (one per expert) multiply the product, as in the
+        reference's ``GemmGroupedV2.forward`` (src/pybind/gemm_only.cc:171-190); ``output_scale`` is
+        accepted and, as there for 16-bit outputs, not applied."""
         N = self.weight.shape[1]
         if not input.is_cuda:
             outs, row = [], 0
             for e, n in enumerate(splits_cpu.tolist()):
-                outs.append(input[row:row + n].float() @ self.weight[e].float().t())
+                y = input[row:row + n].float() @ self.weight[e].float().t()
+                if weight_scale is not None:
+                    y = y * weight_scale.reshape(-1)[e].float()
+                if input_scale is not None:
+                    y = y * input_scale.reshape(-1)[0].float()
+                outs.append(y)
                 row += n
             return torch.cat(outs).to(input.dtype)
         dev = input.device
@@ -438,6 +448,10 @@ class GemmGroupedV3:
         a.N, a.K = N, x.shape[1]
         a.a, a.a_rows = x.data_ptr(), x.shape[0]
         a.weights, a.d, a.ldd = self.weight.data_ptr(), out.data_ptr(), N
+        ws = _f32(weight_scale, dev) if weight_scale is not None else None
+        isc = _f32(input_scale, dev) if input_scale is not None else None
+        a.expert_scale = ws.data_ptr() if ws is not None else None
+        a.scalar_scale = isc.data_ptr() if isc is not None else None
         a.scratch = self._scratch.data_ptr()
         a.rank, a.world = 0, 1
         a.status = self._status.data_ptr()
@@ -447,8 +461,24 @@ class GemmGroupedV3:
 
     __call__ = forward
 
+    def profiling(self, input: torch.Tensor, splits_cpu: torch.Tensor, prof_ctx=None) -> torch.Tensor:
+        from ..tuning.profiling import profile_call
+        return profile_call(self, "gemm_grouped_v3", lambda: self.forward(input, splits_cpu), prof_ctx)
 
-GemmGroupedV2 = GemmGroupedV3
+
+class GemmGroupedV2(GemmGroupedV3):
+    """Same kernel behind the reference's older constructor:
+    ``GemmGroupedV2(weight, num_experts, in_type, out_type)``."""
+
+    def __init__(self, weight: torch.Tensor, num_experts: int, in_type: Optional[torch.dtype] = None,
+                 out_type: Optional[torch.dtype] = None):
+        super().__init__(weight, num_experts)
+        if in_type is not None and in_type != weight.dtype:
+            raise TypeError("in_type must be the dtype of the weights")
+        if out_type is not None and out_type != weight.dtype:
+            raise NotImplementedError("the grouped kernel writes the input dtype")
+
+
 GemmGroupedV2AGScatterOp = GemmGroupedV3AGScatter
 GemmGroupedV2GatherRSOp = GemmGroupedV3GatherRS
 

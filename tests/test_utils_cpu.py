@@ -187,3 +187,20 @@ def test_blocked_moe_index_helpers():
     # several weight groups repeat the per-group tensors
     out2 = flux.prepare_moe_ag_scatter_args(splits, scatter, tokens, topk, 2, ep_start, ep_n, 0, W, tile)
     assert out2[2].numel() == 2 * gA.numel() and out2[4].tolist() == exp_e * 2
+
+
+def test_grouped_gemm_v2_constructor_and_scales():
+    import torch
+    import tempname_new_b200 as flux
+    w = torch.randn(3, 4, 8)
+    x = torch.randn(10, 8)
+    sp = torch.tensor([3, 5, 2])
+    op = flux.GemmGroupedV2(w, 3, torch.float32, torch.float32)
+    y = op.forward(x, sp, input_scale=torch.tensor([2.0]), weight_scale=torch.tensor([1.0, 0.5, 3.0]))
+    ref = torch.cat([x[:3] @ w[0].t() * 2, x[3:8] @ w[1].t(), x[8:] @ w[2].t() * 6])
+    torch.testing.assert_close(y, ref, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(flux.GemmGroupedV3(w, 3).forward(x, sp), torch.cat(
+        [x[:3] @ w[0].t(), x[3:8] @ w[1].t(), x[8:] @ w[2].t()]), rtol=1e-5, atol=1e-5)
+    import pytest
+    with pytest.raises(TypeError):
+        flux.GemmGroupedV2(w, 3, torch.bfloat16)
