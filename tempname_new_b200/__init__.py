@@ -11,7 +11,8 @@ from .ops.options import (A2ARingMode, AGRingMode, AllGatherOption, AllToAllOpti
                           PreAttnAllToAllCommOp, ReduceScatterOption, RingMode,
                           get_default_a2a_ring_mode, get_default_ag_ring_mode,
                           get_default_rs_ring_mode)
-from .parallel.symm import (FluxTimeoutError, GroupBarrier, SymmBuffer, create_tensor_list,  # noqa: F401
+from .parallel.symm import (FluxTimeoutError, GroupBarrier, SymmBuffer, create_tensor, create_tensor_list,  # noqa: F401
+                            flux_create_shm_tensor_list,
                             init_flux_shm)
 from .parallel.dist_env import DistEnvTP, DistEnvTPWithEP, MoeArguments  # noqa: F401
 from .ops.gemm_only import GemmOnly  # noqa: F401
@@ -42,6 +43,7 @@ from .ops.ep_dispatch import (AGKernelInterNode, AGKernelXNode, All2AllInference
                               load_tuning_record, pad_m_to_TPxTile)
 from .parallel.teams import (TEAM_INVALID, TEAM_WORLD, TeamConfig, _nvshmem_team_destroy,  # noqa: F401,E402
                              _nvshmem_team_get_config, _nvshmem_team_my_pe, _nvshmem_team_npes,
+                             _nvshmem_team_npes as _nvshmem_team_n_pes,
                              _nvshmem_team_split_2d, _nvshmem_team_split_strided, _nvshmem_team_translate_pe,
                              team_group)
 

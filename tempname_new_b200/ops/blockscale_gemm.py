@@ -121,6 +121,7 @@ class BlockScaleGemm:
         return self._per_expert(input, input_splits, weight, bias, output, input_scale, weight_scale)
 
     wgrad_multistream = forward_multistream
+    forward_multi_stream = forward_multistream   # spelling of the reference's stub file
     forward_grouped = forward_multistream
     wgrad_grouped = forward_multistream
 

@@ -66,6 +66,30 @@ class DisScatterForward:
     forward_no_cpy = forward
     forward_gpu_no_cpy = forward_gpu
 
+    def pre_comm_index(self, ep_token_counts: torch.Tensor, cur_topk_indices: torch.Tensor,
+                       cur_topk_values: torch.Tensor, ag_topk_indices: torch.Tensor, ag_topk_values: torch.Tensor,
+                       sm_margin: int = 0) -> None:
+        """Gather every rank's routing choice ([tokens_r, topk] expert ids and gate values,
+        ``ep_token_counts[r]`` tokens on rank r) into the two outputs, rank after rank (reference:
+        ``DisScatterForward.pre_comm_index``, python/flux/cpp_mod.pyi:1169-1177)."""
+        counts = [int(v) for v in ep_token_counts.tolist()]
+        mx = max(counts)
+        for cur, out in ((cur_topk_indices, ag_topk_indices), (cur_topk_values, ag_topk_values)):
+            pad = torch.zeros((mx,) + tuple(cur.shape[1:]), dtype=cur.dtype, device=cur.device)
+            pad[: cur.shape[0]] = cur
+            parts = [torch.empty_like(pad) for _ in range(self.world)]
+            dist.all_gather(parts, pad, group=self.pg)
+            row = 0
+            for r, n in enumerate(counts):
+                out[row:row + n] = parts[r][:n]
+                row += n
+
+    def profiling(self, input, ag_exp_indices, ag_scatter_idx, splits_cpu, ep_token_counts=None, sm_margin: int = 0,
+                  copy_to_local_tensor: bool = True, prof_ctx=None):
+        from ..tuning.profiling import profile_call
+        return profile_call(self, "dis_scatter_forward",
+                            lambda: self.forward(input, ag_exp_indices, ag_scatter_idx, splits_cpu), prof_ctx)
+
     def ep_barrier_all(self) -> None:
         dist.barrier(group=self.pg)
 
@@ -239,6 +263,10 @@ def _multi_node(name: str):
         def __init__(self, *a, **k):
             raise NotImplementedError(
                 f"{name}: multi-node operation is outside the single NVSwitch domain this library targets")
+        def _no(self, *a, **k):
+            raise NotImplementedError(f"{name}: multi-node operation is not built")
+
+        forward = gemm_only = copy_local = reset_signals = _no
     _Unavailable.__name__ = name
     return _Unavailable
 

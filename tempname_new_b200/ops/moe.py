@@ -481,6 +481,10 @@ class GemmGroupedV2(GemmGroupedV3):
 
 GemmGroupedV2AGScatterOp = GemmGroupedV3AGScatter
 GemmGroupedV2GatherRSOp = GemmGroupedV3GatherRS
+# the reference's Triton entry points of the two MoE ops compute the same results through its Triton
+# kernels; here there is one implementation, so the names lead to it
+GemmGroupedV3AGScatter.forward_triton_aot = GemmGroupedV3AGScatter.forward
+GemmGroupedV3GatherRS.forward_gather_rs_triton_aot = GemmGroupedV3GatherRS.forward_gather_rs
 
 
 def topk_scatter_reduce(inputs: torch.Tensor, scatter_idx: torch.Tensor, topk: int) -> torch.Tensor:

@@ -200,6 +200,17 @@ def create_tensor_list(shape: Sequence[int], dtype: torch.dtype, pg=None, ring_m
     return out
 
 
+def create_tensor(shape: Sequence[int], dtype: torch.dtype, pg=None) -> torch.Tensor:
+    """This rank's tensor of a symmetric allocation (reference: ``flux.create_tensor``,
+    python/flux/cpp_mod.pyi:31); the peers' views stay reachable through ``t._fluxb_symm``."""
+    ts = create_tensor_list(shape, dtype, pg)
+    return ts[ts[0]._fluxb_symm.rank]
+
+
+# the reference exports the same allocator under a second name (cpp_mod.pyi:35-37)
+flux_create_shm_tensor_list = create_tensor_list
+
+
 class GroupBarrier:
     """Barrier over the ranks of ``pg`` that runs on the GPU stream (CPU groups: in shared
     memory). Flags carry the call number, so no reset pass is needed between calls and every

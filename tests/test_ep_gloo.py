@@ -35,6 +35,17 @@ def _ep(rank, world):
     table = torch.zeros(world, 4, dtype=torch.int32)
     assert flux.calc_gemm_rs_threadblock_segments_info(table, (64 * world, 32), (16, 16), rank, world) == world
     assert table[:, 3].tolist() == [4 * i for i in range(world)]
+    # routing choices of all ranks, gathered rank after rank (ranks may hold different token counts)
+    counts = torch.tensor([3 + r for r in range(world)], dtype=torch.int32)
+    mine_i = torch.full((3 + rank, topk), rank, dtype=torch.int32)
+    mine_v = torch.full((3 + rank, topk), float(rank) + 0.5)
+    all_i = torch.empty(int(counts.sum()), topk, dtype=torch.int32)
+    all_v = torch.empty(int(counts.sum()), topk)
+    fwd.pre_comm_index(counts, mine_i, mine_v, all_i, all_v, 0)
+    exp = torch.cat([torch.full((3 + r, topk), r, dtype=torch.int32) for r in range(world)])
+    assert torch.equal(all_i, exp) and torch.equal(all_v, exp.float() + 0.5)
+    mine = flux.create_tensor((2, 3), torch.float32)
+    assert mine.shape == (2, 3) and len(flux.flux_create_shm_tensor_list((2, 3), torch.float32)) == world
     import pytest
     with pytest.raises(NotImplementedError):
         flux.AGKernelXNode()
