@@ -40,3 +40,39 @@ def log_perf(result: PerfResult, file=None) -> None:
             f.write(line + "\n")
     else:
         sys.stdout.write(line + "\n")
+
+
+# ------------------------------------------------------------------------------------------
+# names of the reference's perf database helper (python/flux/testing/perf_db_helper.py:135-386).
+# The MySQL ("RDS") upload has no counterpart: there is no database on the other side, so the
+# switch is always off and the upload says so.
+# ------------------------------------------------------------------------------------------
+def should_log_to_rds() -> bool:
+    return False
+
+
+def log_perf_stdout(result: PerfResult) -> None:
+    print(result)
+
+
+def upload_to_rds(result: PerfResult) -> None:
+    raise NotImplementedError("no performance database is attached to this library; use log_perf "
+                              "(JSON lines, FLUXB_PERF_LOG) instead")
+
+
+def log_perf_rds(result: PerfResult) -> None:
+    if should_log_to_rds():
+        upload_to_rds(result)
+
+
+def query(delete: bool = False):
+    """Records written so far to ``$FLUXB_PERF_LOG`` (the reference queries its database);
+    ``delete`` empties the file."""
+    path = os.environ.get("FLUXB_PERF_LOG")
+    if not path or not os.path.exists(path):
+        return []
+    with open(path) as f:
+        recs = [json.loads(line) for line in f if line.strip()]
+    if delete:
+        open(path, "w").close()
+    return recs

@@ -124,3 +124,106 @@ def split_torch_process_group(pg, group_size: int):
         if start <= rank < start + group_size:
             mine = sub
     return mine
+
+
+# ------------------------------------------------------------------------------------------
+# node-local group, fp8-friendly tensor constructors, int8 matmul, team split
+# (reference: python/flux/testing/utils.py:98-124, 198-248, 280-290)
+# ------------------------------------------------------------------------------------------
+_TP_LOCAL_GROUP = None
+
+
+def is_local_tp_group_initialized() -> bool:
+    return _TP_LOCAL_GROUP is not None
+
+
+def init_local_groups():
+    """The group of the ranks on this node: the tensor-parallel group itself on one node (the
+    only case this library runs), one new group per node otherwise."""
+    global _TP_LOCAL_GROUP
+    if _TP_LOCAL_GROUP is not None:
+        raise RuntimeError("the node-local group exists already")
+    tp = TP_GROUP()
+    nnodes = NNODES()
+    if nnodes == 1:
+        _TP_LOCAL_GROUP = tp
+        return _TP_LOCAL_GROUP
+    lws = int(os.environ.get("LOCAL_WORLD_SIZE", 1))
+    rank = dist.get_rank(tp)
+    for n in range(nnodes):
+        ranks = list(range(lws * n, lws * (n + 1)))
+        pg = dist.new_group(ranks=ranks)
+        if rank in ranks:
+            _TP_LOCAL_GROUP = pg
+    return _TP_LOCAL_GROUP
+
+
+def _fp8(dtype) -> bool:
+    return dtype in (torch.float8_e4m3fn, torch.float8_e5m2)
+
+
+def _relaxed(fn, *args, **kwargs):
+    # fill / copy kernels of 8-bit float types have no deterministic variant in torch
+    from ..utils.util import with_torch_deterministic
+    with with_torch_deterministic(False):
+        return fn(*args, **kwargs)
+
+
+def zeros_with_fp8(*args, **kwargs):
+    return _relaxed(torch.zeros, *args, **kwargs)
+
+
+def ones_with_fp8(*args, **kwargs):
+    return _relaxed(torch.ones, *args, **kwargs)
+
+
+def empty_non_determinisitc(*args, **kwargs):   # (spelling of the reference)
+    return _relaxed(torch.empty, *args, **kwargs)
+
+
+def rand_with_fp8(*args, dtype=None, **kwargs):
+    if _fp8(dtype):
+        return _relaxed(lambda: torch.rand(*args, dtype=torch.bfloat16, **kwargs).to(dtype))
+    return torch.rand(*args, dtype=dtype, **kwargs)
+
+
+def clone_with_fp8(tensor: torch.Tensor) -> torch.Tensor:
+    return _relaxed(tensor.clone)
+
+
+def all_gather_into_tensor_with_fp8(output_tensor, input_tensor, group=None, async_op=False):
+    """NCCL has no 8-bit float type: such tensors travel as bytes."""
+    if _fp8(input_tensor.dtype):
+        return dist.all_gather_into_tensor(output_tensor.view(torch.uint8), input_tensor.view(torch.uint8),
+                                           group=group, async_op=async_op)
+    return dist.all_gather_into_tensor(output_tensor, input_tensor, group=group, async_op=async_op)
+
+
+def matmul_int8(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a [M, K] int8 @ b [K, N] int8 -> int32 (exact). ``torch._int_mm`` on CUDA needs more than 16
+    rows, so short inputs are padded; on CPU the product is taken in int32 directly."""
+    if not a.is_cuda:
+        return a.to(torch.int32) @ b.to(torch.int32)
+    M = a.shape[0]
+    if M <= 16:
+        return torch._int_mm(torch.nn.functional.pad(a, (0, 0, 0, 32 - M)), b)[:M]
+    return torch._int_mm(a, b)
+
+
+def nvshmem_split_team_2d(group_size: int):
+    """(team of my ``group_size`` consecutive ranks, team of the ranks ``group_size`` apart)."""
+    from ..parallel import teams
+    return teams._nvshmem_team_split_2d(teams.TEAM_WORLD, group_size)
+
+
+_GLOBAL_ARGS = {}
+
+
+def set_global_args(**kwargs) -> None:
+    """Key/value context that the perf log attaches to every record (reference:
+    python/flux/testing/perf_db_helper.py)."""
+    _GLOBAL_ARGS.update(kwargs)
+
+
+def get_global_args() -> dict:
+    return dict(_GLOBAL_ARGS)
