@@ -4,8 +4,12 @@ the local heads, fused heads->seq all-to-all + output projection.
     ./launch.sh examples/ulysses_attention.py --seq 32768 --heads 32 --head-dim 128
 """
 import argparse
+import os
+import sys
 
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))  # run from a checkout
 
 import tempname_new_b200 as flux
 from tempname_new_b200.testing import initialize_distributed, run_perf
@@ -19,15 +23,17 @@ args = ap.parse_args()
 
 pg = initialize_distributed()
 rank, world = pg.rank(), pg.size()
+# GPUs run the sm_100a kernels in bf16; without one the same script runs the CPU statements in fp32
+DEV, DT = ("cuda", torch.bfloat16) if torch.cuda.is_available() else ("cpu", torch.float32)
 hidden = args.heads * args.head_dim
 nh3 = 3 * args.heads                                           # q, k, v heads (gqa = 1: equal counts)
 pre = flux.GemmAllToAllTranspose(pg, 1, world, args.bs, args.seq, hidden, args.head_dim, nh3 * args.head_dim,
-                                 torch.bfloat16, gqa=1, comm_op=flux.PreAttnAllToAllCommOp.QKVPackA2A)
-post = flux.AllToAllTransposeGemm(pg, 1, world, args.bs, args.heads, args.seq, args.head_dim, torch.bfloat16,
+                                 DT, gqa=1, comm_op=flux.PreAttnAllToAllCommOp.QKVPackA2A)
+post = flux.AllToAllTransposeGemm(pg, 1, world, args.bs, args.heads, args.seq, args.head_dim, DT,
                                   a2a_only=True)
-w_qkv = (torch.randn(nh3 * args.head_dim, hidden, device="cuda") * 0.02).bfloat16()
-w_o = (torch.randn(hidden, hidden, device="cuda") * 0.02).bfloat16()
-x = torch.randn(args.bs, args.seq // world, hidden, device="cuda").bfloat16()
+w_qkv = (torch.randn(nh3 * args.head_dim, hidden, device=DEV) * 0.02).to(DT)
+w_o = (torch.randn(hidden, hidden, device=DEV) * 0.02).to(DT)
+x = torch.randn(args.bs, args.seq // world, hidden, device=DEV).to(DT)
 
 
 def block():

@@ -84,24 +84,33 @@ def generate_data(configs: List[Tuple[Sequence[int], torch.dtype, Tuple[float, f
 
 
 def run_perf(expname: str, warmups: int, iters: int, func: Callable, sync_per_iter: bool = False):
-    """(result, ms per call): CUDA-event timed after warm-up, max over ranks when distributed."""
+    """(result, ms per call): CUDA-event timed after warm-up (wall clock on CPU-only hosts), max
+    over ranks when distributed."""
+    import time
+    gpu = torch.cuda.is_available()
     out = None
     for _ in range(warmups):
         out = func()
-    torch.cuda.synchronize()
+    if gpu:
+        torch.cuda.synchronize()
     if dist.is_initialized():
         dist.barrier()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
+    if gpu:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+    t0 = time.perf_counter()
     for _ in range(iters):
         out = func()
-        if sync_per_iter:
+        if sync_per_iter and gpu:
             torch.cuda.synchronize()
-    stop.record()
-    stop.synchronize()
-    ms = start.elapsed_time(stop) / max(iters, 1)
+    if gpu:
+        stop.record()
+        stop.synchronize()
+        ms = start.elapsed_time(stop) / max(iters, 1)
+    else:
+        ms = (time.perf_counter() - t0) * 1e3 / max(iters, 1)
     if dist.is_initialized() and dist.get_world_size() > 1:
-        t = torch.tensor([ms], device="cuda")
+        t = torch.tensor([ms], device="cuda" if gpu else "cpu")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     return out, ms
