@@ -38,7 +38,8 @@ from .parallel.layers import ColumnParallelLinear, RowParallelLinear, patch_mega
 from . import models, ops, parallel, testing, tuning, utils  # noqa: F401
 from .ops.coll import All2AllOp, All2AllSingle, AllGatherOp, AsyncSendRecv  # noqa: F401
 from .ops.ep_dispatch import (AGKernelInterNode, AGKernelXNode, All2AllInference, DisScatterBackward,  # noqa: F401
-                              DisScatterForward, GemmRS_multinode, GemmRSInterNode, TopkReduceScatterOp, TransportOp,
+                              DisScatterForward, GemmRS_multinode, GemmRSInterNode, GemmRSTaco,
+                              GemmRSTacoDoubleBuffered, TopkReduceScatterOp, TransportOp,
                               bsr_reduce,
                               load_tuning_record, pad_m_to_TPxTile)
 from .parallel.teams import (TEAM_INVALID, TEAM_WORLD, TeamConfig, _nvshmem_team_destroy,  # noqa: F401,E402
@@ -46,4 +47,6 @@ from .parallel.teams import (TEAM_INVALID, TEAM_WORLD, TeamConfig, _nvshmem_team
                              _nvshmem_team_npes as _nvshmem_team_n_pes,
                              _nvshmem_team_split_2d, _nvshmem_team_split_strided, _nvshmem_team_translate_pe,
                              team_group)
+from .utils.dist_utils import (DistEnv, get_inter_node_ag_group, get_inter_node_rs_group,  # noqa: F401,E402
+                               get_intra_node_ag_group, get_intra_node_pg_group, initialize_inter_node_rs_group)
 

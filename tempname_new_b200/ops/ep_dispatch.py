@@ -277,6 +277,20 @@ AGKernelInterNode = _multi_node("AGKernelInterNode")
 AGKernelXNode = _multi_node("AGKernelXNode")
 
 
+def _taco(name: str):
+    class _Unavailable:
+        def __init__(self, *a, **k):
+            raise NotImplementedError(
+                f"{name}: the compressed (TACO) reduce-scatter of the reference fork is a research add-on "
+                "for sm80 links and is not built; GemmRS moves bf16 partial tiles over NVLink")
+    _Unavailable.__name__ = name
+    return _Unavailable
+
+
+GemmRSTaco = _taco("GemmRSTaco")
+GemmRSTacoDoubleBuffered = _taco("GemmRSTacoDoubleBuffered")
+
+
 def load_tuning_record(record) -> None:
     """Add a tuning record (``TuningRecord`` or dict with ``key`` = [M, N, K] and ``best``) to the
     in-memory table (reference: ``flux.load_tuning_record``)."""

@@ -66,3 +66,67 @@ def exec_in_rank_order(group, func: Callable) -> None:
         dist.barrier(group=group)
         if torch.cuda.is_available():
             torch.cuda.synchronize()
+
+
+# ------------------------------------------------------------------------------------------
+# Node-level process groups of a tensor-parallel group that spans several nodes (reference:
+# python/flux/gemm_rs_sm80.py:31-84 and python/flux/ag_kernel_internode.py:32-73, where the
+# multi-node GEMM-RS / AG-GEMM variants use them). The fused ops of this library run inside one
+# node; the groups are plain torch groups and are provided so that scripts which build them keep
+# working (a job can still shard its outer dimension across nodes with them).
+# ------------------------------------------------------------------------------------------
+_NODE_GROUPS = {}
+
+
+def _node_group(kind: str, tp_group, nnodes: int):
+    key = (kind, id(tp_group), nnodes)
+    if key in _NODE_GROUPS:
+        return _NODE_GROUPS[key]
+    tp_world = dist.get_world_size(tp_group)
+    world = dist.get_world_size()
+    if tp_world % nnodes or world % tp_world:
+        raise ValueError(f"{tp_world} ranks do not divide over {nnodes} nodes (world {world})")
+    local = tp_world // nnodes
+    me = dist.get_rank()
+    mine = None
+    if kind == "intra":
+        sets = [list(range(tp0 + n * local, tp0 + (n + 1) * local))
+                for tp0 in range(0, world, tp_world) for n in range(nnodes)]
+    else:
+        sets = [[tp0 + n * local + lr for n in range(nnodes)]
+                for tp0 in range(0, world, tp_world) for lr in range(local)]
+    for ranks in sets:                       # every rank creates every group: new_group is collective
+        g = dist.new_group(ranks=ranks)
+        if me in ranks:
+            mine = g
+    _NODE_GROUPS[key] = mine
+    return mine
+
+
+def get_intra_node_pg_group(tp_group, nnodes: int):
+    """The ranks of ``tp_group`` that share this rank's node."""
+    return _node_group("intra", tp_group, nnodes)
+
+
+def get_intra_node_ag_group(tp_group, nnodes: int):
+    return _node_group("intra", tp_group, nnodes)
+
+
+def get_inter_node_ag_group(tp_group, nnodes: int):
+    """The ranks of ``tp_group`` with this rank's local index, one per node."""
+    return _node_group("inter", tp_group, nnodes)
+
+
+_INTER_NODE_RS_GROUP = None
+
+
+def initialize_inter_node_rs_group(tp_group, nnodes: int) -> None:
+    global _INTER_NODE_RS_GROUP
+    if _INTER_NODE_RS_GROUP is None:
+        _INTER_NODE_RS_GROUP = _node_group("inter", tp_group, nnodes)
+
+
+def get_inter_node_rs_group():
+    if _INTER_NODE_RS_GROUP is None:
+        raise RuntimeError("call initialize_inter_node_rs_group(tp_group, nnodes) first")
+    return _INTER_NODE_RS_GROUP

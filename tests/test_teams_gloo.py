@@ -31,6 +31,21 @@ def _teams(rank, world):
         a, w = torch.ones(8, 3) * (rank + 1), torch.ones(4, 3)
         out = op.forward(a, w)
         assert torch.allclose(out, torch.full((4, 4), 3.0 * (2 + 4)))
+    # node-level groups of a tensor-parallel group laid over two "nodes" of two ranks
+    intra = flux.get_intra_node_pg_group(dist.group.WORLD, 2)
+    inter = flux.get_inter_node_ag_group(dist.group.WORLD, 2)
+    assert dist.get_world_size(intra) == 2 and dist.get_world_size(inter) == 2
+    t = torch.tensor([float(rank)])
+    dist.all_reduce(t, group=intra)
+    assert t.item() == float((rank // 2) * 4 + 1)
+    t = torch.tensor([float(rank)])
+    dist.all_reduce(t, group=inter)
+    assert t.item() == float(2 * (rank % 2) + 2)
+    flux.initialize_inter_node_rs_group(dist.group.WORLD, 2)
+    assert flux.get_inter_node_rs_group() is inter
+    import pytest
+    with pytest.raises(NotImplementedError):
+        flux.GemmRSTaco()
     dist.barrier()
     flux._nvshmem_team_destroy(odd)
     flux._nvshmem_team_destroy(xt)
