@@ -204,3 +204,17 @@ def test_grouped_gemm_v2_constructor_and_scales():
     import pytest
     with pytest.raises(TypeError):
         flux.GemmGroupedV2(w, 3, torch.bfloat16)
+
+
+def test_tune_file_and_load_tuning_record(tmp_path, monkeypatch):
+    import json
+    import tempname_new_b200 as flux
+    from tempname_new_b200.tuning import table
+    f = tmp_path / "tune.json"
+    f.write_text(json.dumps([{"key": [1234, 512, 256], "best": {"cta_group": 1, "tile_n": 128, "group_m": 4}}]))
+    monkeypatch.setenv("FLUXB_TUNE_FILE", str(f))
+    monkeypatch.setattr(table, "_EXTRA", None)
+    assert table.lookup(1234, 512, 256) == {"cta_group": 1, "tile_n": 128, "group_m": 4}
+    flux.load_tuning_record({"key": [77, 256, 128], "best": {"cta_group": 2, "tile_n": 256, "group_m": 2}})
+    assert table.lookup(77, 256, 128)["group_m"] == 2
+    monkeypatch.setattr(table, "_EXTRA", None)
