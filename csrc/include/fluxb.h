@@ -29,8 +29,9 @@ typedef struct {
  *   FLUXB_PLAIN          D[M, N]
  *   FLUXB_ALLGATHER      a = this rank's shard [M/world, K]; D[M, N]; peers' shards arrive in
  *                        ag_land[rank] ([world][M/world][K]) pushed by the peers' kernels
- *   FLUXB_REDUCE_SCATTER a = [M, K]; partial tiles go to rs_stage[owner] ([world][M/world][N]);
- *                        rs_out [M/world, N] receives the sum over ranks
+ *   FLUXB_REDUCE_SCATTER a = [M, K]; partial tiles of the peers' segments go to rs_stage[owner]
+ *                        ([world][M/world][N]); the tiles of the own segment, computed last, add the
+ *                        peers' slabs and store the sum over ranks to rs_out [M/world, N]
  * With world == 1 every mode degenerates to FLUXB_PLAIN on (a, d / rs_out). */
 typedef struct {
   const void* a;
@@ -60,7 +61,9 @@ typedef struct {
   void* rs_stage[FLUXB_MAX_RANKS];
   uint32_t* rs_ctr[FLUXB_MAX_RANKS];
   void* rs_out;
-  uint32_t* rs_work;         /* local uint32, zero at first use */
+  uint32_t* wave_ctr;        /* optional: a device word owned by the caller (one per op object), zero between
+                                launches, that wave-synchronous tile starts count in; null = a word of the
+                                launcher's per-stream pool */
   uint32_t* local_cnt;       /* local scratch of world * ceil(M/world/128) uint32, zero at first use */
   /* block-scaled fp8 (blockscale != 0): inverse scales as fluxb_quantize_blockwise stores them.
    * sa [rows/128, K/128, 128] for the rows of `a`; sb [N/128, K/128]. In all-gather mode the
@@ -70,7 +73,8 @@ typedef struct {
   const float* sb;
   float* ag_scale_land[FLUXB_MAX_RANKS];
   int32_t blockscale;
-  int32_t reserved3;
+  int32_t tile_m;            /* 0 = auto, else 128 * cta_group, or 512 (CTA pairs on 256-column tiles: two
+                                256-row MMAs per k-step share one B tile) */
   void* stream;
   /* optional timeline: [CTAs][16] uint64 of device memory receiving %globaltimer stamps (ns):
    * 0 roles start, 1 start handshake done, 2 pushes of communication warp 2 published, 3 loads of
@@ -88,6 +92,9 @@ int fluxb_decode_tiles(int32_t num_seg, int32_t seg_first, int32_t m_tiles_seg, 
                        int32_t* out, int32_t n);
 /* number of kernels libfluxb launched from this process so far */
 uint64_t fluxb_launch_count(void);
+/* zero the launcher's per-stream wave counters of the current device (synchronises the device);
+ * needed only after a launch was cut short by a timed-out wait */
+int fluxb_reset_wave_counters(void);
 
 /* ---- Ulysses sequence-parallel projections (base.mode = FLUXB_GEMM_A2A | FLUXB_A2A_GEMM) ----
  * FLUXB_GEMM_A2A  (pre-attention): base.a = x [bs*local_seq, K], base.b = W [N, K] with

@@ -6,26 +6,40 @@
 
 #include <atomic>
 #include <cstdlib>
+#include <mutex>
 
 namespace fluxb {
 
 std::atomic<uint64_t> g_launches{0};
 
-// Wave counters: a small pool per device, zeroed once; a launch takes the next slot and leaves
-// it at zero again when it finishes.
-uint32_t* next_wave_counter() {
-  constexpr int kSlots = 64;
-  static uint32_t* pool[64] = {nullptr};
-  static std::atomic<unsigned> next{0};
+// Wave counters for launches whose caller brings none: a small pool per device, zeroed once. A
+// slot belongs to one stream (launches of a stream run one after the other, and each leaves its
+// counter at zero), so launches that overlap on the GPU never share a word. A process that uses
+// more streams than slots gets no counter for the extra ones (those launches run free).
+namespace {
+constexpr int kWaveSlots = 64;
+std::mutex g_wave_mu;
+uint32_t* g_wave_pool[64] = {nullptr};
+cudaStream_t g_wave_owner[64][kWaveSlots];
+int g_wave_used[64] = {0};
+}  // namespace
+
+uint32_t* wave_counter_for(cudaStream_t stream) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (pool[dev] == nullptr) {
+  std::lock_guard<std::mutex> lock(g_wave_mu);
+  if (g_wave_pool[dev] == nullptr) {
     uint32_t* p = nullptr;
-    if (cudaMalloc(&p, kSlots * 128) != cudaSuccess) return nullptr;
-    cudaMemset(p, 0, kSlots * 128);
-    pool[dev] = p;
+    if (cudaMalloc(&p, kWaveSlots * 128) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, kWaveSlots * 128);
+    g_wave_pool[dev] = p;
   }
-  return pool[dev] + (next.fetch_add(1) % kSlots) * 32;
+  for (int i = 0; i < g_wave_used[dev]; ++i)
+    if (g_wave_owner[dev][i] == stream) return g_wave_pool[dev] + i * 32;
+  if (g_wave_used[dev] == kWaveSlots) return nullptr;
+  const int i = g_wave_used[dev]++;
+  g_wave_owner[dev][i] = stream;
+  return g_wave_pool[dev] + i * 32;
 }
 
 namespace {
@@ -69,6 +83,18 @@ int launch_dense(const DenseGemmParams& p, int grid, cudaStream_t stream) {
 using namespace fluxb;
 
 extern "C" uint64_t fluxb_launch_count(void) { return g_launches.load(); }
+
+// Zero the launcher's wave-counter pool of the current device (after a launch was cut short by a
+// timed-out wait; a completed launch leaves its counter at zero by itself). Synchronises the device.
+extern "C" int fluxb_reset_wave_counters(void) {
+  int dev = 0;
+  FLUXB_CUDA_OK(cudaGetDevice(&dev));
+  FLUXB_CUDA_OK(cudaDeviceSynchronize());
+  std::lock_guard<std::mutex> lock(g_wave_mu);
+  if (dev >= 0 && dev < 64 && g_wave_pool[dev] != nullptr)
+    FLUXB_CUDA_OK(cudaMemset(g_wave_pool[dev], 0, kWaveSlots * 128));
+  return kOk;
+}
 
 static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x);
 
@@ -191,7 +217,25 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   }
   // int8 is built for 256-wide CTA-pair tiles and 128-wide tiles only
   if (a->in_dtype == FLUXB_INT8 && !a->blockscale && !(cg == 2 && bn == 256)) bn = 128;
-  const int bm = 128 * cg;
+  // 512-row tiles (two MMAs per k-step on one B tile): CTA pairs on 256 columns, 16-bit and fp8 inputs,
+  // segments that 512 rows tile without much padding
+  int mt = 1;
+  {
+    static const int tile_m_env = [] {
+      const char* e = getenv("FLUXB_TILE_M");
+      return e ? atoi(e) : 0;
+    }();
+    const int want = a->tile_m > 0 ? a->tile_m : tile_m_env;
+    const int seg_rows = a->M / (segmented ? a->world : 1);
+    const bool can = cg == 2 && bn == 256 && !a->blockscale && !a2a && a->in_dtype != FLUXB_INT8 && seg_rows >= 512;
+    if (want > 0) {
+      FLUXB_REQUIRE(want == 128 * cg || (want == 512 && can), "tile_m must be 128 * cta_group, or 512 for CTA pairs on 256-column tiles");
+      mt = want == 512 ? 2 : 1;
+    } else if (can && (seg_rows % 512 == 0 || seg_rows >= 4096)) {
+      mt = 2;
+    }
+  }
+  const int bm = 128 * cg * mt;
   const int bk = 128 / elt;
   const CUtensorMapDataType in_dt =
       in16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
@@ -209,7 +253,7 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     }
     uint64_t dims[2] = {static_cast<uint64_t>(a->K), rows};
     uint64_t str[1] = {static_cast<uint64_t>(lda) * elt};
-    uint32_t box[2] = {static_cast<uint32_t>(bk), 128};
+    uint32_t box[2] = {static_cast<uint32_t>(bk), static_cast<uint32_t>(128 * mt)};
     if ((rc = encode_tmap(&p.tm_a, in_dt, 2, a_base, dims, str, box, Swz::B128))) return rc;
   }
   if (a2a) {
@@ -302,7 +346,7 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     FLUXB_REQUIRE(a->ag_land[a->rank] != nullptr, "all-gather landing buffer missing");
     uint64_t dims[2] = {static_cast<uint64_t>(a->K), static_cast<uint64_t>(a->M)};
     uint64_t str[1] = {static_cast<uint64_t>(a->K) * elt};
-    uint32_t box[2] = {static_cast<uint32_t>(bk), 128};
+    uint32_t box[2] = {static_cast<uint32_t>(bk), static_cast<uint32_t>(128 * mt)};
     if ((rc = encode_tmap(&p.tm_a_land, in_dt, 2, a->ag_land[a->rank], dims, str, box, Swz::B128)))
       return rc;
     FLUXB_REQUIRE(a->lda == a->K, "all-gather input shard must be contiguous");
@@ -319,32 +363,27 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     p.ag_scale_src = a->sa;
     p.sa_land = a->ag_scale_land[a->rank];
   }
-  // ---- B
-  {
-    uint64_t dims[2] = {static_cast<uint64_t>(a->K), static_cast<uint64_t>(a->N)};
-    uint64_t str[1] = {static_cast<uint64_t>(a->ldb) * elt};
-    uint32_t box[2] = {static_cast<uint32_t>(bk), static_cast<uint32_t>(bn / cg)};
-    if ((rc = encode_tmap(&p.tm_b, in_dt, 2, a->b, dims, str, box, Swz::B128))) return rc;
-  }
   // ---- D
   {
     uint32_t box[3] = {64, 32, 1};
     if (p.mode == kModeReduceScatter) {
-      FLUXB_REQUIRE(a->rs_out && a->rs_work, "reduce-scatter output / work counter missing");
+      FLUXB_REQUIRE(a->rs_out != nullptr, "reduce-scatter output missing");
       for (int r = 0; r < a->world; ++r) {
         FLUXB_REQUIRE(a->rs_stage[r] && a->rs_ctr[r], "reduce-scatter peer pointers missing");
+        // peers: their staging slabs [W][seg_rows][N]; own entry: the output, as a single slab (the
+        // own segment's tiles add the peers' slabs in their epilogue and store the result)
+        const bool own = r == a->rank;
         uint64_t dims[3] = {static_cast<uint64_t>(a->N), static_cast<uint64_t>(p.seg_rows),
-                            static_cast<uint64_t>(a->world)};
+                            own ? 1ull : static_cast<uint64_t>(a->world)};
         uint64_t str[2] = {static_cast<uint64_t>(a->N) * 2,
                            static_cast<uint64_t>(a->N) * 2 * p.seg_rows};
-        if ((rc = encode_tmap(&p.tm_d[r], out_dt, 3, a->rs_stage[r], dims,
+        if ((rc = encode_tmap(&p.tm_d[r], out_dt, 3, own ? a->rs_out : a->rs_stage[r], dims,
                               str, box, Swz::B128)))
           return rc;
         p.rs_ctr[r] = a->rs_ctr[r];
       }
       p.rs_stage = a->rs_stage[a->rank];
       p.rs_out = a->rs_out;
-      p.rs_work = a->rs_work;
     } else if (p.mode != kModeGemmA2A) {
       void* out = a->d ? a->d : a->rs_out;
       const int64_t ldd = a->d ? a->ldd : a->N;
@@ -427,8 +466,45 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   const int64_t tiles = static_cast<int64_t>(p.num_seg) * m_tiles_seg * ((a->N + bn - 1) / bn);
   int grid = sms;
   // every CTA of a multi-rank launch takes part in the flag protocol, so the grid stays full
-  if (!multi && !a2a && tiles * cg < grid) grid = static_cast<int>(tiles) * cg;
+  // (a plain launch shrinks to its work items below)
   if (cg == 2) grid &= ~1;
+  // ---- the last, partial wave: cut its tiles into 2 or 4 column pieces when all the pieces still
+  // fit one wave (a problem smaller than one wave is all "last wave")
+  p.split_from = static_cast<int32_t>(tiles);
+  p.split_shift = 0;
+  {
+    static const int split_env = [] {
+      const char* e = getenv("FLUXB_TAIL_SPLIT");
+      return e ? atoi(e) : 1;
+    }();
+    const int64_t slots = grid / cg;
+    const int64_t rest = tiles % slots;
+    if (split_env != 0 && bn == 256 && !a->blockscale && rest > 0) {
+      int shift = 0;
+      if (4 * rest <= slots && split_env >= 1) shift = 2;
+      else if (2 * rest <= slots) shift = 1;
+      if (split_env == 2 && shift > 1) shift = 1;   // FLUXB_TAIL_SPLIT=2: halves only
+      p.split_from = static_cast<int32_t>(tiles - rest);
+      p.split_shift = shift;
+    }
+  }
+  p.total_vtiles = p.split_from + static_cast<int32_t>((tiles - p.split_from) << p.split_shift);
+  if (!multi && !a2a && static_cast<int64_t>(p.total_vtiles) * cg < grid) grid = p.total_vtiles * cg;
+  // ---- B (the pieces of split tiles load narrower boxes)
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(a->K), static_cast<uint64_t>(a->N)};
+    uint64_t str[1] = {static_cast<uint64_t>(a->ldb) * elt};
+    uint32_t box[2] = {static_cast<uint32_t>(bk), static_cast<uint32_t>(bn / cg)};
+    if ((rc = encode_tmap(&p.tm_b, in_dt, 2, a->b, dims, str, box, Swz::B128))) return rc;
+    if (p.split_shift >= 1) {
+      box[1] = static_cast<uint32_t>(bn / cg / 2);
+      if ((rc = encode_tmap(&p.tm_b_half, in_dt, 2, a->b, dims, str, box, Swz::B128))) return rc;
+    }
+    if (p.split_shift >= 2) {
+      box[1] = static_cast<uint32_t>(bn / cg / 4);
+      if ((rc = encode_tmap(&p.tm_b_quarter, in_dt, 2, a->b, dims, str, box, Swz::B128))) return rc;
+    }
+  }
 
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
   {
@@ -440,7 +516,7 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     // (tiles long enough that the bubble at a wave boundary is noise, and more than two waves)
     const int kblocks = (a->K + bk - 1) / bk;
     const bool want = wave_env >= 0 ? wave_env != 0 : kblocks >= 48;
-    if (want && tiles > 2 * (grid / cg)) p.wave_ctr = next_wave_counter();
+    if (want && p.total_vtiles > 2 * (grid / cg)) p.wave_ctr = a->wave_ctr ? a->wave_ctr : wave_counter_for(stream);
   }
   if (a->blockscale) {
     if (p.mode == kModeAllGather) return launch_dense<DenseCfg<128, 1, 4, 1, 32768, true>>(p, grid, stream);
@@ -448,6 +524,10 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   }
   if (p.mode == kModeAllGather || p.mode == kModeA2AGemm) {
     // variants that carry the staging rings of the all-gather / all-to-all push
+    if (mt == 2) {
+      if (in16) return launch_dense<DenseCfg<256, 0, 4, 2, 16384, false, 2>>(p, grid, stream);
+      return launch_dense<DenseCfg<256, 1, 4, 2, 16384, false, 2>>(p, grid, stream);
+    }
     if (cg == 2 && bn == 256) {
       if (in16) return launch_dense<DenseCfg<256, 0, 6, 2, 16384>>(p, grid, stream);
       if (a->in_dtype == FLUXB_INT8) return launch_dense<DenseCfg<256, 2, 6, 2, 16384>>(p, grid, stream);
@@ -464,6 +544,10 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     FLUXB_REQUIRE(bn == 128, "int8 runs on 256-wide CTA-pair tiles or 128-wide single-CTA tiles");
     if (cg == 2) return launch_dense<DenseCfg<128, 2, 8, 2>>(p, grid, stream);
     return launch_dense<DenseCfg<128, 2, 6>>(p, grid, stream);
+  }
+  if (mt == 2) {
+    if (in16) return launch_dense<DenseCfg<256, 0, 4, 2, 0, false, 2>>(p, grid, stream);
+    return launch_dense<DenseCfg<256, 1, 4, 2, 0, false, 2>>(p, grid, stream);
   }
   if (cg == 2) {
     if (in16) {

@@ -381,7 +381,7 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
     p.ring_inflight = inflight_env;
   }
   // (the cp.async variant keeps its own producer warps per tile and is left alone)
-  if (wave_env != 0 && !(a->gathered && gather_mode == 1)) p.wave_ctr = next_wave_counter();
+  if (wave_env != 0 && !(a->gathered && gather_mode == 1)) p.wave_ctr = wave_counter_for(stream);
   if (pregather) {
     if (bn == 256) return launch_grouped<GroupedCfg<256, 0, 4, 3>>(p, sms, stream);
     return launch_grouped<GroupedCfg<128, 0, 5, 3>>(p, sms, stream);

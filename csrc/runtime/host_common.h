@@ -47,7 +47,8 @@ int encode_tmap(CUtensorMap* out, CUtensorMapDataType dt, int nd, const void* ba
 
 int device_sm_count(int* out);
 // A zeroed device word from a small per-device pool, for launches that keep their CTAs in step wave
-// by wave; the launch leaves it at zero again (csrc/ops/dense_gemm.cu).
-uint32_t* next_wave_counter();
+// by wave; the launch leaves it at zero again. One word per stream (csrc/ops/dense_gemm.cu); null
+// when the pool has no word left for a new stream.
+uint32_t* wave_counter_for(cudaStream_t stream);
 
 }  // namespace fluxb

@@ -10,8 +10,9 @@
 //   warps 4..7  epilogue        tcgen05.ld -> (+bias) -> bf16 -> swizzled smem -> TMA store, to
 //                                local memory or, in reduce-scatter mode, straight into the
 //                                owner rank's staging buffer over NVLink
-// After the role loops a reduce-scatter launch sums the W partial slabs that the peers pushed
-// into this rank's staging buffer (all 256 threads, work claimed dynamically).
+// In reduce-scatter mode the tiles of this rank's own segment come last; their epilogue adds the
+// W-1 partial tiles that the peers have pushed into this rank's staging buffer to the fp32
+// accumulator and stores the finished rows, so no separate reduction pass exists.
 //
 // The same kernel serves the three dense ops of the library; they differ only in how the M
 // dimension is cut into per-rank segments and where tiles come from / go to:
@@ -20,7 +21,17 @@
 //                   landing buffer once its flags show that the owner's push has landed.
 //                                                                (reference: src/ag_gemm, src/coll)
 //   GEMM+ReduceScatter  W segments, own last; a tile of segment s is stored into rank s's
-//                   staging slab [this rank]; the owner reduces.  (reference: src/gemm_rs)
+//                   staging slab [this rank]; the owner adds the slabs to its own tiles.
+//                                                                (reference: src/gemm_rs)
+//
+// Tile shapes. CG_ = 2, MT_ = 2 is the large-problem shape: a CTA pair owns a 512 x 256 tile, each
+// CTA stages 256 rows of A and 128 rows of B per k-block and the leader issues two 256 x 256
+// MMAs that share the B tile, so 96 KB enter the pair's shared memory per k-block where two
+// 256 x 256 tiles would take 128 KB. Its two accumulators fill TMEM, so the epilogue of a tile
+// overlaps only the first STAGES k-blocks of the next one (issued into accumulator 0 while
+// accumulator 1 is still being read).
+// The last, partial wave of tiles may be cut into 2 or 4 column pieces each (split_shift), so that
+// all CTAs share the remaining work instead of a few CTAs running whole tiles.
 #pragma once
 
 #include "ptx.cuh"
@@ -48,7 +59,7 @@ enum TraceSlot : int {
   kTraceEnd = 6,          // epilogue warp 4: done
   kTraceFlagWait = 7,     // producer: total time spent waiting for arrival flags
   kTraceSlice0 = 8,       // producer, first tile: 8 + j = K slice j (post-attention) became readable;
-                          // reduce-scatter: 8 = reduce tail entered, 9 = reduce tail left
+                          // reduce-scatter: 8 = first tile of the own segment reached by epilogue warp 4
 };
 constexpr int kTraceWords = 16;  // words per CTA
 constexpr int kMaxHeadGroups = 3;  // q, k, v
@@ -56,14 +67,20 @@ constexpr int kMaxHeadGroups = 3;  // q, k, v
 struct DenseGemmParams {
   CUtensorMap tm_a;              // A rows owned by this launch: [rows, K], box {BK, 128}
   CUtensorMap tm_a_land;         // all-gather landing buffer viewed as [W*seg_rows, K]
-  CUtensorMap tm_b;              // B [N, K], box {BK, BN}
-  CUtensorMap tm_d[kMaxRanks];   // 3-D store maps [slab][seg_rows][N], box {64, 32, 1}
+  CUtensorMap tm_b;              // B [N, K], box {BK, BN / CG}
+  CUtensorMap tm_b_half;         // same, box {BK, BN / CG / 2}: column pieces of split tiles
+  CUtensorMap tm_b_quarter;      // same, box {BK, BN / CG / 4}
+  CUtensorMap tm_d[kMaxRanks];   // 3-D store maps [slab][seg_rows][N], box {64, 32, 1}; in reduce-scatter
+                                 // mode entry `rank` covers rs_out ([1][seg_rows][N])
   int32_t M, N, K;
   int32_t num_seg, seg_rows, seg_first;
   int32_t rank, world;
   int32_t mode;
   int32_t group_m;
   int32_t seg_span, seg_solo_first;  // raster groups of visited segments, see decode_tile
+  int32_t split_from, split_shift;   // tiles >= split_from are cut into 1 << split_shift column pieces
+  int32_t total_vtiles;              // work items of the launch: split_from + ((tiles - split_from) << split_shift)
+  int32_t reserved5;
   int32_t ag_inflight;           // all-gather push: loads in flight ahead of the stores (1..3)
   int32_t l2_hints;              // 1: A tiles are loaded evict_last (the band is reused by the next waves),
                                  // B tiles evict_first (streamed once per wave)
@@ -102,7 +119,6 @@ struct DenseGemmParams {
                                  // warps of this GPU that finished their part of one (peer, tile row)
   const void* rs_stage;          // local staging [W][seg_rows][N] bf16
   void* rs_out;                  // [seg_rows, N] bf16
-  uint32_t* rs_work;             // local work-claim counter, zero between calls
   uint32_t* wave_ctr;            // optional, zero between launches: number of tiles whose loads have been
                                  // issued. CTAs start wave i only after all of wave i-1 has been issued, so
                                  // the whole grid walks K together and shared tiles are read while in L2.
@@ -128,30 +144,36 @@ struct DenseGemmParams {
                                    // kModeA2AGemm: [W src][m_tiles] per tile row
 };
 
-// CG_ = 1: one CTA per 128 x BN tile. CG_ = 2: a pair of CTAs (one cluster) shares a 256 x BN
-// tile: each CTA stages its own 128 rows of A and its own BN/2 rows of B, the pair leader issues
-// tcgen05.mma.cta_group::2, and each CTA ends up with its 128 x BN slice of D in its own TMEM.
+// CG_ = 1: one CTA per 128 x BN tile. CG_ = 2: a pair of CTAs (one cluster) shares a (256 * MT_) x BN
+// tile: each CTA stages its own 128 * MT_ rows of A and its own BN/2 rows of B, the pair leader issues
+// tcgen05.mma.cta_group::2 (MT_ of them per k-step, one per 256-row half), and each CTA ends up with
+// its 128 * MT_ x BN slice of D in its own TMEM.
 // COMM_ > 0 reserves COMM_ bytes of shared memory as staging rings for the all-gather push.
 // BS_ = true: block-scaled fp8 (1x128 A scales, 128x128 B scales): every 128-deep k-block is
 // accumulated into a fresh TMEM buffer and promoted into fp32 registers, multiplied by its
 // scales, by eight epilogue warps (two per TMEM lane quadrant, 64 columns each).
-template <int BN_, int KIND_, int STAGES_, int CG_ = 1, int COMM_ = 0, bool BS_ = false>
+template <int BN_, int KIND_, int STAGES_, int CG_ = 1, int COMM_ = 0, bool BS_ = false, int MT_ = 1>
 struct DenseCfg {
   static constexpr int COMM_BYTES = COMM_;
   static constexpr bool BS = BS_;
+  static constexpr int MT = MT_;
   static constexpr int EPI_WARPS = BS_ ? 8 : 4;
   static constexpr int THREADS = 128 + 32 * EPI_WARPS;
-  static constexpr int ACC_BUFS = BS_ ? 3 : 2;   // block-scaled: 3 k-block buffers + 1 exchange region
+  // MT_ == 1: two accumulators used alternately (the epilogue of a tile overlaps the next main loop);
+  // MT_ == 2: the two row halves of one tile; block-scaled: 3 k-block buffers + 1 exchange region
+  static constexpr int ACC_BUFS = BS_ ? 3 : 2;
   static_assert(!BS_ || (KIND_ == 1 && BN_ == 128 && CG_ == 1), "block-scaled variant: fp8, 128x128 tiles");
+  static_assert(MT_ == 1 || (MT_ == 2 && CG_ == 2 && BN_ == 256 && !BS_), "512-row tiles: CTA pairs, 256 columns");
   static constexpr int CG = CG_;
-  static constexpr int BM_CTA = 128;                       // rows of A / D per CTA
-  static constexpr int BM = 128 * CG_;                     // rows per tile
+  static constexpr int BM_CTA = 128 * MT_;                 // rows of A / D per CTA
+  static constexpr int BM = BM_CTA * CG_;                  // rows per tile
   static constexpr int BN = BN_;
   static constexpr int KIND = KIND_;                       // 0 = bf16 / fp16, 1 = fp8, 2 = int8 (s32 accumulators)
   static constexpr int ELT = KIND_ == 0 ? 2 : 1;
   static constexpr int BK = 128 / ELT;                     // one 128-byte swizzle row
   static constexpr int UMMA_K = 32 / ELT;
   static constexpr int STAGES = STAGES_;
+  static constexpr int A_HALF_BYTES = 128 * 128;           // one 128-row block of A
   static constexpr int A_BYTES = BM_CTA * 128;
   static constexpr int B_ROWS_CTA = BN / CG_;
   static constexpr int B_BYTES = B_ROWS_CTA * 128;
@@ -166,6 +188,8 @@ struct DenseCfg {
   static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared memory limit");
   static constexpr int TMEM_COLS = 512;
   static_assert((ACC_BUFS + (BS_ ? 1 : 0)) * BN <= TMEM_COLS, "accumulators must fit TMEM");
+  // column pieces of a split tile are BN >> shift wide; the epilogue moves 64 columns at a time
+  static constexpr int MAX_SPLIT_SHIFT = (BN_ == 256 && !BS_) ? 2 : 0;
 };
 
 struct TileCoord {
@@ -173,10 +197,19 @@ struct TileCoord {
   int m_in_seg;  // first row inside the segment
   int m_tile;    // tile row index inside the segment
   int n0;        // first output column
+  int shift;     // the work item is BN >> shift columns wide (a piece of a split tile)
 };
 
 __host__ __device__ __forceinline__ TileCoord decode_tile(const DenseGemmParams& p, int t, int m_tiles_seg,
                                                  int n_tiles, int BM, int BN) {
+  // Work items past split_from are column pieces of the tiles at the end of the order
+  int shift = 0, piece = 0;
+  if (t >= p.split_from) {
+    const int h = t - p.split_from;
+    shift = p.split_shift;
+    piece = h & ((1 << shift) - 1);
+    t = p.split_from + (h >> shift);
+  }
   // Segments are visited in the order seg_first, seg_first + 1, ... and rastered in groups of
   // seg_span consecutive segments (1 or 2; seg_solo_first: the first visited segment is a group
   // of its own), so that a band of group_m tile rows can span two segments.
@@ -218,7 +251,8 @@ __host__ __device__ __forceinline__ TileCoord decode_tile(const DenseGemmParams&
   c.seg = seg;
   c.m_tile = mt;
   c.m_in_seg = mt * BM;
-  c.n0 = nt * BN;
+  c.n0 = nt * BN + piece * (BN >> shift);
+  c.shift = shift;
   return c;
 }
 
@@ -246,7 +280,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
   volatile uint32_t* tmem_slot =
       reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * STAGES + 2 * NACC));
   volatile uint32_t* abort_word = tmem_slot + 1;
-  volatile uint32_t* claim_slot = tmem_slot + 2;
   const uint32_t ring_bar_base = bar_base + 8u * (2 * STAGES + 2 * NACC) + 16u;
   const uint32_t xfull_bar = ring_bar_base + 64u, xempty_bar = ring_bar_base + 72u;  // block-scaled exchange
   static_assert(8 * (2 * STAGES + 2 * NACC) + 16 + 64 + 16 <= Cfg::BAR_BYTES, "barrier block too small");
@@ -294,7 +327,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
 
   const int m_tiles_seg = (p.seg_rows + BM - 1) / BM;
   const int n_tiles = (p.N + BN - 1) / BN;
-  const int total_tiles = p.num_seg * m_tiles_seg * n_tiles;
+  const int total_tiles = p.total_vtiles;   // work items: whole tiles, then the column pieces of split ones
   const int k_blocks = (p.K + BK - 1) / BK;
   const bool multi = p.world > 1 && p.mode != kModePlain;
 
@@ -325,6 +358,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           flag_wait_ge(wc, p.wave_ctr, need, kSiteStartBarrier);
         }
         const CUtensorMap* tma = &p.tm_a;
+        const CUtensorMap* tmb = c.shift == 0 ? &p.tm_b : (c.shift == 1 ? &p.tm_b_half : &p.tm_b_quarter);
+        const uint32_t stage_tx = Cfg::A_BYTES + (Cfg::B_BYTES >> c.shift);
+        const int b_row = c.n0 + static_cast<int>(cta_rank) * (Cfg::B_ROWS_CTA >> c.shift);
         const int m_cta = c.m_in_seg + static_cast<int>(cta_rank) * Cfg::BM_CTA;
         int a_row = c.seg * p.seg_rows + m_cta;
         if (p.mode == kModeAllGather && multi) {
@@ -392,27 +428,23 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             src = src == 0 ? p.world - 1 : src - 1;
           }
           if constexpr (CG == 1) {
-            ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::STAGE_BYTES);
+            ptx::mbar_arrive_expect_tx(full_bar(stage), stage_tx);
             if (in_place) ptx::tma_load_4d(sa, &p.tm_a_own, full_bar(stage), own_col, own_s, own_head, own_b);
             else if (a2a_in) ptx::tma_load_4d(sa, &p.tm_a_land4, full_bar(stage), own_col, m_cta, own_head, ld_src);
             else if (p.l2_hints) ptx::tma_load_2d_hint(sa, tma, full_bar(stage), kb * BK, a_row, pol_a);
             else ptx::tma_load_2d(sa, tma, full_bar(stage), kb * BK, a_row);
-            if (p.l2_hints) ptx::tma_load_2d_hint(sa + Cfg::A_BYTES, &p.tm_b, full_bar(stage), kb * BK, c.n0, pol_b);
-            else ptx::tma_load_2d(sa + Cfg::A_BYTES, &p.tm_b, full_bar(stage), kb * BK, c.n0);
+            if (p.l2_hints) ptx::tma_load_2d_hint(sa + Cfg::A_BYTES, tmb, full_bar(stage), kb * BK, b_row, pol_b);
+            else ptx::tma_load_2d(sa + Cfg::A_BYTES, tmb, full_bar(stage), kb * BK, b_row);
           } else {
             // both CTAs' bytes are counted on the leader's barrier
             const uint32_t fb = full_owner0 + 8u * stage;
-            if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * Cfg::STAGE_BYTES);
+            if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * stage_tx);
             if (in_place) ptx::tma_load_4d_cg2(sa, &p.tm_a_own, fb, own_col, own_s, own_head, own_b);
             else if (a2a_in) ptx::tma_load_4d_cg2(sa, &p.tm_a_land4, fb, own_col, m_cta, own_head, ld_src);
             else if (p.l2_hints) ptx::tma_load_2d_cg2_hint(sa, tma, fb, kb * BK, a_row, pol_a);
             else ptx::tma_load_2d_cg2(sa, tma, fb, kb * BK, a_row);
-            if (p.l2_hints)
-              ptx::tma_load_2d_cg2_hint(sa + Cfg::A_BYTES, &p.tm_b, fb, kb * BK,
-                                        c.n0 + static_cast<int>(cta_rank) * Cfg::B_ROWS_CTA, pol_b);
-            else
-              ptx::tma_load_2d_cg2(sa + Cfg::A_BYTES, &p.tm_b, fb, kb * BK,
-                                   c.n0 + static_cast<int>(cta_rank) * Cfg::B_ROWS_CTA);
+            if (p.l2_hints) ptx::tma_load_2d_cg2_hint(sa + Cfg::A_BYTES, tmb, fb, kb * BK, b_row, pol_b);
+            else ptx::tma_load_2d_cg2(sa + Cfg::A_BYTES, tmb, fb, kb * BK, b_row);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -432,11 +464,17 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && leader) {
-      const uint32_t idesc = ptx::umma_idesc(p.ab_fmt, p.ab_fmt, BM, BN, 0, 0, Cfg::KIND == 2 ? 2u : 1u);
+      // one instruction covers 128 rows per CTA of the group
+      const uint32_t idesc_full = ptx::umma_idesc(p.ab_fmt, p.ab_fmt, 128 * CG, BN, 0, 0, Cfg::KIND == 2 ? 2u : 1u);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       for (int t = tile_slot; t < total_tiles; t += tile_stride, ++it) {
+        // a column piece of a split tile is a narrower instruction on the same operands
+        const int shift = t >= p.split_from ? p.split_shift : 0;
+        const uint32_t idesc = shift == 0 ? idesc_full
+                                          : ptx::umma_idesc(p.ab_fmt, p.ab_fmt, 128 * CG, BN >> shift, 0, 0,
+                                                            Cfg::KIND == 2 ? 2u : 1u);
         if constexpr (Cfg::BS) {
           // every k-block goes to its own TMEM buffer; the epilogue warps promote it
           for (int kb = 0; kb < k_blocks; ++kb) {
@@ -459,6 +497,61 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
               phase ^= 1u;
             }
           }
+          continue;
+        }
+        if constexpr (Cfg::MT == 2) {
+          // Two accumulators = the two 256-row halves of the tile; both read the same B tile. The
+          // epilogue of the previous tile drains accumulator 0 first: the first k-blocks of this
+          // tile go into accumulator 0 while accumulator 1 is still being read, then the same
+          // k-blocks into accumulator 1 (which releases their stages).
+          const uint32_t par_e = (static_cast<uint32_t>(it) & 1u) ^ 1u;
+          const int head = k_blocks < STAGES ? k_blocks : STAGES;
+          auto issue_half = [&](int st, int half, bool first) {
+            const uint32_t sa = smem_base + st * Cfg::STAGE_BYTES;
+            const uint64_t adesc = ptx::umma_desc_k_sw128(sa + half * Cfg::A_HALF_BYTES);
+            const uint64_t bdesc = ptx::umma_desc_k_sw128(sa + Cfg::A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / Cfg::UMMA_K; ++k)
+              ptx::umma_ss<CG, Cfg::KIND>(tmem_base + half * BN, adesc + 2u * k, bdesc + 2u * k, idesc,
+                                          (!first || k != 0) ? 1u : 0u);
+          };
+          mbar_wait(wc, tempty_bar(0), par_e, kSiteTmemEmpty);
+          ptx::tc_fence_after();
+          {
+            int st = stage;
+            uint32_t ph = phase;
+            for (int kb = 0; kb < head; ++kb) {
+              mbar_wait(wc, full_bar(st), ph, kSiteSmemFull);
+              ptx::tc_fence_after();
+              issue_half(st, 0, kb == 0);
+              if (++st == STAGES) {
+                st = 0;
+                ph ^= 1u;
+              }
+            }
+          }
+          mbar_wait(wc, tempty_bar(1), par_e, kSiteTmemEmpty);
+          ptx::tc_fence_after();
+          for (int kb = 0; kb < head; ++kb) {
+            issue_half(stage, 1, kb == 0);
+            ptx::umma_commit_cg2(empty_bar(stage), 3);
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          for (int kb = head; kb < k_blocks; ++kb) {
+            mbar_wait(wc, full_bar(stage), phase, kSiteSmemFull);
+            ptx::tc_fence_after();
+            issue_half(stage, 0, false);
+            issue_half(stage, 1, false);
+            ptx::umma_commit_cg2(empty_bar(stage), 3);
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          ptx::umma_commit_cg2(tfull_bar(0), 3);
           continue;
         }
         const int acc = it & 1;
@@ -835,10 +928,60 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     uint32_t nstore = 0;
     bool started = !(multi && (p.mode == kModeReduceScatter || p.mode == kModeGemmA2A));
 
+    // Reduce-scatter, tiles of the own segment: add the partial results that the W-1 peers stored
+    // into this rank's staging slabs (64 columns of this thread's row per source, sources in the
+    // order rank+1, rank+2, ...; the loads of the next source are in flight while one is added).
+    const uint8_t* rs_stage_b = reinterpret_cast<const uint8_t*>(p.rs_stage);
+    auto add_peers = [&](uint32_t (&r0)[32], uint32_t (&r1)[32], int col0, int row) {
+      if (row >= p.seg_rows || col0 >= p.N) return;
+      uint4 v[2][8];
+      const int64_t row_bytes = static_cast<int64_t>(p.N) * 2;
+      const int64_t slab_bytes = row_bytes * p.seg_rows;
+      const int ncol = p.N - col0;   // valid columns from col0 on (a multiple of 8)
+      auto load_src = [&](uint4 (&dst)[8], int d) {
+        int src = p.rank + d;
+        if (src >= p.world) src -= p.world;
+        const uint8_t* base = rs_stage_b + src * slab_bytes + row * row_bytes + static_cast<int64_t>(col0) * 2;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (8 * j < ncol) dst[j] = ptx::ld_global_cs_v4(base + 16 * j);
+          else dst[j] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      };
+      auto add_src = [&](const uint4 (&src)[8]) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t w[4] = {src[j].x, src[j].y, src[j].z, src[j].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = 8 * j + 2 * e;   // column inside the 64-column chunk
+            const float lo = ptx::half_bits_to_float(static_cast<uint16_t>(w[e] & 0xFFFFu), f16);
+            const float hi = ptx::half_bits_to_float(static_cast<uint16_t>(w[e] >> 16), f16);
+            if (c < 32) {
+              r0[c] = __float_as_uint(__uint_as_float(r0[c]) + lo);
+              r0[c + 1] = __float_as_uint(__uint_as_float(r0[c + 1]) + hi);
+            } else {
+              r1[c - 32] = __float_as_uint(__uint_as_float(r1[c - 32]) + lo);
+              r1[c - 31] = __float_as_uint(__uint_as_float(r1[c - 31]) + hi);
+            }
+          }
+        }
+      };
+      load_src(v[1], 1);
+#pragma unroll
+      for (int d = 1; d < kMaxRanks; ++d) {
+        if (d < p.world) {
+          if (d + 1 < p.world) load_src(v[(d + 1) & 1], d + 1);
+          add_src(v[d & 1]);
+        }
+      }
+    };
+
     // 32 rows x 64 columns of fp32 results (r0: columns 0..31, r1: 32..63 of the chunk, this
-    // thread's row) -> scale, bias, activation -> 16-bit -> swizzled staging -> TMA store
+    // thread's row) -> scale, bias, activation (-> + peers' partial results) -> 16-bit -> swizzled
+    // staging -> TMA store
     auto emit_chunk = [&](uint32_t (&r0)[32], uint32_t (&r1)[32], int col0, int row, int64_t grow,
-                          int store_row0, const CUtensorMap* tmd, int z) {
+                          int store_row0, const CUtensorMap* tmd, int z, bool own_rs) {
       if constexpr (Cfg::KIND == 2) {   // s32 accumulators of the int8 kind
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -872,6 +1015,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           r1[j] = __float_as_uint(ptx::activate(__uint_as_float(r1[j]), p.act));
         }
       }
+      if (own_rs) add_peers(r0, r1, col0, row);
       const uint32_t buf = Cfg::EPI_BUFS == 2 ? (nstore & 1u) : 0u;
       if (lane == 0) ptx::bulk_wait_read<Cfg::EPI_BUFS - 1>();
       __syncwarp();
@@ -921,15 +1065,19 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
 
     // the tile row's slab has fully landed at the owner: the last of the warps that store into
     // it tells the owner
-    auto rs_arrive = [&](int seg, int mt) {
+    // (counted in 64-column chunk stores per warp, so that split tiles add up to the same total)
+    const uint32_t rs_row_total = static_cast<uint32_t>(n_tiles) * (BN / 64) * Cfg::MT * 4u * CG;
+    auto rs_arrive = [&](int seg, int mt, uint32_t chunks) {
       ptx::fence_proxy_async_all();
       uint32_t* cnt = p.local_cnt + seg * m_tiles_seg + mt;
-      if (ptx::atom_add_acq_rel_sys(cnt, 1u) == static_cast<uint32_t>(n_tiles) * 4u * CG - 1u) {
+      if (ptx::atom_add_acq_rel_sys(cnt, chunks) + chunks == rs_row_total) {
         *cnt = 0;
         ptx::st_release_sys(p.rs_ctr[seg] + mt * kMaxRanks + p.rank, p.epoch);
       }
     };
     int pend_seg = -1, pend_mt = 0;
+    uint32_t pend_chunks = 0;
+    uint32_t own_seen = 0;   // tile rows of the own segment whose W-1 slabs were seen to have landed
     uint64_t bs_acc[Cfg::BS ? 64 : 1];
     for (int t = tile_slot; t < total_tiles; t += tile_stride, ++it) {
       const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
@@ -941,9 +1089,23 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         __syncwarp();
         started = true;
       }
+      bool own_rs = false;
       if (p.mode == kModeReduceScatter && multi) {
         tmd = &p.tm_d[c.seg];
         z = p.rank;
+        if (c.seg == p.rank) {
+          // own segment: every peer's partial rows of this tile row must have landed; the result
+          // goes to rs_out (tm_d[rank] covers it as one slab)
+          own_rs = true;
+          z = 0;
+          if (c.m_tile >= 32 || ((own_seen >> c.m_tile) & 1u) == 0u) {
+            if (own_seen == 0 && ew == 0 && lane == 0) stamp(kTraceSlice0);
+            if (lane < p.world && lane != p.rank)
+              flag_wait_ge(wc, p.rs_ctr[p.rank] + c.m_tile * kMaxRanks + lane, p.epoch, kSiteTileCounter);
+            __syncwarp();
+            if (c.m_tile < 32) own_seen |= 1u << c.m_tile;
+          }
+        }
         if (!started) {
           // peers may still be reducing the previous call's slabs until they enter this call
           if (lane < p.world) flag_wait_ge(wc, p.start_ctr[p.rank] + lane, p.epoch, kSiteStartBarrier);
@@ -951,8 +1113,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           started = true;
         }
       }
-      const int row = m_cta + q * 32 + lane;                   // row inside the segment
-      const int64_t grow = static_cast<int64_t>(c.seg) * p.seg_rows + row;  // global row
+      int row = m_cta + q * 32 + lane;                         // row inside the segment
+      int64_t grow = static_cast<int64_t>(c.seg) * p.seg_rows + row;  // global row
 
       if constexpr (Cfg::BS) {
         // ---- block-scaled: promote every k-block's partial product into fp32 registers.
@@ -1062,7 +1224,35 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
               r1[2 * j] = static_cast<uint32_t>(a1);
               r1[2 * j + 1] = static_cast<uint32_t>(a1 >> 32);
             }
-            emit_chunk(r0, r1, c.n0 + h * 64, row, grow, m_cta + q * 32, tmd, z);
+            emit_chunk(r0, r1, c.n0 + h * 64, row, grow, m_cta + q * 32, tmd, z, own_rs);
+          }
+        }
+      } else if constexpr (Cfg::MT == 2) {
+        // both row halves of the tile complete together; accumulator 0 is drained (and handed
+        // back to the issuer) first
+        const uint32_t par = static_cast<uint32_t>(it) & 1u;
+        if (lane == 0) mbar_wait(wc, tfull_bar(0), par, kSiteTmemFull);
+        __syncwarp();
+        mbar_wait(wc, tfull_bar(0), par, kSiteTmemFull);
+        ptx::tc_fence_after();
+        const int nch = (BN >> c.shift) / 64;
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          row = m_cta + h * 128 + q * 32 + lane;
+          grow = static_cast<int64_t>(c.seg) * p.seg_rows + row;
+#pragma unroll 1
+          for (int ch = 0; ch < nch; ++ch) {
+            uint32_t r0[32], r1[32];
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + h * BN + ch * 64;
+            ptx::tmem_ld_32x32b_x32(taddr, r0);
+            ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
+            ptx::tmem_ld_wait();
+            if (ch == nch - 1) {
+              ptx::tc_fence_before();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive_remote(tempty_bar(h), 0);
+            }
+            emit_chunk(r0, r1, c.n0 + ch * 64, row, grow, m_cta + h * 128 + q * 32, tmd, z, own_rs);
           }
         }
       } else {
@@ -1074,14 +1264,15 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         __syncwarp();
         mbar_wait(wc, tfull_bar(acc), acc_phase, kSiteTmemFull);
         ptx::tc_fence_after();
+        const int nch = (BN >> c.shift) / 64;
 #pragma unroll 1
-        for (int ch = 0; ch < BN / 64; ++ch) {
+        for (int ch = 0; ch < nch; ++ch) {
           uint32_t r0[32], r1[32];
           const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + ch * 64;
           ptx::tmem_ld_32x32b_x32(taddr, r0);
           ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
           ptx::tmem_ld_wait();
-          if (ch == BN / 64 - 1) {
+          if (ch == nch - 1) {
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -1089,7 +1280,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
               else ptx::mbar_arrive_remote(tempty_bar(acc), 0);
             }
           }
-          emit_chunk(r0, r1, c.n0 + ch * 64, row, grow, m_cta + q * 32, tmd, z);
+          emit_chunk(r0, r1, c.n0 + ch * 64, row, grow, m_cta + q * 32, tmd, z, own_rs);
         }
       }
       if (p.mode == kModeReduceScatter && multi) {
@@ -1100,18 +1291,23 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         const bool stored = !Cfg::BS || ((it & 1) == (ew >> 2));
         if (stored) {
           if (lane == 0) {
-            constexpr int kGroupsPerTile = Cfg::BS ? 2 : BN / 64;
-            ptx::bulk_wait<kGroupsPerTile>();
-            if (pend_seg >= 0) rs_arrive(pend_seg, pend_mt);
+            // store groups this warp committed for a whole tile; a piece of a split tile commits
+            // fewer, so there everything is waited for
+            constexpr int kGroupsPerTile = Cfg::BS ? 2 : Cfg::MT * BN / 64;
+            if (c.shift == 0) ptx::bulk_wait<kGroupsPerTile>();
+            else ptx::bulk_wait<0>();
+            if (pend_seg >= 0) rs_arrive(pend_seg, pend_mt, pend_chunks);
           }
-          pend_seg = c.seg;
+          // tiles of the own segment stay here: nobody is told
+          pend_seg = own_rs ? -1 : c.seg;
           pend_mt = c.m_tile;
+          pend_chunks = Cfg::BS ? 2u : static_cast<uint32_t>(Cfg::MT * ((BN >> c.shift) / 64));
         }
         __syncwarp();
       }
     }
     if (lane == 0) ptx::bulk_wait<0>();
-    if (p.mode == kModeReduceScatter && multi && lane == 0 && pend_seg >= 0) rs_arrive(pend_seg, pend_mt);
+    if (p.mode == kModeReduceScatter && multi && lane == 0 && pend_seg >= 0) rs_arrive(pend_seg, pend_mt, pend_chunks);
     __syncwarp();
     if (p.mode == kModeGemmA2A && multi) {
       // all stores of this warp have landed; the last warp of the whole grid tells every rank,
@@ -1140,93 +1336,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc<CG>(tmem_base, Cfg::TMEM_COLS);
-  }
-
-  // -------------------------------------------------------------------- reduce-scatter tail
-  if (p.mode == kModeReduceScatter && multi) {
-    // Sum the W slabs of the local staging buffer into rs_out. A work unit is kUnit 16-byte
-    // chunks (8 elements) of the [seg_rows, N] output; units are claimed from a counter. Every
-    // CTA makes exactly one failing claim, and whoever makes the very last claim of the launch
-    // puts the counter back to zero for the next call.
-    constexpr int kUnit = 256 * 8;
-    const int64_t chunks_per_row = p.N >> 3;
-    const int64_t total_chunks = static_cast<int64_t>(p.seg_rows) * chunks_per_row;
-    const uint32_t units = static_cast<uint32_t>((total_chunks + kUnit - 1) / kUnit);
-    const uint4* stage = reinterpret_cast<const uint4*>(p.rs_stage);
-    uint4* out = reinterpret_cast<uint4*>(p.rs_out);
-    const int64_t slab_chunks = total_chunks;
-    const bool tail_f16 = p.out_f16 != 0;
-    if (threadIdx.x == 0) stamp(kTraceSlice0);      // reduce tail entered
-    while (true) {
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        const uint32_t got = atomicAdd(p.rs_work, 1u);
-        if (got == units + gridDim.x - 1u) atomicExch(p.rs_work, 0u);
-        *claim_slot = got;
-      }
-      __syncthreads();
-      const uint32_t u = *claim_slot;
-      if (u >= units) break;
-      {
-        // every source's slab rows of this unit must have landed: one thread per source looks at
-        // the flags of the tile rows the unit touches (usually one), the block barrier passes it on
-        const int64_t c0 = static_cast<int64_t>(u) * kUnit;
-        const int64_t c1 = (c0 + kUnit < total_chunks ? c0 + kUnit : total_chunks) - 1;
-        const int mt0 = static_cast<int>((c0 / chunks_per_row) / BM);
-        const int mt1 = static_cast<int>((c1 / chunks_per_row) / BM);
-        if (static_cast<int>(threadIdx.x) < p.world)
-          for (int mt = mt0; mt <= mt1; ++mt)
-            flag_wait_ge(wc, p.rs_ctr[p.rank] + mt * kMaxRanks + threadIdx.x, p.epoch, kSiteTileCounter);
-        __syncthreads();
-      }
-      if (threadIdx.x >= 256) continue;  // (block-scaled variant runs 384 threads)
-#pragma unroll 1
-      for (int rep = 0; rep < kUnit / 256; rep += 2) {
-        int64_t idx[2];
-        bool ok[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          idx[h] = static_cast<int64_t>(u) * kUnit + (rep + h) * 256 + threadIdx.x;
-          ok[h] = idx[h] < total_chunks;
-
-        }
-        float accv[2][8];
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int e = 0; e < 8; ++e) accv[h][e] = 0.f;
-        uint4 v[kMaxRanks][2];
-#pragma unroll
-        for (int s = 0; s < kMaxRanks; ++s)
-#pragma unroll
-          for (int h = 0; h < 2; ++h)
-            if (s < p.world && ok[h]) v[s][h] = ptx::ld_global_cs_v4(stage + s * slab_chunks + idx[h]);
-#pragma unroll
-        for (int s = 0; s < kMaxRanks; ++s)
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (s < p.world && ok[h]) {
-              const uint32_t w[4] = {v[s][h].x, v[s][h].y, v[s][h].z, v[s][h].w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                accv[h][2 * e] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] & 0xFFFFu), tail_f16);
-                accv[h][2 * e + 1] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] >> 16), tail_f16);
-              }
-            }
-          }
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          if (!ok[h]) continue;
-          uint4 o;
-          o.x = ptx::pack_half2(tail_f16, accv[h][0], accv[h][1]);
-          o.y = ptx::pack_half2(tail_f16, accv[h][2], accv[h][3]);
-          o.z = ptx::pack_half2(tail_f16, accv[h][4], accv[h][5]);
-          o.w = ptx::pack_half2(tail_f16, accv[h][6], accv[h][7]);
-          out[idx[h]] = o;
-        }
-      }
-    }
-    if (threadIdx.x == 0) stamp(kTraceSlice0 + 1);  // reduce tail left
   }
 }
 

@@ -12,6 +12,51 @@ from torch import nn
 from ..parallel.layers import ColumnParallelLinear, RowParallelLinear
 
 
+class HostStep:
+    """Runs ``fn(x_device)`` for a batch that lives in pinned host memory and brings a per-step
+    result back: the shard is copied host->device on a side stream into one of two device buffers
+    (the upload of a step overlaps the kernels of the step before), ``fn`` runs on the current
+    stream, and ``[mean |y|, y[0, :]]`` is copied device->host into a pinned tensor. Works for any
+    ``fn`` (the benchmark drives both this library's block and the torch.matmul + NCCL block
+    through it, so the two end-to-end numbers differ only in ``fn``)."""
+
+    def __init__(self, fn, device):
+        self.fn, self.device = fn, device
+        self.copy_stream = torch.cuda.Stream(device=device)
+        self.bufs = None
+        self.used = [None, None]
+        self.step = 0
+        self.last_result_event = None
+
+    @torch.no_grad()
+    def __call__(self, x_pinned: torch.Tensor, result_pinned: Optional[torch.Tensor] = None):
+        if self.bufs is None or self.bufs[0].shape != x_pinned.shape or self.bufs[0].dtype != x_pinned.dtype:
+            self.bufs = [torch.empty(x_pinned.shape, dtype=x_pinned.dtype, device=self.device) for _ in range(2)]
+            self.used = [None, None]
+        main = torch.cuda.current_stream(self.device)
+        k = self.step & 1
+        self.step += 1
+        cs = self.copy_stream
+        if self.used[k] is not None:
+            cs.wait_event(self.used[k])          # the step that last read this buffer is done with it
+        with torch.cuda.stream(cs):
+            self.bufs[k].copy_(x_pinned, non_blocking=True)
+            up = torch.cuda.Event()
+            up.record(cs)
+        main.wait_event(up)
+        y = self.fn(self.bufs[k])
+        res = torch.cat([y.float().abs().mean().reshape(1), y[0].float()])
+        done = torch.cuda.Event()
+        done.record(main)
+        self.used[k] = done
+        if result_pinned is None:
+            return res.cpu()
+        result_pinned.copy_(res, non_blocking=True)
+        self.last_result_event = torch.cuda.Event()
+        self.last_result_event.record(main)
+        return result_pinned
+
+
 class TPMLP(nn.Module):
     def __init__(self, hidden: int, ffn: int, tp_group=None, bias: bool = True,
                  dtype: torch.dtype = torch.bfloat16, device=None, act: str = "gelu"):
@@ -32,38 +77,10 @@ class TPMLP(nn.Module):
     @torch.no_grad()
     def forward_host(self, x_pinned: torch.Tensor, result_pinned: Optional[torch.Tensor] = None):
         """End-to-end step for a host-resident batch: copy the shard from pinned host memory, run the
-        block, and bring a per-step result (mean |y| and the first output row) back.
-
-        The copies run on a side stream into one of two device buffers, so the upload of this
-        step overlaps the kernels of the previous step that are still in flight; the returned
-        pinned tensor is complete once ``torch.cuda.current_stream().synchronize()`` (or the
-        event in ``self.last_result_event``) has passed."""
-        dev = self.fc1.weight.device
-        st = self.__dict__.setdefault("_host_state", {})
-        if not st or st["shape"] != tuple(x_pinned.shape) or st["dtype"] != x_pinned.dtype:
-            st.update(shape=tuple(x_pinned.shape), dtype=x_pinned.dtype, step=0,
-                      copy_stream=torch.cuda.Stream(device=dev),
-                      bufs=[torch.empty(x_pinned.shape, dtype=x_pinned.dtype, device=dev) for _ in range(2)],
-                      used=[None, None])
-        main = torch.cuda.current_stream(dev)
-        k = st["step"] & 1
-        st["step"] += 1
-        cs = st["copy_stream"]
-        if st["used"][k] is not None:
-            cs.wait_event(st["used"][k])          # the step that last read this buffer is done with it
-        with torch.cuda.stream(cs):
-            st["bufs"][k].copy_(x_pinned, non_blocking=True)
-            up = torch.cuda.Event()
-            up.record(cs)
-        main.wait_event(up)
-        y = self.forward(st["bufs"][k])
-        res = torch.cat([y.float().abs().mean().reshape(1), y[0].float()])
-        done = torch.cuda.Event()
-        done.record(main)
-        st["used"][k] = done
-        if result_pinned is None:
-            return res.cpu()
-        result_pinned.copy_(res, non_blocking=True)
-        self.last_result_event = torch.cuda.Event()
-        self.last_result_event.record(main)
-        return result_pinned
+        block, and bring a per-step result (mean |y| and the first output row) back; see
+        ``HostStep``. The returned pinned tensor is complete once
+        ``torch.cuda.current_stream().synchronize()`` has passed."""
+        hs = self.__dict__.get("_host_step")
+        if hs is None:
+            hs = self.__dict__["_host_step"] = HostStep(self.forward, self.fc1.weight.device)
+        return hs(x_pinned, result_pinned)

@@ -34,9 +34,9 @@ class DenseArgs(ctypes.Structure):
         ("ag_land", _VP * MAX_RANKS), ("ag_flags", _VP * MAX_RANKS),
         ("start_ctr", _VP * MAX_RANKS),
         ("rs_stage", _VP * MAX_RANKS), ("rs_ctr", _VP * MAX_RANKS),
-        ("rs_out", _VP), ("rs_work", _VP), ("local_cnt", _VP),
+        ("rs_out", _VP), ("wave_ctr", _VP), ("local_cnt", _VP),
         ("sa", _VP), ("sb", _VP), ("ag_scale_land", _VP * MAX_RANKS),
-        ("blockscale", ctypes.c_int32), ("reserved3", ctypes.c_int32),
+        ("blockscale", ctypes.c_int32), ("tile_m", ctypes.c_int32),
         ("stream", _VP),
         ("trace", _VP),
     ]
@@ -132,7 +132,7 @@ class KernelTimeline:
 def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
               scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None, *,
               tile_n: int = 0, group_m: int = 0, num_sms: int = 0, act: Optional[str] = None,
-              cta_group: int = 0, m: Optional[int] = None,
+              cta_group: int = 0, m: Optional[int] = None, tile_m: int = 0,
               status: Optional[torch.Tensor] = None, keep: Optional[list] = None) -> DenseArgs:
     """Fill the operand part of a DenseArgs for A[rows,K], B[N,K]. ``m`` is the number of output
     rows this GPU computes; when no tile knobs are given they come from the tuning table."""
@@ -171,7 +171,10 @@ def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], ou
         tile_n, cta_group = knobs["tile_n"], knobs["cta_group"]
         if group_m == 0:
             group_m = knobs["group_m"]
+        if tile_m == 0:
+            tile_m = knobs.get("tile_m", 0)
     args.group_m, args.num_sms, args.tile_n = group_m, num_sms, tile_n
+    args.tile_m = tile_m
     args.act = ACT[act]
     args.cta_group = cta_group
     args.status = status.data_ptr() if status is not None else None
@@ -182,12 +185,13 @@ def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], ou
 def plain_gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor,
                bias: Optional[torch.Tensor] = None, scale_a: Optional[torch.Tensor] = None,
                scale_b: Optional[torch.Tensor] = None, *, tile_n: int = 0, group_m: int = 0,
-               num_sms: int = 0, act: Optional[str] = None, cta_group: int = 0,
+               num_sms: int = 0, act: Optional[str] = None, cta_group: int = 0, tile_m: int = 0,
                status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[M,N] = a[M,K] @ b[N,K]^T (* scales) (+bias) on the tcgen05 kernel."""
     keep: list = []
     args = base_args(a, b, bias, out.dtype, scale_a, scale_b, tile_n=tile_n, group_m=group_m,
-                     num_sms=num_sms, act=act, cta_group=cta_group, m=a.shape[0], status=status, keep=keep)
+                     num_sms=num_sms, act=act, cta_group=cta_group, m=a.shape[0], tile_m=tile_m,
+                     status=status, keep=keep)
     if out.stride(1) != 1 or out.shape != (a.shape[0], b.shape[0]):
         raise ValueError("output must be [M, N] with contiguous rows")
     args.d, args.ldd = out.data_ptr(), out.stride(0)

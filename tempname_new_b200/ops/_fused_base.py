@@ -14,7 +14,7 @@ from ..parallel.symm import FluxTimeoutError, SymmBuffer
 
 # byte offsets inside the control block
 OFF_START = 0          # [8] uint32  last call number entered, by source rank
-OFF_WORK = 64          # [1] uint32  work-claim counter of the reduce tail
+OFF_WORK = 64          # [1] uint32  this op's wave counter (tile starts kept in step, zero between calls)
 OFF_CTR = 128          # arrival flags written by peers, op specific (up to 32 KiB)
 OFF_LOCAL = 32 * 1024  # local arrival scratch (never touched by peers)
 CTRL_BYTES = 64 * 1024
@@ -55,6 +55,9 @@ class FusedOpBase:
         self.device = self.ctrl.device
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device) if self.is_cuda else None
         self.check_every_call = os.environ.get("FLUXB_CHECK_STATUS", "0") == "1"
+        # set when a wait of this op gave up: its arrival counters may be left partly counted and
+        # the ranks' call numbers may disagree, so the op refuses to run until reset()
+        self.poisoned: Optional[str] = None
 
     # -- device status ---------------------------------------------------------------
     def check_status(self) -> None:
@@ -64,11 +67,13 @@ class FusedOpBase:
         st = self.status.tolist()
         if st[0] >= 100:
             self.status.zero_()
+            self.poisoned = "a device-side check failed"
             raise FluxDeviceCheckError(
                 f"{type(self).__name__}: device check '{CHECK_NAMES.get(st[0], st[0])}' failed in block {st[1]} "
                 f"(details {st[2] & 0xFFFFFFFF}, {st[3] & 0xFFFFFFFF})")
         if st[0] != 0:
             self.status.zero_()
+            self.poisoned = "a device wait timed out"
             raise FluxTimeoutError(
                 f"{type(self).__name__}: device wait '{SITE_NAMES.get(st[0], st[0])}' timed out in "
                 f"block {st[1]} (saw {st[2] & 0xFFFFFFFF}, expected {st[3] & 0xFFFFFFFF})")
@@ -76,6 +81,43 @@ class FusedOpBase:
     def _after_launch(self) -> None:
         if self.check_every_call:
             self.check_status()
+
+    def _begin_call(self) -> int:
+        """Every forward starts here: refuses a poisoned op, then takes the next call number."""
+        if self.poisoned is not None:
+            raise RuntimeError(
+                f"{type(self).__name__}: {self.poisoned} in an earlier call; its counters and the ranks' call "
+                "numbers may be inconsistent. Call reset() on every rank of the group before using it again.")
+        self.epoch += 1
+        return self.epoch
+
+    # -- recovery ----------------------------------------------------------------------
+    def _local_scratch_regions(self):
+        """(offset, bytes) ranges of the control block that only this rank's kernels write and
+        that must read zero between calls: the work-claim word and the arrival scratch."""
+        return [(OFF_WORK, 64), (OFF_LOCAL, CTRL_BYTES - OFF_LOCAL)]
+
+    def reset(self) -> None:
+        """Collective over the op's group: bring the op back to a usable state after a
+        ``FluxTimeoutError`` / ``FluxDeviceCheckError`` (or any failed call). Waits for this
+        rank's outstanding work, zeroes the local arrival counters that an aborted kernel may
+        have left partly counted (and the launcher's wave counters), agrees on a call number
+        above every rank's, and clears the status word. Flags written by peers need no clearing:
+        they carry call numbers, and the agreed number is larger than any of them."""
+        if self.is_cuda:
+            torch.cuda.synchronize(self.device)
+        for off, nbytes in self._local_scratch_regions():
+            self.ctrl.local[off:off + nbytes].zero_()
+        if self.is_cuda:
+            from .. import _native
+            _native.check(_native.lib().fluxb_reset_wave_counters(), "fluxb_reset_wave_counters")
+            self.status.zero_()
+            torch.cuda.synchronize(self.device)
+        t = torch.tensor([self.epoch], dtype=torch.int64, device=self.device if self.is_cuda else "cpu")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.pg)
+        self.epoch = int(t.item()) + 1     # the next call uses a number no rank has used
+        self.poisoned = None
+        dist.barrier(group=self.pg)
 
     # -- CPU emulation of the flag protocol -------------------------------------------
     def _cpu_words(self, r: int, off: int, n: int) -> torch.Tensor:
@@ -86,6 +128,7 @@ class FusedOpBase:
         while int(words.min()) < expected:
             if time.monotonic() > deadline:
                 late = [i for i in range(words.numel()) if int(words[i]) < expected]
+                self.poisoned = f"the wait for {what} timed out"
                 raise FluxTimeoutError(f"{type(self).__name__}: {what} timed out waiting for {late}")
             time.sleep(0.0002)
 

@@ -51,7 +51,7 @@ class AGKernel(FusedOpBase):
         M, N = seg * self.world, w.shape[0]
         if M > self.full_m or K != self.k_dim:
             raise ValueError(f"AGKernel was built for M <= {self.full_m}, K = {self.k_dim}; got M={M}, K={K}")
-        self.epoch += 1
+        self._begin_call()
         if not input.is_cuda:
             if input_scale is not None and input_scale.dim() == 3:
                 raise NotImplementedError("block-scaled AG+GEMM has no CPU path")

@@ -43,7 +43,7 @@ class _RowExchange(FusedOpBase):
 
     def _launch(self, x: torch.Tensor, in_splits: Optional[torch.Tensor], broadcast: bool,
                 out_splits: Optional[torch.Tensor], out_offsets: Optional[torch.Tensor], num_ctas: int = 0):
-        self.epoch += 1
+        self._begin_call()
         a = A2ARowsArgs()
         a.in_ = x.data_ptr()
         a.in_splits = in_splits.data_ptr() if in_splits is not None else None

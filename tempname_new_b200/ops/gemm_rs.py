@@ -62,7 +62,7 @@ class GemmRS(FusedOpBase):
             raise ValueError(f"GemmRS was built for M <= {self.max_m}, N = {self.n_dim}; got M={M}, N={N}")
         if M % self.world != 0:
             raise ValueError("M must be a multiple of the world size")
-        self.epoch += 1
+        self._begin_call()
         if not input.is_cuda:
             return self._forward_cpu(input, w, bias, input_scale, weight_scale)
         a = input if input.stride(-1) == 1 else input.contiguous()
@@ -87,7 +87,7 @@ class GemmRS(FusedOpBase):
                 args.rs_stage[r] = self.stage.ptr(r)
                 args.rs_ctr[r] = self.ctrl.ptr(r, OFF_CTR)
                 args.start_ctr[r] = self.ctrl.ptr(r, OFF_START)
-            args.rs_work = self.ctrl.ptr(self.rank, OFF_WORK)
+            args.wave_ctr = self.ctrl.ptr(self.rank, OFF_WORK)
             args.local_cnt = self.ctrl.ptr(self.rank, OFF_LOCAL)
         _dense.run(args)
         self._after_launch()

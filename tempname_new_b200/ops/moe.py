@@ -219,7 +219,7 @@ class GemmGroupedV3AGScatter(FusedOpBase):
                 self._sorted = torch.empty((max(rows_cap, 128), H), dtype=x.dtype, device=dev)
             a.a_sorted, a.a_sorted_rows = self._sorted.data_ptr(), self._sorted.shape[0]
             a.local_cnt = self.ctrl.ptr(self.rank, OFF_LOCAL)
-            self.epoch += 1
+            self._begin_call()
             a.epoch = self.epoch
             if self.world > 1:
                 a.a_tokens = self.land.ptr(self.rank)
@@ -354,7 +354,7 @@ class GemmGroupedV3GatherRS(FusedOpBase):
         return out
 
     def _combine(self, y: torch.Tensor, ridx: torch.Tensor, tpr: int, out: torch.Tensor) -> None:
-        self.epoch += 1
+        self._begin_call()
         c = MoeCombineArgs()
         c.y, c.routing_idx = y.data_ptr(), ridx.data_ptr()
         c.hdr = _hdr_ptr(self._scratch, self.E, self.world)

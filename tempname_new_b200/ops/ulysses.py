@@ -194,7 +194,7 @@ class GemmAllToAllTranspose(FusedOpBase):
             return self._forward_varlen(input, weight, _seq_lens_list(seq_lens_cpu, self.world), bias, outputs)
         w = as_nk(weight, self.transpose_weight)
         x2 = input.reshape(self.bs * self.local_seq, self.hidden)
-        self.epoch += 1
+        self._begin_call()
         if not input.is_cuda:
             res = self._forward_cpu(x2, w, bias)
         else:
@@ -326,7 +326,7 @@ class AllToAllTransposeGemm(FusedOpBase):
         w = as_nk(weight, transpose_weight)
         N = w.shape[0]
         M = self.bs * self.local_seq
-        self.epoch += 1
+        self._begin_call()
         if not input.is_cuda:
             gi = post_attn_a2a_torch(input, self.pg, self.a2a_only)
             y = gi.reshape(M, self.hidden).float() @ w.float().t()

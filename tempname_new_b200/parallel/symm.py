@@ -38,6 +38,19 @@ class FluxTimeoutError(RuntimeError):
     """A bounded wait (device flag, CPU flag or barrier) ran out of time."""
 
 
+class _SymmHandle:
+    """Owns one rank's symmetric block and its peer mappings; frees them when the last holder
+    (the ``SymmBuffer`` or any tensor viewing its memory) is gone. Views keep this object alive,
+    not the ``SymmBuffer`` itself, so a dropped buffer is collected by reference counting."""
+
+    def __init__(self, is_cuda: bool, own_ptr: int, opened: Sequence[int]):
+        self._fin = weakref.finalize(self, SymmBuffer._finalize, is_cuda, own_ptr, list(opened))
+
+    @property
+    def alive(self) -> bool:
+        return self._fin.alive
+
+
 class _CudaRaw:
     """``__cuda_array_interface__`` carrier for a raw device pointer."""
 
@@ -76,13 +89,14 @@ class SymmBuffer:
         self._opened: List[int] = []
         self._own_ptr = 0
         self._closed = False
+        self._handle: Optional[_SymmHandle] = None
         if self.is_cuda:
             self.device = device or torch.device("cuda", torch.cuda.current_device())
             self._alloc_cuda()
         else:
             self.device = torch.device("cpu")
             self._alloc_shm()
-        weakref.finalize(self, SymmBuffer._finalize, self.is_cuda, self._own_ptr, list(self._opened))
+            self._handle = _SymmHandle(False, 0, [])
 
     # ------------------------------------------------------------------ CUDA IPC
     def _alloc_cuda(self) -> None:
@@ -108,8 +122,9 @@ class SymmBuffer:
                 _native.check(lib.fluxb_symm_open(buf, ctypes.byref(p)), f"opening rank {r}'s block")
                 self.ptrs[r] = int(p.value)
                 self._opened.append(int(p.value))
+        self._handle = _SymmHandle(True, self._own_ptr, self._opened)
         self._views[self.rank] = torch.as_tensor(
-            _CudaRaw(self._own_ptr, self.nbytes, self), device=self.device)
+            _CudaRaw(self._own_ptr, self.nbytes, self._handle), device=self.device)
 
     # ------------------------------------------------------------------ /dev/shm
     def _alloc_shm(self) -> None:
@@ -150,7 +165,7 @@ class SymmBuffer:
 
     def flat(self, r: int) -> torch.Tensor:
         if r not in self._views:
-            self._views[r] = torch.as_tensor(_CudaRaw(self.ptrs[r], self.nbytes, self), device=self.device)
+            self._views[r] = torch.as_tensor(_CudaRaw(self.ptrs[r], self.nbytes, self._handle), device=self.device)
         return self._views[r]
 
     def view(self, r: int, dtype: torch.dtype, shape: Sequence[int], offset_bytes: int = 0) -> torch.Tensor:

@@ -59,7 +59,7 @@ def cmd_gemm(a):
         fn = lambda: torch.matmul(x, w.t(), out=out)  # noqa: E731
     else:
         fn = lambda: _dense.plain_gemm(x, w, out, tile_n=a.tile_n, group_m=a.group_m,  # noqa: E731
-                                       cta_group=a.cta_group)
+                                       cta_group=a.cta_group, tile_m=a.tile_m)
     ms = timed(fn, a.iters, a.warmup, not a.no_flush)
     tf = 2.0 * a.m * a.n * a.k / ms / 1e9
     pk, _, src = peaks()
@@ -214,6 +214,7 @@ def main(argv=None):
     g.add_argument("--impl", default="fluxb", choices=["fluxb", "torch"])
     g.add_argument("--cta-group", type=int, default=0)
     g.add_argument("--tile-n", type=int, default=0)
+    g.add_argument("--tile-m", type=int, default=0)
     g.add_argument("--group-m", type=int, default=0)
     g.set_defaults(fn=cmd_gemm)
     q = sub.add_parser("quant")

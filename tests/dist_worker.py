@@ -433,6 +433,18 @@ def check_failure():
         x = torch.randn(512, 512, device=dev).bfloat16()
         g = flux.GemmOnly(torch.bfloat16).forward(x, x)
         close(g, x.float() @ x.float().t(), "GemmOnly after the timeout")
+        # ... and the op itself refuses to run on half-counted state
+        try:
+            op.forward(a, w)
+            raise AssertionError("a poisoned op accepted a call")
+        except RuntimeError as e:
+            assert "reset" in str(e), str(e)
+    torch.cuda.synchronize()
+    # every rank (the one that sat out too) resets the op; then it is right again, twice
+    op.reset()
+    for _ in range(2):
+        close(op.forward(a, w), ref32, "GemmRS after reset")
+    op.check_status()
     torch.cuda.synchronize()
     print(f"[rank {rank}] failure ok", flush=True)
 

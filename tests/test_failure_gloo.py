@@ -49,12 +49,45 @@ def _ag_late_rank_recovers(rank, world):
         assert float(out[32 * r, 0]) == 16.0 * (r + 1)
 
 
+def _gemm_rs_recovers_after_reset(rank, world):
+    """One rank sleeps past the limit: the others time out, the op refuses further calls, every rank
+    calls reset(), and the next forward is right again (call numbers re-agreed, counters zeroed)."""
+    import tempname_new_b200 as flux
+    torch.manual_seed(3 + rank)
+    op = flux.GemmRS(dist.group.WORLD, 1, 64, 32, torch.float32, timeout_s=1.0)
+    a, w = torch.randn(64, 16), torch.randn(32, 16)
+
+    def reference():
+        part = a @ w.t()
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part)
+        seg = 64 // world
+        return sum(parts)[rank * seg:(rank + 1) * seg]
+
+    assert torch.allclose(op.forward(a, w), reference(), atol=1e-4)
+    if rank == 0:
+        time.sleep(2.0)                   # misses the call the others are making now
+    else:
+        with pytest.raises(flux.FluxTimeoutError):
+            op.forward(a, w)
+        with pytest.raises(RuntimeError, match="reset"):
+            op.forward(a, w)              # poisoned until reset
+    op.reset()                            # collective: rank 0 joins late, the others wait in it
+    assert op.poisoned is None
+    for _ in range(2):
+        assert torch.allclose(op.forward(a, w), reference(), atol=1e-4)
+
+
 def test_barrier_times_out_when_a_rank_never_arrives():
     run_gloo(_barrier_missing_rank, 3)
 
 
 def test_gemm_rs_times_out_when_a_rank_leaves_between_steps():
     run_gloo(_gemm_rs_missing_rank, 2)
+
+
+def test_op_recovers_after_reset():
+    run_gloo(_gemm_rs_recovers_after_reset, 2)
 
 
 def test_late_rank_within_limit_is_fine():
