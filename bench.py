@@ -330,8 +330,8 @@ def main():
             "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world,
             "steps": K, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong",
-            # BASELINE.md publishes no B200 number; the operative baseline it names is torch.matmul +
-            # NCCL on the same box, timed here in the same process around the headline steps
+            # the reference publishes no B200 number; the baseline is torch.matmul + NCCL on the same
+            # box, timed here in the same process around the headline steps
             "vs_baseline": value / base_value,
             "baseline": {"impl": "torch.matmul (cuBLAS) + NCCL all_gather_into_tensor / reduce_scatter_tensor",
                          "value": base_value, "ms_per_step": ms_base, "ratio": value / base_value,

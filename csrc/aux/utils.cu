@@ -283,7 +283,9 @@ extern "C" int fluxb_uniform_fill(void* out, int64_t n, int dtype, uint64_t seed
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   switch (dtype) {
     case FLUXB_FP32: uniform_fill_kernel<float><<<sms * 8, 256, 0, s>>>(static_cast<float*>(out), n, seed, lo, hi); break;
-    case FLUXB_BF16: uniform_fill_kernel<__nv_bfloat16><<<sms * 8, 256, 0, s>>>(static_cast<__nv_bfloat16*>(out), n, seed, lo, hi); break;
+    case FLUXB_BF16:
+      uniform_fill_kernel<__nv_bfloat16><<<sms * 8, 256, 0, s>>>(static_cast<__nv_bfloat16*>(out), n, seed, lo, hi);
+      break;
     case FLUXB_FP16: uniform_fill_kernel<__half><<<sms * 8, 256, 0, s>>>(static_cast<__half*>(out), n, seed, lo, hi); break;
     default: return fail(kErrUnsupported, "uniform fill supports fp32, bf16, fp16");
   }

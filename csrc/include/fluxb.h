@@ -169,6 +169,19 @@ typedef struct {
   uint32_t* local_cnt;       /* local scratch, 1152 uint32, zero at first use: push-step counters, then
                                 one arrival counter and one flag per (expert, source) sub-problem */
   void* stream;
+  /* Layer 1 with the top-k combine and the reduce-scatter fused in (scatter != 0, gathered == 0,
+   * every expert whole on one rank): the epilogue stores row r, times its scales, into slot
+   * [token][k] of sc_stage[owner of the token] ([tokens_per_rank][topk][N] on every rank), and the
+   * tail of the kernel adds the topk slots of each local token into sc_out [tokens_per_rank, N].
+   * routing_idx [world * tokens_per_rank * topk] = sorted row of every (token, k); row_entry: int32
+   * scratch of at least (rows of this rank) words; sc_flags[r]: world uint32 on rank r, zero at first
+   * use; start_ctr and local_cnt (1 word) as above. d is not written. */
+  int32_t scatter, reserved2;
+  const int32_t* routing_idx;
+  int32_t* row_entry;
+  void* sc_stage[FLUXB_MAX_RANKS];
+  uint32_t* sc_flags[FLUXB_MAX_RANKS];
+  void* sc_out;
 } fluxb_moe_gemm_args_t;
 
 int64_t fluxb_moe_schedule_scratch_bytes(int E, int world);
@@ -224,6 +237,35 @@ typedef struct {
 } fluxb_a2a_rows_args_t;
 
 int fluxb_a2a_rows(const fluxb_a2a_rows_args_t* args);
+
+/* ---- expert-parallel dispatch (csrc/ops/ep_dispatch.cu) ----
+ * Row (token, k) of this rank's tokens x [tokens_local, row_bytes] goes to every rank of the expert
+ * group that owns sorted row r = scatter_index[(token0 + token) * topk + k], at row r - (first row of
+ * that group) of its receive buffer out[rank] ([capacity_rows][row_bytes], symmetric memory). Expert
+ * group g = ranks [g * tp, (g + 1) * tp) owns experts [g * E_local, (g + 1) * E_local). The kernel
+ * returns when the rows of every source have landed here. flags[r]: world uint32 on rank r;
+ * local_cnt: 1 uint32; both zero at first use. out_rows (optional, local) receives the number of
+ * rows this rank got. A row beyond capacity_rows is dropped and reported through `status` (code 13). */
+typedef struct {
+  const void* x;
+  const int32_t* scatter_index;
+  const int32_t* splits;
+  int64_t token0;
+  int32_t tokens_local, topk, E, E_local, tp, num_ctas;
+  int64_t row_bytes, capacity_rows;
+  int32_t rank, world;
+  uint32_t epoch, reserved;
+  uint64_t timeout_ns;
+  fluxb_status_t* status;
+  void* out[FLUXB_MAX_RANKS];
+  uint32_t* flags[FLUXB_MAX_RANKS];
+  uint32_t* start_ctr[FLUXB_MAX_RANKS];
+  uint32_t* local_cnt;
+  int32_t* out_rows;
+  void* stream;
+} fluxb_ep_dispatch_args_t;
+
+int fluxb_ep_dispatch(const fluxb_ep_dispatch_args_t* args);
 /* *flag = value with system-scope release, stream ordered (flag may be peer memory) */
 int fluxb_set_flag(uint32_t* flag, uint32_t value, void* stream);
 

@@ -50,9 +50,12 @@ __global__ void moe_gather_index_kernel(const int32_t* scatter_index, const int3
 }
 
 // ---- schedule: sub-problems (expert, source) in the order this rank should run them ---------
+// With routing_idx the launch has more than one block and all of them also fill row_entry: the
+// index token * topk + k of every sorted row that lives on this rank.
 __global__ void moe_schedule_kernel(const int32_t* splits, const int32_t* cnt /* [E][W] or null */,
                                     int E, int e0, int E_local, int rank, int W, int n_tiles, int BM,
-                                    SubProblem* sp, int32_t* tile_begin, int32_t* hdr) {
+                                    SubProblem* sp, int32_t* tile_begin, int32_t* hdr,
+                                    const int32_t* routing_idx, int64_t n_entries, int32_t* row_entry) {
   __shared__ int32_t offs[kMaxE + 1];
   if (threadIdx.x == 0) {
     int run = 0;
@@ -61,6 +64,17 @@ __global__ void moe_schedule_kernel(const int32_t* splits, const int32_t* cnt /*
       run += splits[e];
     }
     offs[E] = run;
+  }
+  __syncthreads();
+  if (routing_idx != nullptr) {
+    const int base = offs[e0], rows = offs[e0 + E_local] - offs[e0];
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_entries; i += stride) {
+      const int r = routing_idx[i] - base;
+      if (r >= 0 && r < rows) row_entry[r] = static_cast<int32_t>(i);
+    }
+  }
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
     hdr[0] = offs[e0];
     hdr[1] = offs[e0 + E_local] - offs[e0];
     int tiles = 0, s = 0;
@@ -255,7 +269,7 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
   FLUXB_REQUIRE(a->N > 0 && a->K > 0 && a->N % 8 == 0, "N, K");
   FLUXB_REQUIRE(a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP16, "grouped GEMM runs on bf16 / fp16");
   FLUXB_REQUIRE(a->world >= 1 && a->world <= FLUXB_MAX_RANKS && a->rank >= 0 && a->rank < a->world, "ranks");
-  FLUXB_REQUIRE(a->splits && a->scratch && a->weights && a->d, "pointers");
+  FLUXB_REQUIRE(a->splits && a->scratch && a->weights && (a->d || a->scatter), "pointers");
   const int elt = 2;
   FLUXB_REQUIRE((a->K * elt) % 16 == 0, "K row bytes must be a multiple of 16");
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
@@ -278,8 +292,18 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
                                                      a->tokens_per_rank, a->world, a->gather_index, cnt);
     g_launches.fetch_add(1, std::memory_order_relaxed);
   }
-  moe_schedule_kernel<<<1, 32, 0, stream>>>(a->splits, by_src ? cnt : nullptr, a->E, a->e0, a->E_local, a->rank,
-                                            a->world, n_tiles, 128, sp, tile_begin, hdr);
+  if (a->scatter) {
+    FLUXB_REQUIRE(!a->gathered, "the fused combine takes contiguous rows");
+    FLUXB_REQUIRE(a->routing_idx && a->row_entry && a->n_entries > 0 && a->topk >= 1 && a->tokens_per_rank > 0 &&
+                      a->sc_out && a->local_cnt,
+                  "fused combine: routing index / scratch / output missing");
+    moe_schedule_kernel<<<148, 256, 0, stream>>>(a->splits, nullptr, a->E, a->e0, a->E_local, a->rank, a->world,
+                                                 n_tiles, 128, sp, tile_begin, hdr, a->routing_idx, a->n_entries,
+                                                 a->row_entry);
+  } else {
+    moe_schedule_kernel<<<1, 32, 0, stream>>>(a->splits, by_src ? cnt : nullptr, a->E, a->e0, a->E_local, a->rank,
+                                              a->world, n_tiles, 128, sp, tile_begin, hdr, nullptr, 0, nullptr);
+  }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   FLUXB_CUDA_OK(cudaGetLastError());
 
@@ -364,6 +388,18 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
       }
     }
   } else {
+    if (a->scatter) {
+      p.topk = a->topk;
+      p.row_entry = a->row_entry;
+      p.sc_out = reinterpret_cast<uint16_t*>(a->sc_out);
+      p.local_cnt = a->local_cnt;
+      for (int r = 0; r < a->world; ++r) {
+        FLUXB_REQUIRE(a->sc_stage[r] && a->sc_flags[r] && a->start_ctr[r], "fused combine: peer pointers missing");
+        p.sc_stage[r] = reinterpret_cast<uint16_t*>(a->sc_stage[r]);
+        p.sc_flags[r] = a->sc_flags[r];
+        p.start_ctr[r] = a->start_ctr[r];
+      }
+    }
     FLUXB_REQUIRE(a->a != nullptr && a->a_rows > 0, "contiguous A missing");
     uint64_t dims[2] = {static_cast<uint64_t>(a->K), static_cast<uint64_t>(a->a_rows)};
     uint64_t str[1] = {static_cast<uint64_t>(a->K) * elt};
@@ -393,6 +429,11 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
   if (a->gathered) {
     if (bn == 256) return launch_grouped<GroupedCfg<256, 0, 4, 1>>(p, sms, stream);
     return launch_grouped<GroupedCfg<128, 0, 5, 1>>(p, sms, stream);
+  }
+  if (a->scatter) {
+    // every CTA takes part in the arrival counting and in the tail: full grid
+    if (bn == 256) return launch_grouped<GroupedCfg<256, 0, 4, 0, true>>(p, sms, stream);
+    return launch_grouped<GroupedCfg<128, 0, 6, 0, true>>(p, sms, stream);
   }
   if (bn == 256) return launch_grouped<GroupedCfg<256, 0, 4, 0>>(p, sms, stream);
   return launch_grouped<GroupedCfg<128, 0, 6, 0>>(p, sms, stream);

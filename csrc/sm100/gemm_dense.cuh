@@ -348,9 +348,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       uint32_t a2a_seen[kMaxRanks] = {};  // post-attention: row units seen, per source
       stamp(kTraceEntry);
       for (int t = tile_slot; t < total_tiles; t += tile_stride, ++wave) {
+        if (*abort_word) break;   // a wait gave up: issue nothing more
         const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
         if (!dcheck(wc, c.seg >= 0 && c.seg < p.num_seg && c.m_in_seg >= 0 && c.m_in_seg < p.seg_rows &&
-                            c.n0 >= 0 && c.n0 < p.N,
+                            c.n0 >= 0 && c.n0 < n_tiles * BN,   // (a piece of a split edge tile may lie past N)
                     kCheckTileDecode, static_cast<uint32_t>(t), static_cast<uint32_t>(c.seg)))
           break;
         if (p.wave_ctr != nullptr && leader && wave > 0) {
@@ -470,6 +471,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       uint32_t phase = 0;
       int it = 0;
       for (int t = tile_slot; t < total_tiles; t += tile_stride, ++it) {
+        if (*abort_word) break;
         // a column piece of a split tile is a narrower instruction on the same operands
         const int shift = t >= p.split_from ? p.split_shift : 0;
         const uint32_t idesc = shift == 0 ? idesc_full
@@ -1080,6 +1082,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     uint32_t own_seen = 0;   // tile rows of the own segment whose W-1 slabs were seen to have landed
     uint64_t bs_acc[Cfg::BS ? 64 : 1];
     for (int t = tile_slot; t < total_tiles; t += tile_stride, ++it) {
+      if (*abort_word) break;
       const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
       const int m_cta = c.m_in_seg + static_cast<int>(cta_rank) * Cfg::BM_CTA;
       const CUtensorMap* tmd = &p.tm_d[0];
@@ -1098,6 +1101,17 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           // goes to rs_out (tm_d[rank] covers it as one slab)
           own_rs = true;
           z = 0;
+          // The arrival of this warp's last tile for a peer is still pending (it is counted one
+          // tile late). It must be counted before this warp waits for the peers, whose own tiles
+          // wait for exactly such arrivals from this rank: otherwise the ranks wait for each other.
+          if (pend_seg >= 0) {
+            if (lane == 0) {
+              ptx::bulk_wait<0>();
+              rs_arrive(pend_seg, pend_mt, pend_chunks);
+            }
+            pend_seg = -1;
+            __syncwarp();
+          }
           if (c.m_tile >= 32 || ((own_seen >> c.m_tile) & 1u) == 0u) {
             if (own_seen == 0 && ew == 0 && lane == 0) stamp(kTraceSlice0);
             if (lane < p.world && lane != p.rank)
@@ -1329,6 +1343,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
 
   // -------------------------------------------------------------------- teardown of the GEMM
   __syncwarp();
+  if (*abort_word) {
+    // A wait gave up and the roles left their loops early: give the copies and MMAs that are
+    // still in flight time to land before this CTA's shared memory and TMEM go away.
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(2000);
+  }
   ptx::tc_fence_before();
   // CG == 2: nobody leaves (or frees TMEM) while the partner may still read this CTA's shared
   // memory or signal its barriers

@@ -9,8 +9,14 @@
 // In MoE layer 0 the kernel also performs the all-gather: warps 2-3 push this rank's token shard
 // into every peer's landing buffer (bulk-copy ring) and sub-problems of source rank s start
 // once s's shard has landed, own shard first.
+// In MoE layer 1 (SCATTER_) the epilogue multiplies every row by its gate weight and stores it
+// straight into the slot [token][k] of the staging buffer of the rank that owns the token, over
+// NVLink; when the rows of all W ranks have landed, the tail of the same kernel adds the top-k
+// rows of each of this rank's tokens in fp32 (k = 0, 1, ...) and writes the result. The
+// expert-sorted product never exists in memory.
 // Reference: src/moe_ag_scatter (GemmGroupedV3AGScatter, sort_util.cu, gather_tensor.hpp,
-// sm90_ag_scatter_fetcher.hpp) and src/moe_gather_rs (grouped GEMM part).
+// sm90_ag_scatter_fetcher.hpp) and src/moe_gather_rs (compute CTAs + DMA CTAs of
+// sm90_gemm_array_threadblock_specialized.hpp, topk_gather_rs.cu).
 #pragma once
 
 #include "gemm_dense.cuh"
@@ -55,14 +61,22 @@ struct GroupedParams {
   uint32_t* local_cnt;             // [W]
   uint32_t* wave_ctr;              // optional: tiles whose loads are all issued (wave-synchronous starts)
   int32_t ring_inflight;           // loads in flight ahead of the stores in the push / gather rings (0 = all slots but one)
+  // ---- layer 1 with the combine fused in (SCATTER_)
+  int32_t topk;
+  const int32_t* row_entry;        // [rows of this rank] token * topk + k of every local sorted row
+  uint16_t* sc_stage[kMaxRanks];   // on every rank: [tokens_per_rank][topk][N], 16-bit
+  uint32_t* sc_flags[kMaxRanks];   // on every rank: [W src] last call whose rows have all landed
+  uint16_t* sc_out;                // [tokens_per_rank, N]
 };
 
 // GATHER_: 0 = contiguous A by TMA; 1 = gathered A rows by cp.async from four producer warps;
 // 2 = gathered A rows by TMA tile::gather4 (four indexed rows per instruction) from the producer lane;
 // 3 = the communication warps copy the gathered rows, whole rows at a time, into an expert-sorted
 //     buffer as soon as their source shard has landed, and the GEMM reads that buffer by TMA.
-template <int BN_, int KIND_, int STAGES_, int GATHER_>
+template <int BN_, int KIND_, int STAGES_, int GATHER_, bool SCATTER_ = false>
 struct GroupedCfg {
+  static constexpr bool SCATTER = SCATTER_;        // layer 1: rows go to the token owner's [token][k] slot
+  static_assert(!SCATTER_ || GATHER_ == 0, "the scatter epilogue reads contiguous A");
   static constexpr int BM = 128, BN = BN_, KIND = KIND_, STAGES = STAGES_;
   static constexpr bool GATHER = GATHER_ == 1;     // cp.async producers
   static constexpr bool GATHER4 = GATHER_ == 2;    // TMA gather4
@@ -165,6 +179,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
     uint32_t phase = 0;
     int32_t* idx_buf = reinterpret_cast<int32_t*>(bar_ptr + 256);
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++nt) {
+      if (*abort_word) break;   // a wait gave up: issue nothing more
       const GroupedTile g = grouped_decode(p, t, cursor, n_tiles, BM, BN);
       int32_t* idx = idx_buf + (nt & 1) * 128;
       if constexpr (Cfg::GATHER4) {
@@ -237,6 +252,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
       int stage = 0, it = 0;
       uint32_t phase = 0;
       for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+        if (*abort_word) break;   // a wait gave up: issue nothing more
         const int acc = it & 1;
         mbar_wait(wc, tempty_bar(acc), (((it >> 1) & 1) ^ 1u), kSiteTmemEmpty);
         ptx::tc_fence_after();
@@ -262,6 +278,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
       }
     }
   } else if (warp == 2 || warp == 3) {
+    if constexpr (Cfg::SCATTER) {
+      // "this rank has entered call `epoch`": its staging slots of the previous call are consumed
+      if (warp == 3 && blockIdx.x == 0 && lane < p.world) ptx::st_release_sys(p.start_ctr[lane] + p.rank, p.epoch);
+    }
     // ------------------------------------------------------------------ all-gather push of the token shard
     if constexpr (Cfg::ANY_GATHER) {
       if (multi && warp == 3 && blockIdx.x == 0 && lane < p.world)
@@ -419,7 +439,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
     const float sscale = p.scalar_scale ? *p.scalar_scale : 1.f;
     int it = 0, cursor = 0;
     uint16_t* dbase = reinterpret_cast<uint16_t*>(p.d);
+    if constexpr (Cfg::SCATTER) {
+      // nobody writes into an owner's slots before that owner has entered this call
+      if (lane < p.world) flag_wait_ge(wc, p.start_ctr[p.rank] + lane, p.epoch, kSiteStartBarrier);
+      __syncwarp();
+    }
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+      if (*abort_word) break;   // a wait gave up: issue nothing more
       const GroupedTile g = grouped_decode(p, t, cursor, n_tiles, BM, BN);
       const int acc = it & 1;
       const uint32_t par = (it >> 1) & 1;
@@ -433,6 +459,16 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
       float scale = sscale;
       if (p.expert_scale) scale *= p.expert_scale[g.expert];
       if (p.row_scale && row_ok) scale *= p.row_scale[orow];
+      uint16_t* drow_base = dbase + orow * p.ldd;
+      if constexpr (Cfg::SCATTER) {
+        if (row_ok) {
+          const int entry = p.row_entry[orow];
+          const int token = entry / p.topk;
+          const int owner = token / p.tokens_per_rank;
+          const int64_t slot = static_cast<int64_t>(token - owner * p.tokens_per_rank) * p.topk + (entry - token * p.topk);
+          drow_base = p.sc_stage[owner] + slot * p.N;
+        }
+      }
 #pragma unroll 1
       for (int ch = 0; ch < BN / 64; ++ch) {
         uint32_t r0[32], r1[32];
@@ -447,7 +483,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
         }
         const int col0 = g.n0 + ch * 64;
         if (row_ok && col0 < p.N) {
-          uint16_t* drow = dbase + orow * p.ldd + col0;
+          uint16_t* drow = drow_base + col0;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             if (col0 + 8 * j < p.N) {
@@ -470,6 +506,17 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
         }
       }
     }
+    if constexpr (Cfg::SCATTER) {
+      // every row this warp had is written; the last warp of the grid tells every owner
+      ptx::fence_acq_rel_sys();
+      __syncwarp();
+      if (lane == 0) {
+        if (ptx::atom_add_acq_rel_sys(p.local_cnt, 1u) == gridDim.x * 4u - 1u) {
+          *p.local_cnt = 0;
+          for (int d = 0; d < p.world; ++d) ptx::st_release_sys(p.sc_flags[d] + p.rank, p.epoch);
+        }
+      }
+    }
   } else {
     // ------------------------------------------------------------------ gathered-A producers (warps 8..11)
     if constexpr (Cfg::GATHER) {
@@ -479,6 +526,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
       int stage = 0, cursor = 0, ready_src = -1;
       uint32_t phase = 0;
       for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        if (*abort_word) break;   // a wait gave up: issue nothing more
         const GroupedTile g = grouped_decode(p, t, cursor, n_tiles, BM, BN);
         if (g.src >= 0 && g.src != ready_src) {
           // tokens of this source must have landed (sub-problems are ordered by source, own first)
@@ -512,11 +560,59 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
   }
 
   __syncwarp();
+  if (*abort_word) {
+    // a wait gave up and the roles left their loops early: let copies and MMAs in flight land
+    // before this CTA's shared memory and TMEM go away
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(2000);
+  }
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc<1>(tmem_base, 512);
+  }
+
+  if constexpr (Cfg::SCATTER) {
+    // ---------------------------------------------------------------- top-k sum of this rank's tokens
+    // The slots of a token are topk consecutive rows of the staging buffer: one warp per token, 16
+    // bytes per lane and trip, all k loads of a trip in flight before the first add.
+    if (static_cast<int>(threadIdx.x) < p.world)
+      flag_wait_ge(wc, p.sc_flags[p.rank] + threadIdx.x, p.epoch, kSiteMoeFlag);
+    __syncthreads();
+    const bool f16 = p.out_f16 != 0;
+    const uint16_t* mine = p.sc_stage[p.rank];
+    const int chunks = p.N / 8;
+    const int gwarp = blockIdx.x * (Cfg::THREADS / 32) + warp, nwarps = gridDim.x * (Cfg::THREADS / 32);
+    for (int tl = gwarp; tl < p.tokens_per_rank; tl += nwarps) {
+      const uint16_t* trow = mine + static_cast<int64_t>(tl) * p.topk * p.N;
+      for (int c = lane; c < chunks; c += 32) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int k0 = 0; k0 < p.topk; k0 += 8) {
+          uint4 v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (k0 + j < p.topk) v[j] = ptx::ld_global_cs_v4(trow + static_cast<int64_t>(k0 + j) * p.N + c * 8);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (k0 + j < p.topk) {
+              const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                acc[2 * e] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] & 0xFFFFu), f16);
+                acc[2 * e + 1] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] >> 16), f16);
+              }
+            }
+          }
+        }
+        uint4 o;
+        o.x = ptx::pack_half2(f16, acc[0], acc[1]);
+        o.y = ptx::pack_half2(f16, acc[2], acc[3]);
+        o.z = ptx::pack_half2(f16, acc[4], acc[5]);
+        o.w = ptx::pack_half2(f16, acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(p.sc_out + static_cast<int64_t>(tl) * p.N + c * 8) = o;
+      }
+    }
   }
 }
 

@@ -600,6 +600,7 @@ enum WaitSite : uint32_t {
   kSiteA2AFlag = 10,
   kSiteMoeFlag = 11,
   kSiteTest = 12,
+  kSiteCapacity = 13,   // not a wait: more rows were routed to a rank than its receive buffer holds
 };
 
 struct WaitCtx {

@@ -24,6 +24,7 @@ SITE_NAMES = {
     1: "smem-empty barrier", 2: "smem-full barrier", 3: "tmem-empty barrier", 4: "tmem-full barrier",
     5: "start handshake", 6: "all-gather shard flag", 7: "reduce-scatter tile counter",
     8: "barrier_all", 9: "inplace cast", 10: "all-to-all flag", 11: "MoE flag", 12: "test wait",
+    13: "receive buffer capacity (rows routed to one rank)",
 }
 # self-checks of the debug build (FLUXB_DEBUG=1), csrc/sm100/ptx.cuh::CheckSite
 CHECK_NAMES = {

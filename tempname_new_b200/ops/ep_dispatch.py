@@ -3,7 +3,9 @@
 * ``DisScatterForward``: every rank contributes its local tokens; each rank receives, in
   expert-sorted order, the rows routed to its own experts (reference: ``flux.DisScatterForward``,
   ``src/coll/dis_scatter_forward_impl.cu``; there a hierarchical NVSHMEM put/signal protocol that
-  also spans nodes). Here: one peer-memory all-gather kernel + a row gather by the routing index.
+  also spans nodes). Here one kernel (``csrc/ops/ep_dispatch.cu``) stores every routed row
+  straight into its place in the receiver's buffer over NVLink: a token travels only to the ranks
+  that own one of its experts.
 * ``DisScatterBackward``: the inverse, the weighted combine: the expert outputs of all ranks are
   summed per token over the top-k entries and delivered to the rank that owns the token — the
   ``moe_combine_kernel`` used by ``GemmGroupedV3GatherRS`` (reference:
@@ -15,6 +17,7 @@
 from __future__ import annotations
 
 import ctypes
+import math
 from typing import Optional
 
 import torch
@@ -22,29 +25,68 @@ import torch.distributed as dist
 
 from .. import _native
 from . import _dense
+from ._fused_base import OFF_CTR, OFF_LOCAL, OFF_START, FusedOpBase
 from .coll import All2AllSingle, AllGatherOp
 from .moe import GemmGroupedV3GatherRS, _scratch
+from ..parallel.symm import SymmBuffer, _ELEM
+
+_VP = ctypes.c_void_p
+_R = _dense.MAX_RANKS
 
 
-class DisScatterForward:
+class EpDispatchArgs(ctypes.Structure):
+    _fields_ = [
+        ("x", _VP), ("scatter_index", _VP), ("splits", _VP), ("token0", ctypes.c_int64),
+        ("tokens_local", ctypes.c_int32), ("topk", ctypes.c_int32), ("E", ctypes.c_int32),
+        ("E_local", ctypes.c_int32), ("tp", ctypes.c_int32), ("num_ctas", ctypes.c_int32),
+        ("row_bytes", ctypes.c_int64), ("capacity_rows", ctypes.c_int64),
+        ("rank", ctypes.c_int32), ("world", ctypes.c_int32),
+        ("epoch", ctypes.c_uint32), ("reserved", ctypes.c_uint32),
+        ("timeout_ns", ctypes.c_uint64), ("status", _VP),
+        ("out", _VP * _R), ("flags", _VP * _R), ("start_ctr", _VP * _R),
+        ("local_cnt", _VP), ("out_rows", _VP), ("stream", _VP),
+    ]
+
+
+class DisScatterForward(FusedOpBase):
     def __init__(self, total_num_experts: int, max_m: int, n_dim: int, topk: int, rank: int, tp_world_size: int,
                  ep_world_size: int, local_world_size: int, moe_capacity_ratio: float = 1.3,
-                 duplicate_comm_buffer: int = 1, team: int = 0, pg=None, dtype: torch.dtype = torch.bfloat16):
-        self.pg = pg if pg is not None else dist.group.WORLD
-        self.world = dist.get_world_size(self.pg)
-        self.rank = rank
+                 duplicate_comm_buffer: int = 1, team: int = 0, pg=None, dtype: torch.dtype = torch.bfloat16,
+                 timeout_s: Optional[float] = None):
+        super().__init__(pg, 1, timeout_s)
+        if rank != self.rank:
+            raise ValueError("rank must be this process's rank in the group")
         if tp_world_size * ep_world_size != self.world:
             raise ValueError("tp_world_size * ep_world_size must equal the group size")
         self.E, self.topk, self.H = total_num_experts, topk, n_dim
+        self.tp = tp_world_size
         self.E_local = self.E // ep_world_size
         self.e0 = (rank // tp_world_size) * self.E_local
-        self.ag = AllGatherOp(self.pg, 1, max_m, n_dim, dtype)
+        self.dtype = dtype
+        if self.is_cuda:
+            # rows one rank can receive: its fair share of max_m * topk times the capacity ratio
+            total = max(max_m * topk, 1)
+            self.capacity = min(total, int(math.ceil(total / ep_world_size * moe_capacity_ratio)))
+            self.recv = SymmBuffer(self.capacity * n_dim * _ELEM[dtype], self.pg)
+            self.ag = None
+        else:
+            self.ag = AllGatherOp(self.pg, 1, max_m, n_dim, dtype)
+
+    def _token0(self, tokens_local: int, ep_token_counts) -> int:
+        if ep_token_counts is None:
+            return self.rank * tokens_local
+        counts = ep_token_counts.tolist() if torch.is_tensor(ep_token_counts) else list(ep_token_counts)
+        return int(sum(counts[: self.rank]))
 
     def forward_gpu(self, input: torch.Tensor, ag_exp_indices: torch.Tensor, ag_scatter_idx: torch.Tensor,
                     splits: torch.Tensor, ep_token_counts=None, output_tensor: Optional[torch.Tensor] = None,
                     sm_margin: int = 0, copy_to_local_tensor: bool = True) -> torch.Tensor:
         """input [local tokens, H]; ag_scatter_idx [tokens, topk] = sorted row of every (token, k);
-        splits [E] rows per expert. Returns this rank's rows [sum(splits[e0:e0+E_local]), H]."""
+        splits [E] rows per expert. Returns this rank's rows [sum(splits[e0:e0+E_local]), H]
+        (``copy_to_local_tensor=False``: a view of the receive buffer, valid until the next call)."""
+        if input.is_cuda:
+            return self._forward_cuda(input, ag_scatter_idx, splits, ep_token_counts, output_tensor,
+                                      copy_to_local_tensor)
         tokens_full = self.ag.run(input)
         n = ag_scatter_idx.numel()
         topk = ag_scatter_idx.shape[-1]
@@ -58,13 +100,57 @@ class DisScatterForward:
             return output_tensor
         return out
 
+    def _forward_cuda(self, x, scatter_idx, splits, ep_token_counts, output_tensor, copy_out) -> torch.Tensor:
+        dev = x.device
+        x = x if x.is_contiguous() else x.contiguous()
+        if x.dtype != self.dtype or x.shape[1] != self.H:
+            raise ValueError("input must be [tokens, n_dim] in the dtype the op was built for")
+        sidx = scatter_idx.reshape(-1).to(device=dev, dtype=torch.int32).contiguous()
+        # the row count of this rank comes from the host copy of the splits when there is one
+        sp_host = splits if not splits.is_cuda else None
+        sp = splits.to(device=dev, dtype=torch.int32, non_blocking=True).contiguous()
+        self._begin_call()
+        a = EpDispatchArgs()
+        a.x, a.scatter_index, a.splits = x.data_ptr(), sidx.data_ptr(), sp.data_ptr()
+        a.tokens_local, a.topk, a.E, a.E_local, a.tp = x.shape[0], self.topk, self.E, self.E_local, self.tp
+        a.token0 = self._token0(x.shape[0], ep_token_counts)
+        a.row_bytes = self.H * x.element_size()
+        a.capacity_rows = self.capacity
+        a.rank, a.world, a.epoch = self.rank, self.world, self.epoch
+        a.timeout_ns, a.status = int(self.timeout_s * 1e9), self.status.data_ptr()
+        for r in range(self.world):
+            a.out[r] = self.recv.ptr(r)
+            a.flags[r] = self.ctrl.ptr(r, OFF_CTR)
+            a.start_ctr[r] = self.ctrl.ptr(r, OFF_START)
+        a.local_cnt = self.ctrl.ptr(self.rank, OFF_LOCAL)
+        a.stream = _dense.current_stream_ptr(dev)
+        _native.check(_native.lib().fluxb_ep_dispatch(ctypes.byref(a)), "fluxb_ep_dispatch")
+        self._after_launch()
+        if sp_host is None:
+            sp_host = splits.cpu()
+        rows = int(sp_host[self.e0:self.e0 + self.E_local].sum())
+        if rows > self.capacity:
+            self.check_status()
+        view = self.recv.view(self.rank, self.dtype, (self.capacity, self.H))[:rows]
+        if output_tensor is not None:
+            output_tensor[:rows].copy_(view)
+            return output_tensor
+        return view.clone() if copy_out else view
+
     def forward(self, input, ag_exp_indices, ag_scatter_idx, splits_cpu, ep_token_counts=None, sm_margin: int = 0,
                 copy_to_local_tensor: bool = True):
-        return self.forward_gpu(input, ag_exp_indices, ag_scatter_idx, splits_cpu.to(input.device),
-                                ep_token_counts, None, sm_margin, copy_to_local_tensor)
+        sp = splits_cpu if input.is_cuda else splits_cpu.to(input.device)
+        return self.forward_gpu(input, ag_exp_indices, ag_scatter_idx, sp, ep_token_counts, None, sm_margin,
+                                copy_to_local_tensor)
 
-    forward_no_cpy = forward
-    forward_gpu_no_cpy = forward_gpu
+    def forward_no_cpy(self, input, ag_exp_indices, ag_scatter_idx, splits_cpu, ep_token_counts=None,
+                       sm_margin: int = 0):
+        return self.forward(input, ag_exp_indices, ag_scatter_idx, splits_cpu, ep_token_counts, sm_margin, False)
+
+    def forward_gpu_no_cpy(self, input, ag_exp_indices, ag_scatter_idx, splits, ep_token_counts=None,
+                           output_tensor=None, sm_margin: int = 0):
+        return self.forward_gpu(input, ag_exp_indices, ag_scatter_idx, splits, ep_token_counts, output_tensor,
+                                sm_margin, False)
 
     def pre_comm_index(self, ep_token_counts: torch.Tensor, cur_topk_indices: torch.Tensor,
                        cur_topk_values: torch.Tensor, ag_topk_indices: torch.Tensor, ag_topk_values: torch.Tensor,

@@ -8,8 +8,12 @@
   ``src/moe_ag_scatter/ths_op/gemm_grouped_v3_ag_scatter.cc``), which synchronises with the host
   to build its problem list.
 * ``GemmGroupedV3GatherRS`` (layer 1): per-expert GEMM with the gate weight applied in the
-  epilogue, then one kernel that sums every token's local top-k rows, sends the partial to the
-  token's owner over NVLink and lets the owner add the W partials. Reference:
+  epilogue. With whole experts per rank (no tensor parallelism inside an expert) the epilogue
+  stores every row straight into the slot ``[token][k]`` of the token owner's staging buffer over
+  NVLink and the tail of the same kernel adds each token's top-k slots: one launch, the
+  expert-sorted product never exists in memory. With experts split over ranks a second kernel
+  sums every token's local top-k rows, sends the partial to the token's owner and lets the owner
+  add the W partials. Reference:
   ``flux.GemmGroupedV3GatherRS`` (``src/pybind/gemm_grouped_v3_gather_rs.cc:35-126``,
   ``src/moe_gather_rs``), ``TopkReduceScatterOp``.
 
@@ -52,6 +56,9 @@ class MoeGemmArgs(ctypes.Structure):
         ("timeout_ns", ctypes.c_uint64), ("status", _VP),
         ("ag_src", _VP), ("ag_land", _VP * _R), ("ag_flags", _VP * _R), ("start_ctr", _VP * _R),
         ("local_cnt", _VP), ("stream", _VP),
+        ("scatter", ctypes.c_int32), ("reserved2", ctypes.c_int32),
+        ("routing_idx", _VP), ("row_entry", _VP),
+        ("sc_stage", _VP * _R), ("sc_flags", _VP * _R), ("sc_out", _VP),
     ]
 
 
@@ -283,8 +290,14 @@ class GemmGroupedV3GatherRS(FusedOpBase):
         self.max_m = max_m                           # rows of the full problem: tokens * topk
         self.max_tpr = max_m // topk // world_size
         self.dtype = dtype
-        self.stage = SymmBuffer(world_size * self.max_tpr * n_dim * _ELEM[dtype], self.pg) if self.world > 1 else None
+        # whole experts per rank: the fused path, staging [tokens / W][topk][H] per rank; experts split
+        # over ranks: partial sums per source, [W][tokens / W][H]
+        self.fused = tp_world_size == 1
+        slots = max(world_size, topk) if self.fused else world_size
+        self.stage = SymmBuffer(slots * self.max_tpr * n_dim * _ELEM[dtype], self.pg) \
+            if (self.world > 1 or self.fused) else None
         self._scratch = None
+        self._row_entry = None
 
     def ep_zero_buffer(self) -> None:
         """Kept for API compatibility: nothing needs zeroing between calls."""
@@ -320,6 +333,11 @@ class GemmGroupedV3GatherRS(FusedOpBase):
         if self._scratch is None:
             self._scratch = _scratch(self.E, self.world, dev)
         rows_ep = x0.shape[0]
+        if self.fused and len(input) == 1 and rows_ep > 0:
+            return self._forward_fused(x0, weight[0], splits, ridx, tpr,
+                                       input_scale[0] if input_scale is not None else None,
+                                       weight_scale[0] if weight_scale is not None else None,
+                                       output_vec_scale[0] if output_vec_scale is not None else None)
         y = None
         keep = []
         for g, (x, w) in enumerate(zip(input, weight)):
@@ -350,6 +368,49 @@ class GemmGroupedV3GatherRS(FusedOpBase):
             y = yg if y is None else y.add_(yg)
         out = torch.empty((tpr, self.H), dtype=x0.dtype, device=dev)
         self._combine(y, ridx, tpr, out)
+        self._after_launch()
+        return out
+
+    def _forward_fused(self, x, w, splits, ridx, tpr, input_scale, weight_scale, output_vec_scale) -> torch.Tensor:
+        """One launch: grouped GEMM whose epilogue scatters the gate-weighted rows to the token
+        owners' [token][k] slots and whose tail adds the top-k slots of the local tokens."""
+        dev = x.device
+        if w.dim() != 3 or w.shape[0] != self.E_local or w.shape[1] != self.H or not w.is_contiguous():
+            raise ValueError("weights must be contiguous [E_local, n_dim, ffn]")
+        x = x if x.is_contiguous() else x.contiguous()
+        rows_ep = x.shape[0]
+        if self._row_entry is None or self._row_entry.numel() < rows_ep:
+            self._row_entry = torch.empty(max(rows_ep, self.max_m // max(self.world, 1)), dtype=torch.int32, device=dev)
+        out = torch.empty((tpr, self.H), dtype=x.dtype, device=dev)
+        self._begin_call()
+        a = MoeGemmArgs()
+        a.splits = splits.data_ptr()
+        a.E, a.e0, a.E_local, a.topk = self.E, self.e0, self.E_local, self.topk
+        a.tokens_per_rank, a.gathered = tpr, 0
+        a.in_dtype = _dense.dtype_code(x.dtype)
+        a.N, a.K = self.H, x.shape[1]
+        a.a, a.a_rows = x.data_ptr(), rows_ep
+        a.weights, a.d, a.ldd = w.data_ptr(), None, self.H
+        ws = _f32(weight_scale, dev) if weight_scale is not None else None
+        isc = _f32(input_scale, dev) if input_scale is not None else None
+        ovs = _f32(output_vec_scale, dev) if output_vec_scale is not None else None
+        a.expert_scale = ws.data_ptr() if ws is not None else None
+        a.scalar_scale = isc.data_ptr() if isc is not None else None
+        a.row_scale = ovs.data_ptr() if ovs is not None else None
+        a.scratch = self._scratch.data_ptr()
+        a.rank, a.world, a.epoch = self.rank, self.world, self.epoch
+        a.timeout_ns, a.status = int(self.timeout_s * 1e9), self.status.data_ptr()
+        a.local_cnt = self.ctrl.ptr(self.rank, OFF_LOCAL)
+        a.scatter = 1
+        a.n_entries = ridx.numel()
+        a.routing_idx, a.row_entry = ridx.data_ptr(), self._row_entry.data_ptr()
+        for r in range(self.world):
+            a.sc_stage[r] = self.stage.ptr(r)
+            a.sc_flags[r] = self.ctrl.ptr(r, OFF_CTR)
+            a.start_ctr[r] = self.ctrl.ptr(r, OFF_START)
+        a.sc_out = out.data_ptr()
+        a.stream = _dense.current_stream_ptr(dev)
+        _native.check(_native.lib().fluxb_moe_grouped_gemm(ctypes.byref(a)), "fluxb_moe_grouped_gemm")
         self._after_launch()
         return out
 

@@ -59,7 +59,10 @@ def close(out, ref, what_, tol=2e-2):
 
 # ------------------------------------------------------------------------------------------
 def check_dense():
-    for (M, Nn, K) in [(256 * W, 256, 64 * W), (512 * W, 768, 512 * W), (200 * W, 264, 72 * W)]:
+    # (the 1024-row segments run as 512-row CTA-pair tiles with a split last wave; the last shape gives
+    # every CTA pair several tiles, remote ones followed by tiles of the own segment)
+    for (M, Nn, K) in [(256 * W, 256, 64 * W), (512 * W, 768, 512 * W), (200 * W, 264, 72 * W),
+                       (1024 * W, 1280, 256 * W), (4096 * W, 4096, 128 * W)]:
         Kl = K // W
         a = (torch.randn(M, Kl, device=dev) * 0.5).bfloat16()
         w = (torch.randn(Nn, Kl, device=dev) * 0.05).bfloat16()
@@ -124,7 +127,7 @@ def check_dense():
                 dist.barrier(pg)
                 op.forward(a, w)
                 torch.cuda.synchronize()
-            p0(f"GEMM-RS timeline (us; slice0 = reduce tail entered, slice1 = left): {tl.summary()}")
+            p0(f"GEMM-RS timeline (us; slice0 = first tile of the own segment reached): {tl.summary()}")
         op.check_status()
         M, N, K = 8192, 49152, 12288
         a = (torch.randn(M // W, K, device=dev) * 0.5).bfloat16()

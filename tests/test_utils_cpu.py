@@ -218,3 +218,16 @@ def test_tune_file_and_load_tuning_record(tmp_path, monkeypatch):
     flux.load_tuning_record({"key": [77, 256, 128], "best": {"cta_group": 2, "tile_n": 256, "group_m": 2}})
     assert table.lookup(77, 256, 128)["group_m"] == 2
     monkeypatch.setattr(table, "_EXTRA", None)
+
+
+def test_source_hygiene_of_the_tree():
+    """The formatter / content check that the pre-commit hook runs passes on the tree itself, and
+    it does find what it is meant to find."""
+    from pathlib import Path
+    from tempname_new_b200.utils import hygiene
+    assert hygiene.main(["--check"]) == 0
+    bad = hygiene.check_text(Path("x.py"), "a = 1 \n\tb = 2\n# see DESIGN" + ".md\nlast")
+    kinds = {what for _, what in bad}
+    assert {"trailing whitespace", "tab character", "no newline at end of file"} <= kinds
+    assert any("outside the source tree" in k for k in kinds)
+    assert hygiene.fix_text("a = 1  \n\n\n") == "a = 1\n"
