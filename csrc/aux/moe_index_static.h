@@ -15,7 +15,8 @@
  * message, nothing is launched.
  *
  * The first call on a device looks up the device address of the array, once, with that device
- * current. Make that first call before any stream capture begins. No call of this entry point
+ * current. Make that first call before any stream capture begins; it may come from any host
+ * thread, also from several at once (the cached address is an atomic). No call of this entry point
  * uses cudaMalloc, cudaFree or any allocating library routine.
  *
  * All calls on a device share the one array, and it keeps whatever the last call left in it.

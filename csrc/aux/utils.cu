@@ -349,19 +349,21 @@ extern "C" int fluxb_moe_index_build_static(const int32_t* experts, int64_t n, i
                 "fluxb_moe_index_build_static: ceil(n/4096)*E = " + std::to_string(nblocks64 * E) +
                     " exceeds the built-in scratch of " + std::to_string(FLUXB_MOE_INDEX_STATIC_ELEMS) +
                     " int32; use fluxb_moe_index_build with a caller-provided scratch buffer");
-  // set-up, once per device, with that device current
-  static int32_t* scratch_of_device[64] = {nullptr};
+  // set-up, once per device, with that device current. The cache is atomic: two host threads that
+  // make their first call on a device at the same time both look the address up and store the same
+  // value.
+  static std::atomic<int32_t*> scratch_of_device[64];
   int dev = 0;
   FLUXB_CUDA_OK(cudaGetDevice(&dev));
   FLUXB_REQUIRE(dev >= 0 && dev < 64, "device ordinal out of range");
-  int32_t* scratch = scratch_of_device[dev];
+  int32_t* scratch = scratch_of_device[dev].load(std::memory_order_relaxed);
   if (scratch == nullptr) {
     void* addr = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&addr, g_moe_index_static);
     if (e != cudaSuccess)
       return fail(kErrCuda, std::string("cudaGetSymbolAddress(g_moe_index_static): ") + cudaGetErrorString(e));
     scratch = static_cast<int32_t*>(addr);
-    scratch_of_device[dev] = scratch;
+    scratch_of_device[dev].store(scratch, std::memory_order_relaxed);
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int nblocks = static_cast<int>(nblocks64);

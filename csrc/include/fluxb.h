@@ -285,6 +285,9 @@ int fluxb_barrier_all(uint32_t* const* flags, int rank, int world, uint32_t epoc
  * limit passes, then returns; the outcome is in `status`. */
 int fluxb_wait_flag(const uint32_t* flag, uint32_t expected, uint64_t timeout_ns,
                     fluxb_status_t* status, void* stream);
+/* Same, but waits for *flag == expected exactly (signals of the send/recv op). */
+int fluxb_wait_flag_eq(const uint32_t* flag, uint32_t expected, uint64_t timeout_ns,
+                       fluxb_status_t* status, void* stream);
 
 /* ---- block-scaled fp8 quantisation (see csrc/aux/quantize.cu for layouts) ---- */
 int fluxb_quantize_blockwise(const void* x, int64_t ldx, int in_dtype, void* q, void* qt,

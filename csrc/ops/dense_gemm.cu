@@ -44,8 +44,11 @@ uint32_t* wave_counter_for(cudaStream_t stream) {
 
 namespace {
 
+// coop: the launch carries the cooperative attribute, so the grid only starts when all of its CTAs
+// can be resident together (and the launch fails, instead of waiting forever inside the kernel, when
+// they never can). Every launch whose CTAs wait for one another or for peers asks for it.
 template <class Cfg>
-int launch_dense(const DenseGemmParams& p, int grid, cudaStream_t stream) {
+int launch_dense(const DenseGemmParams& p, int grid, cudaStream_t stream, bool coop = false) {
   constexpr int kThreads = Cfg::THREADS;
   static bool configured[64] = {false};
   int dev = 0;
@@ -55,21 +58,28 @@ int launch_dense(const DenseGemmParams& p, int grid, cudaStream_t stream) {
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     if (dev < 64) configured[dev] = true;
   }
-  if constexpr (Cfg::CG == 1) {
-    dense_gemm_kernel<Cfg><<<grid, kThreads, Cfg::SMEM_BYTES, stream>>>(p);
-  } else {
+  {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if constexpr (Cfg::CG == 2) {
+      attr[na].id = cudaLaunchAttributeClusterDimension;
+      attr[na].val.clusterDim.x = 2;
+      attr[na].val.clusterDim.y = 1;
+      attr[na].val.clusterDim.z = 1;
+      ++na;
+    }
+    if (coop) {
+      attr[na].id = cudaLaunchAttributeCooperative;
+      attr[na].val.cooperative = 1;
+      ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = na;
     FLUXB_CUDA_OK(cudaLaunchKernelEx(&cfg, dense_gemm_kernel<Cfg>, p));
   }
   FLUXB_CUDA_OK(cudaGetLastError());
@@ -508,6 +518,13 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   }
 
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
+  // CTAs that wait for one another (wave-synchronous starts) or for peers (every multi-rank mode) must
+  // all be resident: those launches are cooperative unless FLUXB_COOPERATIVE=0
+  static const int coop_env = [] {
+    const char* e = getenv("FLUXB_COOPERATIVE");
+    return e ? atoi(e) : 1;
+  }();
+  bool coop = coop_env != 0 && (multi || a2a);
   {
     // wave-synchronous tile starts pay off when a wave's operands do not fit L2 together
     static const int wave_env = [] {
@@ -518,55 +535,56 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     const int kblocks = (a->K + bk - 1) / bk;
     const bool want = wave_env >= 0 ? wave_env != 0 : kblocks >= 48;
     if (want && p.total_vtiles > 2 * (grid / cg)) p.wave_ctr = a->wave_ctr ? a->wave_ctr : wave_counter_for(stream);
+    if (p.wave_ctr != nullptr && coop_env != 0) coop = true;
   }
   if (a->blockscale) {
-    if (p.mode == kModeAllGather) return launch_dense<DenseCfg<128, 1, 4, 1, 32768, true>>(p, grid, stream);
-    return launch_dense<DenseCfg<128, 1, 4, 1, 0, true>>(p, grid, stream);
+    if (p.mode == kModeAllGather) return launch_dense<DenseCfg<128, 1, 4, 1, 32768, true>>(p, grid, stream, coop);
+    return launch_dense<DenseCfg<128, 1, 4, 1, 0, true>>(p, grid, stream, coop);
   }
   if (p.mode == kModeAllGather || p.mode == kModeA2AGemm) {
     // variants that carry the staging rings of the all-gather / all-to-all push
     if (mt == 2) {
-      if (in16) return launch_dense<DenseCfg<256, 0, 4, 2, 16384, false, 2>>(p, grid, stream);
-      return launch_dense<DenseCfg<256, 1, 4, 2, 16384, false, 2>>(p, grid, stream);
+      if (in16) return launch_dense<DenseCfg<256, 0, 4, 2, 16384, false, 2>>(p, grid, stream, coop);
+      return launch_dense<DenseCfg<256, 1, 4, 2, 16384, false, 2>>(p, grid, stream, coop);
     }
     if (cg == 2 && bn == 256) {
-      if (in16) return launch_dense<DenseCfg<256, 0, 6, 2, 16384>>(p, grid, stream);
-      if (a->in_dtype == FLUXB_INT8) return launch_dense<DenseCfg<256, 2, 6, 2, 16384>>(p, grid, stream);
-      return launch_dense<DenseCfg<256, 1, 6, 2, 16384>>(p, grid, stream);
+      if (in16) return launch_dense<DenseCfg<256, 0, 6, 2, 16384>>(p, grid, stream, coop);
+      if (a->in_dtype == FLUXB_INT8) return launch_dense<DenseCfg<256, 2, 6, 2, 16384>>(p, grid, stream, coop);
+      return launch_dense<DenseCfg<256, 1, 6, 2, 16384>>(p, grid, stream, coop);
     }
     FLUXB_REQUIRE(cg == 1 && bn == 128, "all-gather GEMM runs as CTA pairs on 256-wide tiles or single CTAs on 128-wide tiles");
-    if (in16) return launch_dense<DenseCfg<128, 0, 6, 1, 16384>>(p, grid, stream);
-    if (a->in_dtype == FLUXB_INT8) return launch_dense<DenseCfg<128, 2, 6, 1, 16384>>(p, grid, stream);
-    return launch_dense<DenseCfg<128, 1, 6, 1, 16384>>(p, grid, stream);
+    if (in16) return launch_dense<DenseCfg<128, 0, 6, 1, 16384>>(p, grid, stream, coop);
+    if (a->in_dtype == FLUXB_INT8) return launch_dense<DenseCfg<128, 2, 6, 1, 16384>>(p, grid, stream, coop);
+    return launch_dense<DenseCfg<128, 1, 6, 1, 16384>>(p, grid, stream, coop);
   }
   if (a->in_dtype == FLUXB_INT8) {
     // signed 8-bit operands, s32 accumulation (tcgen05 kind::i8)
-    if (cg == 2 && bn == 256) return launch_dense<DenseCfg<256, 2, 6, 2>>(p, grid, stream);
+    if (cg == 2 && bn == 256) return launch_dense<DenseCfg<256, 2, 6, 2>>(p, grid, stream, coop);
     FLUXB_REQUIRE(bn == 128, "int8 runs on 256-wide CTA-pair tiles or 128-wide single-CTA tiles");
-    if (cg == 2) return launch_dense<DenseCfg<128, 2, 8, 2>>(p, grid, stream);
-    return launch_dense<DenseCfg<128, 2, 6>>(p, grid, stream);
+    if (cg == 2) return launch_dense<DenseCfg<128, 2, 8, 2>>(p, grid, stream, coop);
+    return launch_dense<DenseCfg<128, 2, 6>>(p, grid, stream, coop);
   }
   if (mt == 2) {
-    if (in16) return launch_dense<DenseCfg<256, 0, 4, 2, 0, false, 2>>(p, grid, stream);
-    return launch_dense<DenseCfg<256, 1, 4, 2, 0, false, 2>>(p, grid, stream);
+    if (in16) return launch_dense<DenseCfg<256, 0, 4, 2, 0, false, 2>>(p, grid, stream, coop);
+    return launch_dense<DenseCfg<256, 1, 4, 2, 0, false, 2>>(p, grid, stream, coop);
   }
   if (cg == 2) {
     if (in16) {
-      if (bn == 256) return launch_dense<DenseCfg<256, 0, 6, 2>>(p, grid, stream);
-      if (bn == 192) return launch_dense<DenseCfg<192, 0, 6, 2>>(p, grid, stream);
-      return launch_dense<DenseCfg<128, 0, 8, 2>>(p, grid, stream);
+      if (bn == 256) return launch_dense<DenseCfg<256, 0, 6, 2>>(p, grid, stream, coop);
+      if (bn == 192) return launch_dense<DenseCfg<192, 0, 6, 2>>(p, grid, stream, coop);
+      return launch_dense<DenseCfg<128, 0, 8, 2>>(p, grid, stream, coop);
     }
-    if (bn == 256) return launch_dense<DenseCfg<256, 1, 6, 2>>(p, grid, stream);
-    if (bn == 192) return launch_dense<DenseCfg<192, 1, 6, 2>>(p, grid, stream);
-    return launch_dense<DenseCfg<128, 1, 8, 2>>(p, grid, stream);
+    if (bn == 256) return launch_dense<DenseCfg<256, 1, 6, 2>>(p, grid, stream, coop);
+    if (bn == 192) return launch_dense<DenseCfg<192, 1, 6, 2>>(p, grid, stream, coop);
+    return launch_dense<DenseCfg<128, 1, 8, 2>>(p, grid, stream, coop);
   }
   if (in16) {
-    if (bn == 256) return launch_dense<DenseCfg<256, 0, 4>>(p, grid, stream);
-    if (bn == 192) return launch_dense<DenseCfg<192, 0, 4>>(p, grid, stream);
-    return launch_dense<DenseCfg<128, 0, 6>>(p, grid, stream);
+    if (bn == 256) return launch_dense<DenseCfg<256, 0, 4>>(p, grid, stream, coop);
+    if (bn == 192) return launch_dense<DenseCfg<192, 0, 4>>(p, grid, stream, coop);
+    return launch_dense<DenseCfg<128, 0, 6>>(p, grid, stream, coop);
   } else {
-    if (bn == 256) return launch_dense<DenseCfg<256, 1, 4>>(p, grid, stream);
-    if (bn == 192) return launch_dense<DenseCfg<192, 1, 4>>(p, grid, stream);
-    return launch_dense<DenseCfg<128, 1, 6>>(p, grid, stream);
+    if (bn == 256) return launch_dense<DenseCfg<256, 1, 4>>(p, grid, stream, coop);
+    if (bn == 192) return launch_dense<DenseCfg<192, 1, 4>>(p, grid, stream, coop);
+    return launch_dense<DenseCfg<128, 1, 6>>(p, grid, stream, coop);
   }
 }

@@ -267,10 +267,15 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
   FLUXB_REQUIRE(a->E >= 1 && a->E <= kMaxE && a->e0 >= 0 && a->E_local >= 1 && a->e0 + a->E_local <= a->E,
                 "expert range");
   FLUXB_REQUIRE(a->N > 0 && a->K > 0 && a->N % 8 == 0, "N, K");
-  FLUXB_REQUIRE(a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP16, "grouped GEMM runs on bf16 / fp16");
+  FLUXB_REQUIRE(a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP16 || a->in_dtype == FLUXB_FP8_E4M3 ||
+                    a->in_dtype == FLUXB_FP8_E5M2,
+                "grouped GEMM runs on bf16 / fp16 / fp8 (e4m3, e5m2; 16-bit output, scales in the epilogue)");
   FLUXB_REQUIRE(a->world >= 1 && a->world <= FLUXB_MAX_RANKS && a->rank >= 0 && a->rank < a->world, "ranks");
   FLUXB_REQUIRE(a->splits && a->scratch && a->weights && (a->d || a->scatter), "pointers");
-  const int elt = 2;
+  const bool in8 = a->in_dtype == FLUXB_FP8_E4M3 || a->in_dtype == FLUXB_FP8_E5M2;
+  const int elt = in8 ? 1 : 2;
+  const uint32_t bk = 128 / elt;   // elements of one 128-byte swizzle row
+  const CUtensorMapDataType in_dt = in8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   FLUXB_REQUIRE((a->K * elt) % 16 == 0, "K row bytes must be a multiple of 16");
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
   const int bn = (a->N % 256 == 0 || a->N > 1024) ? 256 : 128;
@@ -323,8 +328,8 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
   p.expert_scale = a->expert_scale;
   p.scalar_scale = a->scalar_scale;
   p.row_scale = a->row_scale;
-  p.out_f16 = a->in_dtype == FLUXB_FP16;
-  p.ab_fmt = a->in_dtype == FLUXB_BF16 ? 1 : 0;
+  p.out_f16 = a->in_dtype == FLUXB_FP16;   // 8-bit inputs give bf16 outputs
+  p.ab_fmt = (a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP8_E5M2) ? 1 : 0;
   p.rank = a->rank;
   p.world = a->world;
   p.do_allgather = a->do_allgather;
@@ -335,8 +340,8 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
   {
     uint64_t dims[3] = {static_cast<uint64_t>(a->K), static_cast<uint64_t>(a->N), static_cast<uint64_t>(a->E_local)};
     uint64_t str[2] = {static_cast<uint64_t>(a->K) * elt, static_cast<uint64_t>(a->K) * elt * a->N};
-    uint32_t box[3] = {64, static_cast<uint32_t>(bn), 1};
-    if ((rc = encode_tmap(&p.tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a->weights, dims, str, box, Swz::B128)))
+    uint32_t box[3] = {bk, static_cast<uint32_t>(bn), 1};
+    if ((rc = encode_tmap(&p.tm_b, in_dt, 3, a->weights, dims, str, box, Swz::B128)))
       return rc;
   }
   // gathered rows: by default the communication warps copy them into a sorted buffer (when the
@@ -365,15 +370,15 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
       p.local_cnt = a->local_cnt;
       uint64_t dims[2] = {static_cast<uint64_t>(a->K), static_cast<uint64_t>(a->a_sorted_rows)};
       uint64_t str[1] = {static_cast<uint64_t>(a->K) * elt};
-      uint32_t box[2] = {64, 128};
-      if ((rc = encode_tmap(&p.tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->a_sorted, dims, str, box, Swz::B128)))
+      uint32_t box[2] = {bk, 128};
+      if ((rc = encode_tmap(&p.tm_a, in_dt, 2, a->a_sorted, dims, str, box, Swz::B128)))
         return rc;
     } else if (use_gather4) {
       uint64_t dims[2] = {static_cast<uint64_t>(a->K),
                           static_cast<uint64_t>(a->tokens_per_rank) * (a->do_allgather || a->world > 1 ? a->world : 1)};
       uint64_t str[1] = {static_cast<uint64_t>(a->K) * elt};
-      uint32_t box[2] = {64, 1};
-      if ((rc = encode_tmap(&p.tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->a_tokens, dims, str, box, Swz::B128)))
+      uint32_t box[2] = {bk, 1};
+      if ((rc = encode_tmap(&p.tm_a, in_dt, 2, a->a_tokens, dims, str, box, Swz::B128)))
         return rc;
     }
     if (a->do_allgather) {
@@ -403,8 +408,8 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
     FLUXB_REQUIRE(a->a != nullptr && a->a_rows > 0, "contiguous A missing");
     uint64_t dims[2] = {static_cast<uint64_t>(a->K), static_cast<uint64_t>(a->a_rows)};
     uint64_t str[1] = {static_cast<uint64_t>(a->K) * elt};
-    uint32_t box[2] = {64, 128};
-    if ((rc = encode_tmap(&p.tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->a, dims, str, box, Swz::B128)))
+    uint32_t box[2] = {bk, 128};
+    if ((rc = encode_tmap(&p.tm_a, in_dt, 2, a->a, dims, str, box, Swz::B128)))
       return rc;
   }
   int sms = 0;
@@ -418,6 +423,20 @@ extern "C" int fluxb_moe_grouped_gemm(const fluxb_moe_gemm_args_t* a) {
   }
   // (the cp.async variant keeps its own producer warps per tile and is left alone)
   if (wave_env != 0 && !(a->gathered && gather_mode == 1)) p.wave_ctr = wave_counter_for(stream);
+  if (in8) {
+    // 8-bit operands (tcgen05 kind::f8f6f4): contiguous A, the sorted-buffer gather and the fused combine
+    FLUXB_REQUIRE(!a->gathered || pregather, "fp8 grouped GEMM gathers rows through the sorted buffer only");
+    if (pregather) {
+      if (bn == 256) return launch_grouped<GroupedCfg<256, 1, 4, 3>>(p, sms, stream);
+      return launch_grouped<GroupedCfg<128, 1, 5, 3>>(p, sms, stream);
+    }
+    if (a->scatter) {
+      if (bn == 256) return launch_grouped<GroupedCfg<256, 1, 4, 0, true>>(p, sms, stream);
+      return launch_grouped<GroupedCfg<128, 1, 6, 0, true>>(p, sms, stream);
+    }
+    if (bn == 256) return launch_grouped<GroupedCfg<256, 1, 4, 0>>(p, sms, stream);
+    return launch_grouped<GroupedCfg<128, 1, 6, 0>>(p, sms, stream);
+  }
   if (pregather) {
     if (bn == 256) return launch_grouped<GroupedCfg<256, 0, 4, 3>>(p, sms, stream);
     return launch_grouped<GroupedCfg<128, 0, 5, 3>>(p, sms, stream);

@@ -12,7 +12,7 @@
 namespace fluxb {
 extern std::atomic<uint64_t> g_launches;
 
-__global__ void barrier_all_kernel(uint32_t* const* flags_by_rank_unused, uint32_t* f0,
+__global__ void barrier_all_kernel(uint32_t* f0,
                                    uint32_t* f1, uint32_t* f2, uint32_t* f3, uint32_t* f4,
                                    uint32_t* f5, uint32_t* f6, uint32_t* f7, int rank, int world,
                                    uint32_t epoch, uint64_t timeout_ns, Status* status) {
@@ -98,8 +98,37 @@ extern "C" int fluxb_barrier_all(uint32_t* const* flags, int rank, int world, ui
     f[i] = flags[i];
   }
   barrier_all_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      nullptr, f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7], rank, world, epoch,
+      f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7], rank, world, epoch,
       timeout_ns ? timeout_ns : 2000000000ull, reinterpret_cast<Status*>(status));
+  FLUXB_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return kOk;
+}
+
+// Wait until *flag == expected (not "at least": a larger value left over from an earlier exchange
+// does not satisfy the wait). One thread, system-scope acquire loads, bounded.
+__global__ void wait_flag_eq_kernel(const uint32_t* flag, uint32_t expected, uint64_t timeout_ns, Status* status) {
+  __shared__ uint32_t abort_word;
+  abort_word = 0;
+  WaitCtx wc{status, &abort_word, timeout_ns};
+  const uint64_t t0 = ptx::globaltimer_ns();
+  uint32_t v = ptx::ld_acquire_sys(flag);
+  uint32_t spins = 0;
+  while (v != expected) {
+    if ((++spins & 31u) == 0u && ptx::globaltimer_ns() - t0 > timeout_ns) {
+      wait_give_up(wc, kSiteTest, v, expected);
+      return;
+    }
+    __nanosleep(40);
+    v = ptx::ld_acquire_sys(flag);
+  }
+}
+
+extern "C" int fluxb_wait_flag_eq(const uint32_t* flag, uint32_t expected, uint64_t timeout_ns,
+                                  fluxb_status_t* status, void* stream) {
+  FLUXB_REQUIRE(flag != nullptr, "flag pointer");
+  wait_flag_eq_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      flag, expected, timeout_ns ? timeout_ns : 1000000000ull, reinterpret_cast<Status*>(status));
   FLUXB_CUDA_OK(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return kOk;

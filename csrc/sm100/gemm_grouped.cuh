@@ -86,7 +86,12 @@ struct GroupedCfg {
   static constexpr int BK = 128 / ELT;
   static constexpr int UMMA_K = 32 / ELT;
   static constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128, STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int COMM_BYTES = GATHER_ != 0 ? 32768 : 0;
+  // scatter epilogue: every epilogue warp stages 32 rows x 64 columns (128 bytes per row, 144-byte
+  // pitch so that the lanes' 16-byte writes fall into different banks) before the rows leave as
+  // one bulk copy each
+  static constexpr int SC_PITCH = 144;
+  static constexpr int SC_WARP_BYTES = 32 * SC_PITCH;
+  static constexpr int COMM_BYTES = GATHER_ != 0 ? 32768 : (SCATTER_ ? 4 * SC_WARP_BYTES : 0);
   static constexpr int BAR_BYTES = 256 + 1024;     // barriers, then two 128-entry row-index buffers
   static constexpr int THREADS = GATHER_ == 1 ? 384 : 256;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + COMM_BYTES + BAR_BYTES + 1024;
@@ -482,6 +487,34 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
           if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
         }
         const int col0 = g.n0 + ch * 64;
+        if constexpr (Cfg::SCATTER) {
+          // this lane's 64 columns -> its row of the warp's staging block -> one bulk copy of the
+          // row piece (up to 128 bytes) to the owner's slot: whole lines travel over NVLink instead
+          // of 16-byte stores scattered over 32 rows
+          const uint32_t my_row = comm_base + (warp - 4) * Cfg::SC_WARP_BYTES + lane * Cfg::SC_PITCH;
+          ptx::bulk_wait_read<0>();      // this lane's previous copy has read the row
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t a0 = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 0]) * scale, __uint_as_float(r0[8 * j + 1]) * scale);
+            const uint32_t a1 = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 2]) * scale, __uint_as_float(r0[8 * j + 3]) * scale);
+            const uint32_t a2 = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 4]) * scale, __uint_as_float(r0[8 * j + 5]) * scale);
+            const uint32_t a3 = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 6]) * scale, __uint_as_float(r0[8 * j + 7]) * scale);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + 16 * j), "r"(a0), "r"(a1), "r"(a2), "r"(a3) : "memory");
+            const uint32_t b0 = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 0]) * scale, __uint_as_float(r1[8 * j + 1]) * scale);
+            const uint32_t b1 = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 2]) * scale, __uint_as_float(r1[8 * j + 3]) * scale);
+            const uint32_t b2 = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 4]) * scale, __uint_as_float(r1[8 * j + 5]) * scale);
+            const uint32_t b3 = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 6]) * scale, __uint_as_float(r1[8 * j + 7]) * scale);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + 64 + 16 * j), "r"(b0), "r"(b1), "r"(b2), "r"(b3) : "memory");
+          }
+          ptx::fence_proxy_async_smem();
+          if (row_ok && col0 < p.N) {
+            const int ncol = p.N - col0 < 64 ? p.N - col0 : 64;     // a multiple of 8
+            ptx::bulk_store(drow_base + col0, my_row, static_cast<uint32_t>(ncol) * 2u);
+          }
+          ptx::bulk_commit();
+          continue;
+        }
         if (row_ok && col0 < p.N) {
           uint16_t* drow = drow_base + col0;
 #pragma unroll
@@ -507,7 +540,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
       }
     }
     if constexpr (Cfg::SCATTER) {
-      // every row this warp had is written; the last warp of the grid tells every owner
+      // every row this warp had is written (each lane waits for its own copies); the last warp of
+      // the grid tells every owner
+      ptx::bulk_wait<0>();
+      ptx::fence_proxy_async_all();
       ptx::fence_acq_rel_sys();
       __syncwarp();
       if (lane == 0) {

@@ -59,6 +59,13 @@ class FusedOpBase:
         # set when a wait of this op gave up: its arrival counters may be left partly counted and
         # the ranks' call numbers may disagree, so the op refuses to run until reset()
         self.poisoned: Optional[str] = None
+        # SMs left free for other work (a collective of another group, a second stream): the fused
+        # kernels keep all their CTAs resident and wait for one another, so they must not be launched
+        # wider than what is free. Per-call ``sm_margin`` arguments override this default
+        # (reference: ``sm_margin`` / ``num_comm_sm`` of the Ulysses and MoE ops, e.g.
+        # src/gemm_a2a_transpose/ths_op/gemm_all2all_transpose.cc:559-560).
+        self.sm_margin = int(os.environ.get("FLUXB_SM_MARGIN", "0"))
+        self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count if self.is_cuda else 0
 
     # -- device status ---------------------------------------------------------------
     def check_status(self) -> None:
@@ -82,6 +89,14 @@ class FusedOpBase:
     def _after_launch(self) -> None:
         if self.check_every_call:
             self.check_status()
+
+    def _num_sms(self, sm_margin: Optional[int] = None) -> int:
+        """SMs a launch of this op may use: 0 (= all) without a margin, else the device's count minus
+        the margin (at least 2)."""
+        m = self.sm_margin if not sm_margin else sm_margin
+        if m <= 0 or self._sm_count == 0:
+            return 0
+        return max(self._sm_count - m, 2)
 
     def _begin_call(self) -> int:
         """Every forward starts here: refuses a poisoned op, then takes the next call number."""

@@ -3,9 +3,10 @@
 ``out[M, N/W] = all_gather_M(input[M/W, K]) @ weight[N/W, K]^T (+bias)``
 
 On CUDA one persistent tcgen05 kernel does both: two warps of every CTA push this rank's
-shard into the peers' landing buffers with 16-byte peer stores (first to the peer that will
-consume it first) and bump per-tile-row arrival flags, while the TMA producer of the same
-kernel starts on the local shard and gates each remote M-tile on its flag.
+shard into the peers' landing buffers through a ring of bulk copies (global -> shared ->
+peer global, first to the peer that will consume it first) and publish an arrival flag per
+shard unit, while the TMA producer of the same kernel starts on the local shard and gates
+each remote M-tile on its unit's flag.
 Reference: ``flux.AGKernel`` (``src/pybind/ag_gemm.cc:28-106``,
 ``src/ag_gemm/ths_op/all_gather_gemm_op.cc``, ``src/coll/ths_op/all_gather_op.cc``): copy
 engine pulls on a side stream plus a flag-gated GEMM.
@@ -87,6 +88,7 @@ class AGKernel(FusedOpBase):
                 args.ag_flags[r] = self.ctrl.ptr(r, OFF_CTR)
                 args.start_ctr[r] = self.ctrl.ptr(r, OFF_START)
             args.local_cnt = self.ctrl.ptr(self.rank, OFF_LOCAL)
+        args.num_sms = self._num_sms()
         _dense.run(args)
         if gathered_input is not None:
             self._copy_gathered(a, gathered_input, seg, K)

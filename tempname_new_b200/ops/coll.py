@@ -195,7 +195,10 @@ class AsyncSendRecv:
         self.set_signal(self.rank, comm_buff_id, 0)
 
     def wait_signal_eq(self, comm_buff_id: int, value: int, timeout_s: float = 10.0) -> None:
-        """Waits (stream-ordered on CUDA, bounded) until the local signal is at least ``value``."""
+        """Waits (stream-ordered on CUDA, bounded) until the local signal equals ``value``. On CUDA
+        the wait is a kernel on the current stream: if it runs out of time the stream goes on and
+        the outcome is in the op's status word, which ``check()`` (or the next ``wait_signal_eq``)
+        turns into ``FluxTimeoutError``."""
         if not self.is_cuda:
             w = self.sig.view(self.rank, torch.int32, (64,))
             deadline = time.monotonic() + timeout_s
@@ -206,8 +209,24 @@ class AsyncSendRecv:
             return
         if not hasattr(self, "_status"):
             self._status = torch.zeros(4, dtype=torch.int32, device=self.buf.device)
-        rc = _native.lib().fluxb_wait_flag(ctypes.c_void_p(self.sig.ptr(self.rank, 4 * comm_buff_id)),
-                                           ctypes.c_uint32(value), ctypes.c_uint64(int(timeout_s * 1e9)),
-                                           ctypes.c_void_p(self._status.data_ptr()),
-                                           ctypes.c_void_p(_dense.current_stream_ptr(self.buf.device)))
-        _native.check(rc, "fluxb_wait_flag")
+            self._waits_unchecked = 0
+        elif self._waits_unchecked >= 64:
+            self.check()       # an earlier wait may have given up: do not pile more work on top of it
+        rc = _native.lib().fluxb_wait_flag_eq(ctypes.c_void_p(self.sig.ptr(self.rank, 4 * comm_buff_id)),
+                                              ctypes.c_uint32(value), ctypes.c_uint64(int(timeout_s * 1e9)),
+                                              ctypes.c_void_p(self._status.data_ptr()),
+                                              ctypes.c_void_p(_dense.current_stream_ptr(self.buf.device)))
+        _native.check(rc, "fluxb_wait_flag_eq")
+        self._waits_unchecked += 1
+
+    def check(self) -> None:
+        """Synchronise and raise ``FluxTimeoutError`` if a signal wait since the last check gave up
+        (the consumers of the comm buffer then ran on data that never arrived)."""
+        if not self.is_cuda or not hasattr(self, "_status"):
+            return
+        st = self._status.tolist()
+        self._waits_unchecked = 0
+        if st[0] != 0:
+            self._status.zero_()
+            raise FluxTimeoutError(f"AsyncSendRecv: a signal wait timed out (saw {st[2] & 0xFFFFFFFF}, "
+                                   f"waited for {st[3] & 0xFFFFFFFF})")

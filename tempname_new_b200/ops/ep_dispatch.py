@@ -63,6 +63,8 @@ class DisScatterForward(FusedOpBase):
         self.E_local = self.E // ep_world_size
         self.e0 = (rank // tp_world_size) * self.E_local
         self.dtype = dtype
+        self.max_m = max_m
+        self._index_ag = {}
         if self.is_cuda:
             # rows one rank can receive: its fair share of max_m * topk times the capacity ratio
             total = max(max_m * topk, 1)
@@ -158,6 +160,24 @@ class DisScatterForward(FusedOpBase):
         """Gather every rank's routing choice ([tokens_r, topk] expert ids and gate values,
         ``ep_token_counts[r]`` tokens on rank r) into the two outputs, rank after rank (reference:
         ``DisScatterForward.pre_comm_index``, python/flux/cpp_mod.pyi:1169-1177)."""
+        if cur_topk_indices.is_cuda:
+            # rows of bytes through the row-exchange kernel (variable rows per rank, ordered by source);
+            # nothing visits the host
+            for which, (cur, out) in enumerate(((cur_topk_indices, ag_topk_indices),
+                                                (cur_topk_values, ag_topk_values))):
+                row_b = cur.shape[1] * cur.element_size()
+                pad_b = (row_b + 15) // 16 * 16
+                rows = cur.contiguous().view(torch.uint8).reshape(cur.shape[0], row_b)
+                if pad_b != row_b:
+                    rows = torch.nn.functional.pad(rows, (0, pad_b - row_b))
+                key = (which, pad_b)
+                if key not in self._index_ag:
+                    self._index_ag[key] = AllGatherOp(self.pg, 1, self.max_m, pad_b, torch.uint8)
+                ag = self._index_ag[key]
+                ag.run(rows.contiguous())
+                got = ag.local_input_buffer()[: out.shape[0]]   # rows of all ranks, ordered by source
+                out.copy_(got[:, :row_b].contiguous().view(cur.dtype).reshape(out.shape))
+            return
         counts = [int(v) for v in ep_token_counts.tolist()]
         mx = max(counts)
         for cur, out in ((cur_topk_indices, ag_topk_indices), (cur_topk_values, ag_topk_values)):

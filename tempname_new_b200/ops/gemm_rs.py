@@ -78,6 +78,7 @@ class GemmRS(FusedOpBase):
             args = _dense.base_args(a, w, bias, self.output_dtype, input_scale, weight_scale,
                                     m=M, status=self.status, keep=keep)
         args.M = M
+        args.num_sms = self._num_sms()
         args.mode, args.rank, args.world = _dense.REDUCE_SCATTER, self.rank, self.world
         args.epoch = self.epoch
         args.timeout_ns = int(self.timeout_s * 1e9)

@@ -203,6 +203,9 @@ class GemmAllToAllTranspose(FusedOpBase):
             args = A2AArgs()
             base = _dense.base_args(x2, w, bias, self.output_dtype, m=x2.shape[0], status=self.status, keep=keep)
             base.M = x2.shape[0]
+            # the all-to-all runs in the epilogue of the GEMM's own CTAs: nothing to carve out for
+            # num_comm_sm; sm_margin shrinks the grid
+            base.num_sms = self._num_sms(sm_margin)
             base.mode, base.rank, base.world = 3, self.rank, self.world
             base.epoch, base.timeout_ns = self.epoch, int(self.timeout_s * 1e9)
             base.local_cnt = self.ctrl.ptr(self.rank, OFF_LOCAL)
@@ -344,6 +347,7 @@ class AllToAllTransposeGemm(FusedOpBase):
             base = _dense.base_args(land_local, w, bias, self.output_dtype, m=M, status=self.status, keep=keep)
             base.M = M
             base.d, base.ldd = res.data_ptr(), N
+            base.num_sms = self._num_sms(sm_margin)   # (the push runs in the GEMM's own CTAs)
             base.mode, base.rank, base.world = 4, self.rank, self.world
             base.epoch, base.timeout_ns = self.epoch, int(self.timeout_s * 1e9)
             base.local_cnt = self.ctrl.ptr(self.rank, OFF_LOCAL)

@@ -26,11 +26,25 @@ from ..ops.gemm_rs import GemmRS
 
 
 class _OpCache:
-    """Fused-op objects keyed by shape: they own symmetric buffers, so they are built once."""
+    """Fused-op objects keyed by shape: they own symmetric buffers (an all-gather landing buffer, the
+    reduce-scatter staging slabs: hundreds of MB at transformer shapes), so one set per process group
+    serves every layer of a model: layers run one after the other on a stream, and the ops' call
+    numbers keep consecutive uses apart. ``_OpCache.shared(group)`` returns that per-group instance
+    (the reference's Megatron adapter likewise keeps one op per shape)."""
+
+    _per_group = {}
 
     def __init__(self, group):
         self.group = group
         self.ops = {}
+
+    @classmethod
+    def shared(cls, group) -> "_OpCache":
+        key = id(group)
+        c = cls._per_group.get(key)
+        if c is None or c.group is not group:
+            c = cls._per_group[key] = cls(group)
+        return c
 
     def ag(self, full_m, n, k, dtype) -> AGKernel:
         key = ("ag", full_m, n, k, dtype)
@@ -112,7 +126,7 @@ class ColumnParallelLinear(nn.Module):
         self.weight = nn.Parameter(torch.empty(out_features // W, in_features, dtype=dtype, device=device))
         nn.init.normal_(self.weight, std=init_std)
         self.bias = nn.Parameter(torch.zeros(out_features // W, dtype=dtype, device=device)) if bias else None
-        self._cache = _OpCache(self.group)
+        self._cache = _OpCache.shared(self.group)
 
     def forward(self, x: torch.Tensor, act: Optional[str] = None) -> torch.Tensor:
         need = torch.is_grad_enabled() and self.weight.requires_grad
@@ -133,7 +147,7 @@ class RowParallelLinear(nn.Module):
         self.weight = nn.Parameter(torch.empty(out_features, in_features // W, dtype=dtype, device=device))
         nn.init.normal_(self.weight, std=init_std)
         self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
-        self._cache = _OpCache(self.group)
+        self._cache = _OpCache.shared(self.group)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = _RowParallelFn.apply(x, self.weight, self._cache)
@@ -150,7 +164,7 @@ def patch_megatron_linears(model, tp_group=None, row: bool = True, column: bool 
     except Exception as e:  # pragma: no cover - Megatron is not part of this image
         raise RuntimeError("Megatron-LM is not importable in this environment") from e
     group = tp_group if tp_group is not None else parallel_state.get_tensor_model_parallel_group()
-    cache = _OpCache(group)
+    cache = _OpCache.shared(group)
     n = 0
     for _, mod in model.named_modules():
         if row and isinstance(mod, mlayers.RowParallelLinear) and mod.sequence_parallel and mod.input_is_parallel:

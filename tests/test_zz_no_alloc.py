@@ -54,6 +54,15 @@ def test_static_scratch_entry_matches_allocating_entry():
         names = ["splits", "offsets", "scatter_index", "gather_index", "topk_index"]
         for name, a, b in zip(names, got, ref):
             assert torch.equal(a.reshape(-1), b.reshape(-1)), name
+        # and, independently of the other entry point, against the plain statement of the routing
+        # tensors: counts per expert and the stable expert-sorted order
+        order = torch.argsort(flat.long(), stable=True)
+        scatter_ref = torch.empty_like(order)
+        scatter_ref[order] = torch.arange(order.numel(), device=dev)
+        assert torch.equal(got[0].long(), torch.bincount(flat.long(), minlength=E))
+        assert torch.equal(got[2].long(), scatter_ref)
+        assert torch.equal(got[3].long(), order // topk)
+        assert torch.equal(got[4].long(), order % topk)
 
 
 def test_static_scratch_entry_refuses_oversized_problem():
