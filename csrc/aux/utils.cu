@@ -22,9 +22,14 @@ namespace {
 // ----------------------------------------------------------------------------------------
 constexpr int kCastThreads = 256;
 constexpr int kCastVec = 8;                               // floats per 32-byte piece
-constexpr int kCastPieces = 4;                            // pieces per thread, 2048 elements apart
-constexpr int kChunk = kCastThreads * kCastVec * kCastPieces;  // 8192 elements
+constexpr int kCastPieces = 8;                            // pieces per thread, 2048 elements apart
+constexpr int kChunk = kCastThreads * kCastVec * kCastPieces;  // 16384 elements: 64 KiB in, 32 KiB out
 
+// Every thread converts its pieces as soon as they are loaded and keeps only the packed results
+// (32 registers for eight pieces): the conversion needs the data, so when the CTA's barrier is
+// passed every load of the chunk has completed, and "chunk read" can be published with a gpu-scope
+// release. The chunk whose bytes are about to be overwritten (c / 2) was claimed long before this
+// one except at the very start, so the acquire load of its flag almost never waits.
 __global__ void __launch_bounds__(kCastThreads) inplace_cast_kernel(
     float* data, int64_t n, uint32_t* flags, uint32_t* claim, uint32_t epoch, uint64_t timeout_ns,
     Status* status) {
@@ -44,41 +49,64 @@ __global__ void __launch_bounds__(kCastThreads) inplace_cast_kernel(
     __syncthreads();
     const uint32_t c = chunk_slot;
     if (c >= chunks) break;
-    float v[kCastPieces][kCastVec];
+    uint4 o[kCastPieces];
+    float4 a[kCastPieces], b[kCastPieces];
+    const int64_t cbase = static_cast<int64_t>(c) * kChunk;
+    const bool whole = cbase + kChunk <= n;
+    if (whole) {
 #pragma unroll
-    for (int p = 0; p < kCastPieces; ++p) {
-      const int64_t base = static_cast<int64_t>(c) * kChunk + (p * kCastThreads + threadIdx.x) * kCastVec;
-      if (base + kCastVec <= n) {
-        const float4 a = *reinterpret_cast<const float4*>(data + base);
-        const float4 b = *reinterpret_cast<const float4*>(data + base + 4);
-        v[p][0] = a.x; v[p][1] = a.y; v[p][2] = a.z; v[p][3] = a.w;
-        v[p][4] = b.x; v[p][5] = b.y; v[p][6] = b.z; v[p][7] = b.w;
-      } else {
+      for (int p = 0; p < kCastPieces; ++p) {
+        const int64_t base = cbase + (p * kCastThreads + threadIdx.x) * kCastVec;
+        a[p] = *reinterpret_cast<const float4*>(data + base);
+        b[p] = *reinterpret_cast<const float4*>(data + base + 4);
+      }
+    } else {
 #pragma unroll
-        for (int j = 0; j < kCastVec; ++j) v[p][j] = base + j < n ? data[base + j] : 0.f;
+      for (int p = 0; p < kCastPieces; ++p) {
+        const int64_t base = cbase + (p * kCastThreads + threadIdx.x) * kCastVec;
+        float t[kCastVec];
+#pragma unroll
+        for (int j = 0; j < kCastVec; ++j) t[j] = base + j < n ? data[base + j] : 0.f;
+        a[p] = make_float4(t[0], t[1], t[2], t[3]);
+        b[p] = make_float4(t[4], t[5], t[6], t[7]);
       }
     }
-    __syncthreads();  // every thread of the CTA holds its part of chunk c in registers
-    if (threadIdx.x == 0) {
-      __threadfence();
-      ptx::st_release_sys(flags + c, epoch);
-      flag_wait_ge(wc, flags + (c >> 1), epoch, kSiteInplaceCast);
-    }
-    __syncthreads();
 #pragma unroll
     for (int p = 0; p < kCastPieces; ++p) {
-      const int64_t base = static_cast<int64_t>(c) * kChunk + (p * kCastThreads + threadIdx.x) * kCastVec;
-      if (base + kCastVec <= n) {
-        uint4 o;
-        o.x = ptx::pack_bf16x2(v[p][0], v[p][1]);
-        o.y = ptx::pack_bf16x2(v[p][2], v[p][3]);
-        o.z = ptx::pack_bf16x2(v[p][4], v[p][5]);
-        o.w = ptx::pack_bf16x2(v[p][6], v[p][7]);
-        *reinterpret_cast<uint4*>(out + base) = o;
-      } else {
+      o[p].x = ptx::pack_bf16x2(a[p].x, a[p].y);
+      o[p].y = ptx::pack_bf16x2(a[p].z, a[p].w);
+      o[p].z = ptx::pack_bf16x2(b[p].x, b[p].y);
+      o[p].w = ptx::pack_bf16x2(b[p].z, b[p].w);
+    }
+    __syncthreads();  // every thread of the CTA has consumed its part of chunk c
+    if (threadIdx.x == 0) {
+      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flags + c), "r"(epoch) : "memory");
+      // bounded wait on the chunk whose bytes this one overwrites
+      const uint32_t* f = flags + (c >> 1);
+      const uint64_t t0 = ptx::globaltimer_ns();
+      uint32_t spins = 0;
+      while (static_cast<int32_t>(ptx::ld_acquire_gpu(f) - epoch) < 0) {
+        if ((++spins & 31u) == 0u && ptx::globaltimer_ns() - t0 > timeout_ns) {
+          wait_give_up(wc, kSiteInplaceCast, *f, epoch);
+          break;
+        }
+      }
+    }
+    __syncthreads();
+    if (abort_word) break;   // the wait gave up: write nothing more
+    if (whole) {
+#pragma unroll
+      for (int p = 0; p < kCastPieces; ++p)
+        *reinterpret_cast<uint4*>(out + cbase + (p * kCastThreads + threadIdx.x) * kCastVec) = o[p];
+    } else {
+#pragma unroll
+      for (int p = 0; p < kCastPieces; ++p) {
+        const int64_t base = cbase + (p * kCastThreads + threadIdx.x) * kCastVec;
+        const uint32_t w[4] = {o[p].x, o[p].y, o[p].z, o[p].w};
 #pragma unroll
         for (int j = 0; j < kCastVec; ++j)
-          if (base + j < n) out[base + j] = __float2bfloat16_rn(v[p][j]);
+          if (base + j < n)
+            reinterpret_cast<uint16_t*>(out)[base + j] = static_cast<uint16_t>(w[j >> 1] >> (16 * (j & 1)));
       }
     }
   }

@@ -43,7 +43,9 @@ typedef struct {
   int32_t M, N, K;
   int32_t in_dtype;          /* FLUXB_BF16 | FLUXB_FP16 | FLUXB_FP8_E4M3 | FLUXB_FP8_E5M2 | FLUXB_INT8 (signed) */
   int32_t out_dtype;         /* FLUXB_BF16 | FLUXB_FP16 (also the dtype of bias and rs_stage) */
-  const float* scale_a;      /* optional device scalars: D = (A*B^T) * scale_a * scale_b */
+  const float* scale_a;      /* optional device scales: D = (A*B^T) * scale_a * scale_b; one float each, or - see
+                                scale_flags - scale_a one float per row of the whole problem ([M], the int8
+                                convention of the reference) and scale_b one float per column ([N]) */
   const float* scale_b;
   int32_t mode, rank, world;
   int32_t group_m;           /* 0 = default raster group */
@@ -52,7 +54,7 @@ typedef struct {
   int32_t act;               /* epilogue activation after bias: 0 none, 1 gelu(tanh), 2 relu, 3 silu */
   int32_t cta_group;         /* 0 = auto, 1 = one CTA per 128-row tile, 2 = CTA pair per 256-row tile */
   uint32_t epoch;            /* call number of the owning op, starting at 1 */
-  uint32_t reserved;
+  uint32_t scale_flags;      /* bit 0: scale_a is a vector [M]; bit 1: scale_b is a vector [N] */
   uint64_t timeout_ns;       /* 0 = default (2 s) */
   fluxb_status_t* status;    /* device memory, may be null */
   void* ag_land[FLUXB_MAX_RANKS];
@@ -266,6 +268,33 @@ typedef struct {
 } fluxb_ep_dispatch_args_t;
 
 int fluxb_ep_dispatch(const fluxb_ep_dispatch_args_t* args);
+/* ---- strided exchange: stand-alone all-to-all (+ transpose) over peer memory ----
+ * copy[d][g], g < ncopies: n0 x n1 x n2 items of vec_bytes contiguous bytes; item (i0, i1, i2) is
+ * read at src + i0*ss0 + i1*ss1 + i2*ss2 (local memory) and written at dst + i0*ds0 + i1*ds1 + i2*ds2
+ * (rank d's buffer). All addresses, strides and vec_bytes are multiples of 16 bytes. The kernel
+ * returns when the data of every source has landed in this rank's buffers. flags[r]: world uint32 on
+ * rank r, local_cnt: world uint32, both zero at first use. */
+typedef struct {
+  const void* src;
+  void* dst;
+  int32_t n0, n1, n2, vec_bytes;
+  int64_t ss0, ss1, ss2, ds0, ds1, ds2;
+} fluxb_strided_copy_t;
+
+typedef struct {
+  fluxb_strided_copy_t copy[FLUXB_MAX_RANKS][3];
+  int32_t ncopies, num_ctas;
+  int32_t rank, world;
+  uint32_t epoch, reserved;
+  uint64_t timeout_ns;
+  fluxb_status_t* status;
+  uint32_t* flags[FLUXB_MAX_RANKS];
+  uint32_t* start_ctr[FLUXB_MAX_RANKS];
+  uint32_t* local_cnt;
+  void* stream;
+} fluxb_strided_exchange_args_t;
+
+int fluxb_strided_exchange(const fluxb_strided_exchange_args_t* args);
 /* *flag = value with system-scope release, stream ordered (flag may be peer memory) */
 int fluxb_set_flag(uint32_t* flag, uint32_t value, void* stream);
 

@@ -108,6 +108,87 @@ __global__ void __launch_bounds__(256) a2a_rows_kernel(const __grid_constant__ A
   (void)lane;
 }
 
+// ---- strided exchange: the stand-alone all-to-all (+ transpose) of the Ulysses ops ------------
+// For every destination rank up to kMaxCopies copy descriptors: a 3-D grid of items of `vec_bytes`
+// contiguous bytes, each with its own byte strides on the source (local) and the destination (that
+// rank's buffer) side. One kernel covers seq->heads, heads->seq, packed q/k/v with grouped heads
+// and per-rank sequence lengths: only the descriptors differ.
+// Reference: src/gemm_a2a_transpose/pre_attn_a2a_transpose_impls.cu,
+// pre_attn_qkv_pack_a2a_impls.cu (pull kernels) and src/a2a_transpose_gemm/
+// post_attn_a2a_transpose_impls.cu (push kernels, fixed and dynamic sequence lengths).
+constexpr int kMaxCopies = 3;
+
+struct StridedCopy {
+  const uint8_t* src;
+  uint8_t* dst;
+  int32_t n0, n1, n2, vec_bytes;      // vec_bytes: multiple of 16
+  int64_t ss0, ss1, ss2, ds0, ds1, ds2;
+};
+
+struct ExchangeParams {
+  StridedCopy copy[kR][kMaxCopies];   // [destination][group]
+  int32_t ncopies;
+  int32_t rank, world;
+  uint32_t epoch;
+  uint64_t timeout_ns;
+  Status* status;
+  uint32_t* flags[kR];                // on every rank: [W src] last call whose data has landed
+  uint32_t* start_ctr[kR];
+  uint32_t* local_cnt;                // [W]
+};
+
+__global__ void __launch_bounds__(256) strided_exchange_kernel(const __grid_constant__ ExchangeParams p) {
+  __shared__ uint32_t abort_word;
+  if (threadIdx.x == 0) abort_word = 0;
+  __syncthreads();
+  WaitCtx wc{p.status, &abort_word, p.timeout_ns};
+  const int W = p.world;
+  // nobody writes into a peer before that peer has entered this call
+  if (blockIdx.x == 0 && threadIdx.x < W) ptx::st_release_sys(p.start_ctr[threadIdx.x] + p.rank, p.epoch);
+  if (threadIdx.x < W) flag_wait_ge(wc, p.start_ctr[p.rank] + threadIdx.x, p.epoch, kSiteStartBarrier);
+  __syncthreads();
+  for (int step = 1; step <= W; ++step) {     // nearest peer first, the own part last
+    int d = p.rank + step;
+    if (d >= W) d -= W;
+    for (int g = 0; g < p.ncopies; ++g) {
+      const StridedCopy& c = p.copy[d][g];
+      const int64_t per_item = c.vec_bytes >> 4;
+      const int64_t n = static_cast<int64_t>(c.n0) * c.n1 * c.n2 * per_item;
+      constexpr int kU = 4;
+      for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 * kU + threadIdx.x; i < n;
+           i += static_cast<int64_t>(gridDim.x) * 256 * kU) {
+        uint4 v[kU];
+        int64_t doff[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const int64_t j = i + u * 256;
+          if (j < n) {
+            const int64_t item = j / per_item, piece = j - item * per_item;
+            const int64_t i2 = item % c.n2, r = item / c.n2;
+            const int64_t i1 = r % c.n1, i0 = r / c.n1;
+            v[u] = ptx::ld_global_v4(c.src + i0 * c.ss0 + i1 * c.ss1 + i2 * c.ss2 + piece * 16);
+            doff[u] = i0 * c.ds0 + i1 * c.ds1 + i2 * c.ds2 + piece * 16;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u)
+          if (i + u * 256 < n) ptx::st_global_v4(c.dst + doff[u], v[u]);
+      }
+    }
+    ptx::fence_acq_rel_sys();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t* cnt = p.local_cnt + (step % W);
+      if (ptx::atom_add_acq_rel_sys(cnt, 1u) == gridDim.x - 1u) {
+        *cnt = 0;
+        ptx::st_release_sys(p.flags[d] + p.rank, p.epoch);
+      }
+    }
+  }
+  if (threadIdx.x < W) flag_wait_ge(wc, p.flags[p.rank] + threadIdx.x, p.epoch, kSiteA2AFlag);
+  __syncthreads();
+}
+
 __global__ void set_flag_kernel(uint32_t* flag, uint32_t value) {
   __threadfence_system();
   ptx::st_release_sys(flag, value);
@@ -151,6 +232,49 @@ extern "C" int fluxb_a2a_rows(const fluxb_a2a_rows_args_t* a) {
   int grid = a->num_ctas > 0 ? a->num_ctas : 128;
   if (grid > sms) grid = sms;  // all CTAs must be resident: they count arrivals together
   a2a_rows_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(a->stream)>>>(p);
+  FLUXB_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return kOk;
+}
+
+extern "C" int fluxb_strided_exchange(const fluxb_strided_exchange_args_t* a) {
+  FLUXB_REQUIRE(a != nullptr && a->local_cnt != nullptr, "exchange arguments");
+  FLUXB_REQUIRE(a->world >= 1 && a->world <= kR && a->rank >= 0 && a->rank < a->world, "ranks");
+  FLUXB_REQUIRE(a->ncopies >= 1 && a->ncopies <= kMaxCopies, "1..3 copies per destination");
+  ExchangeParams p;
+  memset(&p, 0, sizeof(p));
+  p.ncopies = a->ncopies;
+  p.rank = a->rank;
+  p.world = a->world;
+  p.epoch = a->epoch;
+  p.timeout_ns = a->timeout_ns ? a->timeout_ns : 5000000000ull;
+  p.status = reinterpret_cast<Status*>(a->status);
+  p.local_cnt = a->local_cnt;
+  for (int r = 0; r < a->world; ++r) {
+    FLUXB_REQUIRE(a->flags[r] && a->start_ctr[r], "peer pointers missing");
+    p.flags[r] = a->flags[r];
+    p.start_ctr[r] = a->start_ctr[r];
+    for (int g = 0; g < a->ncopies; ++g) {
+      const fluxb_strided_copy_t& c = a->copy[r][g];
+      const bool empty = c.n0 == 0 || c.n1 == 0 || c.n2 == 0;
+      FLUXB_REQUIRE(empty || (c.src && c.dst), "copy pointers missing");
+      FLUXB_REQUIRE(c.n0 >= 0 && c.n1 >= 0 && c.n2 >= 0 && c.vec_bytes > 0 && c.vec_bytes % 16 == 0,
+                    "copy extents / item size (multiple of 16 bytes)");
+      FLUXB_REQUIRE(((reinterpret_cast<uintptr_t>(c.src) | reinterpret_cast<uintptr_t>(c.dst) | c.ss0 | c.ss1 |
+                      c.ss2 | c.ds0 | c.ds1 | c.ds2) & 15) == 0,
+                    "copy addresses and strides must be multiples of 16 bytes");
+      StridedCopy& o = p.copy[r][g];
+      o.src = reinterpret_cast<const uint8_t*>(c.src);
+      o.dst = reinterpret_cast<uint8_t*>(c.dst);
+      o.n0 = c.n0; o.n1 = c.n1; o.n2 = c.n2; o.vec_bytes = c.vec_bytes;
+      o.ss0 = c.ss0; o.ss1 = c.ss1; o.ss2 = c.ss2; o.ds0 = c.ds0; o.ds1 = c.ds1; o.ds2 = c.ds2;
+    }
+  }
+  int sms = 0, rc;
+  if ((rc = device_sm_count(&sms))) return rc;
+  int grid = a->num_ctas > 0 ? a->num_ctas : 96;
+  if (grid > sms) grid = sms;  // all CTAs must be resident: they count arrivals together
+  strided_exchange_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(a->stream)>>>(p);
   FLUXB_CUDA_OK(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return kOk;

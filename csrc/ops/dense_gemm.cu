@@ -198,6 +198,9 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   p.bias_row_stride = a->bias_row_stride;
   p.scale_a = a->scale_a;
   p.scale_b = a->scale_b;
+  p.scale_flags = a->scale_flags & 3u;
+  FLUXB_REQUIRE(!(a->scale_flags & 1u) || a->scale_a, "per-row scale vector missing");
+  FLUXB_REQUIRE(!(a->scale_flags & 2u) || a->scale_b, "per-column scale vector missing");
   p.sa = a->sa;
   p.sb = a->sb;
   p.ab_fmt = (a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP8_E5M2 || a->in_dtype == FLUXB_INT8) ? 1 : 0;

@@ -85,7 +85,7 @@ struct DenseGemmParams {
   int32_t l2_hints;              // 1: A tiles are loaded evict_last (the band is reused by the next waves),
                                  // B tiles evict_first (streamed once per wave)
   uint32_t epoch;                // call number of the owning op object, starts at 1
-  uint32_t reserved0;
+  uint32_t scale_flags;          // bit 0: scale_a holds one float per row of the problem, bit 1: scale_b one per column
   uint64_t timeout_ns;
   Status* status;
   uint64_t* trace;               // optional [gridDim.x][kTraceWords] globaltimer stamps (ns), see kTrace*
@@ -922,9 +922,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     const uint32_t my_epi_u32 = epi_base + ew * Cfg::EPI_BUFS * Cfg::EPI_BUF_BYTES;
     const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.bias);
     const bool f16 = p.out_f16 != 0;
+    const bool sa_vec = (p.scale_flags & 1u) != 0u, sb_vec = (p.scale_flags & 2u) != 0u;
     float alpha = 1.f;
-    if (p.scale_a != nullptr) alpha *= *p.scale_a;
-    if (p.scale_b != nullptr) alpha *= *p.scale_b;
+    if (p.scale_a != nullptr && !sa_vec) alpha *= *p.scale_a;
+    if (p.scale_b != nullptr && !sb_vec) alpha *= *p.scale_b;
     const bool scaled = p.scale_a != nullptr || p.scale_b != nullptr;
     int it = 0;
     uint32_t nstore = 0;
@@ -992,10 +993,23 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         }
       }
       if (scaled) {
+        // per-tensor scales, or one scale per row (A) / per column (B)
+        float ar = alpha;
+        if (sa_vec) ar *= row < p.seg_rows ? p.scale_a[grow] : 0.f;
+        if (sb_vec) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          r0[j] = __float_as_uint(__uint_as_float(r0[j]) * alpha);
-          r1[j] = __float_as_uint(__uint_as_float(r1[j]) * alpha);
+          for (int j = 0; j < 32; ++j) {
+            const float b0 = col0 + j < p.N ? p.scale_b[col0 + j] : 0.f;
+            const float b1 = col0 + 32 + j < p.N ? p.scale_b[col0 + 32 + j] : 0.f;
+            r0[j] = __float_as_uint(__uint_as_float(r0[j]) * (ar * b0));
+            r1[j] = __float_as_uint(__uint_as_float(r1[j]) * (ar * b1));
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            r0[j] = __float_as_uint(__uint_as_float(r0[j]) * ar);
+            r1[j] = __float_as_uint(__uint_as_float(r1[j]) * ar);
+          }
         }
       }
       if (bias != nullptr && col0 < p.N) {

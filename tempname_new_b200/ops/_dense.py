@@ -28,7 +28,7 @@ class DenseArgs(ctypes.Structure):
         ("mode", ctypes.c_int32), ("rank", ctypes.c_int32), ("world", ctypes.c_int32),
         ("group_m", ctypes.c_int32), ("num_sms", ctypes.c_int32), ("tile_n", ctypes.c_int32),
         ("act", ctypes.c_int32), ("cta_group", ctypes.c_int32),
-        ("epoch", ctypes.c_uint32), ("reserved", ctypes.c_uint32),
+        ("epoch", ctypes.c_uint32), ("scale_flags", ctypes.c_uint32),
         ("timeout_ns", ctypes.c_uint64),
         ("status", _VP),
         ("ag_land", _VP * MAX_RANKS), ("ag_flags", _VP * MAX_RANKS),
@@ -74,12 +74,24 @@ def run(args: DenseArgs) -> None:
     _native.check(rc, "fluxb_dense_gemm")
 
 
+def check_scale(t: Optional[torch.Tensor], n_vec: int, what: str) -> bool:
+    """A dequantisation scale is one number (per tensor) or one number per row of the input /
+    per output column (the reference's int8 convention: input_scale [M, 1], weight_scale [1, N],
+    python/flux/cpp_mod.pyi:352-353). Returns True for the vector form; anything else is refused
+    rather than silently reduced to its first element."""
+    if t is None or t.numel() == 1:
+        return False
+    if t.numel() == n_vec and max(t.shape) == n_vec:
+        return True
+    raise ValueError(f"{what} must hold 1 or {n_vec} values, got shape {tuple(t.shape)}")
+
+
 def _as_scale(t: Optional[torch.Tensor], dev) -> Optional[torch.Tensor]:
     if t is None:
         return None
     if t.dtype != torch.float32 or t.device != dev:
         t = t.to(device=dev, dtype=torch.float32)
-    return t.reshape(-1)[:1].contiguous()
+    return t.reshape(-1).contiguous()
 
 
 _TIMELINE: Optional[torch.Tensor] = None
@@ -158,11 +170,15 @@ def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], ou
             raise ValueError("bias must be [1|M, N] in the output dtype")
         args.bias = bias.data_ptr()
         args.bias_row_stride = 0 if (bias.dim() == 1 or bias.shape[0] == 1) else bias.stride(0)
+    # per-row scales cover the rows of the whole problem (m), per-column scales the N outputs
+    sa_vec = check_scale(scale_a, m if m is not None else a.shape[0], "input_scale")
+    sb_vec = check_scale(scale_b, b.shape[0], "weight_scale")
     sa, sb = _as_scale(scale_a, a.device), _as_scale(scale_b, a.device)
     if sa is not None:
         args.scale_a = sa.data_ptr()
     if sb is not None:
         args.scale_b = sb.data_ptr()
+    args.scale_flags = (1 if sa_vec else 0) | (2 if sb_vec else 0)
     if keep is not None:
         keep.extend([sa, sb])
     if tile_n == 0 and cta_group == 0 and m is not None:

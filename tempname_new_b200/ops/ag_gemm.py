@@ -75,6 +75,10 @@ class AGKernel(FusedOpBase):
                 for r in range(self.world):
                     args.ag_scale_land[r] = self.scale_land.ptr(r)
         else:
+            if input_scale is not None and input_scale.numel() > 1:
+                # one scale per input row ([M/W, 1], the reference's int8 convention): the GEMM needs
+                # the scales of all M rows, so they are gathered too (a small launch of the row-exchange kernel)
+                input_scale = self._gather_row_scales(input_scale, seg)
             args = _dense.base_args(a, w, bias, self.output_dtype, input_scale, weight_scale,
                                     act=act, m=M, status=self.status, keep=keep)
         args.M = M
@@ -96,6 +100,26 @@ class AGKernel(FusedOpBase):
         return out
 
     __call__ = forward
+
+    def _gather_row_scales(self, scale: torch.Tensor, seg: int) -> torch.Tensor:
+        """[M/W] per-row scales of every rank -> [M] in rank order."""
+        if scale.numel() != seg:
+            raise ValueError(f"input_scale must hold 1 or {seg} (rows of this rank's shard) values")
+        s = scale.reshape(-1).float().contiguous()
+        if self.world == 1:
+            return s
+        if not s.is_cuda:
+            parts = [torch.empty_like(s) for _ in range(self.world)]
+            torch.distributed.all_gather(parts, s, group=self.pg)
+            return torch.cat(parts)
+        from .coll import AllGatherOp
+        rows = (seg + 3) // 4                       # rows of four floats (16 bytes)
+        if getattr(self, "_scale_ag", None) is None or self._scale_ag.max_rows < rows * self.world:
+            self._scale_ag = AllGatherOp(self.pg, 1, rows * self.world, 4, torch.float32)
+        padded = torch.zeros(rows * 4, dtype=torch.float32, device=s.device)
+        padded[:seg] = s
+        got = self._scale_ag.run(padded.view(rows, 4)).reshape(self.world, rows * 4)
+        return got[:, :seg].reshape(-1).contiguous()
 
     def _copy_gathered(self, a, gathered_input, seg, K):
         if self.world == 1:
@@ -121,8 +145,12 @@ class AGKernel(FusedOpBase):
                   output_scale=None, fast_accum=False, transpose_weight=False, all_gather_option=None,
                   gathered_input=None, prof_ctx=None):
         from ..tuning.profiling import profile_call
+        w = as_nk(weight, transpose_weight)
+        blockscaled = input_scale is not None and input_scale.dim() == 3     # fixed tile shape: nothing to sweep
+        key = None if blockscaled else (input.shape[0] * self.world, w.shape[0], input.shape[1])
         return profile_call(self, "ag_gemm", lambda: self.forward(
-            input, weight, bias, output, input_scale, weight_scale, transpose_weight=transpose_weight), prof_ctx)
+            input, weight, bias, output, input_scale, weight_scale, transpose_weight=transpose_weight), prof_ctx,
+            key=key, segmented_rows=input.shape[0])
 
     def _forward_cpu(self, a, w, bias, output, sa, sb, gathered_input, act=None):
         W, r = self.world, self.rank
@@ -143,9 +171,12 @@ class AGKernel(FusedOpBase):
             full = a
         acc = full.float() @ w.float().t()
         if sa is not None:
+            if sa.numel() > 1:
+                sa = self._gather_row_scales(sa, seg).reshape(-1, 1)
             acc = acc * sa.float()
         if sb is not None:
-            acc = acc * sb.float()
+            _dense.check_scale(sb, w.shape[0], "weight_scale")
+            acc = acc * (sb.float().reshape(1, -1) if sb.numel() > 1 else sb.float())
         if bias is not None:
             acc = acc + bias.float()
         acc = apply_act(acc, act)

@@ -70,9 +70,11 @@ class GemmOnly:
     def _forward_cpu(self, a, w, bias, out, sa, sb):
         acc = a.float() @ w.float().t()
         if sa is not None:
-            acc = acc * sa.float()
+            vec = _dense.check_scale(sa, a.shape[0], "input_scale")
+            acc = acc * (sa.float().reshape(-1, 1) if vec else sa.float().reshape(-1)[0])
         if sb is not None:
-            acc = acc * sb.float()
+            vec = _dense.check_scale(sb, w.shape[0], "weight_scale")
+            acc = acc * (sb.float().reshape(1, -1) if vec else sb.float().reshape(-1)[0])
         if bias is not None:
             acc = acc + bias.float()
         res = acc.to(self.output_dtype)

@@ -105,8 +105,11 @@ class GemmRS(FusedOpBase):
     def profiling(self, input, weight, bias=None, input_scale=None, weight_scale=None, output_scale=None,
                   fast_accum=False, reduce_scatter_option=None, prof_ctx=None):
         from ..tuning.profiling import profile_call
+        w = as_nk(weight, self.transpose_weight)
+        blockscaled = input_scale is not None and input_scale.dim() == 3
+        key = None if blockscaled else (input.shape[0], w.shape[0], input.shape[1])
         return profile_call(self, "gemm_rs", lambda: self.forward(input, weight, bias, input_scale, weight_scale),
-                            prof_ctx)
+                            prof_ctx, key=key, segmented_rows=input.shape[0] // self.world)
 
     # ------------------------------------------------------------------------------------
     def _forward_cpu(self, a, w, bias, sa, sb):
@@ -117,9 +120,11 @@ class GemmRS(FusedOpBase):
         seg = M // W
         part = a.float() @ w.float().t()
         if sa is not None:
-            part = part * sa.float()
+            vec = _dense.check_scale(sa, a.shape[0], "input_scale")
+            part = part * (sa.float().reshape(-1, 1) if vec else sa.float().reshape(-1)[0])
         if sb is not None:
-            part = part * sb.float()
+            vec = _dense.check_scale(sb, w.shape[0], "weight_scale")
+            part = part * (sb.float().reshape(1, -1) if vec else sb.float().reshape(-1)[0])
         if bias is not None:
             part = part + bias.float()
         part = part.to(self.output_dtype)

@@ -25,6 +25,7 @@ test oracle).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional, Sequence, Union
 
 import torch
@@ -73,6 +74,11 @@ class MoeCombineArgs(ctypes.Structure):
         ("stage", _VP * _R), ("flags", _VP * _R), ("start_ctr", _VP * _R),
         ("local_cnt", _VP), ("out", _VP), ("stream", _VP),
     ]
+
+
+def _out16(dt: torch.dtype) -> torch.dtype:
+    """Output dtype of the grouped kernel: the 16-bit input dtype, bf16 for 8-bit inputs."""
+    return dt if dt in (torch.bfloat16, torch.float16) else torch.bfloat16
 
 
 def _f32(t: Optional[torch.Tensor], dev) -> Optional[torch.Tensor]:
@@ -161,6 +167,7 @@ class GemmGroupedV3AGScatter(FusedOpBase):
         self._scratch = None
         self._gather = None
         self._sorted = None
+        self._sorted_complete = False
 
     def clear_buffers(self) -> None:
         """Kept for API compatibility: flags carry the call number, nothing needs clearing."""
@@ -213,6 +220,12 @@ class GemmGroupedV3AGScatter(FusedOpBase):
             a.in_dtype = _dense.dtype_code(x.dtype)
             a.N, a.K = N, H
             a.weights, a.d, a.ldd = w.data_ptr(), out.data_ptr(), out.stride(0)
+            # Weight groups after the first (gate | up | ...) multiply the same rows: the first
+            # launch left them, gathered and expert-sorted, in the sorted buffer, so the others
+            # are plain grouped GEMMs on that buffer - no second all-gather, index build or gather
+            # (reference: forward_multiple_weights runs one gathered A against all groups,
+            # src/moe_ag_scatter/ths_op/gemm_grouped_v3_ag_scatter.cc:461-470)
+            reuse_sorted = g > 0 and self._sorted_complete
             sc = _f32(output_scale[g], dev) if output_scale is not None and output_scale[g] is not None else None
             keep.append(sc)
             a.expert_scale = sc.data_ptr() if sc is not None else None
@@ -226,6 +239,13 @@ class GemmGroupedV3AGScatter(FusedOpBase):
                 self._sorted = torch.empty((max(rows_cap, 128), H), dtype=x.dtype, device=dev)
             a.a_sorted, a.a_sorted_rows = self._sorted.data_ptr(), self._sorted.shape[0]
             a.local_cnt = self.ctrl.ptr(self.rank, OFF_LOCAL)
+            if reuse_sorted:
+                a.gathered = 0
+                a.a, a.a_rows = self._sorted.data_ptr(), self._sorted.shape[0]
+                a.scatter_index = a.gather_index = a.a_sorted = None
+                _native.check(_native.lib().fluxb_moe_grouped_gemm(ctypes.byref(a)), "fluxb_moe_grouped_gemm")
+                outs.append(out)
+                continue
             self._begin_call()
             a.epoch = self.epoch
             if self.world > 1:
@@ -240,6 +260,8 @@ class GemmGroupedV3AGScatter(FusedOpBase):
             else:
                 a.a_tokens = x.data_ptr()
             _native.check(_native.lib().fluxb_moe_grouped_gemm(ctypes.byref(a)), "fluxb_moe_grouped_gemm")
+            # (the in-loader gather variants selected by FLUXB_MOE_GATHER do not fill the sorted buffer)
+            self._sorted_complete = os.environ.get("FLUXB_MOE_GATHER", "") in ("", "pregather")
             outs.append(out)
         if allgather_output is not None:
             if self.world > 1:
@@ -344,7 +366,7 @@ class GemmGroupedV3GatherRS(FusedOpBase):
             if w.dim() != 3 or w.shape[0] != self.E_local or w.shape[1] != self.H or not w.is_contiguous():
                 raise ValueError("weights must be contiguous [E_local, n_dim, ffn]")
             x = x if x.is_contiguous() else x.contiguous()
-            yg = torch.empty((max(rows_ep, 1), self.H), dtype=x.dtype, device=dev)
+            yg = torch.empty((max(rows_ep, 1), self.H), dtype=_out16(x.dtype), device=dev)
             a = MoeGemmArgs()
             a.splits = splits.data_ptr()
             a.E, a.e0, a.E_local, a.topk = self.E, self.e0, self.E_local, self.topk
@@ -366,7 +388,7 @@ class GemmGroupedV3GatherRS(FusedOpBase):
             a.stream = _dense.current_stream_ptr(dev)
             _native.check(_native.lib().fluxb_moe_grouped_gemm(ctypes.byref(a)), "fluxb_moe_grouped_gemm")
             y = yg if y is None else y.add_(yg)
-        out = torch.empty((tpr, self.H), dtype=x0.dtype, device=dev)
+        out = torch.empty((tpr, self.H), dtype=y.dtype, device=dev)
         self._combine(y, ridx, tpr, out)
         self._after_launch()
         return out
@@ -381,7 +403,7 @@ class GemmGroupedV3GatherRS(FusedOpBase):
         rows_ep = x.shape[0]
         if self._row_entry is None or self._row_entry.numel() < rows_ep:
             self._row_entry = torch.empty(max(rows_ep, self.max_m // max(self.world, 1)), dtype=torch.int32, device=dev)
-        out = torch.empty((tpr, self.H), dtype=x.dtype, device=dev)
+        out = torch.empty((tpr, self.H), dtype=_out16(x.dtype), device=dev)
         self._begin_call()
         a = MoeGemmArgs()
         a.splits = splits.data_ptr()
@@ -501,7 +523,7 @@ class GemmGroupedV3:
             self._status = torch.zeros(4, dtype=torch.int32, device=dev)
         splits = splits_cpu.to(device=dev, dtype=torch.int32, non_blocking=True).contiguous()
         x = input if input.is_contiguous() else input.contiguous()
-        out = torch.empty((x.shape[0], N), dtype=x.dtype, device=dev)
+        out = torch.empty((x.shape[0], N), dtype=_out16(x.dtype), device=dev)
         a = MoeGemmArgs()
         a.splits = splits.data_ptr()
         a.E, a.e0, a.E_local, a.topk = self.E, 0, self.E, 1

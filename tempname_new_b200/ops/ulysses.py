@@ -5,6 +5,10 @@
   head, already in the head-sharded layout. Reference: ``flux.GemmAllToAllTranspose``
   (``src/pybind/gemm_a2a_transpose.cc:30-140``, ``src/gemm_a2a_transpose/``), which writes a local
   GEMM output, flags tiles and runs a separate pull kernel on carved-out SMs.
+  The stand-alone exchanges (``pre_attn_a2a``, ``pre_attn_qkv_pack_a2a``, ``post_attn_a2a``) and
+  the forms with per-rank sequence lengths run on one strided-exchange kernel over peer memory
+  (``fluxb_strided_exchange``, csrc/ops/a2a.cu) instead of a library collective; with per-rank
+  lengths the projection and the exchange are two launches.
 * ``AllToAllTransposeGemm`` (post-attention): the head-sharded attention output is pushed into
   the peers' GEMM-input buffers by two warps of every CTA while the out-projection GEMM of the
   same kernel walks its K loop one source slice at a time, own slice first. Reference:
@@ -46,6 +50,53 @@ class A2AArgs(ctypes.Structure):
         ("a2a_flags", _VP * _dense.MAX_RANKS),
         ("copy_local", ctypes.c_int32),
     ]
+
+
+class StridedCopy(ctypes.Structure):
+    _fields_ = [
+        ("src", _VP), ("dst", _VP),
+        ("n0", ctypes.c_int32), ("n1", ctypes.c_int32), ("n2", ctypes.c_int32), ("vec_bytes", ctypes.c_int32),
+        ("ss0", ctypes.c_int64), ("ss1", ctypes.c_int64), ("ss2", ctypes.c_int64),
+        ("ds0", ctypes.c_int64), ("ds1", ctypes.c_int64), ("ds2", ctypes.c_int64),
+    ]
+
+
+class ExchangeArgs(ctypes.Structure):
+    _fields_ = [
+        ("copy", (StridedCopy * 3) * _dense.MAX_RANKS),
+        ("ncopies", ctypes.c_int32), ("num_ctas", ctypes.c_int32),
+        ("rank", ctypes.c_int32), ("world", ctypes.c_int32),
+        ("epoch", ctypes.c_uint32), ("reserved", ctypes.c_uint32),
+        ("timeout_ns", ctypes.c_uint64), ("status", _VP),
+        ("flags", _VP * _dense.MAX_RANKS), ("start_ctr", _VP * _dense.MAX_RANKS),
+        ("local_cnt", _VP), ("stream", _VP),
+    ]
+
+
+def _strided_exchange(op: FusedOpBase, copies, device, num_ctas: int = 0) -> None:
+    """One launch of the strided-exchange kernel on ``op``'s control block. ``copies[d]`` is the list
+    (the same length for every d, at most 3) of ``(src_ptr, dst_ptr, (n0, n1, n2), vec_bytes,
+    (ss0, ss1, ss2), (ds0, ds1, ds2))`` for destination rank d; strides in bytes."""
+    op._begin_call()
+    a = ExchangeArgs()
+    a.ncopies = len(copies[0])
+    a.num_ctas = num_ctas if num_ctas > 0 else 0
+    a.rank, a.world, a.epoch = op.rank, op.world, op.epoch
+    a.timeout_ns, a.status = int(op.timeout_s * 1e9), op.status.data_ptr()
+    for d in range(op.world):
+        a.flags[d] = op.ctrl.ptr(d, OFF_CTR)
+        a.start_ctr[d] = op.ctrl.ptr(d, OFF_START)
+        for g, (src, dst, n, vec, ss, ds) in enumerate(copies[d]):
+            c = a.copy[d][g]
+            c.src, c.dst = src, dst
+            c.n0, c.n1, c.n2 = n
+            c.vec_bytes = vec
+            c.ss0, c.ss1, c.ss2 = ss
+            c.ds0, c.ds1, c.ds2 = ds
+    a.local_cnt = op.ctrl.ptr(op.rank, OFF_LOCAL)
+    a.stream = _dense.current_stream_ptr(device)
+    _native.check(_native.lib().fluxb_strided_exchange(ctypes.byref(a)), "fluxb_strided_exchange")
+    op._after_launch()
 
 
 # ------------------------------------------------------------------------------------------
@@ -138,10 +189,33 @@ def post_attn_a2a_varlen_torch(x: torch.Tensor, group, a2a_only: bool, seq_lens:
     return recv.reshape(W, ls, bs, lh, hd).permute(2, 1, 0, 3, 4).reshape(bs, ls, W * lh * hd).contiguous()
 
 
-def _check_sp(sp_size: int, world: int) -> None:
-    if sp_size != world:
-        raise NotImplementedError("sp_size must equal the size of the process group that is passed in; "
-                                  "build a sub-group for a smaller sequence-parallel degree")
+_SP_GROUPS = {}
+
+
+def _sp_group(tp_group, sp_size: int):
+    """The sequence-parallel group of this rank: ``tp_group`` itself when ``sp_size`` is its size,
+    else the block of ``sp_size`` consecutive ranks of ``tp_group`` that contains this rank
+    (reference: ``sp_size`` smaller than the group, src/gemm_a2a_transpose/ths_op/
+    gemm_all2all_transpose.cc:145-160). Sub-groups are created once per (group, sp_size); creating
+    them is a collective over all processes, so every rank must build its ops in the same order."""
+    pg = tp_group if tp_group is not None else dist.group.WORLD
+    world = dist.get_world_size(pg)
+    if sp_size in (0, None) or sp_size == world:
+        return pg
+    if sp_size < 1 or world % sp_size:
+        raise ValueError("sp_size must divide the size of the process group")
+    key = (id(pg), sp_size)
+    if key not in _SP_GROUPS:
+        ranks = dist.get_process_group_ranks(pg)
+        me = dist.get_rank()
+        mine = None
+        for c in range(world // sp_size):
+            block = ranks[c * sp_size:(c + 1) * sp_size]
+            sub = dist.new_group(block)
+            if me in block:
+                mine = sub
+        _SP_GROUPS[key] = mine
+    return _SP_GROUPS[key]
 
 
 class GemmAllToAllTranspose(FusedOpBase):
@@ -150,8 +224,7 @@ class GemmAllToAllTranspose(FusedOpBase):
                  output_dtype: Optional[torch.dtype] = None, transpose_weight: bool = False, gqa: int = 0,
                  comm_op: PreAttnAllToAllCommOp = PreAttnAllToAllCommOp.A2ATranspose,
                  max_num_comm_buf: int = 1, timeout_s: Optional[float] = None):
-        super().__init__(tp_group, nnodes, timeout_s)
-        _check_sp(sp_size, self.world)
+        super().__init__(_sp_group(tp_group, sp_size), nnodes, timeout_s)
         self.bs, self.seq, self.hidden, self.hd, self.n_dim = bs, seq, hidden_dim, head_dim, n_dim
         self.input_dtype = input_dtype
         self.output_dtype = _out_dtype(input_dtype, output_dtype)
@@ -252,9 +325,12 @@ class GemmAllToAllTranspose(FusedOpBase):
             y = y.to(self.output_dtype)
         y = y.reshape(self.bs, ls, self.nh, self.hd)
         W = self.world
-        lq, lk = self.group_heads[0] // W, self.group_heads[1] // W
-        parts = (y[:, :, :lq * W], y[:, :, lq * W:(lq + lk) * W], y[:, :, (lq + lk) * W:])
-        res = [pre_attn_a2a_varlen_torch(t.contiguous(), self.pg, seq_lens) for t in parts]
+        if y.is_cuda:
+            res = self._exchange_cuda(y, seq_lens)
+        else:
+            lq, lk = self.group_heads[0] // W, self.group_heads[1] // W
+            parts = (y[:, :, :lq * W], y[:, :, lq * W:(lq + lk) * W], y[:, :, (lq + lk) * W:])
+            res = [pre_attn_a2a_varlen_torch(t.contiguous(), self.pg, seq_lens) for t in parts]
         if outputs is not None:
             for dst, src in zip(outputs, res):
                 dst.copy_(src)
@@ -270,18 +346,72 @@ class GemmAllToAllTranspose(FusedOpBase):
             return pre_attn_qkv_pack_a2a_torch(y, self.pg, self.bs, self.local_seq, self.nh, self.hd, self.gqa)
         return pre_attn_a2a_torch(y, self.pg, self.bs, self.local_seq, self.nh, self.hd)
 
-    # a2a without the GEMM (input already projected): collective through the process group
-    def pre_attn_a2a(self, input, seq_lens_cpu=None, num_comm_sm: int = -1):
-        return pre_attn_a2a_torch(input, self.pg, self.bs, self.local_seq, self.nh, self.hd)[0]
+    def _exchange_cuda(self, y: torch.Tensor, seq_lens: Optional[List[int]] = None, group_heads=None,
+                       layout: Optional[int] = None, num_ctas: int = 0) -> List[torch.Tensor]:
+        """seq -> heads exchange of y [bs, ls, heads, hd] on the strided-exchange kernel: head group g
+        of rank d's share lands in d's output buffer at this rank's place in the full sequence.
+        Returns views of this rank's outputs, one per head group (valid until the next call)."""
+        W, r = self.world, self.rank
+        lens = seq_lens if seq_lens is not None else [self.local_seq] * W
+        ls, S, off_r = lens[r], sum(lens), sum(lens[:r])
+        if S > self.seq:
+            raise ValueError("the sequence lengths add up to more than the op was built for")
+        groups = group_heads if group_heads is not None else self.group_heads
+        layout = self.layout if layout is None else layout
+        y = y if y.is_contiguous() else y.contiguous()
+        if y.dtype != self.output_dtype:
+            raise TypeError("the exchange moves the op's output dtype")
+        e = y.element_size()
+        nh, hd, bs = y.shape[2], self.hd, self.bs
+        copies = [[] for _ in range(W)]
+        views, g0, boff = [], 0, 0
+        for g, (heads, n) in enumerate(zip(groups, self.out_elems)):
+            lh = heads // W
+            for d in range(W):
+                src = y.data_ptr() + (g0 + d * lh) * hd * e
+                if layout == 0:      # [bs, lh, S, hd]
+                    dst = self.out_buf.ptr(d, boff) + off_r * hd * e
+                    ds = (lh * S * hd * e, hd * e, S * hd * e)
+                else:                # [bs, S, lh, hd]
+                    dst = self.out_buf.ptr(d, boff) + off_r * lh * hd * e
+                    ds = (S * lh * hd * e, lh * hd * e, hd * e)
+                copies[d].append((src, dst, (bs, ls, lh), hd * e, (ls * nh * hd * e, nh * hd * e, hd * e), ds))
+            shape = (bs, lh, S, hd) if layout == 0 else (bs, S, lh, hd)
+            views.append(self.out_buf.view(r, self.output_dtype, shape, boff))
+            g0 += heads
+            boff += n * _ELEM[self.output_dtype]
+        _strided_exchange(self, copies, y.device, num_ctas)
+        return views
 
-    def pre_attn_qkv_pack_a2a(self, qkv, seq_lens_cpu=None, num_comm_sm: int = -1):
-        return pre_attn_qkv_pack_a2a_torch(qkv, self.pg, self.bs, self.local_seq, self.nh, self.hd, self.gqa)
+    # a2a without the GEMM (input already projected)
+    def pre_attn_a2a(self, input, seq_lens_cpu=None, num_comm_sm: int = -1, copy_out: bool = True):
+        """input [bs, seq/W, heads, hd] (or [bs * seq/W, heads * hd]) -> [bs, heads/W, seq, hd]."""
+        if not input.is_cuda:
+            return pre_attn_a2a_torch(input, self.pg, self.bs, self.local_seq, self.nh, self.hd)[0]
+        lens = _seq_lens_list(seq_lens_cpu, self.world) if seq_lens_cpu is not None else None
+        ls = lens[self.rank] if lens is not None else self.local_seq
+        out = self._exchange_cuda(input.reshape(self.bs, ls, self.nh, self.hd), lens, [self.nh], 0,
+                                  max(num_comm_sm, 0))[0]
+        return out.clone() if copy_out else out
+
+    def pre_attn_qkv_pack_a2a(self, qkv, seq_lens_cpu=None, num_comm_sm: int = -1, copy_out: bool = True):
+        """qkv [bs, seq/W, heads, hd] with the heads packed q | k | v -> [q, k, v], each
+        [bs, seq, heads_x/W, hd]."""
+        if not qkv.is_cuda:
+            return pre_attn_qkv_pack_a2a_torch(qkv, self.pg, self.bs, self.local_seq, self.nh, self.hd, self.gqa)
+        if self.comm_op != PreAttnAllToAllCommOp.QKVPackA2A:
+            raise RuntimeError("build the op with comm_op=QKVPackA2A for the packed exchange")
+        lens = _seq_lens_list(seq_lens_cpu, self.world) if seq_lens_cpu is not None else None
+        ls = lens[self.rank] if lens is not None else self.local_seq
+        outs = self._exchange_cuda(qkv.reshape(self.bs, ls, self.nh, self.hd), lens, None, 1, max(num_comm_sm, 0))
+        return [o.clone() for o in outs] if copy_out else outs
 
     def pre_attn_a2a_no_cpy(self, input, seq_lens_cpu=None, num_comm_sm: int = -1, comm_buf_idx: int = 0):
-        return self.pre_attn_a2a(input, seq_lens_cpu, num_comm_sm)
+        """Same, returning views of the op's symmetric output buffer (valid until the next call)."""
+        return self.pre_attn_a2a(input, seq_lens_cpu, num_comm_sm, copy_out=False)
 
     def pre_attn_qkv_pack_a2a_no_cpy(self, qkv, seq_lens_cpu=None, num_comm_sm: int = -1, comm_buf_idx: int = 0):
-        return self.pre_attn_qkv_pack_a2a(qkv, seq_lens_cpu, num_comm_sm)
+        return self.pre_attn_qkv_pack_a2a(qkv, seq_lens_cpu, num_comm_sm, copy_out=False)
 
     def get_input_comm_buf(self, input, comm_buf_idx: int = 0):
         return input
@@ -292,15 +422,16 @@ class GemmAllToAllTranspose(FusedOpBase):
     def profiling(self, input, weight, bias=None, input_scale=None, weight_scale=None, output_scale=None,
                   fast_accum=False, num_comm_sm=-1, sm_margin=0, prof_ctx=None):
         from ..tuning.profiling import profile_call
-        return profile_call(self, "gemm_a2a_transpose", lambda: self.forward(input, weight, bias=bias), prof_ctx)
+        w = as_nk(weight, self.transpose_weight)
+        return profile_call(self, "gemm_a2a_transpose", lambda: self.forward(input, weight, bias=bias), prof_ctx,
+                            key=(self.bs * self.local_seq, w.shape[0], self.hidden))
 
 
 class AllToAllTransposeGemm(FusedOpBase):
     def __init__(self, tp_group, nnodes: int, sp_size: int, bs: int, num_head: int, seq: int, head_dim: int,
                  input_dtype: torch.dtype, output_dtype: Optional[torch.dtype] = None,
                  max_num_comm_buf: int = 1, a2a_only: bool = False, timeout_s: Optional[float] = None):
-        super().__init__(tp_group, nnodes, timeout_s)
-        _check_sp(sp_size, self.world)
+        super().__init__(_sp_group(tp_group, sp_size), nnodes, timeout_s)
         W = self.world
         if seq % W or num_head % W:
             raise ValueError("seq and num_head must divide over the group")
@@ -320,8 +451,8 @@ class AllToAllTransposeGemm(FusedOpBase):
                 sm_margin: int = 0) -> torch.Tensor:
         """input [bs, heads/W, seq, hd] (``a2a_only``: [bs, seq, heads/W, hd]) -> [bs, seq/W, N]."""
         if seq_lens_cpu is not None:
-            # ranks with different sequence lengths: variable-split collective, then the GEMM kernel
-            gi = post_attn_a2a_varlen_torch(input, self.pg, self.a2a_only, _seq_lens_list(seq_lens_cpu, self.world))
+            # ranks with different sequence lengths: the strided exchange, then the GEMM kernel
+            gi = self.post_attn_a2a(input, seq_lens_cpu, copy_out=False)
             if a2a_transpose_output is not None:
                 a2a_transpose_output.copy_(gi.reshape(a2a_transpose_output.shape))
             res = self.gemm_only(gi, weight, bias=bias, output=output, transpose_weight=transpose_weight)
@@ -377,14 +508,42 @@ class AllToAllTransposeGemm(FusedOpBase):
 
     __call__ = forward
 
-    def post_attn_a2a(self, input, seq_lens_cpu=None, all_to_all_option=None, num_comm_sm: int = -1):
-        if seq_lens_cpu is not None:
-            return post_attn_a2a_varlen_torch(input, self.pg, self.a2a_only, _seq_lens_list(seq_lens_cpu, self.world))
-        return post_attn_a2a_torch(input, self.pg, self.a2a_only)
+    def post_attn_a2a(self, input, seq_lens_cpu=None, all_to_all_option=None, num_comm_sm: int = -1,
+                      copy_out: bool = True):
+        """heads -> seq exchange alone: input [bs, heads/W, seq, hd] (``a2a_only``: [bs, seq, heads/W,
+        hd]) -> [bs, seq/W (this rank's length), heads * hd], heads ordered by source rank."""
+        lens = _seq_lens_list(seq_lens_cpu, self.world) if seq_lens_cpu is not None else None
+        if not input.is_cuda:
+            if lens is not None:
+                return post_attn_a2a_varlen_torch(input, self.pg, self.a2a_only, lens)
+            return post_attn_a2a_torch(input, self.pg, self.a2a_only)
+        W, r = self.world, self.rank
+        lens = lens if lens is not None else [self.local_seq] * W
+        S = sum(lens)
+        x = input if input.is_contiguous() else input.contiguous()
+        e, hd, lh, nh, bs = x.element_size(), self.hd, self.local_nh, self.nh, self.bs
+        need = bs * max(lens) * self.hidden * e
+        if need > self.land.nbytes:          # every rank sees the same lengths: a collective re-allocation
+            self.land = SymmBuffer(need, self.pg)
+        copies = [[] for _ in range(W)]
+        for d in range(W):
+            off_d, ls_d = sum(lens[:d]), lens[d]
+            if self.a2a_only:                # [bs, S, lh, hd]
+                src = x.data_ptr() + off_d * lh * hd * e
+                ss = (S * lh * hd * e, lh * hd * e, hd * e)
+            else:                            # [bs, lh, S, hd]
+                src = x.data_ptr() + off_d * hd * e
+                ss = (lh * S * hd * e, hd * e, S * hd * e)
+            dst = self.land.ptr(d) + r * lh * hd * e
+            copies[d].append((src, dst, (bs, ls_d, lh), hd * e, ss, (ls_d * nh * hd * e, nh * hd * e, hd * e)))
+        _strided_exchange(self, copies, x.device, max(num_comm_sm, 0))
+        out = self.land.view(r, self.input_dtype, (bs, lens[r], self.hidden))
+        return out.clone() if copy_out else out
 
     def post_attn_a2a_no_cpy(self, input, seq_lens_cpu=None, all_to_all_option=None, num_comm_sm: int = -1,
                              comm_buf_idx: int = 0):
-        return self.post_attn_a2a(input, seq_lens_cpu)
+        """Same, returning a view of the op's symmetric buffer (valid until the next call)."""
+        return self.post_attn_a2a(input, seq_lens_cpu, copy_out=False)
 
     def gemm_only(self, input, weight, bias=None, output=None, input_scale=None, weight_scale=None,
                   output_scale=None, fast_accum=False, transpose_weight=False):
@@ -408,4 +567,6 @@ class AllToAllTransposeGemm(FusedOpBase):
 
     def profiling(self, input, weight, bias=None, output=None, prof_ctx=None, **kw):
         from ..tuning.profiling import profile_call
-        return profile_call(self, "a2a_transpose_gemm", lambda: self.forward(input, weight, bias=bias), prof_ctx)
+        w = as_nk(weight, kw.get("transpose_weight", False))
+        return profile_call(self, "a2a_transpose_gemm", lambda: self.forward(input, weight, bias=bias), prof_ctx,
+                            key=(self.bs * self.local_seq, w.shape[0], self.hidden))

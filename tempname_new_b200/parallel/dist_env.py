@@ -62,4 +62,5 @@ class MoeArguments:
 
     def __post_init__(self):
         if self.output_dtype is None:
-            self.output_dtype = self.input_dtype
+            # 8-bit inputs produce 16-bit results (the kernels' epilogues write bf16 / fp16 only)
+            self.output_dtype = self.input_dtype if self.input_dtype.itemsize > 1 else torch.bfloat16

@@ -71,12 +71,35 @@ def time_cuda(fn: Callable[[], object], warmup: int = 5, iters: int = 10, group=
     return ms
 
 
-def profile_call(op, name: str, fn: Callable[[], object], prof_ctx: Optional[ProfilingContext]):
+def profile_call(op, name: str, fn: Callable[[], object], prof_ctx: Optional[ProfilingContext],
+                 key=None, segmented_rows: int = 0):
+    """Run ``fn`` (one call of a fused op). With a ``ProfilingContext`` on a GPU: time it - for the ops
+    built on the dense kernel (``key`` = the (M, N, K) their knobs are looked up under) once per
+    candidate knob set, pinned with ``tuning.table.override``, five warm-up and ten timed calls each,
+    maximum over the ranks of the op's group - record the ranking, and install the winner in the
+    run-time table so that later calls use it (reference: the per-op ``profiling`` methods iterate
+    every registered hparams set the same way, src/gemm_rs/ths_op/gemm_reduce_scatter.cc:979-1060)."""
     out = fn()
-    if prof_ctx is not None and torch.cuda.is_available():
-        ms = time_cuda(fn, group=getattr(op, "pg", None))
-        prof_ctx.add(TuningRecord(name, {}, {}, ms))
-    return out
+    if prof_ctx is None or not torch.cuda.is_available():
+        return out
+    group = getattr(op, "pg", None)
+    if key is None:
+        prof_ctx.add(TuningRecord(name, {}, {}, time_cuda(fn, group=group)))
+        return out
+    from .table import candidates, load_tuning_record, override
+    ranked = []
+    for knobs in candidates(*key, segmented_rows=segmented_rows):
+        with override(key, knobs):
+            ms = time_cuda(fn, group=group)
+        if hasattr(op, "check_status"):
+            op.check_status()
+        ranked.append((ms, knobs))
+    ranked.sort(key=lambda r: r[0])
+    best_ms, best = ranked[0]
+    prof_ctx.add(TuningRecord(name, {"m": key[0], "n": key[1], "k": key[2],
+                                     "top": [dict(k, ms=round(ms, 5)) for ms, k in ranked[:5]]}, best, best_ms))
+    load_tuning_record({"key": list(key), "best": best})
+    return fn()
 
 
 def profile_dense_plain(op, input, weight, bias, output_buf, input_scale, weight_scale,
@@ -86,15 +109,15 @@ def profile_dense_plain(op, input, weight, bias, output_buf, input_scale, weight
     w = as_nk(weight, op.transpose_weight)
     out = output_buf if output_buf is not None else torch.empty(
         (input.shape[0], w.shape[0]), dtype=op.output_dtype, device=input.device)
-    best = None
-    for tile_n in (256, 128):
-        for group_m in (8, 16):
-            ms = time_cuda(lambda: _dense.plain_gemm(input, w, out, bias, input_scale, weight_scale,
-                                                     tile_n=tile_n, group_m=group_m))
-            if best is None or ms < best[0]:
-                best = (ms, {"tile_n": tile_n, "group_m": group_m})
+    from .table import candidates
+    ranked = []
+    for knobs in candidates(input.shape[0], w.shape[0], w.shape[1]):
+        ms = time_cuda(lambda: _dense.plain_gemm(input, w, out, bias, input_scale, weight_scale, **knobs))
+        ranked.append((ms, knobs))
+    ranked.sort(key=lambda r: r[0])
     if prof_ctx is not None:
-        prof_ctx.add(TuningRecord("gemm_only", {"m": input.shape[0], "n": w.shape[0], "k": w.shape[1]},
-                                  best[1], best[0]))
-    _dense.plain_gemm(input, w, out, bias, input_scale, weight_scale, **best[1])
+        prof_ctx.add(TuningRecord("gemm_only", {"m": input.shape[0], "n": w.shape[0], "k": w.shape[1],
+                                                "top": [dict(k, ms=round(ms, 5)) for ms, k in ranked[:5]]},
+                                  ranked[0][1], ranked[0][0]))
+    _dense.plain_gemm(input, w, out, bias, input_scale, weight_scale, **ranked[0][1])
     return out

@@ -15,19 +15,23 @@ from typing import Dict, Tuple
 
 Key = Tuple[int, int, int]
 
-# (M rows computed per GPU, N, K) -> knobs. Measured on B200 (148 SMs, 1000 W cap), bf16.
+# (M rows computed per GPU, N, K) -> knobs. Measured on B200 (148 SMs, 1000 W cap), bf16, with
+# `tune_dense --seconds 0.6` (back-to-back launches, so the power cap decides): TFLOP/s of the winner
+# and of torch.matmul on the same box in the same process.
 DENSE_TABLE: Dict[Key, Dict[str, int]] = {
-    # CTA pairs on 256 x 256 tiles, raster groups of 8 tile rows, wave-synchronous tile starts:
-    # winners of `tune_dense` on all six TP-MLP shapes (1454-1539 TFLOP/s, cuBLAS 1514-1630)
-    (8192, 49152, 12288): {"cta_group": 2, "tile_n": 256, "group_m": 8},
-    (8192, 12288, 49152): {"cta_group": 2, "tile_n": 256, "group_m": 8},
-    (8192, 24576, 12288): {"cta_group": 2, "tile_n": 256, "group_m": 8},
-    (8192, 12288, 24576): {"cta_group": 2, "tile_n": 256, "group_m": 8},
-    (8192, 12288, 12288): {"cta_group": 2, "tile_n": 256, "group_m": 8},
-    (8192, 6144, 12288): {"cta_group": 2, "tile_n": 256, "group_m": 8},
-    (8192, 12288, 6144): {"cta_group": 2, "tile_n": 256, "group_m": 8},
-    (8192, 8192, 8192): {"cta_group": 2, "tile_n": 256, "group_m": 8},
-    (4096, 4096, 4096): {"cta_group": 2, "tile_n": 256, "group_m": 8},
+    # 512 x 256 CTA-pair tiles (two MMAs per k-step share one B tile) win every large shape; the raster
+    # group differs: 8 tile rows (4096 rows) unless N is small next to K
+    (8192, 49152, 12288): {"cta_group": 2, "tile_n": 256, "tile_m": 512, "group_m": 8},   # 1358 | 1400
+    (8192, 12288, 49152): {"cta_group": 2, "tile_n": 256, "tile_m": 512, "group_m": 4},   # 1354 | 1291
+    (8192, 24576, 12288): {"cta_group": 2, "tile_n": 256, "tile_m": 512, "group_m": 8},   # 1354 | 1388
+    (8192, 12288, 24576): {"cta_group": 2, "tile_n": 256, "tile_m": 512, "group_m": 8},   # 1333 | 1305
+    (8192, 12288, 12288): {"cta_group": 2, "tile_n": 256, "tile_m": 512, "group_m": 8},   # 1323 | 1313
+    (8192, 6144, 12288): {"cta_group": 2, "tile_n": 256, "tile_m": 512, "group_m": 8},    # 1267 | 1316
+    (8192, 12288, 6144): {"cta_group": 2, "tile_n": 256, "tile_m": 512, "group_m": 8},    # 1291 | 1316
+    (4096, 4096, 4096): {"cta_group": 2, "tile_n": 256, "tile_m": 512, "group_m": 8},     # 1176 | 1268
+    (4096, 12288, 4096): {"cta_group": 2, "tile_n": 256, "tile_m": 512, "group_m": 8},    # 1229 | 1295
+    (16384, 3584, 8192): {"cta_group": 2, "tile_n": 256, "tile_m": 512, "group_m": 2},    # 1255 | 1272
+    (16384, 8192, 3584): {"cta_group": 2, "tile_n": 256, "tile_m": 512, "group_m": 8},    # 1279 | 1371
 }
 
 _NUM_SMS = 148
@@ -43,13 +47,29 @@ def heuristic(m: int, n: int, k: int, elt: int = 2) -> Dict[str, int]:
     of 2048 rows (with wave-synchronous tile starts the grid walks K together, so the group does
     not have to fit L2 over the whole K extent)."""
     if m >= 256 and n >= 256 and (m // 256) * -(-n // 256) >= _NUM_SMS // 4:
-        cg, bn = 2, 256
+        cg, bn = 2, 256      # (tile_m stays 0: the launcher picks 512-row tiles when the rows allow them)
     elif n % 256 == 0 or n > 2048:
         cg, bn = 1, 256
     else:
         cg, bn = 1, 128
     group = 8 if cg == 2 else 16
     return {"cta_group": cg, "tile_n": bn, "group_m": group}
+
+
+def candidates(m: int, n: int, k: int, elt: int = 2, segmented_rows: int = 0):
+    """Knob sets worth timing for a dense-kernel problem: 512-row CTA-pair tiles (two MMAs share a B
+    tile) where the rows allow them, 256-row CTA pairs, single CTAs; a few raster groups each.
+    ``segmented_rows``: rows per rank segment of a fused op (0: plain GEMM over m rows)."""
+    rows = segmented_rows or m
+    out = []
+    if rows >= 512 and n >= 256:
+        out += [{"cta_group": 2, "tile_n": 256, "tile_m": 512, "group_m": g} for g in (2, 4, 8)]
+    if rows >= 256 and n >= 256:
+        out += [{"cta_group": 2, "tile_n": 256, "tile_m": 256, "group_m": g} for g in (4, 8)]
+    out += [{"cta_group": 1, "tile_n": 256 if n >= 256 else 128, "tile_m": 128, "group_m": g} for g in (8, 16)]
+    if n % 256:
+        out.append({"cta_group": 1, "tile_n": 128, "tile_m": 128, "group_m": 16})
+    return out
 
 
 def _load_extra() -> Dict[Key, Dict[str, int]]:

@@ -102,7 +102,34 @@ def check_dense():
     dist.all_gather_into_tensor(full8, a8)
     close(op.forward(a8, w8, input_scale=sa, weight_scale=sb), (full8.float() @ w8.float().t()) * 2e-4,
           "AGKernel int8")
+    # one scale per input row (this rank's [M/W, 1]) and per output column ([1, N]), fp16 output with bias
+    sa_r = torch.rand(M // W, 1, device=dev) * 0.02 + 0.001
+    sb_c = torch.rand(1, Nn, device=dev) * 0.02 + 0.001
+    dist.broadcast(sb_c, 0)
+    sa_all = torch.empty(M, 1, device=dev)
+    dist.all_gather_into_tensor(sa_all, sa_r)
+    close(op.forward(a8, w8, input_scale=sa_r, weight_scale=sb_c), (full8.float() @ w8.float().t()) * sa_all * sb_c,
+          "AGKernel int8, per-row x per-column scales", tol=1e-2)
     op.check_status()
+    # 16-bit extras on more than one rank: fp16, bias, weights given as [K, N]
+    Mh, Nh, Kh = 512 * W, 512, 256 * W
+    ah = (torch.randn(Mh // W, Kh, device=dev) * 0.5).half()
+    wh = (torch.randn(Nh, Kh, device=dev) * 0.05).half()
+    bh = torch.randn(1, Nh, device=dev).half()
+    oph = flux.AGKernel(pg, 1, Mh, Nh, Kh, torch.float16)
+    fullh = torch.empty(Mh, Kh, device=dev, dtype=torch.float16)
+    dist.all_gather_into_tensor(fullh, ah)
+    close(oph.forward(ah, wh.t().contiguous(), bias=bh, transpose_weight=True),
+          fullh.float() @ wh.float().t() + bh.float(), "AGKernel fp16 + bias + transpose_weight", tol=1e-2)
+    oph.check_status()
+    ar = (torch.randn(Mh, Kh // W, device=dev) * 0.5).half()
+    wr = (torch.randn(Nh, Kh // W, device=dev) * 0.05).half()
+    br = torch.randn(Mh, Nh, device=dev).half()          # [M, N] bias: added on every rank, as in the reference
+    opr = flux.GemmRS(pg, 1, Mh, Nh, torch.float16, transpose_weight=True)
+    refh = torch.empty(Mh // W, Nh, device=dev)
+    dist.reduce_scatter_tensor(refh, (ar.float() @ wr.float().t() + br.float()).half().float())
+    close(opr.forward(ar, wr.t().contiguous(), bias=br), refh, "GemmRS fp16 + bias + transpose_weight", tol=1e-2)
+    opr.check_status()
     gb = flux.GroupBarrier(pg)
     for _ in range(3):
         gb.barrier_all()
@@ -247,7 +274,19 @@ def check_ulysses():
             for _ in range(2):   # own slice read in place from the attention output
                 out = op3.forward(inp, wo)
                 close(out.reshape(-1, N), ref, f"a2a_transpose_gemm (in place) bs{bs} seq{seq} a2a_only={a2a_only}")
+            # the exchange alone, on the strided-exchange kernel
+            for _ in range(2):
+                assert torch.equal(op3.post_attn_a2a(inp), gi_ref), f"[rank {rank}] post_attn_a2a differs"
             op3.check_status()
+        # stand-alone seq -> heads exchanges against the collective statement
+        ref_pre = pre_attn_a2a_torch(y, pg, bs, ls, nh, hd)[0]
+        for _ in range(2):
+            assert torch.equal(op.pre_attn_a2a(y.reshape(bs, ls, nh, hd)), ref_pre), "pre_attn_a2a differs"
+        if (nh // W) % 4 == 0:
+            for o, r in zip(op2.pre_attn_qkv_pack_a2a(y.reshape(bs, ls, nh, hd)), refs):
+                assert torch.equal(o, r), "pre_attn_qkv_pack_a2a differs"
+            op2.check_status()
+        op.check_status()
         if perf and seq >= 8192:
             full_flops = 2.0 * bs * ls * hidden * nh * hd
             t_f = timeit(lambda: op.forward(x, w))
@@ -272,6 +311,37 @@ def check_ulysses():
                     op3.forward(attn, wo)
                     torch.cuda.synchronize()
                 p0(f"a2a_transpose_gemm timeline (us): {tl.summary()}")
+    # ---- per-rank sequence lengths: projection kernel + strided exchange, exchange + projection
+    from tempname_new_b200.ops.ulysses import post_attn_a2a_varlen_torch, pre_attn_a2a_varlen_torch
+    bs, hidden, hd, nh = 2, 256, 64, 4 * W
+    lens = [32 + 16 * r for r in range(W)]
+    seq_cap = sum(lens) + 64
+    seq_cap += (-seq_cap) % W
+    lens_cpu = torch.tensor(lens, dtype=torch.int32)
+    x = (torch.randn(bs, lens[rank], hidden, device=dev) * 0.5).bfloat16()
+    w = (torch.randn(nh * hd, hidden, device=dev) * 0.05).bfloat16()
+    y = (x.reshape(-1, hidden).float() @ w.float().t()).bfloat16().reshape(bs, lens[rank], nh, hd)
+    opv = flux.GemmAllToAllTranspose(pg, 1, W, bs, seq_cap, hidden, hd, nh * hd, torch.bfloat16, gqa=2,
+                                     comm_op=flux.PreAttnAllToAllCommOp.QKVPackA2A)
+    lq, lk = 2, 1
+    parts = (y[:, :, :lq * W], y[:, :, lq * W:(lq + lk) * W], y[:, :, (lq + lk) * W:])
+    refs = [pre_attn_a2a_varlen_torch(t.contiguous(), pg, lens) for t in parts]
+    for _ in range(2):
+        for o, r, n in zip(opv.forward(x, w, seq_lens_cpu=lens_cpu), refs, "qkv"):
+            close(o, r, f"varlen qkv_pack {n}")
+    opv.check_status()
+    attn = (torch.randn(bs, nh // W, sum(lens), hd, device=dev) * 0.5).bfloat16()
+    wo = (torch.randn(hidden, nh * hd, device=dev) * 0.05).bfloat16()
+    for a2a_only in (False, True):
+        inp = attn.permute(0, 2, 1, 3).contiguous() if a2a_only else attn
+        gi_ref = post_attn_a2a_varlen_torch(inp, pg, a2a_only, lens)
+        opw = flux.AllToAllTransposeGemm(pg, 1, W, bs, nh, seq_cap, hd, torch.bfloat16, a2a_only=a2a_only)
+        for _ in range(2):
+            assert torch.equal(opw.post_attn_a2a(inp, seq_lens_cpu=lens_cpu), gi_ref), "varlen post_attn_a2a differs"
+            out = opw.forward(inp, wo, seq_lens_cpu=lens_cpu)
+            close(out.reshape(-1, hidden), gi_ref.reshape(-1, nh * hd).float() @ wo.float().t(),
+                  f"varlen a2a_transpose_gemm a2a_only={a2a_only}")
+        opw.check_status()
     p0(f"ulysses ok (W={W})")
 
 

@@ -206,3 +206,25 @@ def test_kernel_timeline_records_stamps(dev):
     torch.cuda.synchronize()
     assert torch.equal(before, tl.buf)
 
+
+
+def test_int8_per_row_and_per_column_scales(dev):
+    """The reference's int8 convention: input_scale [M, 1], weight_scale [1, N] - honoured element by
+    element on the GPU, and any other shape is refused instead of being cut to its first element."""
+    import tempname_new_b200 as flux
+    M, N, K = 384, 640, 512
+    g = torch.Generator(device="cpu").manual_seed(9)
+    a8 = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8).to(dev)
+    b8 = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8).to(dev)
+    sa = (torch.rand(M, 1, device=dev) * 0.02 + 0.001)
+    sb = (torch.rand(1, N, device=dev) * 0.02 + 0.001)
+    op = flux.GemmOnly(torch.int8, output_dtype=torch.bfloat16)
+    out = op.forward(a8, b8, input_scale=sa, weight_scale=sb)
+    ref = (a8.double() @ b8.double().t()).float() * sa * sb
+    assert (out.float() - ref).abs().max().item() <= 1e-2 * max(1.0, ref.abs().max().item())
+    # per-row scale with a per-tensor weight scale
+    out2 = op.forward(a8, b8, input_scale=sa, weight_scale=torch.tensor([0.01], device=dev))
+    ref2 = (a8.double() @ b8.double().t()).float() * sa * 0.01
+    assert (out2.float() - ref2).abs().max().item() <= 1e-2 * max(1.0, ref2.abs().max().item())
+    with pytest.raises(ValueError):
+        op.forward(a8, b8, input_scale=sa[:7], weight_scale=sb)

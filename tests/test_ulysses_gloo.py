@@ -105,3 +105,30 @@ def _varlen(rank, world):
 
 def test_per_rank_sequence_lengths_gloo():
     run_gloo(_varlen, 2)
+
+
+def _sp_subgroups(rank, world):
+    """sp_size smaller than the group: two independent sequence-parallel blocks of two ranks each."""
+    import tempname_new_b200 as flux
+    sp = 2
+    block, r = rank // sp, rank % sp
+    bs, seq, hidden, hd, nh = 1, 8 * sp, 16, 8, 2 * sp
+    ls, lh = seq // sp, nh // sp
+    torch.manual_seed(100 + block)                                      # each block has its own data
+    x_full = torch.randn(bs, seq, hidden)
+    w = torch.randn(nh * hd, hidden) * 0.2
+    op = flux.GemmAllToAllTranspose(dist.group.WORLD, 1, sp, bs, seq, hidden, hd, nh * hd, torch.float32)
+    assert op.world == sp and op.rank == r
+    (out,) = op.forward(x_full[:, r * ls:(r + 1) * ls].contiguous(), w)
+    y = (x_full @ w.t()).reshape(bs, seq, nh, hd)
+    torch.testing.assert_close(out, y[:, :, r * lh:(r + 1) * lh].permute(0, 2, 1, 3), rtol=1e-5, atol=1e-5)
+    attn_full = torch.randn(bs, nh, seq, hd)
+    wo = torch.randn(24, nh * hd) * 0.2
+    op2 = flux.AllToAllTransposeGemm(dist.group.WORLD, 1, sp, bs, nh, seq, hd, torch.float32)
+    out2 = op2.forward(attn_full[:, r * lh:(r + 1) * lh].contiguous(), wo)
+    ref_in = attn_full.permute(0, 2, 1, 3).reshape(bs, seq, nh * hd)[:, r * ls:(r + 1) * ls]
+    torch.testing.assert_close(out2, ref_in @ wo.t(), rtol=1e-5, atol=1e-5)
+
+
+def test_sp_size_smaller_than_the_group_gloo():
+    run_gloo(_sp_subgroups, 4)

@@ -32,7 +32,11 @@ def test_tuning_table_and_profiling_context(tmp_path, monkeypatch):
     from tempname_new_b200.tuning import table
     from tempname_new_b200.tuning.profiling import ProfilingContext, TuningRecord
     k = table.lookup(8192, 6144, 12288)
-    assert k == {"cta_group": 2, "tile_n": 256, "group_m": 8}
+    assert k == {"cta_group": 2, "tile_n": 256, "tile_m": 512, "group_m": 8}
+    assert table.lookup(8192, 12288, 49152)["group_m"] == 4          # measured entries differ by shape
+    cands = table.candidates(8192, 6144, 12288)
+    assert {c["tile_m"] for c in cands} == {512, 256, 128} and all("group_m" in c for c in cands)
+    assert all(c["tile_m"] != 512 for c in table.candidates(8192, 6144, 12288, segmented_rows=256))
     h = table.lookup(333, 264, 72)
     assert h["cta_group"] == 1 and h["tile_n"] in (128, 256)
     assert table.heuristic(8192, 4096, 32768) == {"cta_group": 2, "tile_n": 256, "group_m": 8}
