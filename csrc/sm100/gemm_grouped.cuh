@@ -494,18 +494,17 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
           const uint32_t my_row = comm_base + (warp - 4) * Cfg::SC_WARP_BYTES + lane * Cfg::SC_PITCH;
           ptx::bulk_wait_read<0>();      // this lane's previous copy has read the row
           __syncwarp();
+          auto pk = [&](const uint32_t (&r)[32], int i) {
+            return ptx::pack_half2(f16, __uint_as_float(r[i]) * scale, __uint_as_float(r[i + 1]) * scale);
+          };
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const uint32_t a0 = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 0]) * scale, __uint_as_float(r0[8 * j + 1]) * scale);
-            const uint32_t a1 = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 2]) * scale, __uint_as_float(r0[8 * j + 3]) * scale);
-            const uint32_t a2 = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 4]) * scale, __uint_as_float(r0[8 * j + 5]) * scale);
-            const uint32_t a3 = ptx::pack_half2(f16, __uint_as_float(r0[8 * j + 6]) * scale, __uint_as_float(r0[8 * j + 7]) * scale);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + 16 * j), "r"(a0), "r"(a1), "r"(a2), "r"(a3) : "memory");
-            const uint32_t b0 = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 0]) * scale, __uint_as_float(r1[8 * j + 1]) * scale);
-            const uint32_t b1 = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 2]) * scale, __uint_as_float(r1[8 * j + 3]) * scale);
-            const uint32_t b2 = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 4]) * scale, __uint_as_float(r1[8 * j + 5]) * scale);
-            const uint32_t b3 = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 6]) * scale, __uint_as_float(r1[8 * j + 7]) * scale);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + 64 + 16 * j), "r"(b0), "r"(b1), "r"(b2), "r"(b3) : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + 16 * j), "r"(pk(r0, 8 * j)),
+                         "r"(pk(r0, 8 * j + 2)), "r"(pk(r0, 8 * j + 4)), "r"(pk(r0, 8 * j + 6))
+                         : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + 64 + 16 * j), "r"(pk(r1, 8 * j)),
+                         "r"(pk(r1, 8 * j + 2)), "r"(pk(r1, 8 * j + 4)), "r"(pk(r1, 8 * j + 6))
+                         : "memory");
           }
           ptx::fence_proxy_async_smem();
           if (row_ok && col0 < p.N) {
