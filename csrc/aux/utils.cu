@@ -113,6 +113,56 @@ __global__ void __launch_bounds__(kCastThreads) inplace_cast_kernel(
 }
 
 // ----------------------------------------------------------------------------------------
+// Sum of `cnt` rows per output row in fp32, 16-bit rows: out[t] = sum_j in[row(t, j)] with
+// row(t, j) = idx[t * cnt + j] (the top-k reduce of expert outputs) or j * slab_rows + t (the sum
+// over the leading dimension of a [B, M, N] tensor). One warp per output row, 16 bytes per lane and
+// trip, up to eight source rows in flight.
+// Reference: topk_scatter_reduce (src/pybind/gemm_grouped_v3_gather_rs.cc:33), bsr_reduce
+// (src/gemm_rs/bsr_reduce.cu:26-126).
+// ----------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) rows_sum_kernel(const uint16_t* __restrict__ in, const int32_t* __restrict__ idx,
+                                                       uint16_t* __restrict__ out, int64_t rows_out, int cols,
+                                                       int cnt, int64_t slab_rows, int f16) {
+  const int lane = threadIdx.x & 31;
+  const int64_t gwarp = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * 8;
+  const int chunks = cols / 8;
+  const bool h = f16 != 0;
+  for (int64_t t = gwarp; t < rows_out; t += nwarps) {
+    for (int c = lane; c < chunks; c += 32) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int j0 = 0; j0 < cnt; j0 += 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (j0 + j < cnt) {
+            const int64_t r = idx != nullptr ? idx[t * cnt + j0 + j] : (j0 + j) * slab_rows + t;
+            v[j] = ptx::ld_global_v4(in + r * cols + c * 8);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (j0 + j < cnt) {
+            const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              acc[2 * e] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] & 0xFFFFu), h);
+              acc[2 * e + 1] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] >> 16), h);
+            }
+          }
+        }
+      }
+      uint4 o;
+      o.x = ptx::pack_half2(h, acc[0], acc[1]);
+      o.y = ptx::pack_half2(h, acc[2], acc[3]);
+      o.z = ptx::pack_half2(h, acc[4], acc[5]);
+      o.w = ptx::pack_half2(h, acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(out + t * cols + c * 8) = o;
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
 // bitwise compare / uniform fill / copy
 // ----------------------------------------------------------------------------------------
 __global__ void bitwise_check_kernel(const uint8_t* a, const uint8_t* b, int64_t nbytes,
@@ -282,6 +332,26 @@ extern "C" int fluxb_inplace_cast_fp32_to_bf16(float* data, int64_t n, uint32_t*
   inplace_cast_kernel<<<grid, kCastThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       data, n, flags, claim, epoch, timeout_ns ? timeout_ns : 2000000000ull,
       reinterpret_cast<Status*>(status));
+  FLUXB_CUDA_OK(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return kOk;
+}
+
+extern "C" int fluxb_rows_sum(const void* in, const int32_t* idx, void* out, int64_t rows_out, int cols, int cnt,
+                              int64_t slab_rows, int dtype, void* stream) {
+  FLUXB_REQUIRE(in && out && rows_out >= 0 && cnt >= 1, "rows_sum arguments");
+  FLUXB_REQUIRE(cols > 0 && cols % 8 == 0, "rows must be multiples of 8 elements (16 bytes)");
+  FLUXB_REQUIRE(dtype == FLUXB_BF16 || dtype == FLUXB_FP16, "rows_sum runs on bf16 / fp16");
+  FLUXB_REQUIRE(((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0,
+                "buffers must be 16-byte aligned");
+  if (rows_out == 0) return kOk;
+  int sms = 0, rc;
+  if ((rc = device_sm_count(&sms))) return rc;
+  int64_t blocks = (rows_out + 7) / 8;
+  if (blocks > sms * 8) blocks = sms * 8;
+  rows_sum_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint16_t*>(in), idx, reinterpret_cast<uint16_t*>(out), rows_out, cols, cnt, slab_rows,
+      dtype == FLUXB_FP16);
   FLUXB_CUDA_OK(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return kOk;

@@ -74,7 +74,8 @@ typedef struct {
   const float* sa;
   const float* sb;
   float* ag_scale_land[FLUXB_MAX_RANKS];
-  int32_t blockscale;
+  int32_t blockscale;        /* 0 off, 1: sb is [N/128, K/128], 2: sb is [N/128, K/128, 128] (one scale per weight row
+                                and k-block: both operands carry 1x128 scales, the weight-gradient form) */
   int32_t tile_m;            /* 0 = auto, else 128 * cta_group, or 512 (CTA pairs on 256-column tiles: two
                                 256-row MMAs per k-step share one B tile) */
   void* stream;
@@ -330,6 +331,10 @@ int fluxb_quantize_blockwise(const void* x, int64_t ldx, int in_dtype, void* q, 
 int fluxb_inplace_cast_fp32_to_bf16(float* data, int64_t n, uint32_t* flags, uint32_t* claim,
                                     uint32_t epoch, uint64_t timeout_ns, fluxb_status_t* status,
                                     void* stream);
+/* out[t, :] = sum over j < cnt of in[row(t, j), :] in fp32, bf16 / fp16 rows of `cols` elements
+ * (a multiple of 8): row(t, j) = idx[t * cnt + j], or j * slab_rows + t when idx is null. */
+int fluxb_rows_sum(const void* in, const int32_t* idx, void* out, int64_t rows_out, int cols, int cnt,
+                   int64_t slab_rows, int dtype, void* stream);
 int fluxb_bitwise_check(const void* a, const void* b, int64_t nbytes,
                         unsigned long long* mismatches, void* stream);
 int fluxb_uniform_fill(void* out, int64_t n, int dtype, uint64_t seed, float lo, float hi,

@@ -203,6 +203,7 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   FLUXB_REQUIRE(!(a->scale_flags & 2u) || a->scale_b, "per-column scale vector missing");
   p.sa = a->sa;
   p.sb = a->sb;
+  p.sb_groupwise = a->blockscale == 2 ? 1 : 0;
   p.ab_fmt = (a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP8_E5M2 || a->in_dtype == FLUXB_INT8) ? 1 : 0;
   p.out_f16 = a->out_dtype == FLUXB_FP16 ? 1 : 0;
   p.act = a->act;
@@ -217,7 +218,9 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     FLUXB_REQUIRE(a->in_dtype == FLUXB_FP8_E4M3, "block-scaled GEMM takes e4m3 operands");
     FLUXB_REQUIRE(a->sa && a->sb, "block scales missing");
     FLUXB_REQUIRE(a->K % 128 == 0 && a->N % 128 == 0, "block-scaled GEMM needs K and N multiples of 128");
-    FLUXB_REQUIRE((a->M / (multi ? a->world : 1)) % 128 == 0, "block-scaled GEMM needs rows per rank in multiples of 128");
+    // (one rank: the last row block may be partial - its scales exist, its rows are clipped)
+    FLUXB_REQUIRE(!multi || (a->M / a->world) % 128 == 0,
+                  "block-scaled fused ops need rows per rank in multiples of 128");
     cg = 1;
     bn = 128;
   } else if (a->mode == FLUXB_A2A_GEMM) {
@@ -523,9 +526,12 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
   // CTAs that wait for one another (wave-synchronous starts) or for peers (every multi-rank mode) must
   // all be resident: those launches are cooperative unless FLUXB_COOPERATIVE=0
+  // (a kernel profiler that replays launches could not replay a cooperative cluster launch here:
+  // under an injected profiler the attribute is left off unless FLUXB_COOPERATIVE=1 asks for it)
   static const int coop_env = [] {
     const char* e = getenv("FLUXB_COOPERATIVE");
-    return e ? atoi(e) : 1;
+    if (e) return atoi(e);
+    return (getenv("CUDA_INJECTION64_PATH") || getenv("NV_COMPUTE_PROFILER_PERFWORKS_DIR")) ? 0 : 1;
   }();
   bool coop = coop_env != 0 && (multi || a2a);
   {
@@ -542,7 +548,7 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   }
   if (a->blockscale) {
     if (p.mode == kModeAllGather) return launch_dense<DenseCfg<128, 1, 4, 1, 32768, true>>(p, grid, stream, coop);
-    return launch_dense<DenseCfg<128, 1, 4, 1, 0, true>>(p, grid, stream, coop);
+    return launch_dense<DenseCfg<128, 1, 5, 1, 0, true>>(p, grid, stream, coop);
   }
   if (p.mode == kModeAllGather || p.mode == kModeA2AGemm) {
     // variants that carry the staging rings of the all-gather / all-to-all push

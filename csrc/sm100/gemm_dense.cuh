@@ -101,7 +101,9 @@ struct DenseGemmParams {
   // block scales (fp8 block-scaled variant): inverse scales as the quantiser stores them
   const float* sa;               // for the rows of tm_a:      [rows/128, K/128, 128]
   const float* sa_land;          // for the rows of tm_a_land: [W*seg_rows/128, K/128, 128]
-  const float* sb;               // [N/128, K/128]
+  const float* sb;               // [N/128, K/128], or with sb_groupwise [N/128, K/128, 128] (one per column)
+  int32_t sb_groupwise;          // 1: the weight carries 1x128 scales too (the weight-gradient form)
+  int32_t reserved6;
   const float* ag_scale_src;     // all-gather: this rank's A scales (== sa), pushed with the shard
   float* ag_scale_land[kMaxRanks];
   // all-gather
@@ -150,8 +152,9 @@ struct DenseGemmParams {
 // its 128 * MT_ x BN slice of D in its own TMEM.
 // COMM_ > 0 reserves COMM_ bytes of shared memory as staging rings for the all-gather push.
 // BS_ = true: block-scaled fp8 (1x128 A scales, 128x128 B scales): every 128-deep k-block is
-// accumulated into a fresh TMEM buffer and promoted into fp32 registers, multiplied by its
-// scales, by eight epilogue warps (two per TMEM lane quadrant, 64 columns each).
+// accumulated into a fresh TMEM buffer (four of them, so the issuer runs up to four k-blocks ahead)
+// and promoted into fp32 registers, multiplied by its scales, by eight epilogue warps: two per
+// TMEM lane quadrant, each owning 64 of the tile's 128 columns for the whole tile.
 template <int BN_, int KIND_, int STAGES_, int CG_ = 1, int COMM_ = 0, bool BS_ = false, int MT_ = 1>
 struct DenseCfg {
   static constexpr int COMM_BYTES = COMM_;
@@ -160,8 +163,8 @@ struct DenseCfg {
   static constexpr int EPI_WARPS = BS_ ? 8 : 4;
   static constexpr int THREADS = 128 + 32 * EPI_WARPS;
   // MT_ == 1: two accumulators used alternately (the epilogue of a tile overlaps the next main loop);
-  // MT_ == 2: the two row halves of one tile; block-scaled: 3 k-block buffers + 1 exchange region
-  static constexpr int ACC_BUFS = BS_ ? 3 : 2;
+  // MT_ == 2: the two row halves of one tile; block-scaled: 4 k-block buffers
+  static constexpr int ACC_BUFS = BS_ ? 4 : 2;
   static_assert(!BS_ || (KIND_ == 1 && BN_ == 128 && CG_ == 1), "block-scaled variant: fp8, 128x128 tiles");
   static_assert(MT_ == 1 || (MT_ == 2 && CG_ == 2 && BN_ == 256 && !BS_), "512-row tiles: CTA pairs, 256 columns");
   static constexpr int CG = CG_;
@@ -187,7 +190,7 @@ struct DenseCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + COMM_BYTES + BAR_BYTES + 1024;
   static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared memory limit");
   static constexpr int TMEM_COLS = 512;
-  static_assert((ACC_BUFS + (BS_ ? 1 : 0)) * BN <= TMEM_COLS, "accumulators must fit TMEM");
+  static_assert(ACC_BUFS * BN <= TMEM_COLS, "accumulators must fit TMEM");
   // column pieces of a split tile are BN >> shift wide; the epilogue moves 64 columns at a time
   static constexpr int MAX_SPLIT_SHIFT = (BN_ == 256 && !BS_) ? 2 : 0;
 };
@@ -281,7 +284,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * STAGES + 2 * NACC));
   volatile uint32_t* abort_word = tmem_slot + 1;
   const uint32_t ring_bar_base = bar_base + 8u * (2 * STAGES + 2 * NACC) + 16u;
-  const uint32_t xfull_bar = ring_bar_base + 64u, xempty_bar = ring_bar_base + 72u;  // block-scaled exchange
   static_assert(8 * (2 * STAGES + 2 * NACC) + 16 + 64 + 16 <= Cfg::BAR_BYTES, "barrier block too small");
 
   const int warp = threadIdx.x >> 5;
@@ -301,10 +303,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     }
     for (int a = 0; a < NACC; ++a) {
       ptx::mbar_init(tfull_bar(a), 1);
-      ptx::mbar_init(tempty_bar(a), 4 * CG);   // one epilogue warp per TMEM lane quadrant reads a buffer
+      // one epilogue warp per TMEM lane quadrant reads a buffer (block-scaled: two, 64 columns each)
+      ptx::mbar_init(tempty_bar(a), Cfg::BS ? 8 : 4 * CG);
     }
-    ptx::mbar_init(xfull_bar, 4);
-    ptx::mbar_init(xempty_bar, 4);
     for (int i = 0; i < 8; ++i) ptx::mbar_init(ring_bar_base + 8u * i, 1);
     *abort_word = 0;
     ptx::fence_mbar_init();
@@ -914,7 +915,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     }
   }
   } else {
-    if constexpr (Cfg::BS) ptx::setmaxnreg_inc<208>();  // 128 fp32 accumulators per thread
+      if constexpr (Cfg::BS) ptx::setmaxnreg_inc<208>();
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;              // TMEM lane quadrant this warp may read
     const int ew = warp - 4;             // epilogue warp index
@@ -1094,7 +1095,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     int pend_seg = -1, pend_mt = 0;
     uint32_t pend_chunks = 0;
     uint32_t own_seen = 0;   // tile rows of the own segment whose W-1 slabs were seen to have landed
-    uint64_t bs_acc[Cfg::BS ? 64 : 1];
+    uint64_t bs_acc[Cfg::BS ? 32 : 1];   // block-scaled: this thread's row x 64 columns, fp32 pairs
     for (int t = tile_slot; t < total_tiles; t += tile_stride, ++it) {
       if (*abort_word) break;
       const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
@@ -1146,12 +1147,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
 
       if constexpr (Cfg::BS) {
         // ---- block-scaled: promote every k-block's partial product into fp32 registers.
-        // The eight epilogue warps form two sets (warps 4..7 and 8..11, one warp per TMEM lane
-        // quadrant each). The sets take alternate k-blocks, each over all 128 columns, so that
-        // one set's TMEM read latency hides behind the other's FMAs. At the end of a tile the
-        // sets' partial sums are added through a spare 128-column TMEM region; the sets take
-        // turns (by tile parity) at being the one that adds, converts and stores.
-        const int set = ew >> 2;
+        // Eight epilogue warps: warp (quadrant q, half) owns rows q*32.. of the tile and columns
+        // half*64.. for every k-block, so its partial sums never leave its registers. Two warps share
+        // a scheduler: while one waits for its TMEM read, the other multiplies.
+        const int half = ew >> 2;
         const int kbs = k_blocks;                               // scale blocks along K (BK == 128)
         const float* sa_rows = p.sa;
         int64_t srow = grow;                                    // row in the scale tensor's frame
@@ -1169,91 +1168,69 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         }
         const float* sa_ptr = sa_rows + (srow >> 7) * static_cast<int64_t>(kbs) * 128 + (srow & 127);
         const float* sb_ptr = p.sb + static_cast<int64_t>(c.n0 >> 7) * kbs;
-        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + half * 64;
 #pragma unroll
-        for (int j = 0; j < 64; ++j) bs_acc[j] = 0ull;
+        for (int j = 0; j < 32; ++j) bs_acc[j] = 0ull;
         const uint32_t n0 = static_cast<uint32_t>(it) * kbs;
-        for (int kb = ((n0 & 1u) == static_cast<uint32_t>(set)) ? 0 : 1; kb < kbs; kb += 2) {
+        // scales of the next k-block are fetched while this one is promoted
+        float sa_next = sa_ptr[0];
+        float sb_next = p.sb_groupwise ? 1.f : sb_ptr[0];
+        for (int kb = 0; kb < kbs; ++kb) {
           const uint32_t n = n0 + kb;
           const int buf = n % NACC;
           const uint32_t par = (n / NACC) & 1u;
-          const float sc = sa_ptr[static_cast<int64_t>(kb) * 128] * sb_ptr[kb];
+          const float sc = sa_next * sb_next;
+          if (kb + 1 < kbs) {
+            sa_next = sa_ptr[static_cast<int64_t>(kb + 1) * 128];
+            if (!p.sb_groupwise) sb_next = sb_ptr[kb + 1];
+          }
           const uint64_t sc2 = ptx::pack_f32x2(sc, sc);
           if (lane == 0) mbar_wait(wc, tfull_bar(buf), par, kSiteTmemFull);
           __syncwarp();
           mbar_wait(wc, tfull_bar(buf), par, kSiteTmemFull);
           ptx::tc_fence_after();
+          uint32_t r0[32], r1[32];
+          ptx::tmem_ld_32x32b_x32(lane_base + buf * BN, r0);
+          ptx::tmem_ld_32x32b_x32(lane_base + buf * BN + 32, r1);
+          ptx::tmem_ld_wait();
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+          if (p.sb_groupwise) {
+            // per-column weight scales of this k-block: 64 floats of this warp's columns, the same for every row
+            const float4* sbv =
+                reinterpret_cast<const float4*>(p.sb + (static_cast<int64_t>(c.n0 >> 7) * kbs + kb) * 128 + half * 64);
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t r0[32], r1[32];
-            const uint32_t taddr = lane_base + buf * BN + h * 64;
-            ptx::tmem_ld_32x32b_x32(taddr, r0);
-            ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
-            ptx::tmem_ld_wait();
-            if (h == 1) {
-              ptx::tc_fence_before();
-              __syncwarp();
-              if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+            for (int j = 0; j < 8; ++j) {
+              const float4 s0 = sbv[j], s1 = sbv[8 + j];
+              bs_acc[2 * j] = ptx::ffma2(ptx::pack_b32x2(r0[4 * j], r0[4 * j + 1]), ptx::pack_f32x2(sc * s0.x, sc * s0.y),
+                                         bs_acc[2 * j]);
+              bs_acc[2 * j + 1] = ptx::ffma2(ptx::pack_b32x2(r0[4 * j + 2], r0[4 * j + 3]),
+                                             ptx::pack_f32x2(sc * s0.z, sc * s0.w), bs_acc[2 * j + 1]);
+              bs_acc[16 + 2 * j] = ptx::ffma2(ptx::pack_b32x2(r1[4 * j], r1[4 * j + 1]),
+                                              ptx::pack_f32x2(sc * s1.x, sc * s1.y), bs_acc[16 + 2 * j]);
+              bs_acc[16 + 2 * j + 1] = ptx::ffma2(ptx::pack_b32x2(r1[4 * j + 2], r1[4 * j + 3]),
+                                                  ptx::pack_f32x2(sc * s1.z, sc * s1.w), bs_acc[16 + 2 * j + 1]);
             }
+          } else {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              bs_acc[h * 32 + j] = ptx::ffma2(ptx::pack_b32x2(r0[2 * j], r0[2 * j + 1]), sc2, bs_acc[h * 32 + j]);
-              bs_acc[h * 32 + 16 + j] =
-                  ptx::ffma2(ptx::pack_b32x2(r1[2 * j], r1[2 * j + 1]), sc2, bs_acc[h * 32 + 16 + j]);
+              bs_acc[j] = ptx::ffma2(ptx::pack_b32x2(r0[2 * j], r0[2 * j + 1]), sc2, bs_acc[j]);
+              bs_acc[16 + j] = ptx::ffma2(ptx::pack_b32x2(r1[2 * j], r1[2 * j + 1]), sc2, bs_acc[16 + j]);
             }
           }
         }
-        // ---- add the two sets' partial sums through the spare TMEM columns
-        const uint32_t xaddr = lane_base + NACC * BN;
-        const bool emitter = (it & 1) == set;
-        if (!emitter) {
-          if (lane == 0) mbar_wait(wc, xempty_bar, ((it & 1) ^ 1u), kSiteTmemEmpty);
-          __syncwarp();
-          mbar_wait(wc, xempty_bar, ((it & 1) ^ 1u), kSiteTmemEmpty);
-          ptx::tc_fence_after();
+        // ---- this warp's 32 rows x 64 columns of the tile
+        {
+          uint32_t r0[32], r1[32];
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint32_t r[32];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              r[2 * j] = static_cast<uint32_t>(bs_acc[g * 16 + j]);
-              r[2 * j + 1] = static_cast<uint32_t>(bs_acc[g * 16 + j] >> 32);
-            }
-            ptx::tmem_st_32x32b_x32(xaddr + g * 32, r);
+          for (int j = 0; j < 16; ++j) {
+            r0[2 * j] = static_cast<uint32_t>(bs_acc[j]);
+            r0[2 * j + 1] = static_cast<uint32_t>(bs_acc[j] >> 32);
+            r1[2 * j] = static_cast<uint32_t>(bs_acc[16 + j]);
+            r1[2 * j + 1] = static_cast<uint32_t>(bs_acc[16 + j] >> 32);
           }
-          ptx::tmem_st_wait();
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(xfull_bar);
-        } else {
-          if (lane == 0) mbar_wait(wc, xfull_bar, (it & 1), kSiteTmemFull);
-          __syncwarp();
-          mbar_wait(wc, xfull_bar, (it & 1), kSiteTmemFull);
-          ptx::tc_fence_after();
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t r0[32], r1[32];
-            ptx::tmem_ld_32x32b_x32(xaddr + h * 64, r0);
-            ptx::tmem_ld_32x32b_x32(xaddr + h * 64 + 32, r1);
-            ptx::tmem_ld_wait();
-            if (h == 1) {
-              ptx::tc_fence_before();
-              __syncwarp();
-              if (lane == 0) ptx::mbar_arrive(xempty_bar);
-            }
-            const uint64_t one2 = ptx::pack_f32x2(1.f, 1.f);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const uint64_t a0 = ptx::ffma2(ptx::pack_b32x2(r0[2 * j], r0[2 * j + 1]), one2, bs_acc[h * 32 + j]);
-              const uint64_t a1 =
-                  ptx::ffma2(ptx::pack_b32x2(r1[2 * j], r1[2 * j + 1]), one2, bs_acc[h * 32 + 16 + j]);
-              r0[2 * j] = static_cast<uint32_t>(a0);
-              r0[2 * j + 1] = static_cast<uint32_t>(a0 >> 32);
-              r1[2 * j] = static_cast<uint32_t>(a1);
-              r1[2 * j + 1] = static_cast<uint32_t>(a1 >> 32);
-            }
-            emit_chunk(r0, r1, c.n0 + h * 64, row, grow, m_cta + q * 32, tmd, z, own_rs);
-          }
+          emit_chunk(r0, r1, c.n0 + half * 64, row, grow, m_cta + q * 32, tmd, z, own_rs);
         }
       } else if constexpr (Cfg::MT == 2) {
         // both row halves of the tile complete together; accumulator 0 is drained (and handed
@@ -1315,13 +1292,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         // Arrival counting runs one tile behind: waiting for this tile's stores to land would
         // stall the warp for an NVLink round trip, so wait only for the previous tile's (all but
         // the store groups committed for this tile) and count that one.
-        // (block-scaled variant: only the set that stored this tile takes part)
-        const bool stored = !Cfg::BS || ((it & 1) == (ew >> 2));
+        const bool stored = true;
         if (stored) {
           if (lane == 0) {
             // store groups this warp committed for a whole tile; a piece of a split tile commits
             // fewer, so there everything is waited for
-            constexpr int kGroupsPerTile = Cfg::BS ? 2 : Cfg::MT * BN / 64;
+            constexpr int kGroupsPerTile = Cfg::BS ? 1 : Cfg::MT * BN / 64;
             if (c.shift == 0) ptx::bulk_wait<kGroupsPerTile>();
             else ptx::bulk_wait<0>();
             if (pend_seg >= 0) rs_arrive(pend_seg, pend_mt, pend_chunks);
@@ -1329,7 +1305,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           // tiles of the own segment stay here: nobody is told
           pend_seg = own_rs ? -1 : c.seg;
           pend_mt = c.m_tile;
-          pend_chunks = Cfg::BS ? 2u : static_cast<uint32_t>(Cfg::MT * ((BN >> c.shift) / 64));
+          pend_chunks = Cfg::BS ? 1u : static_cast<uint32_t>(Cfg::MT * ((BN >> c.shift) / 64));
         }
         __syncwarp();
       }

@@ -49,13 +49,15 @@ def blockscale_args(a, w, sa, sb, bias, out_dtype, m, status=None, keep=None) ->
         raise ValueError("K and N must be multiples of 128")
     if sa.dtype != torch.float32 or sb.dtype != torch.float32 or not sa.is_contiguous() or not sb.is_contiguous():
         raise TypeError("scales must be contiguous float32 tensors")
-    if sa.dim() != 3 or sa.shape[1] != K // BLOCK or sa.shape[2] != BLOCK:
-        raise ValueError(f"input_scale must be [rows/128, {K // BLOCK}, 128], got {tuple(sa.shape)}")
-    if tuple(sb.shape) != (N // BLOCK, K // BLOCK):
-        raise ValueError(f"weight_scale must be [{N // BLOCK}, {K // BLOCK}], got {tuple(sb.shape)}")
+    if sa.dim() != 3 or sa.shape[1] != K // BLOCK or sa.shape[2] != BLOCK or sa.shape[0] < -(-a.shape[0] // BLOCK):
+        raise ValueError(f"input_scale must be [ceil(rows/128), {K // BLOCK}, 128], got {tuple(sa.shape)}")
+    groupwise = sb.dim() == 3
+    if tuple(sb.shape) not in ((N // BLOCK, K // BLOCK), (N // BLOCK, K // BLOCK, BLOCK)):
+        raise ValueError(f"weight_scale must be [{N // BLOCK}, {K // BLOCK}] or, one per weight row, "
+                         f"[{N // BLOCK}, {K // BLOCK}, {BLOCK}]; got {tuple(sb.shape)}")
     args = _dense.base_args(a, w, bias, out_dtype, tile_n=128, cta_group=1, m=m, status=status, keep=keep)
     args.sa, args.sb = sa.data_ptr(), sb.data_ptr()
-    args.blockscale = 1
+    args.blockscale = 2 if groupwise else 1
     return args
 
 
@@ -75,9 +77,8 @@ class BlockScaleGemm:
         if input_scale is None or weight_scale is None:
             raise ValueError("block-scaled GEMM needs input_scale and weight_scale")
         M, N = input.shape[0], weight.shape[0]
-        if weight_scale.dim() == 3 or not input.is_cuda or M % BLOCK:
-            # per-column weight scales (the wgrad form), CPU tensors and ragged M go through the
-            # PyTorch statement of the op
+        if not input.is_cuda:
+            # CPU tensors go through the PyTorch statement of the op
             res = blockscale_gemm_torch(input, weight, input_scale, weight_scale, self.output_dtype, bias)
             if output is not None:
                 output.copy_(res)
@@ -102,6 +103,7 @@ class BlockScaleGemm:
     def _per_expert(self, input, input_splits: Sequence[int], weight, bias, output, input_scale, weight_scale):
         M, N = input.shape[0], weight.shape[1]
         out = output if output is not None else torch.empty((M, N), dtype=self.output_dtype, device=input.device)
+        # (splits normally live on the host, as in the reference; a device tensor costs one sync here)
         splits = [int(v) for v in (input_splits.tolist() if torch.is_tensor(input_splits) else input_splits)]
         row = 0
         for e, cnt in enumerate(splits):

@@ -411,6 +411,15 @@ def load_tuning_record(record) -> None:
 def bsr_reduce(input: torch.Tensor, output: torch.Tensor, block_h: int = 128, block_w: int = 128) -> torch.Tensor:
     """output[M, N] = sum over dim 0 of input[B, M, N] (reference: ``flux.bsr_reduce``; the block
     sizes only shaped the reference kernel's grid)."""
+    if (input.is_cuda and input.dtype in (torch.bfloat16, torch.float16) and input.dtype == output.dtype
+            and input.is_contiguous() and output.is_contiguous() and input.shape[-1] % 8 == 0):
+        B, M, N = input.shape
+        rc = _native.lib().fluxb_rows_sum(ctypes.c_void_p(input.data_ptr()), None, ctypes.c_void_p(output.data_ptr()),
+                                          ctypes.c_int64(M), ctypes.c_int(N), ctypes.c_int(B), ctypes.c_int64(M),
+                                          ctypes.c_int(_dense.dtype_code(input.dtype)),
+                                          ctypes.c_void_p(_dense.current_stream_ptr(input.device)))
+        _native.check(rc, "fluxb_rows_sum")
+        return output
     output.copy_(input.float().sum(0).to(output.dtype))
     return output
 

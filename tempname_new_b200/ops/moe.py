@@ -571,9 +571,27 @@ GemmGroupedV3GatherRS.forward_gather_rs_triton_aot = GemmGroupedV3GatherRS.forwa
 
 
 def topk_scatter_reduce(inputs: torch.Tensor, scatter_idx: torch.Tensor, topk: int) -> torch.Tensor:
-    """out[t] = sum_k inputs[scatter_idx[t * topk + k]] (reference: ``flux.topk_scatter_reduce``)."""
+    """out[t] = sum_k inputs[scatter_idx[t * topk + k]] in fp32 (reference: ``flux.topk_scatter_reduce``,
+    src/pybind/gemm_grouped_v3_gather_rs.cc:33). ``inputs`` may be a list of tensors (one per weight
+    group), which are added first."""
+    if isinstance(inputs, (list, tuple)):
+        x = inputs[0] if len(inputs) == 1 else torch.stack([t.float() for t in inputs]).sum(0).to(inputs[0].dtype)
+    else:
+        x = inputs
+    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.shape[1] % 8 == 0:
+        x = x if x.is_contiguous() else x.contiguous()
+        idx = scatter_idx.reshape(-1).to(device=x.device, dtype=torch.int32).contiguous()
+        rows = idx.numel() // topk
+        out = torch.empty((rows, x.shape[1]), dtype=x.dtype, device=x.device)
+        rc = _native.lib().fluxb_rows_sum(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(idx.data_ptr()),
+                                          ctypes.c_void_p(out.data_ptr()), ctypes.c_int64(rows),
+                                          ctypes.c_int(x.shape[1]), ctypes.c_int(topk), ctypes.c_int64(0),
+                                          ctypes.c_int(_dense.dtype_code(x.dtype)),
+                                          ctypes.c_void_p(_dense.current_stream_ptr(x.device)))
+        _native.check(rc, "fluxb_rows_sum")
+        return out
     idx = scatter_idx.reshape(-1, topk).long()
-    return inputs[idx].float().sum(1).to(inputs.dtype)
+    return x[idx].float().sum(1).to(x.dtype)
 
 
 _PAD_ROW = 2 ** 31 - 1    # marks padding rows of a blocked index (INT32_MAX, as in the reference)

@@ -182,6 +182,28 @@ def cmd_combine(a):
                       "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / pk, "peak": src}))
 
 
+def cmd_moe_l1(a):
+    """World-size-1 run of MoE layer 1 with the combine fused in: grouped GEMM whose epilogue sends the
+    gate-weighted rows to their [token][k] slots, and the top-k sum in the tail of the same kernel."""
+    import tempname_new_b200 as flux
+    pg, dev = _single_rank_group()
+    E, topk, H, ffn = a.experts, a.topk, a.hidden, a.ffn
+    g = flux.testing.gen_moe_gating_args(E, topk, a.tokens, device=dev, seed=1)
+    rows = a.tokens * topk
+    act = (torch.randn(rows, ffn, device=dev) * 0.5).bfloat16()
+    w2 = (torch.randn(E, H, ffn, device=dev) * 0.02).bfloat16()
+    gate_rows = g.gate_weight.reshape(-1)[torch.argsort(g.choosed_experts.reshape(-1), stable=True)].contiguous()
+    op = flux.GemmGroupedV3GatherRS(E, rows, H, topk, 0, 1, 1, 1, tp_group=pg)
+    fn = lambda: op.forward_gather_rs(act, w2, g.splits_gpu, g.scatter_index.reshape(-1),  # noqa: E731
+                                      output_vec_scale=gate_rows)
+    ms = timed(fn, a.iters, a.warmup, not a.no_flush)
+    op.check_status()
+    tf = 2.0 * rows * H * ffn / ms / 1e9
+    pk, _, src = peaks()
+    print(json.dumps({"op": "moe_layer1_fused", "tokens": a.tokens, "topk": topk, "experts": E, "hidden": H,
+                      "ffn": ffn, "ms": ms, "tflops": tf, "frac_of_bf16_peak": tf / pk, "peak": src}))
+
+
 def cmd_small(a):
     """In-place cast, routing-index build and row all-gather (world size 1) in one go."""
     import tempname_new_b200 as flux
@@ -215,6 +237,13 @@ def main(argv=None):
     g.add_argument("--cta-group", type=int, default=0)
     g.add_argument("--tile-n", type=int, default=0)
     g.add_argument("--tile-m", type=int, default=0)
+    m1 = sub.add_parser("moe_l1")
+    m1.add_argument("--tokens", type=int, default=8192)
+    m1.add_argument("--topk", type=int, default=8)
+    m1.add_argument("--experts", type=int, default=8)
+    m1.add_argument("--hidden", type=int, default=4096)
+    m1.add_argument("--ffn", type=int, default=1536)
+    m1.set_defaults(fn=cmd_moe_l1)
     g.add_argument("--group-m", type=int, default=0)
     g.set_defaults(fn=cmd_gemm)
     q = sub.add_parser("quant")
@@ -251,7 +280,7 @@ def main(argv=None):
     sm = sub.add_parser("small")
     sm.add_argument("--elems", type=int, default=1 << 26)
     sm.set_defaults(fn=cmd_small)
-    for p in (g, q, b, gg, u, c, sm):
+    for p in (g, q, b, gg, u, c, sm, m1):
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--no-flush", action="store_true")

@@ -112,3 +112,21 @@ def test_moe_index_build(dev, tokens, topk, E):
     assert torch.equal(gather.long(), order // topk)
     assert torch.equal(tki.long(), order % topk)
     assert torch.equal(calc_scatter_index(ce, splits).reshape(-1).long(), ref_scatter)
+
+
+def test_rows_sum_kernels(dev):
+    """topk_scatter_reduce and bsr_reduce on the row-sum kernel against fp32 statements."""
+    import tempname_new_b200 as flux
+    g = torch.Generator(device=dev).manual_seed(4)
+    rows, topk, H = 1000, 4, 384
+    x = torch.randn(rows * topk, H, device=dev, generator=g).bfloat16()
+    idx = torch.randperm(rows * topk, device=dev, generator=g).to(torch.int32)
+    out = flux.topk_scatter_reduce(x, idx, topk)
+    ref = x[idx.long().view(rows, topk)].float().sum(1)
+    assert out.shape == (rows, H)
+    assert (out.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    slabs = torch.randn(6, 300, 256, device=dev, generator=g).half()
+    o2 = torch.empty(300, 256, device=dev, dtype=torch.float16)
+    flux.bsr_reduce(slabs, o2, 128, 128)
+    ref2 = slabs.float().sum(0)
+    assert (o2.float() - ref2).abs().max().item() <= 1e-2 * max(1.0, ref2.abs().max().item())

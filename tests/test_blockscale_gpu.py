@@ -55,3 +55,30 @@ def test_blockscale_bias_and_grouped(dev):
     for e in range(E):
         r = flux.blockscale_gemm_torch(xq[e * 256:(e + 1) * 256], wq3[e], sx[e * 2:(e + 1) * 2], sw3[e], torch.float32)
         assert (outg[e * 256:(e + 1) * 256].float() - r).abs().max().item() <= 2e-2 * max(1.0, r.abs().max().item())
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (1024, 1024, 1024)])
+def test_blockscale_wgrad_form_per_column_weight_scales(dev, M, N, K):
+    """Both operands carry 1x128 scales (weight_scale [N/128, K/128, 128]): the weight-gradient form,
+    on the kernel, against the PyTorch statement."""
+    import tempname_new_b200 as flux
+    x, w, xq, sx, _, _ = _quantized(M, N, K, dev, seed=2)
+    qz = flux.Quantization(torch.bfloat16, torch.float8_e4m3fn)
+    wq, sw, _, _ = qz.quantize_vector_blockwise(w, False)           # 1x128 scales for the weight rows too
+    assert tuple(sw.shape) == (N // 128, K // 128, 128)
+    op = flux.BlockScaleGemm()
+    out = op.wgrad(xq, wq, input_scale=sx, weight_scale=sw)
+    ref = flux.blockscale_gemm_torch(xq, wq, sx, sw, torch.float32)
+    assert (out.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+
+
+def test_blockscale_ragged_rows(dev):
+    """M that is not a multiple of 128: the last row block is partial (its scales exist, rows clipped)."""
+    import tempname_new_b200 as flux
+    M, N, K = 300, 256, 512
+    x, w, xq, sx, wq, sw = _quantized(M, N, K, dev, seed=3)
+    assert sx.shape[0] == 3
+    out = flux.BlockScaleGemm().forward(xq, wq, input_scale=sx, weight_scale=sw)
+    ref = flux.blockscale_gemm_torch(xq, wq, sx, sw, torch.float32)
+    assert out.shape == (M, N)
+    assert (out.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
