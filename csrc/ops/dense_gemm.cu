@@ -221,7 +221,9 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     // (one rank: the last row block may be partial - its scales exist, its rows are clipped)
     FLUXB_REQUIRE(!multi || (a->M / a->world) % 128 == 0,
                   "block-scaled fused ops need rows per rank in multiples of 128");
-    cg = 1;
+    // CTA pairs on 256 x 128 tiles (half of B per CTA) unless the caller pins single CTAs or a segment
+    // is shorter than one pair tile
+    cg = (a->cta_group == 1 || a->M / (multi ? a->world : 1) < 256) ? 1 : 2;
     bn = 128;
   } else if (a->mode == FLUXB_A2A_GEMM) {
     if (cg == 2 && a->M >= 256) bn = 256;
@@ -547,6 +549,10 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     if (p.wave_ctr != nullptr && coop_env != 0) coop = true;
   }
   if (a->blockscale) {
+    if (cg == 2) {
+      if (p.mode == kModeAllGather) return launch_dense<DenseCfg<128, 1, 5, 2, 32768, true>>(p, grid, stream, coop);
+      return launch_dense<DenseCfg<128, 1, 6, 2, 0, true>>(p, grid, stream, coop);
+    }
     if (p.mode == kModeAllGather) return launch_dense<DenseCfg<128, 1, 4, 1, 32768, true>>(p, grid, stream, coop);
     return launch_dense<DenseCfg<128, 1, 5, 1, 0, true>>(p, grid, stream, coop);
   }

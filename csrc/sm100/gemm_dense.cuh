@@ -154,7 +154,9 @@ struct DenseGemmParams {
 // BS_ = true: block-scaled fp8 (1x128 A scales, 128x128 B scales): every 128-deep k-block is
 // accumulated into a fresh TMEM buffer (four of them, so the issuer runs up to four k-blocks ahead)
 // and promoted into fp32 registers, multiplied by its scales, by eight epilogue warps: two per
-// TMEM lane quadrant, each owning 64 of the tile's 128 columns for the whole tile.
+// TMEM lane quadrant, each owning 64 of the tile's 128 columns for the whole tile. With CG_ = 2 a
+// CTA pair shares a 256 x 128 tile (each CTA loads half of B): 24 KB instead of 32 KB enter an SM
+// per k-block, which matters because at fp8 rates 128 x 128 tiles are bound by L2 -> SM bandwidth.
 template <int BN_, int KIND_, int STAGES_, int CG_ = 1, int COMM_ = 0, bool BS_ = false, int MT_ = 1>
 struct DenseCfg {
   static constexpr int COMM_BYTES = COMM_;
@@ -165,7 +167,7 @@ struct DenseCfg {
   // MT_ == 1: two accumulators used alternately (the epilogue of a tile overlaps the next main loop);
   // MT_ == 2: the two row halves of one tile; block-scaled: 4 k-block buffers
   static constexpr int ACC_BUFS = BS_ ? 4 : 2;
-  static_assert(!BS_ || (KIND_ == 1 && BN_ == 128 && CG_ == 1), "block-scaled variant: fp8, 128x128 tiles");
+  static_assert(!BS_ || (KIND_ == 1 && BN_ == 128), "block-scaled variant: fp8, 128 columns (128 or 256 rows)");
   static_assert(MT_ == 1 || (MT_ == 2 && CG_ == 2 && BN_ == 256 && !BS_), "512-row tiles: CTA pairs, 256 columns");
   static constexpr int CG = CG_;
   static constexpr int BM_CTA = 128 * MT_;                 // rows of A / D per CTA
@@ -304,7 +306,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     for (int a = 0; a < NACC; ++a) {
       ptx::mbar_init(tfull_bar(a), 1);
       // one epilogue warp per TMEM lane quadrant reads a buffer (block-scaled: two, 64 columns each)
-      ptx::mbar_init(tempty_bar(a), Cfg::BS ? 8 : 4 * CG);
+      ptx::mbar_init(tempty_bar(a), Cfg::BS ? 8 * CG : 4 * CG);
     }
     for (int i = 0; i < 8; ++i) ptx::mbar_init(ring_bar_base + 8u * i, 1);
     *abort_word = 0;
@@ -493,8 +495,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             for (int k = 0; k < BK / Cfg::UMMA_K; ++k)
               ptx::umma_ss<CG, Cfg::KIND>(tmem_base + buf * BN, adesc + 2u * k, bdesc + 2u * k, idesc,
                                           k != 0 ? 1u : 0u);
-            ptx::umma_commit(empty_bar(stage));
-            ptx::umma_commit(tfull_bar(buf));
+            if constexpr (CG == 1) {
+              ptx::umma_commit(empty_bar(stage));
+              ptx::umma_commit(tfull_bar(buf));
+            } else {
+              ptx::umma_commit_cg2(empty_bar(stage), 3);
+              ptx::umma_commit_cg2(tfull_bar(buf), 3);
+            }
             if (++stage == STAGES) {
               stage = 0;
               phase ^= 1u;
@@ -1195,7 +1202,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           ptx::tmem_ld_wait();
           ptx::tc_fence_before();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+          if (lane == 0) {
+            if constexpr (CG == 1) ptx::mbar_arrive(tempty_bar(buf));
+            else ptx::mbar_arrive_remote(tempty_bar(buf), 0);
+          }
           if (p.sb_groupwise) {
             // per-column weight scales of this k-block: 64 floats of this warp's columns, the same for every row
             const float4* sbv =

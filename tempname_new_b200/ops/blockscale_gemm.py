@@ -9,6 +9,7 @@ by ``Quantization``. ``blockscale_gemm_torch`` states the same math in PyTorch (
 ``test/python/gemm_only/test_blockwise_scale_gemm_only.py:200-261``)."""
 from __future__ import annotations
 
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -55,7 +56,10 @@ def blockscale_args(a, w, sa, sb, bias, out_dtype, m, status=None, keep=None) ->
     if tuple(sb.shape) not in ((N // BLOCK, K // BLOCK), (N // BLOCK, K // BLOCK, BLOCK)):
         raise ValueError(f"weight_scale must be [{N // BLOCK}, {K // BLOCK}] or, one per weight row, "
                          f"[{N // BLOCK}, {K // BLOCK}, {BLOCK}]; got {tuple(sb.shape)}")
-    args = _dense.base_args(a, w, bias, out_dtype, tile_n=128, cta_group=1, m=m, status=status, keep=keep)
+    # 128-column tiles; the launcher pairs CTAs on 256 x 128 tiles when the rows allow (FLUXB_BS_CTA_GROUP=1 pins
+    # single CTAs)
+    args = _dense.base_args(a, w, bias, out_dtype, tile_n=128, cta_group=int(os.environ.get("FLUXB_BS_CTA_GROUP", "0")),
+                            m=m, status=status, keep=keep)
     args.sa, args.sb = sa.data_ptr(), sb.data_ptr()
     args.blockscale = 2 if groupwise else 1
     return args
