@@ -204,6 +204,13 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   p.sa = a->sa;
   p.sb = a->sb;
   p.sb_groupwise = a->blockscale == 2 ? 1 : 0;
+  {
+    static const int rel_env = [] {
+      const char* e = getenv("FLUXB_BS_RELEASE_ARRIVE");
+      return e ? atoi(e) : 0;
+    }();
+    p.bs_release_arrive = rel_env;
+  }
   p.ab_fmt = (a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP8_E5M2 || a->in_dtype == FLUXB_INT8) ? 1 : 0;
   p.out_f16 = a->out_dtype == FLUXB_FP16 ? 1 : 0;
   p.act = a->act;
@@ -221,9 +228,10 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     // (one rank: the last row block may be partial - its scales exist, its rows are clipped)
     FLUXB_REQUIRE(!multi || (a->M / a->world) % 128 == 0,
                   "block-scaled fused ops need rows per rank in multiples of 128");
-    // CTA pairs on 256 x 128 tiles (half of B per CTA) unless the caller pins single CTAs or a segment
-    // is shorter than one pair tile
-    cg = (a->cta_group == 1 || a->M / (multi ? a->world : 1) < 256) ? 1 : 2;
+    // Single CTAs on 128 x 128 tiles. CTA pairs on 256 x 128 tiles (half of B per CTA) exist and are
+    // chosen by cta_group = 2, but measured slower (977 against 1128 TFLOP/s at 16384 x 3584 x 8192): the
+    // k-block hand-over then waits for the slowest of sixteen promotion warps on two SMs.
+    cg = (a->cta_group == 2 && a->M / (multi ? a->world : 1) >= 256) ? 2 : 1;
     bn = 128;
   } else if (a->mode == FLUXB_A2A_GEMM) {
     if (cg == 2 && a->M >= 256) bn = 256;

@@ -103,7 +103,7 @@ struct DenseGemmParams {
   const float* sa_land;          // for the rows of tm_a_land: [W*seg_rows/128, K/128, 128]
   const float* sb;               // [N/128, K/128], or with sb_groupwise [N/128, K/128, 128] (one per column)
   int32_t sb_groupwise;          // 1: the weight carries 1x128 scales too (the weight-gradient form)
-  int32_t reserved6;
+  int32_t bs_release_arrive;     // 1: the peer CTA's TMEM hand-over arrives with release ordering
   const float* ag_scale_src;     // all-gather: this rank's A scales (== sa), pushed with the shard
   float* ag_scale_land[kMaxRanks];
   // all-gather
@@ -1160,10 +1160,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         const int half = ew >> 2;
         const int kbs = k_blocks;                               // scale blocks along K (BK == 128)
         const float* sa_rows = p.sa;
-        int64_t srow = grow;                                    // row in the scale tensor's frame
+        // rows of a pair tile past the end of the segment (their results are clipped by the store) have no
+        // scales: they read those of the segment's first row
+        const int row_s = row < ((p.seg_rows + 127) & ~127) ? row : 0;
+        int64_t srow = static_cast<int64_t>(c.seg) * p.seg_rows + row_s;   // row in the scale tensor's frame
         if (p.mode == kModeAllGather && multi) {
           if (c.seg == p.rank) {
-            srow = row;
+            srow = row_s;
           } else {
             sa_rows = p.sa_land;
             // the scales travelled with the shard: make this thread's reads follow the flag
@@ -1179,18 +1182,28 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
 #pragma unroll
         for (int j = 0; j < 32; ++j) bs_acc[j] = 0ull;
         const uint32_t n0 = static_cast<uint32_t>(it) * kbs;
-        // scales of the next k-block are fetched while this one is promoted
-        float sa_next = sa_ptr[0];
-        float sb_next = p.sb_groupwise ? 1.f : sb_ptr[0];
-        for (int kb = 0; kb < kbs; ++kb) {
+        // Scales are fetched four k-blocks at a time, one group ahead: a fetch per k-block, used one
+        // k-block later, put the latency of a global load into every iteration.
+        float csa[4], csb[4], nsa[4], nsb[4];
+        auto load_scales = [&](int kb0, float* dsa, float* dsb) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int kk = kb0 + i < kbs ? kb0 + i : kbs - 1;   // past the end: a repeated, unused load
+            dsa[i] = sa_ptr[static_cast<int64_t>(kk) * 128];
+            dsb[i] = p.sb_groupwise ? 1.f : sb_ptr[kk];
+          }
+        };
+        load_scales(0, csa, csb);
+        for (int kb0 = 0; kb0 < kbs; kb0 += 4) {
+        load_scales(kb0 + 4, nsa, nsb);
+#pragma unroll
+        for (int ki = 0; ki < 4; ++ki) {
+          const int kb = kb0 + ki;
+          if (kb >= kbs) break;
           const uint32_t n = n0 + kb;
           const int buf = n % NACC;
           const uint32_t par = (n / NACC) & 1u;
-          const float sc = sa_next * sb_next;
-          if (kb + 1 < kbs) {
-            sa_next = sa_ptr[static_cast<int64_t>(kb + 1) * 128];
-            if (!p.sb_groupwise) sb_next = sb_ptr[kb + 1];
-          }
+          const float sc = csa[ki] * csb[ki];
           const uint64_t sc2 = ptx::pack_f32x2(sc, sc);
           if (lane == 0) mbar_wait(wc, tfull_bar(buf), par, kSiteTmemFull);
           __syncwarp();
@@ -1203,8 +1216,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) {
-            if constexpr (CG == 1) ptx::mbar_arrive(tempty_bar(buf));
-            else ptx::mbar_arrive_remote(tempty_bar(buf), 0);
+            // the buffer's contents are in registers (wait::ld): the hand-over needs no release ordering,
+            // which would also wait for the scale loads in flight
+            if (CG == 1 || cta_rank == 0) ptx::mbar_arrive(tempty_bar(buf));
+            else if (p.bs_release_arrive) ptx::mbar_arrive_remote(tempty_bar(buf), 0);
+            else ptx::mbar_arrive_remote_relaxed(tempty_bar(buf), 0);
           }
           if (p.sb_groupwise) {
             // per-column weight scales of this k-block: 64 floats of this warp's columns, the same for every row
@@ -1229,6 +1245,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
               bs_acc[16 + j] = ptx::ffma2(ptx::pack_b32x2(r1[2 * j], r1[2 * j + 1]), sc2, bs_acc[16 + j]);
             }
           }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          csa[i] = nsa[i];
+          csb[i] = nsb[i];
+        }
         }
         // ---- this warp's 32 rows x 64 columns of the tile
         {

@@ -79,6 +79,19 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t bar, uint32_t cta_ra
       "r"(cta_rank)
       : "memory");
 }
+// The same without release ordering: for a hand-over whose data is already safe when the arrive is
+// issued (TMEM reads completed by tcgen05.wait::ld), so that the arrive does not wait for the warp's
+// unrelated global loads in flight.
+__device__ __forceinline__ void mbar_arrive_remote_relaxed(uint32_t bar, uint32_t cta_rank) {
+  asm volatile(
+      "{\n"
+      " .reg .b32 ra;\n"
+      " mapa.shared::cluster.u32 ra, %0, %1;\n"
+      " mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [ra];\n"
+      "}\n" ::"r"(bar),
+      "r"(cta_rank)
+      : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(

@@ -56,9 +56,8 @@ def blockscale_args(a, w, sa, sb, bias, out_dtype, m, status=None, keep=None) ->
     if tuple(sb.shape) not in ((N // BLOCK, K // BLOCK), (N // BLOCK, K // BLOCK, BLOCK)):
         raise ValueError(f"weight_scale must be [{N // BLOCK}, {K // BLOCK}] or, one per weight row, "
                          f"[{N // BLOCK}, {K // BLOCK}, {BLOCK}]; got {tuple(sb.shape)}")
-    # 128-column tiles; the launcher pairs CTAs on 256 x 128 tiles when the rows allow (FLUXB_BS_CTA_GROUP=1 pins
-    # single CTAs)
-    args = _dense.base_args(a, w, bias, out_dtype, tile_n=128, cta_group=int(os.environ.get("FLUXB_BS_CTA_GROUP", "0")),
+    # 128-column tiles on single CTAs; FLUXB_BS_CTA_GROUP=2 pairs CTAs on 256 x 128 tiles when the rows allow
+    args = _dense.base_args(a, w, bias, out_dtype, tile_n=128, cta_group=int(os.environ.get("FLUXB_BS_CTA_GROUP", "1")),
                             m=m, status=status, keep=keep)
     args.sa, args.sb = sa.data_ptr(), sb.data_ptr()
     args.blockscale = 2 if groupwise else 1
