@@ -85,6 +85,10 @@ typedef struct {
    * done, 7 total ns the producer spent waiting for arrival flags, 8 + j: K slice j of the first tile
    * became readable (post-attention mode). Null = off. */
   uint64_t* trace;
+  int32_t b_kn;              /* 1: b is [K, N] with N contiguous and ldb elements between k-rows (a weight held
+                                transposed, e.g. for the data gradient): read in place as an MN-major operand;
+                                16-bit inputs, not block-scaled */
+  int32_t reserved_tail;
 } fluxb_dense_args_t;
 
 int fluxb_dense_gemm(const fluxb_dense_args_t* args);

@@ -204,6 +204,9 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   p.sa = a->sa;
   p.sb = a->sb;
   p.sb_groupwise = a->blockscale == 2 ? 1 : 0;
+  p.b_kn = a->b_kn ? 1 : 0;
+  FLUXB_REQUIRE(!a->b_kn || (in16 && !a->blockscale), "a [K, N] weight is read in place for 16-bit inputs only");
+  FLUXB_REQUIRE(!a->b_kn || (a->ldb % 8 == 0 && a->N % 8 == 0), "[K, N] weight: N and its row pitch in multiples of 8");
   {
     static const int rel_env = [] {
       const char* e = getenv("FLUXB_BS_RELEASE_ARRIVE");
@@ -262,6 +265,8 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
       mt = 2;
     }
   }
+  FLUXB_REQUIRE(!a->b_kn || (bn / cg) % 64 == 0,
+                "[K, N] weight: 64-column operand boxes need tile_n / cta_group in multiples of 64");
   const int bm = 128 * cg * mt;
   const int bk = 128 / elt;
   const CUtensorMapDataType in_dt =
@@ -506,7 +511,7 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     }();
     const int64_t slots = grid / cg;
     const int64_t rest = tiles % slots;
-    if (split_env != 0 && bn == 256 && !a->blockscale && rest > 0) {
+    if (split_env != 0 && bn == 256 && !a->blockscale && !a->b_kn && rest > 0) {
       int shift = 0;
       if (4 * rest <= slots && split_env >= 1) shift = 2;
       else if (2 * rest <= slots) shift = 1;
@@ -522,6 +527,13 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     uint64_t dims[2] = {static_cast<uint64_t>(a->K), static_cast<uint64_t>(a->N)};
     uint64_t str[1] = {static_cast<uint64_t>(a->ldb) * elt};
     uint32_t box[2] = {static_cast<uint32_t>(bk), static_cast<uint32_t>(bn / cg)};
+    if (a->b_kn) {
+      // [K, N], N contiguous: boxes of 64 columns x bk k-rows (128-byte rows along N)
+      dims[0] = static_cast<uint64_t>(a->N);
+      dims[1] = static_cast<uint64_t>(a->K);
+      box[0] = 64;
+      box[1] = static_cast<uint32_t>(bk);
+    }
     if ((rc = encode_tmap(&p.tm_b, in_dt, 2, a->b, dims, str, box, Swz::B128))) return rc;
     if (p.split_shift >= 1) {
       box[1] = static_cast<uint32_t>(bn / cg / 2);

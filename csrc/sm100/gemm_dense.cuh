@@ -103,6 +103,7 @@ struct DenseGemmParams {
   const float* sa_land;          // for the rows of tm_a_land: [W*seg_rows/128, K/128, 128]
   const float* sb;               // [N/128, K/128], or with sb_groupwise [N/128, K/128, 128] (one per column)
   int32_t sb_groupwise;          // 1: the weight carries 1x128 scales too (the weight-gradient form)
+  int32_t b_kn;                  // 1: B is [K, N] with N contiguous (16-bit inputs): MN-major operand tiles
   int32_t bs_release_arrive;     // 1: the peer CTA's TMEM hand-over arrives with release ordering
   const float* ag_scale_src;     // all-gather: this rank's A scales (== sa), pushed with the shard
   float* ag_scale_land[kMaxRanks];
@@ -437,7 +438,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             else if (a2a_in) ptx::tma_load_4d(sa, &p.tm_a_land4, full_bar(stage), own_col, m_cta, own_head, ld_src);
             else if (p.l2_hints) ptx::tma_load_2d_hint(sa, tma, full_bar(stage), kb * BK, a_row, pol_a);
             else ptx::tma_load_2d(sa, tma, full_bar(stage), kb * BK, a_row);
-            if (p.l2_hints) ptx::tma_load_2d_hint(sa + Cfg::A_BYTES, tmb, full_bar(stage), kb * BK, b_row, pol_b);
+            if (Cfg::KIND == 0 && p.b_kn) {
+              // B as [K, N]: boxes of 64 columns x BK k-rows, one after the other
+#pragma unroll
+              for (int j = 0; j < Cfg::B_ROWS_CTA / 64; ++j)
+                ptx::tma_load_2d(sa + Cfg::A_BYTES + j * (BK * 128), tmb, full_bar(stage), b_row + j * 64, kb * BK);
+            } else if (p.l2_hints) ptx::tma_load_2d_hint(sa + Cfg::A_BYTES, tmb, full_bar(stage), kb * BK, b_row, pol_b);
             else ptx::tma_load_2d(sa + Cfg::A_BYTES, tmb, full_bar(stage), kb * BK, b_row);
           } else {
             // both CTAs' bytes are counted on the leader's barrier
@@ -447,7 +453,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             else if (a2a_in) ptx::tma_load_4d_cg2(sa, &p.tm_a_land4, fb, own_col, m_cta, own_head, ld_src);
             else if (p.l2_hints) ptx::tma_load_2d_cg2_hint(sa, tma, fb, kb * BK, a_row, pol_a);
             else ptx::tma_load_2d_cg2(sa, tma, fb, kb * BK, a_row);
-            if (p.l2_hints) ptx::tma_load_2d_cg2_hint(sa + Cfg::A_BYTES, tmb, fb, kb * BK, b_row, pol_b);
+            if (Cfg::KIND == 0 && p.b_kn) {
+#pragma unroll
+              for (int j = 0; j < Cfg::B_ROWS_CTA / 64; ++j)
+                ptx::tma_load_2d_cg2(sa + Cfg::A_BYTES + j * (BK * 128), tmb, fb, b_row + j * 64, kb * BK);
+            } else if (p.l2_hints) ptx::tma_load_2d_cg2_hint(sa + Cfg::A_BYTES, tmb, fb, kb * BK, b_row, pol_b);
             else ptx::tma_load_2d_cg2(sa + Cfg::A_BYTES, tmb, fb, kb * BK, b_row);
           }
           if (++stage == STAGES) {
@@ -469,7 +479,16 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && leader) {
       // one instruction covers 128 rows per CTA of the group
-      const uint32_t idesc_full = ptx::umma_idesc(p.ab_fmt, p.ab_fmt, 128 * CG, BN, 0, 0, Cfg::KIND == 2 ? 2u : 1u);
+      // B as [K, N] (16-bit inputs): MN-major operand tiles - 64-column groups BK * 128 bytes apart, 8-k-row
+      // groups 1024 bytes apart, one UMMA_K step = 16 k-rows of 128 bytes
+      const bool b_kn = Cfg::KIND == 0 && p.b_kn != 0;
+      const uint32_t b_major = b_kn ? 1u : 0u;
+      const uint32_t bstep = b_kn ? static_cast<uint32_t>(Cfg::UMMA_K * 128) >> 4 : 2u;
+      auto make_bdesc = [&](uint32_t saddr) -> uint64_t {
+        return b_kn ? ptx::umma_desc_mn_sw128(saddr, BK * 128, 1024) : ptx::umma_desc_k_sw128(saddr);
+      };
+      const uint32_t idesc_full =
+          ptx::umma_idesc(p.ab_fmt, p.ab_fmt, 128 * CG, BN, 0, b_major, Cfg::KIND == 2 ? 2u : 1u);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -478,15 +497,28 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         // a column piece of a split tile is a narrower instruction on the same operands
         const int shift = t >= p.split_from ? p.split_shift : 0;
         const uint32_t idesc = shift == 0 ? idesc_full
-                                          : ptx::umma_idesc(p.ab_fmt, p.ab_fmt, 128 * CG, BN >> shift, 0, 0,
+                                          : ptx::umma_idesc(p.ab_fmt, p.ab_fmt, 128 * CG, BN >> shift, 0, b_major,
                                                             Cfg::KIND == 2 ? 2u : 1u);
         if constexpr (Cfg::BS) {
           // every k-block goes to its own TMEM buffer; the epilogue warps promote it
           for (int kb = 0; kb < k_blocks; ++kb) {
             const uint32_t n = static_cast<uint32_t>(it) * k_blocks + kb;
             const int buf = n % NACC;
+#ifdef FLUXB_DEBUG_CHECKS
+            const long long pc0 = clock64();
+#endif
             mbar_wait(wc, tempty_bar(buf), ((n / NACC) & 1u) ^ 1u, kSiteTmemEmpty);
+#ifdef FLUXB_DEBUG_CHECKS
+            const long long pc1 = clock64();
+#endif
             mbar_wait(wc, full_bar(stage), phase, kSiteSmemFull);
+#ifdef FLUXB_DEBUG_CHECKS
+            if (p.trace != nullptr) {
+              // self-checking build: cycles the issuer waited for a free TMEM buffer / for operands
+              p.trace[blockIdx.x * kTraceWords + 12] += static_cast<uint64_t>(pc1 - pc0);
+              p.trace[blockIdx.x * kTraceWords + 13] += static_cast<uint64_t>(clock64() - pc1);
+            }
+#endif
             ptx::tc_fence_after();
             const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
             const uint64_t adesc = ptx::umma_desc_k_sw128(sa);
@@ -519,10 +551,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           auto issue_half = [&](int st, int half, bool first) {
             const uint32_t sa = smem_base + st * Cfg::STAGE_BYTES;
             const uint64_t adesc = ptx::umma_desc_k_sw128(sa + half * Cfg::A_HALF_BYTES);
-            const uint64_t bdesc = ptx::umma_desc_k_sw128(sa + Cfg::A_BYTES);
+            const uint64_t bdesc = make_bdesc(sa + Cfg::A_BYTES);
 #pragma unroll
             for (int k = 0; k < BK / Cfg::UMMA_K; ++k)
-              ptx::umma_ss<CG, Cfg::KIND>(tmem_base + half * BN, adesc + 2u * k, bdesc + 2u * k, idesc,
+              ptx::umma_ss<CG, Cfg::KIND>(tmem_base + half * BN, adesc + 2u * k, bdesc + bstep * k, idesc,
                                           (!first || k != 0) ? 1u : 0u);
           };
           mbar_wait(wc, tempty_bar(0), par_e, kSiteTmemEmpty);
@@ -574,11 +606,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           ptx::tc_fence_after();
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
           const uint64_t adesc = ptx::umma_desc_k_sw128(sa);
-          const uint64_t bdesc = ptx::umma_desc_k_sw128(sa + Cfg::A_BYTES);
+          const uint64_t bdesc = make_bdesc(sa + Cfg::A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / Cfg::UMMA_K; ++k) {
             // 32 bytes per UMMA_K step inside the 128-byte swizzled row: +2 in 16-byte units
-            ptx::umma_ss<CG, Cfg::KIND>(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc,
+            ptx::umma_ss<CG, Cfg::KIND>(d_tmem, adesc + 2u * k, bdesc + bstep * k, idesc,
                                         (kb | k) != 0 ? 1u : 0u);
           }
           if constexpr (CG == 1) ptx::umma_commit(empty_bar(stage));
@@ -1189,8 +1221,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int kk = kb0 + i < kbs ? kb0 + i : kbs - 1;   // past the end: a repeated, unused load
-            dsa[i] = sa_ptr[static_cast<int64_t>(kk) * 128];
-            dsb[i] = p.sb_groupwise ? 1.f : sb_ptr[kk];
+            dsa[i] = (p.bs_release_arrive & 8) ? 1.f : sa_ptr[static_cast<int64_t>(kk) * 128];
+            dsb[i] = (p.sb_groupwise || (p.bs_release_arrive & 8)) ? 1.f : sb_ptr[kk];
           }
         };
         load_scales(0, csa, csb);
@@ -1205,24 +1237,51 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           const uint32_t par = (n / NACC) & 1u;
           const float sc = csa[ki] * csb[ki];
           const uint64_t sc2 = ptx::pack_f32x2(sc, sc);
+#ifdef FLUXB_DEBUG_CHECKS
+          const long long pc0 = clock64();
+#endif
           if (lane == 0) mbar_wait(wc, tfull_bar(buf), par, kSiteTmemFull);
           __syncwarp();
           mbar_wait(wc, tfull_bar(buf), par, kSiteTmemFull);
           ptx::tc_fence_after();
+#ifdef FLUXB_DEBUG_CHECKS
+          const long long pc1 = clock64();
+#endif
           uint32_t r0[32], r1[32];
+          if (!(p.bs_release_arrive & 4)) {
           ptx::tmem_ld_32x32b_x32(lane_base + buf * BN, r0);
           ptx::tmem_ld_32x32b_x32(lane_base + buf * BN + 32, r1);
           ptx::tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r0[j] = r1[j] = kb + j;
+          }
+#ifdef FLUXB_DEBUG_CHECKS
+          const long long pc2 = clock64();
+#endif
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) {
             // the buffer's contents are in registers (wait::ld): the hand-over needs no release ordering,
             // which would also wait for the scale loads in flight
             if (CG == 1 || cta_rank == 0) ptx::mbar_arrive(tempty_bar(buf));
-            else if (p.bs_release_arrive) ptx::mbar_arrive_remote(tempty_bar(buf), 0);
+            else if (p.bs_release_arrive & 1) ptx::mbar_arrive_remote(tempty_bar(buf), 0);
             else ptx::mbar_arrive_remote_relaxed(tempty_bar(buf), 0);
           }
-          if (p.sb_groupwise) {
+#ifdef FLUXB_DEBUG_CHECKS
+          if (p.trace != nullptr && ew == 0 && lane == 0) {
+            // self-checking build: cycles of epilogue warp 4 per phase of the promotion (the multiply-adds
+            // of k-block kb are charged to the wait of k-block kb + 1 where they are still in flight)
+            uint64_t* tr = p.trace + blockIdx.x * kTraceWords;
+            tr[8] += static_cast<uint64_t>(pc1 - pc0);          // waiting for the k-block's MMAs
+            tr[9] += static_cast<uint64_t>(pc2 - pc1);          // TMEM -> registers
+            tr[10] += static_cast<uint64_t>(clock64() - pc2);   // fence, warp barrier, hand-over
+            tr[11] += 1;                                        // k-blocks
+          }
+#endif
+          if (p.bs_release_arrive & 2) {
+            bs_acc[0] += sc2 + r0[0] + r1[1];
+          } else if (p.sb_groupwise) {
             // per-column weight scales of this k-block: 64 floats of this warp's columns, the same for every row
             const float4* sbv =
                 reinterpret_cast<const float4*>(p.sb + (static_cast<int64_t>(c.n0 >> 7) * kbs + kb) * 128 + half * 64);

@@ -3,6 +3,7 @@ GemmRS."""
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -39,6 +40,7 @@ class DenseArgs(ctypes.Structure):
         ("blockscale", ctypes.c_int32), ("tile_m", ctypes.c_int32),
         ("stream", _VP),
         ("trace", _VP),
+        ("b_kn", ctypes.c_int32), ("reserved_tail", ctypes.c_int32),
     ]
 
 
@@ -141,6 +143,14 @@ class KernelTimeline:
         return out
 
 
+def kn_in_place(w_nk: torch.Tensor) -> bool:
+    """True when ``w_nk`` ([N, K] as the kernels see it) is a transposed view of [K, N] memory that the
+    16-bit kernels can read without a copy (MN-major operand tiles): N contiguous, 16-byte aligned rows."""
+    return (w_nk.dim() == 2 and w_nk.dtype in (torch.bfloat16, torch.float16) and w_nk.stride(0) == 1
+            and w_nk.shape[0] % 8 == 0 and w_nk.stride(1) % 8 == 0 and w_nk.data_ptr() % 16 == 0
+            and os.environ.get("FLUXB_KN_IN_PLACE", "1") != "0")
+
+
 def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
               scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None, *,
               tile_n: int = 0, group_m: int = 0, num_sms: int = 0, act: Optional[str] = None,
@@ -152,8 +162,14 @@ def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], ou
         raise RuntimeError("the sm_100a GEMM kernels need CUDA tensors")
     if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
         raise ValueError(f"shape mismatch: A {tuple(a.shape)} B {tuple(b.shape)} (B is [N, K])")
-    if a.stride(1) != 1 or b.stride(1) != 1:
-        raise ValueError("A and B must have a contiguous K dimension")
+    # B is [N, K]; a transposed view of [K, N] memory (N contiguous) is read in place by the 16-bit kernels
+    b_kn = b.stride(1) != 1 and kn_in_place(b)
+    if b.stride(1) != 1 and not b_kn:
+        b = b.contiguous()
+        if keep is not None:
+            keep.append(b)
+    if a.stride(1) != 1:
+        raise ValueError("A must have a contiguous K dimension")
     if a.dtype != b.dtype:
         raise TypeError("A and B must share a dtype")
     args = DenseArgs()
@@ -161,7 +177,9 @@ def base_args(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], ou
         _TIMELINE.zero_()
         args.trace = _TIMELINE.data_ptr()
     args.a, args.b = a.data_ptr(), b.data_ptr()
-    args.lda, args.ldb = a.stride(0), b.stride(0)
+    args.lda, args.ldb = a.stride(0), (b.stride(1) if b_kn else b.stride(0))
+    args.b_kn = 1 if b_kn else 0
+    args._b_ref = b   # (a re-laid-out copy must outlive the launch)
     args.N, args.K = b.shape[0], a.shape[1]
     args.in_dtype = dtype_code(a.dtype)
     args.out_dtype = dtype_code(out_dtype)

@@ -18,13 +18,15 @@ def _out_dtype(input_dtype: torch.dtype, output_dtype: Optional[torch.dtype]) ->
 
 
 def as_nk(weight: torch.Tensor, transpose_weight: bool) -> torch.Tensor:
-    """The kernels read B as [N, K] with K contiguous. With ``transpose_weight`` the caller
-    holds [K, N]; a [K, N] tensor that is itself a transposed view of contiguous [N, K] memory
-    costs nothing, anything else is re-laid out once per call."""
-    if not transpose_weight:
-        return weight if weight.stride(-1) == 1 else weight.contiguous()
-    w = weight.t()
-    return w if w.stride(-1) == 1 else w.contiguous()
+    """The kernels take B as [N, K]. K contiguous is the native form; 16-bit weights held as [K, N]
+    (``transpose_weight``, or a transposed view passed without it) are read in place as MN-major
+    operand tiles on the GPU. Anything else (8-bit [K, N] weights, odd pitches, CPU tensors' views are
+    fine as they are) is re-laid out once per call."""
+    from ._dense import kn_in_place
+    w = weight.t() if transpose_weight else weight
+    if w.stride(-1) == 1 or (w.is_cuda and kn_in_place(w)):
+        return w
+    return w.contiguous()
 
 
 def apply_act(x: torch.Tensor, act: Optional[str]) -> torch.Tensor:

@@ -54,6 +54,8 @@ def cmd_gemm(a):
     dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp8": torch.float8_e4m3fn}[a.dtype]
     x = torch.randn(a.m, a.k, device=dev).to(dt)
     w = (torch.randn(a.n, a.k, device=dev) * 0.02).to(dt)
+    if a.weight_kn:
+        w = w.t().contiguous().t()   # [N, K] view of [K, N] memory: read in place as MN-major tiles
     out = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16 if dt != torch.float16 else dt)
     if a.impl == "torch":
         fn = lambda: torch.matmul(x, w.t(), out=out)  # noqa: E731
@@ -64,7 +66,8 @@ def cmd_gemm(a):
     tf = 2.0 * a.m * a.n * a.k / ms / 1e9
     pk, _, src = peaks()
     print(json.dumps({"op": "gemm", "impl": a.impl, "m": a.m, "n": a.n, "k": a.k, "dtype": a.dtype,
-                      "cta_group": a.cta_group, "tile_n": a.tile_n, "group_m": a.group_m, "ms": ms,
+                      "cta_group": a.cta_group, "tile_n": a.tile_n, "group_m": a.group_m,
+                      "weight_kn": bool(a.weight_kn), "ms": ms,
                       "tflops": tf, "frac_of_bf16_peak": tf / pk, "peak": src}))
 
 
@@ -237,6 +240,7 @@ def main(argv=None):
     g.add_argument("--cta-group", type=int, default=0)
     g.add_argument("--tile-n", type=int, default=0)
     g.add_argument("--tile-m", type=int, default=0)
+    g.add_argument("--weight-kn", action="store_true", help="hold the weight as [K, N] (read in place)")
     m1 = sub.add_parser("moe_l1")
     m1.add_argument("--tokens", type=int, default=8192)
     m1.add_argument("--topk", type=int, default=8)

@@ -67,6 +67,34 @@ def test_gemm_only_fp16_and_transpose_weight(dev):
     assert (out.float() - ref).abs().max().item() <= 1e-2 * max(1.0, ref.abs().max().item())
 
 
+@pytest.mark.parametrize("M,N,K,knobs", [
+    (512, 384, 320, {}),                                            # 128-wide single-CTA tiles, ragged K
+    (1024, 512, 1024, {"cta_group": 2, "tile_n": 256}),             # CTA pairs, 256 x 256
+    (2048, 1024, 512, {"cta_group": 2, "tile_n": 256, "tile_m": 512}),   # CTA pairs, 512 x 256
+    (1000, 520, 264, {"cta_group": 1, "tile_n": 256}),              # ragged everywhere
+])
+def test_weight_held_as_kn_is_read_in_place(dev, M, N, K, knobs, monkeypatch):
+    """A [K, N] weight (``transpose_weight``) goes to the kernel as it is: MN-major operand tiles.
+    The result must equal both the fp32 statement and the kernel's result on a re-laid-out copy."""
+    import tempname_new_b200 as flux
+    from tempname_new_b200.ops import _dense
+    torch.manual_seed(M + N)
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    w_kn = torch.randn(K, N, device=dev, dtype=torch.bfloat16)     # [K, N], N contiguous
+    assert _dense.kn_in_place(w_kn.t())
+    out = _dense.plain_gemm(a, w_kn.t(), torch.empty(M, N, device=dev, dtype=torch.bfloat16), **knobs)
+    ref = a.float() @ w_kn.float()
+    assert (out.float() - ref).abs().max().item() <= _tol(ref)
+    out_copy = _dense.plain_gemm(a, w_kn.t().contiguous(), torch.empty_like(out), **knobs)
+    assert torch.equal(out, out_copy)
+    # the public op takes the same route
+    op = flux.GemmOnly(torch.bfloat16, transpose_weight=True)
+    assert (op.forward(a, w_kn).float() - ref).abs().max().item() <= _tol(ref)
+    # and the copy is still there for whoever switches the in-place read off
+    monkeypatch.setenv("FLUXB_KN_IN_PLACE", "0")
+    assert (op.forward(a, w_kn).float() - ref).abs().max().item() <= _tol(ref)
+
+
 @pytest.mark.parametrize("dtype", [torch.float8_e4m3fn, torch.float8_e5m2])
 def test_gemm_only_fp8_per_tensor_scale(dev, dtype):
     import tempname_new_b200 as flux
