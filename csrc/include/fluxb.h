@@ -92,6 +92,9 @@ typedef struct {
 } fluxb_dense_args_t;
 
 int fluxb_dense_gemm(const fluxb_dense_args_t* args);
+/* Tile order of the reduce-scatter mode when raster bands span two segments: 1 when the first visited
+ * segment must be a group of its own so that the own segment, visited last, is one too. */
+int fluxb_rs_solo_first(int32_t num_seg);
 /* Host evaluation of the dense kernel's tile order (the function the kernel itself calls):
  * out[3t..3t+2] = (segment, tile row in the segment, first column) of tile t, t < n. No GPU needed. */
 int fluxb_decode_tiles(int32_t num_seg, int32_t seg_first, int32_t m_tiles_seg, int32_t n_tiles,

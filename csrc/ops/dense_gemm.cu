@@ -116,6 +116,10 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
 
 // The tile order of the dense kernel, evaluated on the host by the same function the kernel
 // calls: out[3 * t .. 3 * t + 2] = (segment, tile row inside the segment, first column) of tile t.
+// Reduce-scatter with bands that span two segments: whether the first visited segment is a group of
+// its own, so that the last one (the own segment) is too: W even -> 1 | 2 2 ... 2 | 1, W odd -> 2 ... 2 | 1.
+extern "C" int fluxb_rs_solo_first(int32_t num_seg) { return num_seg % 2 == 0 ? 1 : 0; }
+
 extern "C" int fluxb_decode_tiles(int32_t num_seg, int32_t seg_first, int32_t m_tiles_seg, int32_t n_tiles,
                                   int32_t group_m, int32_t seg_span, int32_t seg_solo_first, int32_t bm,
                                   int32_t bn, int32_t* out, int32_t n) {
@@ -207,13 +211,6 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   p.b_kn = a->b_kn ? 1 : 0;
   FLUXB_REQUIRE(!a->b_kn || (in16 && !a->blockscale), "a [K, N] weight is read in place for 16-bit inputs only");
   FLUXB_REQUIRE(!a->b_kn || (a->ldb % 8 == 0 && a->N % 8 == 0), "[K, N] weight: N and its row pitch in multiples of 8");
-  {
-    static const int rel_env = [] {
-      const char* e = getenv("FLUXB_BS_RELEASE_ARRIVE");
-      return e ? atoi(e) : 0;
-    }();
-    p.bs_release_arrive = rel_env;
-  }
   p.ab_fmt = (a->in_dtype == FLUXB_BF16 || a->in_dtype == FLUXB_FP8_E5M2 || a->in_dtype == FLUXB_INT8) ? 1 : 0;
   p.out_f16 = a->out_dtype == FLUXB_FP16 ? 1 : 0;
   p.act = a->act;
@@ -234,8 +231,10 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     // Single CTAs on 128 x 128 tiles. CTA pairs on 256 x 128 tiles (half of B per CTA) exist and are
     // chosen by cta_group = 2, but measured slower (977 against 1128 TFLOP/s at 16384 x 3584 x 8192): the
     // k-block hand-over then waits for the slowest of sixteen promotion warps on two SMs.
-    cg = (a->cta_group == 2 && a->M / (multi ? a->world : 1) >= 256) ? 2 : 1;
-    bn = 128;
+    cg = (a->cta_group == 2 && a->tile_n != 256 && a->M / (multi ? a->world : 1) >= 256) ? 2 : 1;
+    // 128 x 256 tiles wherever N allows: per-tensor fp8 GEMMs on 128 x 128 tiles stop at 1450 TFLOP/s here (the
+    // operand stream into the SM is the bound), on 128 x 256 at 2600
+    bn = (cg == 1 && a->tile_n != 128 && (a->N % 256 == 0 || a->N >= 2048)) ? 256 : 128;
   } else if (a->mode == FLUXB_A2A_GEMM) {
     if (cg == 2 && a->M >= 256) bn = 256;
     else { cg = 1; bn = 128; }
@@ -488,6 +487,10 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     if (segmented && pair_env != 0 && p.num_seg >= 3 && p.group_m > m_tiles_seg) {
       p.seg_span = 2;
       p.seg_solo_first = p.mode == kModeAllGather ? 1 : 0;
+      // Reduce-scatter: the own segment (visited last) must stay a group of its own. Its tiles wait for
+      // the peers' partial tiles; in a band shared with another segment such a wait would sit in front of
+      // partial tiles that a peer's own tiles wait for in turn, and the ranks would wait in a circle.
+      if (p.mode == kModeReduceScatter) p.seg_solo_first = fluxb_rs_solo_first(p.num_seg);
     }
   }
   if (p.group_m > p.seg_span * m_tiles_seg) p.group_m = p.seg_span * m_tiles_seg;
@@ -572,6 +575,10 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     if (cg == 2) {
       if (p.mode == kModeAllGather) return launch_dense<DenseCfg<128, 1, 5, 2, 32768, true>>(p, grid, stream, coop);
       return launch_dense<DenseCfg<128, 1, 6, 2, 0, true>>(p, grid, stream, coop);
+    }
+    if (bn == 256) {
+      if (p.mode == kModeAllGather) return launch_dense<DenseCfg<256, 1, 3, 1, 32768, true>>(p, grid, stream, coop);
+      return launch_dense<DenseCfg<256, 1, 4, 1, 0, true>>(p, grid, stream, coop);
     }
     if (p.mode == kModeAllGather) return launch_dense<DenseCfg<128, 1, 4, 1, 32768, true>>(p, grid, stream, coop);
     return launch_dense<DenseCfg<128, 1, 5, 1, 0, true>>(p, grid, stream, coop);

@@ -104,7 +104,7 @@ struct DenseGemmParams {
   const float* sb;               // [N/128, K/128], or with sb_groupwise [N/128, K/128, 128] (one per column)
   int32_t sb_groupwise;          // 1: the weight carries 1x128 scales too (the weight-gradient form)
   int32_t b_kn;                  // 1: B is [K, N] with N contiguous (16-bit inputs): MN-major operand tiles
-  int32_t bs_release_arrive;     // 1: the peer CTA's TMEM hand-over arrives with release ordering
+  int32_t reserved7;
   const float* ag_scale_src;     // all-gather: this rank's A scales (== sa), pushed with the shard
   float* ag_scale_land[kMaxRanks];
   // all-gather
@@ -167,8 +167,9 @@ struct DenseCfg {
   static constexpr int THREADS = 128 + 32 * EPI_WARPS;
   // MT_ == 1: two accumulators used alternately (the epilogue of a tile overlaps the next main loop);
   // MT_ == 2: the two row halves of one tile; block-scaled: 4 k-block buffers
-  static constexpr int ACC_BUFS = BS_ ? 4 : 2;
-  static_assert(!BS_ || (KIND_ == 1 && BN_ == 128), "block-scaled variant: fp8, 128 columns (128 or 256 rows)");
+  static constexpr int ACC_BUFS = BS_ ? 512 / BN_ : 2;
+  static_assert(!BS_ || (KIND_ == 1 && (BN_ == 128 || (BN_ == 256 && CG_ == 1))),
+                "block-scaled variant: fp8; 128 columns (128 or 256 rows) or 128 x 256 tiles");
   static_assert(MT_ == 1 || (MT_ == 2 && CG_ == 2 && BN_ == 256 && !BS_), "512-row tiles: CTA pairs, 256 columns");
   static constexpr int CG = CG_;
   static constexpr int BM_CTA = 128 * MT_;                 // rows of A / D per CTA
@@ -187,7 +188,7 @@ struct DenseCfg {
   static constexpr int EPI_BUF_BYTES = 32 * 128;           // 32 rows x 64 bf16
   // staging buffers per epilogue warp: the variants with a communication ring give one of the two
   // to a sixth pipeline stage (the epilogue of a tile hides behind the next tile's main loop anyway)
-  static constexpr int EPI_BUFS = (COMM_ > 0 && !BS_) ? 1 : 2;
+  static constexpr int EPI_BUFS = ((COMM_ > 0 && !BS_) || (BS_ && BN_ == 256)) ? 1 : 2;
   static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUFS * EPI_BUF_BYTES;
   static constexpr int BAR_BYTES = 256;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + COMM_BYTES + BAR_BYTES + 1024;
@@ -338,7 +339,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
   if (warp < 4) {
   // (block-scaled variant) producer, issuer and communication warps give registers to the
   // promotion warps; all four warps of the group execute the same instruction here
-  if constexpr (Cfg::BS) ptx::setmaxnreg_dec<88>();
+  if constexpr (Cfg::BS) ptx::setmaxnreg_dec<(BN == 256 ? 56 : 88)>();
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -420,7 +421,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
               }
             }
           }
-          mbar_wait(wc, empty_bar(stage), phase ^ 1u, kSiteSmemEmpty);
+          // (a wait that gave up, here or in another role: stop issuing at once, so that what is in flight
+          // at the teardown is bounded by the depth of the pipeline)
+          if (!mbar_wait(wc, empty_bar(stage), phase ^ 1u, kSiteSmemEmpty)) break;
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
           // post-attention input: (column in head, head of the slice, source); the own slice comes
           // straight from the attention output
@@ -492,6 +495,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
+#ifdef FLUXB_DEBUG_CHECKS
+      uint64_t probe_tempty = 0, probe_full = 0;
+#endif
       for (int t = tile_slot; t < total_tiles; t += tile_stride, ++it) {
         if (*abort_word) break;
         // a column piece of a split tile is a narrower instruction on the same operands
@@ -507,17 +513,15 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
 #ifdef FLUXB_DEBUG_CHECKS
             const long long pc0 = clock64();
 #endif
-            mbar_wait(wc, tempty_bar(buf), ((n / NACC) & 1u) ^ 1u, kSiteTmemEmpty);
+            if (!mbar_wait(wc, tempty_bar(buf), ((n / NACC) & 1u) ^ 1u, kSiteTmemEmpty)) break;
 #ifdef FLUXB_DEBUG_CHECKS
             const long long pc1 = clock64();
 #endif
-            mbar_wait(wc, full_bar(stage), phase, kSiteSmemFull);
+            if (!mbar_wait(wc, full_bar(stage), phase, kSiteSmemFull)) break;
 #ifdef FLUXB_DEBUG_CHECKS
-            if (p.trace != nullptr) {
-              // self-checking build: cycles the issuer waited for a free TMEM buffer / for operands
-              p.trace[blockIdx.x * kTraceWords + 12] += static_cast<uint64_t>(pc1 - pc0);
-              p.trace[blockIdx.x * kTraceWords + 13] += static_cast<uint64_t>(clock64() - pc1);
-            }
+            // self-checking build: cycles the issuer waited for a free TMEM buffer / for operands
+            probe_tempty += static_cast<uint64_t>(pc1 - pc0);
+            probe_full += static_cast<uint64_t>(clock64() - pc1);
 #endif
             ptx::tc_fence_after();
             const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
@@ -557,13 +561,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
               ptx::umma_ss<CG, Cfg::KIND>(tmem_base + half * BN, adesc + 2u * k, bdesc + bstep * k, idesc,
                                           (!first || k != 0) ? 1u : 0u);
           };
-          mbar_wait(wc, tempty_bar(0), par_e, kSiteTmemEmpty);
+          if (!mbar_wait(wc, tempty_bar(0), par_e, kSiteTmemEmpty)) break;
           ptx::tc_fence_after();
           {
             int st = stage;
             uint32_t ph = phase;
             for (int kb = 0; kb < head; ++kb) {
-              mbar_wait(wc, full_bar(st), ph, kSiteSmemFull);
+              if (!mbar_wait(wc, full_bar(st), ph, kSiteSmemFull)) break;
               ptx::tc_fence_after();
               issue_half(st, 0, kb == 0);
               if (++st == STAGES) {
@@ -572,7 +576,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
               }
             }
           }
-          mbar_wait(wc, tempty_bar(1), par_e, kSiteTmemEmpty);
+          if (*abort_word || !mbar_wait(wc, tempty_bar(1), par_e, kSiteTmemEmpty)) break;
           ptx::tc_fence_after();
           for (int kb = 0; kb < head; ++kb) {
             issue_half(stage, 1, kb == 0);
@@ -583,7 +587,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             }
           }
           for (int kb = head; kb < k_blocks; ++kb) {
-            mbar_wait(wc, full_bar(stage), phase, kSiteSmemFull);
+            if (!mbar_wait(wc, full_bar(stage), phase, kSiteSmemFull)) break;
             ptx::tc_fence_after();
             issue_half(stage, 0, false);
             issue_half(stage, 1, false);
@@ -598,11 +602,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         }
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        mbar_wait(wc, tempty_bar(acc), acc_phase ^ 1u, kSiteTmemEmpty);
+        if (!mbar_wait(wc, tempty_bar(acc), acc_phase ^ 1u, kSiteTmemEmpty)) break;
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          mbar_wait(wc, full_bar(stage), phase, kSiteSmemFull);
+          if (!mbar_wait(wc, full_bar(stage), phase, kSiteSmemFull)) break;
           ptx::tc_fence_after();
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
           const uint64_t adesc = ptx::umma_desc_k_sw128(sa);
@@ -623,6 +627,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         if constexpr (CG == 1) ptx::umma_commit(tfull_bar(acc));
         else ptx::umma_commit_cg2(tfull_bar(acc), 3);
       }
+#ifdef FLUXB_DEBUG_CHECKS
+      if (Cfg::BS && p.trace != nullptr) {
+        p.trace[blockIdx.x * kTraceWords + 12] = probe_tempty;
+        p.trace[blockIdx.x * kTraceWords + 13] = probe_full;
+      }
+#endif
     }
   } else if (warp == 2 || warp == 3) {
     // ------------------------------------------------------------------ handshake + all-gather push
@@ -954,7 +964,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     }
   }
   } else {
-      if constexpr (Cfg::BS) ptx::setmaxnreg_inc<208>();
+      if constexpr (Cfg::BS) ptx::setmaxnreg_inc<(BN == 256 ? 224 : 208)>();
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;              // TMEM lane quadrant this warp may read
     const int ew = warp - 4;             // epilogue warp index
@@ -1134,7 +1144,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     int pend_seg = -1, pend_mt = 0;
     uint32_t pend_chunks = 0;
     uint32_t own_seen = 0;   // tile rows of the own segment whose W-1 slabs were seen to have landed
-    uint64_t bs_acc[Cfg::BS ? 32 : 1];   // block-scaled: this thread's row x 64 columns, fp32 pairs
+    uint64_t bs_acc[Cfg::BS ? BN / 4 : 1];   // block-scaled: this thread's row x BN / 2 columns, fp32 pairs
+#ifdef FLUXB_DEBUG_CHECKS
+    uint64_t probe_wait = 0, probe_ld = 0, probe_kb = 0;
+#endif
     for (int t = tile_slot; t < total_tiles; t += tile_stride, ++it) {
       if (*abort_word) break;
       const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, BM, BN);
@@ -1209,10 +1222,16 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           }
         }
         const float* sa_ptr = sa_rows + (srow >> 7) * static_cast<int64_t>(kbs) * 128 + (srow & 127);
-        const float* sb_ptr = p.sb + static_cast<int64_t>(c.n0 >> 7) * kbs;
-        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + half * 64;
+        // this warp's columns: half * CW .. + CW of the tile (CW = 64 of 128, or 128 of 256: then the two
+        // halves lie in different 128-column scale blocks of the weight)
+        constexpr int CW = BN / 2, NCH = CW / 64;
+        int nblk = (c.n0 >> 7) + (BN == 256 ? half : 0);
+        if (nblk >= (p.N >> 7)) nblk = (p.N >> 7) - 1;          // (the clipped half of the last tile)
+        const float* sb_ptr = p.sb + static_cast<int64_t>(nblk) * kbs;
+        const int sb_col = BN == 256 ? 0 : half * 64;           // first column of the warp inside its scale block
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + half * CW;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) bs_acc[j] = 0ull;
+        for (int j = 0; j < NCH * 32; ++j) bs_acc[j] = 0ull;
         const uint32_t n0 = static_cast<uint32_t>(it) * kbs;
         // Scales are fetched four k-blocks at a time, one group ahead: a fetch per k-block, used one
         // k-block later, put the latency of a global load into every iteration.
@@ -1221,107 +1240,116 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int kk = kb0 + i < kbs ? kb0 + i : kbs - 1;   // past the end: a repeated, unused load
-            dsa[i] = (p.bs_release_arrive & 8) ? 1.f : sa_ptr[static_cast<int64_t>(kk) * 128];
-            dsb[i] = (p.sb_groupwise || (p.bs_release_arrive & 8)) ? 1.f : sb_ptr[kk];
+            dsa[i] = sa_ptr[static_cast<int64_t>(kk) * 128];
+            dsb[i] = p.sb_groupwise ? 1.f : sb_ptr[kk];
           }
         };
         load_scales(0, csa, csb);
         for (int kb0 = 0; kb0 < kbs; kb0 += 4) {
-        load_scales(kb0 + 4, nsa, nsb);
+          load_scales(kb0 + 4, nsa, nsb);
 #pragma unroll
-        for (int ki = 0; ki < 4; ++ki) {
-          const int kb = kb0 + ki;
-          if (kb >= kbs) break;
-          const uint32_t n = n0 + kb;
-          const int buf = n % NACC;
-          const uint32_t par = (n / NACC) & 1u;
-          const float sc = csa[ki] * csb[ki];
-          const uint64_t sc2 = ptx::pack_f32x2(sc, sc);
-#ifdef FLUXB_DEBUG_CHECKS
-          const long long pc0 = clock64();
-#endif
-          if (lane == 0) mbar_wait(wc, tfull_bar(buf), par, kSiteTmemFull);
-          __syncwarp();
-          mbar_wait(wc, tfull_bar(buf), par, kSiteTmemFull);
-          ptx::tc_fence_after();
-#ifdef FLUXB_DEBUG_CHECKS
-          const long long pc1 = clock64();
-#endif
-          uint32_t r0[32], r1[32];
-          if (!(p.bs_release_arrive & 4)) {
-          ptx::tmem_ld_32x32b_x32(lane_base + buf * BN, r0);
-          ptx::tmem_ld_32x32b_x32(lane_base + buf * BN + 32, r1);
-          ptx::tmem_ld_wait();
-          } else {
+          for (int ki = 0; ki < 4; ++ki) {
+            const int kb = kb0 + ki;
+            if (kb >= kbs) break;
+            const uint32_t n = n0 + kb;
+            const int buf = n % NACC;
+            const uint32_t par = (n / NACC) & 1u;
+            const float sc = csa[ki] * csb[ki];
+            const uint64_t sc2 = ptx::pack_f32x2(sc, sc);
+            // 32 columns of the k-block's partial product (in r), first accumulator a0, first column col
+            // of the warp's range: acc += r * scale
+            auto promote = [&](const uint32_t (&r)[32], int a0, int col) {
+              if (p.sb_groupwise) {
+                // per-column weight scales of this k-block (the same for every row)
+                const float4* sbv = reinterpret_cast<const float4*>(
+                    p.sb + (static_cast<int64_t>(nblk) * kbs + kb) * 128 + sb_col + col);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) r0[j] = r1[j] = kb + j;
-          }
-#ifdef FLUXB_DEBUG_CHECKS
-          const long long pc2 = clock64();
-#endif
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) {
-            // the buffer's contents are in registers (wait::ld): the hand-over needs no release ordering,
-            // which would also wait for the scale loads in flight
-            if (CG == 1 || cta_rank == 0) ptx::mbar_arrive(tempty_bar(buf));
-            else if (p.bs_release_arrive & 1) ptx::mbar_arrive_remote(tempty_bar(buf), 0);
-            else ptx::mbar_arrive_remote_relaxed(tempty_bar(buf), 0);
-          }
-#ifdef FLUXB_DEBUG_CHECKS
-          if (p.trace != nullptr && ew == 0 && lane == 0) {
-            // self-checking build: cycles of epilogue warp 4 per phase of the promotion (the multiply-adds
-            // of k-block kb are charged to the wait of k-block kb + 1 where they are still in flight)
-            uint64_t* tr = p.trace + blockIdx.x * kTraceWords;
-            tr[8] += static_cast<uint64_t>(pc1 - pc0);          // waiting for the k-block's MMAs
-            tr[9] += static_cast<uint64_t>(pc2 - pc1);          // TMEM -> registers
-            tr[10] += static_cast<uint64_t>(clock64() - pc2);   // fence, warp barrier, hand-over
-            tr[11] += 1;                                        // k-blocks
-          }
-#endif
-          if (p.bs_release_arrive & 2) {
-            bs_acc[0] += sc2 + r0[0] + r1[1];
-          } else if (p.sb_groupwise) {
-            // per-column weight scales of this k-block: 64 floats of this warp's columns, the same for every row
-            const float4* sbv =
-                reinterpret_cast<const float4*>(p.sb + (static_cast<int64_t>(c.n0 >> 7) * kbs + kb) * 128 + half * 64);
+                for (int j = 0; j < 8; ++j) {
+                  const float4 sv = sbv[j];
+                  bs_acc[a0 + 2 * j] = ptx::ffma2(ptx::pack_b32x2(r[4 * j], r[4 * j + 1]),
+                                                  ptx::pack_f32x2(sc * sv.x, sc * sv.y), bs_acc[a0 + 2 * j]);
+                  bs_acc[a0 + 2 * j + 1] = ptx::ffma2(ptx::pack_b32x2(r[4 * j + 2], r[4 * j + 3]),
+                                                      ptx::pack_f32x2(sc * sv.z, sc * sv.w), bs_acc[a0 + 2 * j + 1]);
+                }
+              } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 s0 = sbv[j], s1 = sbv[8 + j];
-              bs_acc[2 * j] = ptx::ffma2(ptx::pack_b32x2(r0[4 * j], r0[4 * j + 1]), ptx::pack_f32x2(sc * s0.x, sc * s0.y),
-                                         bs_acc[2 * j]);
-              bs_acc[2 * j + 1] = ptx::ffma2(ptx::pack_b32x2(r0[4 * j + 2], r0[4 * j + 3]),
-                                             ptx::pack_f32x2(sc * s0.z, sc * s0.w), bs_acc[2 * j + 1]);
-              bs_acc[16 + 2 * j] = ptx::ffma2(ptx::pack_b32x2(r1[4 * j], r1[4 * j + 1]),
-                                              ptx::pack_f32x2(sc * s1.x, sc * s1.y), bs_acc[16 + 2 * j]);
-              bs_acc[16 + 2 * j + 1] = ptx::ffma2(ptx::pack_b32x2(r1[4 * j + 2], r1[4 * j + 3]),
-                                                  ptx::pack_f32x2(sc * s1.z, sc * s1.w), bs_acc[16 + 2 * j + 1]);
+                for (int j = 0; j < 16; ++j)
+                  bs_acc[a0 + j] = ptx::ffma2(ptx::pack_b32x2(r[2 * j], r[2 * j + 1]), sc2, bs_acc[a0 + j]);
+              }
+            };
+            auto hand_over = [&]() {
+              ptx::tc_fence_before();
+              __syncwarp();
+              if (lane == 0) {
+                // The buffer's contents are in registers (wait::ld), so the hand-over needs no release ordering.
+                // A cluster-scope release arrive also waits for the warp's scale loads in flight, which
+                // halved the throughput of CTA pairs.
+                if (CG == 1 || cta_rank == 0) ptx::mbar_arrive(tempty_bar(buf));
+                else ptx::mbar_arrive_remote_relaxed(tempty_bar(buf), 0);
+              }
+            };
+#ifdef FLUXB_DEBUG_CHECKS
+            const long long pc0 = clock64();
+#endif
+            if (lane == 0) mbar_wait(wc, tfull_bar(buf), par, kSiteTmemFull);
+            __syncwarp();
+            mbar_wait(wc, tfull_bar(buf), par, kSiteTmemFull);
+            ptx::tc_fence_after();
+#ifdef FLUXB_DEBUG_CHECKS
+            const long long pc1 = clock64();
+#endif
+            uint32_t r0[32], r1[32];
+            const uint32_t taddr = lane_base + buf * BN;
+            ptx::tmem_ld_32x32b_x32(taddr, r0);
+            ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
+            ptx::tmem_ld_wait();
+            if constexpr (NCH == 1) {
+#ifdef FLUXB_DEBUG_CHECKS
+              probe_ld += static_cast<uint64_t>(clock64() - pc1);
+#endif
+              hand_over();
+              promote(r0, 0, 0);
+              promote(r1, 16, 32);
+            } else {
+              // the second 64 columns are fetched while the first are multiplied
+              promote(r0, 0, 0);
+              ptx::tmem_ld_32x32b_x32(taddr + 64, r0);
+              promote(r1, 16, 32);
+              ptx::tmem_ld_32x32b_x32(taddr + 96, r1);
+              ptx::tmem_ld_wait();
+#ifdef FLUXB_DEBUG_CHECKS
+              probe_ld += static_cast<uint64_t>(clock64() - pc1);
+#endif
+              hand_over();
+              promote(r0, 32, 64);
+              promote(r1, 48, 96);
             }
-          } else {
+#ifdef FLUXB_DEBUG_CHECKS
+            // self-checking build: cycles of this warp waiting for the k-block's MMAs (the multiply-adds of
+            // k-block kb are charged to the wait of k-block kb + 1 where they are still in flight) and
+            // reading TMEM (with 256-column tiles: including the first half's multiply-adds)
+            probe_wait += static_cast<uint64_t>(pc1 - pc0);
+            probe_kb += 1;
+#endif
+          }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              bs_acc[j] = ptx::ffma2(ptx::pack_b32x2(r0[2 * j], r0[2 * j + 1]), sc2, bs_acc[j]);
-              bs_acc[16 + j] = ptx::ffma2(ptx::pack_b32x2(r1[2 * j], r1[2 * j + 1]), sc2, bs_acc[16 + j]);
-            }
+          for (int i = 0; i < 4; ++i) {
+            csa[i] = nsa[i];
+            csb[i] = nsb[i];
           }
         }
+        // ---- this warp's 32 rows x CW columns of the tile
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          csa[i] = nsa[i];
-          csb[i] = nsb[i];
-        }
-        }
-        // ---- this warp's 32 rows x 64 columns of the tile
-        {
+        for (int ch = 0; ch < NCH; ++ch) {
           uint32_t r0[32], r1[32];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            r0[2 * j] = static_cast<uint32_t>(bs_acc[j]);
-            r0[2 * j + 1] = static_cast<uint32_t>(bs_acc[j] >> 32);
-            r1[2 * j] = static_cast<uint32_t>(bs_acc[16 + j]);
-            r1[2 * j + 1] = static_cast<uint32_t>(bs_acc[16 + j] >> 32);
+            r0[2 * j] = static_cast<uint32_t>(bs_acc[ch * 32 + j]);
+            r0[2 * j + 1] = static_cast<uint32_t>(bs_acc[ch * 32 + j] >> 32);
+            r1[2 * j] = static_cast<uint32_t>(bs_acc[ch * 32 + 16 + j]);
+            r1[2 * j + 1] = static_cast<uint32_t>(bs_acc[ch * 32 + 16 + j] >> 32);
           }
-          emit_chunk(r0, r1, c.n0 + half * 64, row, grow, m_cta + q * 32, tmd, z, own_rs);
+          emit_chunk(r0, r1, c.n0 + half * CW + ch * 64, row, grow, m_cta + q * 32, tmd, z, own_rs);
         }
       } else if constexpr (Cfg::MT == 2) {
         // both row halves of the tile complete together; accumulator 0 is drained (and handed
@@ -1388,7 +1416,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           if (lane == 0) {
             // store groups this warp committed for a whole tile; a piece of a split tile commits
             // fewer, so there everything is waited for
-            constexpr int kGroupsPerTile = Cfg::BS ? 1 : Cfg::MT * BN / 64;
+            constexpr int kGroupsPerTile = Cfg::BS ? BN / 128 : Cfg::MT * BN / 64;
             if (c.shift == 0) ptx::bulk_wait<kGroupsPerTile>();
             else ptx::bulk_wait<0>();
             if (pend_seg >= 0) rs_arrive(pend_seg, pend_mt, pend_chunks);
@@ -1396,7 +1424,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           // tiles of the own segment stay here: nobody is told
           pend_seg = own_rs ? -1 : c.seg;
           pend_mt = c.m_tile;
-          pend_chunks = Cfg::BS ? 1u : static_cast<uint32_t>(Cfg::MT * ((BN >> c.shift) / 64));
+          pend_chunks = Cfg::BS ? static_cast<uint32_t>(BN / 128) : static_cast<uint32_t>(Cfg::MT * ((BN >> c.shift) / 64));
         }
         __syncwarp();
       }
@@ -1420,6 +1448,14 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       __syncwarp();
     }
     if (ew == 0 && lane == 0) stamp(kTraceEnd);
+#ifdef FLUXB_DEBUG_CHECKS
+    if (Cfg::BS && p.trace != nullptr && ew == 0 && lane == 0) {
+      uint64_t* tr = p.trace + blockIdx.x * kTraceWords;
+      tr[8] = probe_wait;
+      tr[9] = probe_ld;
+      tr[11] = probe_kb;
+    }
+#endif
   }
 
   // -------------------------------------------------------------------- teardown of the GEMM

@@ -52,6 +52,25 @@ def test_bands_span_two_segments_but_the_own_shard_stays_alone():
         assert len(set(t1[s * per_seg:(s + 1) * per_seg, 0].tolist())) == 1
 
 
+@pytest.mark.parametrize("W", [3, 4, 5, 6, 7, 8])
+@pytest.mark.parametrize("rank", [0, 2])
+def test_reduce_scatter_keeps_the_own_segment_in_a_group_of_its_own(W, rank):
+    """The own segment's tiles wait for the peers' partial tiles. If a raster band mixed them with
+    tiles of another segment, a CTA could wait there while a partial tile that a peer waits for is
+    still behind it in its queue - on every rank at once. So with bands spanning two segments the own
+    segment, visited last, must still be a group of its own."""
+    from tempname_new_b200 import _native
+    mts, nt, G = 4, 6, 8
+    solo = _native.lib().fluxb_rs_solo_first(W)
+    t = _decode(W, (rank + 1) % W, mts, nt, G, 2, solo)
+    per_seg = mts * nt
+    assert set(t[-per_seg:, 0].tolist()) == {rank}
+    assert rank not in set(t[:-per_seg, 0].tolist())
+    # and the pairing is still there for the others
+    start = per_seg if solo else 0
+    assert any(len(set(t[i:i + G * nt, 0].tolist())) == 2 for i in range(start, len(t) - per_seg, G * nt))
+
+
 def test_decode_rejects_a_bad_grid():
     from tempname_new_b200 import _native
     out = np.zeros(3, dtype=np.int32)
