@@ -257,9 +257,11 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     const int seg_rows = a->M / (segmented ? a->world : 1);
     const bool can = cg == 2 && bn == 256 && !a->blockscale && !a2a && a->in_dtype != FLUXB_INT8 && seg_rows >= 512;
     if (want > 0) {
-      FLUXB_REQUIRE(want == 128 * cg || (want == 512 && can),
+      // (512 is honoured where the mode, the types and the rows allow it; elsewhere - the Ulysses projections,
+      // short segments - it falls back to one MMA per k-step)
+      FLUXB_REQUIRE(want == 128 * cg || want == 512,
                     "tile_m must be 128 * cta_group, or 512 for CTA pairs on 256-column tiles");
-      mt = want == 512 ? 2 : 1;
+      mt = (want == 512 && can) ? 2 : 1;
     } else if (can && (seg_rows % 512 == 0 || seg_rows >= 4096)) {
       mt = 2;
     }
