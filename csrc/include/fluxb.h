@@ -63,9 +63,10 @@ typedef struct {
   void* rs_stage[FLUXB_MAX_RANKS];
   uint32_t* rs_ctr[FLUXB_MAX_RANKS];
   void* rs_out;
-  uint32_t* wave_ctr;        /* optional: a device word owned by the caller (one per op object), zero between
-                                launches, that wave-synchronous tile starts count in; null = a word of the
-                                launcher's per-stream pool */
+  uint32_t* wave_ctr;        /* optional: two device words owned by the caller (per op object), zero between
+                                launches: [0] counts wave-synchronous tile starts (null = a word of the
+                                launcher's per-stream pool), [1] hands out the work units of the
+                                reduce-scatter tail (null = units dealt out round-robin) */
   uint32_t* local_cnt;       /* local scratch of world * ceil(M/world/128) uint32, zero at first use */
   /* block-scaled fp8 (blockscale != 0): inverse scales as fluxb_quantize_blockwise stores them.
    * sa [rows/128, K/128, 128] for the rows of `a`; sb [N/128, K/128]. In all-gather mode the

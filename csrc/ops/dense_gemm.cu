@@ -232,9 +232,11 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     // chosen by cta_group = 2, but measured slower (977 against 1128 TFLOP/s at 16384 x 3584 x 8192): the
     // k-block hand-over then waits for the slowest of sixteen promotion warps on two SMs.
     cg = (a->cta_group == 2 && a->tile_n != 256 && a->M / (multi ? a->world : 1) >= 256) ? 2 : 1;
-    // 128 x 256 tiles wherever N allows: per-tensor fp8 GEMMs on 128 x 128 tiles stop at 1450 TFLOP/s here (the
-    // operand stream into the SM is the bound), on 128 x 256 at 2600
-    bn = (cg == 1 && a->tile_n != 128 && (a->N % 256 == 0 || a->N >= 2048)) ? 256 : 128;
+    // 128 x 256 tiles on request (tile_n = 256). Per-tensor fp8 GEMMs on 128 x 128 tiles stop at 1450 TFLOP/s
+    // here (the operand stream into the SM is the bound), on 128 x 256 at 2600; the block-scaled variant on
+    // 128 x 256 tiles measured between 0.6 and 1.1 times the 128 x 128 one depending on where the compiler put
+    // the spills of its 128 accumulator registers per thread, so it is not the default.
+    bn = (cg == 1 && a->tile_n == 256) ? 256 : 128;
   } else if (a->mode == FLUXB_A2A_GEMM) {
     if (cg == 2 && a->M >= 256) bn = 256;
     else { cg = 1; bn = 128; }
@@ -401,11 +403,22 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     uint32_t box[3] = {64, 32, 1};
     if (p.mode == kModeReduceScatter) {
       FLUXB_REQUIRE(a->rs_out != nullptr, "reduce-scatter output missing");
+      {
+        // Two ranks: the own tiles add the peer's slab in their epilogue. Three and more: the own tiles go to
+        // the own staging slab and a tail of the same kernel sums the W slabs (FLUXB_RS_TAIL=0 / 1 overrides).
+        static const int tail_env = [] {
+          const char* e = getenv("FLUXB_RS_TAIL");
+          return e ? atoi(e) : -1;
+        }();
+        // (the block-scaled variants, whose warps 0-3 have given their registers away, keep the epilogue form)
+        p.rs_tail = (multi && !a->blockscale && (tail_env >= 0 ? tail_env != 0 : a->world >= 3)) ? 1 : 0;
+        p.rs_claim = a->wave_ctr ? a->wave_ctr + 1 : nullptr;
+      }
       for (int r = 0; r < a->world; ++r) {
         FLUXB_REQUIRE(a->rs_stage[r] && a->rs_ctr[r], "reduce-scatter peer pointers missing");
-        // peers: their staging slabs [W][seg_rows][N]; own entry: the output, as a single slab (the
-        // own segment's tiles add the peers' slabs in their epilogue and store the result)
-        const bool own = r == a->rank;
+        // peers: their staging slabs [W][seg_rows][N]; own entry without the tail: the output, as a single
+        // slab (the own segment's tiles add the peers' slabs in their epilogue and store the result)
+        const bool own = r == a->rank && !p.rs_tail;
         uint64_t dims[3] = {static_cast<uint64_t>(a->N), static_cast<uint64_t>(p.seg_rows),
                             own ? 1ull : static_cast<uint64_t>(a->world)};
         uint64_t str[2] = {static_cast<uint64_t>(a->N) * 2,

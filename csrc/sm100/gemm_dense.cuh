@@ -103,6 +103,8 @@ struct DenseGemmParams {
   const float* sa_land;          // for the rows of tm_a_land: [W*seg_rows/128, K/128, 128]
   const float* sb;               // [N/128, K/128], or with sb_groupwise [N/128, K/128, 128] (one per column)
   int32_t sb_groupwise;          // 1: the weight carries 1x128 scales too (the weight-gradient form)
+  int32_t rs_tail;               // reduce-scatter: 1 = own tiles go to the own staging slab too and a tail sums the W slabs
+  uint32_t* rs_claim;            // tail: work-claim counter (zero between calls); null = units dealt out round-robin
   int32_t b_kn;                  // 1: B is [K, N] with N contiguous (16-bit inputs): MN-major operand tiles
   int32_t reserved7;
   const float* ag_scale_src;     // all-gather: this rank's A scales (== sa), pushed with the shard
@@ -287,6 +289,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
   volatile uint32_t* tmem_slot =
       reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * STAGES + 2 * NACC));
   volatile uint32_t* abort_word = tmem_slot + 1;
+  volatile uint32_t* claim_slot = tmem_slot + 2;   // reduce-scatter tail: the work unit this CTA claimed
   const uint32_t ring_bar_base = bar_base + 8u * (2 * STAGES + 2 * NACC) + 16u;
   static_assert(8 * (2 * STAGES + 2 * NACC) + 16 + 64 + 16 <= Cfg::BAR_BYTES, "barrier block too small");
 
@@ -981,52 +984,71 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     uint32_t nstore = 0;
     bool started = !(multi && (p.mode == kModeReduceScatter || p.mode == kModeGemmA2A));
 
-    // Reduce-scatter, tiles of the own segment: add the partial results that the W-1 peers stored
-    // into this rank's staging slabs (64 columns of this thread's row per source, sources in the
-    // order rank+1, rank+2, ...; the loads of the next source are in flight while one is added).
+    // Reduce-scatter, tiles of the own segment: add the partial results that the W-1 peers stored into
+    // this rank's staging slabs to the staged 32 x 64 tile (16-bit, 16-byte pieces swizzled by row & 7).
+    // Eight lanes read the 128 bytes of one row, so a warp instruction covers four whole lines of each
+    // slab, the loads of all sources of a row group are in flight together, and the next group's are
+    // issued before this one is added. The sum runs in fp32 over 16-bit addends, sources in the order
+    // rank+1, rank+2, ..., like a reduce-scatter of the ranks' 16-bit partial outputs.
     const uint8_t* rs_stage_b = reinterpret_cast<const uint8_t*>(p.rs_stage);
-    auto add_peers = [&](uint32_t (&r0)[32], uint32_t (&r1)[32], int col0, int row) {
-      if (row >= p.seg_rows || col0 >= p.N) return;
-      uint4 v[2][8];
+    auto add_peers_staged = [&](uint8_t* tile, int col0, int row0) {
       const int64_t row_bytes = static_cast<int64_t>(p.N) * 2;
       const int64_t slab_bytes = row_bytes * p.seg_rows;
-      const int ncol = p.N - col0;   // valid columns from col0 on (a multiple of 8)
-      auto load_src = [&](uint4 (&dst)[8], int d) {
-        int src = p.rank + d;
-        if (src >= p.world) src -= p.world;
-        const uint8_t* base = rs_stage_b + src * slab_bytes + row * row_bytes + static_cast<int64_t>(col0) * 2;
+      const int pc = lane & 7;
+      const bool col_ok = col0 + pc * 8 < p.N;
+      // (the promotion warps of the block-scaled variants have no registers to spare: no look-ahead there)
+      constexpr int LOOK = Cfg::BS ? 0 : 1;
+      uint4 v[1 + LOOK][kMaxRanks - 1];
+      auto load_group = [&](uint4 (&dst)[kMaxRanks - 1], int g) {
+        const int r = g * 4 + (lane >> 3);
+        const bool ok = col_ok && row0 + r < p.seg_rows;
+        const uint8_t* base = rs_stage_b + static_cast<int64_t>(row0 + r) * row_bytes +
+                              static_cast<int64_t>(col0 + pc * 8) * 2;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (8 * j < ncol) dst[j] = ptx::ld_global_cs_v4(base + 16 * j);
-          else dst[j] = make_uint4(0u, 0u, 0u, 0u);
-        }
-      };
-      auto add_src = [&](const uint4 (&src)[8]) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t w[4] = {src[j].x, src[j].y, src[j].z, src[j].w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int c = 8 * j + 2 * e;   // column inside the 64-column chunk
-            const float lo = ptx::half_bits_to_float(static_cast<uint16_t>(w[e] & 0xFFFFu), f16);
-            const float hi = ptx::half_bits_to_float(static_cast<uint16_t>(w[e] >> 16), f16);
-            if (c < 32) {
-              r0[c] = __float_as_uint(__uint_as_float(r0[c]) + lo);
-              r0[c + 1] = __float_as_uint(__uint_as_float(r0[c + 1]) + hi);
-            } else {
-              r1[c - 32] = __float_as_uint(__uint_as_float(r1[c - 32]) + lo);
-              r1[c - 31] = __float_as_uint(__uint_as_float(r1[c - 31]) + hi);
-            }
+        for (int d = 1; d < kMaxRanks; ++d) {
+          if (d < p.world) {
+            int src = p.rank + d;
+            if (src >= p.world) src -= p.world;
+            dst[d - 1] = ok ? ptx::ld_global_cs_v4(base + src * slab_bytes) : make_uint4(0u, 0u, 0u, 0u);
           }
         }
       };
-      load_src(v[1], 1);
+      if constexpr (LOOK == 1) load_group(v[0], 0);
 #pragma unroll
-      for (int d = 1; d < kMaxRanks; ++d) {
-        if (d < p.world) {
-          if (d + 1 < p.world) load_src(v[(d + 1) & 1], d + 1);
-          add_src(v[d & 1]);
+      for (int g = 0; g < 8; ++g) {
+        if constexpr (LOOK == 1) {
+          if (g + 1 < 8) load_group(v[(g + 1) & LOOK], g + 1);
+        } else {
+          load_group(v[0], g);
         }
+        const int r = g * 4 + (lane >> 3);
+        uint4* sp = reinterpret_cast<uint4*>(tile + r * 128 + ((pc ^ (r & 7)) << 4));
+        const uint4 own = *sp;
+        const uint32_t ow[4] = {own.x, own.y, own.z, own.w};
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[2 * e] = ptx::half_bits_to_float(static_cast<uint16_t>(ow[e] & 0xFFFFu), f16);
+          acc[2 * e + 1] = ptx::half_bits_to_float(static_cast<uint16_t>(ow[e] >> 16), f16);
+        }
+#pragma unroll
+        for (int d = 1; d < kMaxRanks; ++d) {
+          if (d < p.world) {
+            const uint4 pv = v[g & LOOK][d - 1];
+            const uint32_t w[4] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              acc[2 * e] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] & 0xFFFFu), f16);
+              acc[2 * e + 1] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] >> 16), f16);
+            }
+          }
+        }
+        uint4 o;
+        o.x = ptx::pack_half2(f16, acc[0], acc[1]);
+        o.y = ptx::pack_half2(f16, acc[2], acc[3]);
+        o.z = ptx::pack_half2(f16, acc[4], acc[5]);
+        o.w = ptx::pack_half2(f16, acc[6], acc[7]);
+        *sp = o;
       }
     };
 
@@ -1081,7 +1103,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           r1[j] = __float_as_uint(ptx::activate(__uint_as_float(r1[j]), p.act));
         }
       }
-      if (own_rs) add_peers(r0, r1, col0, row);
       const uint32_t buf = Cfg::EPI_BUFS == 2 ? (nstore & 1u) : 0u;
       if (lane == 0) ptx::bulk_wait_read<Cfg::EPI_BUFS - 1>();
       __syncwarp();
@@ -1103,6 +1124,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         v.z = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
         v.w = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
         *reinterpret_cast<uint4*>(dst + (((j + 4) ^ (lane & 7)) << 4)) = v;
+      }
+      if (own_rs) {
+        __syncwarp();
+        add_peers_staged(my_epi + buf * Cfg::EPI_BUF_BYTES, col0, store_row0);
       }
       ptx::fence_proxy_async_smem();
       __syncwarp();
@@ -1163,7 +1188,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       if (p.mode == kModeReduceScatter && multi) {
         tmd = &p.tm_d[c.seg];
         z = p.rank;
-        if (c.seg == p.rank) {
+        if (c.seg == p.rank && !p.rs_tail) {
           // own segment: every peer's partial rows of this tile row must have landed; the result
           // goes to rs_out (tm_d[rank] covers it as one slab)
           own_rs = true;
@@ -1473,6 +1498,105 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc<CG>(tmem_base, Cfg::TMEM_COLS);
+  }
+
+  // -------------------------------------------------------------------- reduce-scatter tail
+  if constexpr (!Cfg::BS) if (p.mode == kModeReduceScatter && multi && p.rs_tail) {
+    // Three ranks and more: the own tiles went to the own staging slab like everybody else's, and
+    // all threads of the grid now sum the W slabs into rs_out (fp32 sums of 16-bit addends, slabs in
+    // rank order). Adding W-1 slabs inside the epilogue of the own tiles, as two ranks do, costs
+    // more here than this tail: those epilogues hold the accumulators that the next tile waits for.
+    // A work unit is kUnit 16-byte pieces of the [seg_rows, N] output; units are claimed from a
+    // counter (every CTA makes exactly one failing claim; whoever makes the very last claim of the
+    // launch puts the counter back to zero), or dealt out round-robin when there is no counter.
+    constexpr int kUnit = 256 * 8;
+    const int64_t pieces_per_row = p.N >> 3;
+    const int64_t total_pieces = static_cast<int64_t>(p.seg_rows) * pieces_per_row;
+    const uint32_t units = static_cast<uint32_t>((total_pieces + kUnit - 1) / kUnit);
+    const uint4* stage = reinterpret_cast<const uint4*>(p.rs_stage);
+    uint4* out = reinterpret_cast<uint4*>(p.rs_out);
+    const bool tail_f16 = p.out_f16 != 0;
+    if (threadIdx.x == 0) stamp(kTraceSlice0 + 1);      // reduce tail entered
+    uint32_t next_static = blockIdx.x;
+    uint32_t rows_seen = 0;   // (threads 0..W-1) tile rows whose slab of source threadIdx.x was seen to have landed
+    while (true) {
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        uint32_t got;
+        if (p.rs_claim != nullptr) {
+          got = atomicAdd(p.rs_claim, 1u);
+          if (got == units + gridDim.x - 1u) atomicExch(p.rs_claim, 0u);
+        } else {
+          got = next_static;
+          next_static += gridDim.x;
+        }
+        *claim_slot = *abort_word ? 0xFFFFFFFFu : got;
+      }
+      __syncthreads();
+      const uint32_t u = *claim_slot;
+      if (u >= units) break;
+      {
+        // every source's rows of this unit must have landed: one thread per source looks at the flags
+        // of the tile rows that the unit touches (usually one); the block barrier passes it on
+        const int64_t c0 = static_cast<int64_t>(u) * kUnit;
+        const int64_t c1 = (c0 + kUnit < total_pieces ? c0 + kUnit : total_pieces) - 1;
+        const int mt0 = static_cast<int>((c0 / pieces_per_row) / BM);
+        const int mt1 = static_cast<int>((c1 / pieces_per_row) / BM);
+        if (static_cast<int>(threadIdx.x) < p.world)
+          for (int mt = mt0; mt <= mt1; ++mt) {
+            if (mt < 32 && ((rows_seen >> mt) & 1u)) continue;
+            flag_wait_ge(wc, p.rs_ctr[p.rank] + mt * kMaxRanks + threadIdx.x, p.epoch, kSiteTileCounter);
+            if (mt < 32) rows_seen |= 1u << mt;
+          }
+        __syncthreads();
+      }
+      constexpr int PIECES = 4;          // 16-byte pieces per thread in flight per source
+#pragma unroll 1
+      for (int rep = 0; rep < kUnit / 256; rep += PIECES) {
+        int64_t idx[PIECES];
+        bool ok[PIECES];
+#pragma unroll
+        for (int h = 0; h < PIECES; ++h) {
+          idx[h] = static_cast<int64_t>(u) * kUnit + (rep + h) * 256 + threadIdx.x;
+          ok[h] = idx[h] < total_pieces;
+        }
+        uint4 v[kMaxRanks][PIECES];
+#pragma unroll
+        for (int sr = 0; sr < kMaxRanks; ++sr)
+#pragma unroll
+          for (int h = 0; h < PIECES; ++h)
+            if (sr < p.world && ok[h]) v[sr][h] = ptx::ld_global_cs_v4(stage + sr * total_pieces + idx[h]);
+        float accv[PIECES][8];
+#pragma unroll
+        for (int h = 0; h < PIECES; ++h)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) accv[h][e] = 0.f;
+#pragma unroll
+        for (int sr = 0; sr < kMaxRanks; ++sr)
+#pragma unroll
+          for (int h = 0; h < PIECES; ++h) {
+            if (sr < p.world && ok[h]) {
+              const uint32_t w[4] = {v[sr][h].x, v[sr][h].y, v[sr][h].z, v[sr][h].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                accv[h][2 * e] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] & 0xFFFFu), tail_f16);
+                accv[h][2 * e + 1] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] >> 16), tail_f16);
+              }
+            }
+          }
+#pragma unroll
+        for (int h = 0; h < PIECES; ++h) {
+          if (!ok[h]) continue;
+          uint4 o;
+          o.x = ptx::pack_half2(tail_f16, accv[h][0], accv[h][1]);
+          o.y = ptx::pack_half2(tail_f16, accv[h][2], accv[h][3]);
+          o.z = ptx::pack_half2(tail_f16, accv[h][4], accv[h][5]);
+          o.w = ptx::pack_half2(tail_f16, accv[h][6], accv[h][7]);
+          out[idx[h]] = o;
+        }
+      }
+    }
+    if (threadIdx.x == 0) stamp(kTraceSlice0 + 2);  // reduce tail left
   }
 }
 

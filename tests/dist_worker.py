@@ -33,9 +33,26 @@ def p0(*a):
         print(*a, flush=True)
 
 
+SUSTAIN_S = float(next((a.split("=")[1] for a in sys.argv if a.startswith("--sustain=")), "0"))
+
+
 def timeit(fn, iters=10, warm=3):
+    """Mean time of ``iters`` back-to-back calls, maximum over ranks. With ``--sustain=S`` every
+    measurement runs for about S seconds instead (the same count on every rank), so that the power
+    cap, not the boost clock of a short burst, sets the clock of all the numbers being compared."""
     for _ in range(warm):
         fn()
+    if SUSTAIN_S > 0:
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(3):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        n = torch.tensor([SUSTAIN_S * 3e3 / max(s.elapsed_time(e), 1e-3)], device=dev)
+        dist.all_reduce(n, op=dist.ReduceOp.MIN)
+        iters = max(iters, int(n.item()))
     torch.cuda.synchronize()
     dist.barrier()
     torch.cuda.synchronize()
@@ -150,9 +167,10 @@ def check_dense():
         p0(f"GEMM-RS M={M} N={N} K={K} W={W}: fluxb {t_f:.3f} ms | torch+nccl {t_t:.3f} ms | matmul {t_g:.3f} ms"
            f" | fluxb plain GEMM {t_p:.3f} ms")
         if "--timeline" in sys.argv:
-            with flux.KernelTimeline(dev) as tl:
+            with flux.KernelTimeline(dev) as tl:   # the last of twelve back-to-back calls: steady state
                 dist.barrier(pg)
-                op.forward(a, w)
+                for _ in range(12):
+                    op.forward(a, w)
                 torch.cuda.synchronize()
             p0(f"GEMM-RS timeline (us; slice0 = first tile of the own segment reached): {tl.summary()}")
         op.check_status()
@@ -172,9 +190,10 @@ def check_dense():
         p0(f"AG-GEMM M={M} N={N} K={K} W={W}: fluxb {t_f:.3f} ms | torch+nccl {t_t:.3f} ms | matmul {t_g:.3f} ms"
            f" | fluxb plain GEMM {t_p:.3f} ms")
         if "--timeline" in sys.argv:
-            with flux.KernelTimeline(dev) as tl:
+            with flux.KernelTimeline(dev) as tl:   # the last of twelve back-to-back calls: steady state
                 dist.barrier(pg)
-                op.forward(a, w, output=out)
+                for _ in range(12):
+                    op.forward(a, w, output=out)
                 torch.cuda.synchronize()
             p0(f"AG-GEMM timeline (us): {tl.summary()}")
         op.check_status()
