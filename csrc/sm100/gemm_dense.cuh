@@ -1509,7 +1509,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     // A work unit is kUnit 16-byte pieces of the [seg_rows, N] output; units are claimed from a
     // counter (every CTA makes exactly one failing claim; whoever makes the very last claim of the
     // launch puts the counter back to zero), or dealt out round-robin when there is no counter.
-    constexpr int kUnit = 256 * 8;
+    constexpr int kUnit = 256 * 16;
     const int64_t pieces_per_row = p.N >> 3;
     const int64_t total_pieces = static_cast<int64_t>(p.seg_rows) * pieces_per_row;
     const uint32_t units = static_cast<uint32_t>((total_pieces + kUnit - 1) / kUnit);
@@ -1519,22 +1519,28 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     if (threadIdx.x == 0) stamp(kTraceSlice0 + 1);      // reduce tail entered
     uint32_t next_static = blockIdx.x;
     uint32_t rows_seen = 0;   // (threads 0..W-1) tile rows whose slab of source threadIdx.x was seen to have landed
-    while (true) {
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        uint32_t got;
-        if (p.rs_claim != nullptr) {
-          got = atomicAdd(p.rs_claim, 1u);
-          if (got == units + gridDim.x - 1u) atomicExch(p.rs_claim, 0u);
-        } else {
-          got = next_static;
-          next_static += gridDim.x;
-        }
-        *claim_slot = *abort_word ? 0xFFFFFFFFu : got;
+    auto claim = [&]() -> uint32_t {
+      if (*abort_word) return 0xFFFFFFFFu;
+      uint32_t got;
+      if (p.rs_claim != nullptr) {
+        got = atomicAdd(p.rs_claim, 1u);
+        if (got == units + gridDim.x - 1u) atomicExch(p.rs_claim, 0u);
+      } else {
+        got = next_static;
+        next_static += gridDim.x;
       }
-      __syncthreads();
-      const uint32_t u = *claim_slot;
+      return got;
+    };
+    int par = 0;
+    __syncthreads();
+    // (claims are made by a thread that does not also look at arrival flags)
+    if (threadIdx.x == 32) claim_slot[0] = claim();
+    __syncthreads();
+    while (true) {
+      const uint32_t u = claim_slot[par];
       if (u >= units) break;
+      // the next unit is claimed while this one is summed
+      if (threadIdx.x == 32) claim_slot[par ^ 1] = claim();
       {
         // every source's rows of this unit must have landed: one thread per source looks at the flags
         // of the tile rows that the unit touches (usually one); the block barrier passes it on
@@ -1595,6 +1601,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           out[idx[h]] = o;
         }
       }
+      __syncthreads();
+      par ^= 1;
     }
     if (threadIdx.x == 0) stamp(kTraceSlice0 + 2);  // reduce tail left
   }
