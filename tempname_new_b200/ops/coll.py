@@ -73,8 +73,33 @@ class AllGatherOp(_RowExchange):
         super().__init__(tp_group, max_m_dim, k_dim, input_dtype, timeout_s)
         self.k_dim = k_dim
         self._cpu = None
+        self._scale_op: Optional[_RowExchange] = None    # built at the first call that carries scales
+        self._scales: Optional[torch.Tensor] = None      # [M, 1] fp32 in rank order, of the latest such call
+
+    def _gather_scales(self, input_scale: torch.Tensor, seg: int) -> None:
+        """Per-row input scales ([M/W, 1] fp32, the int8 convention of the reference's all-gather op,
+        python/flux/cpp_mod.pyi:130-132) travel through a second, small exchange."""
+        sc = input_scale.reshape(-1).float().contiguous()
+        if sc.numel() != seg:
+            raise ValueError(f"input_scale must hold one value per row of the shard ({seg}), got {sc.numel()}")
+        if not sc.is_cuda:
+            parts = [torch.empty_like(sc) for _ in range(self.world)]
+            dist.all_gather(parts, sc, group=self.pg)
+            self._scales = torch.cat(parts).reshape(-1, 1)
+            return
+        rows = (seg + 3) // 4                             # rows of four floats (16 bytes)
+        need = (self.max_rows // self.world + 3) // 4 * self.world
+        if self._scale_op is None:
+            self._scale_op = _RowExchange(self.pg, need, 4, torch.float32, self.timeout_s)
+        padded = torch.zeros(rows * 4, dtype=torch.float32, device=sc.device)
+        padded[:seg] = sc
+        self._scale_op._launch(padded.view(rows, 4), None, True, None, None)
+        got = self._scale_op.buf.view(self.rank, torch.float32, (need, 4))[: rows * self.world]
+        self._scales = got.reshape(self.world, rows * 4)[:, :seg].reshape(-1, 1).contiguous()
 
     def run(self, input: torch.Tensor, input_scale=None, all_gather_option=None, stream=None) -> torch.Tensor:
+        if input_scale is not None:
+            self._gather_scales(input_scale, input.shape[0])
         if not input.is_cuda:
             parts = [torch.empty_like(input) for _ in range(self.world)]
             dist.all_gather(parts, input.contiguous(), group=self.pg)
@@ -92,8 +117,9 @@ class AllGatherOp(_RowExchange):
     def local_barrier_buffer(self) -> torch.Tensor:
         return self.ctrl.view(self.rank, torch.int32, (2 * self.world,), OFF_CTR)
 
-    def local_input_scale_buffer(self):
-        return None
+    def local_input_scale_buffer(self) -> Optional[torch.Tensor]:
+        """[M, 1] fp32 scales of all ranks' rows, from the latest ``run`` that was given ``input_scale``."""
+        return self._scales
 
 
 class All2AllSingle(_RowExchange):

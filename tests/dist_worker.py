@@ -372,6 +372,17 @@ def check_coll():
     for _ in range(2):
         assert torch.equal(ag.run(x), ref)
     ag.check_status()
+    # per-row scales of an int8 shard ride along (rows not a multiple of four: padded rows of 16 bytes)
+    xs = torch.randint(-100, 100, (1022, 512), device=dev, dtype=torch.int8)
+    ss = torch.rand(1022, 1, device=dev) + rank
+    ag8 = flux.AllGatherOp(pg, 1, 1024 * W, 512, torch.int8)
+    got = ag8.run(xs, input_scale=ss)
+    ref8 = torch.empty(1022 * W, 512, device=dev, dtype=torch.int8)
+    dist.all_gather_into_tensor(ref8, xs)
+    refs = torch.empty(1022 * W, 1, device=dev)
+    dist.all_gather_into_tensor(refs, ss)
+    assert torch.equal(got, ref8) and torch.equal(ag8.local_input_scale_buffer(), refs)
+    ag8.check_status()
     a2a = flux.All2AllSingle(pg, 4096, 256, W, torch.bfloat16)
     ins = torch.tensor([64 * (1 + (rank + d) % 3) for d in range(W)], device=dev, dtype=torch.int32)
     inp = torch.randn(int(ins.sum()), 256, device=dev).bfloat16()

@@ -12,6 +12,11 @@ def _coll(rank, world):
     full = ag.run(x)
     for r in range(world):
         assert float(full[4 * r, 0]) == r
+    assert ag.local_input_scale_buffer() is None
+    ag.run(x, input_scale=torch.arange(4, dtype=torch.float32).reshape(4, 1) + 10.0 * rank)   # int8 convention
+    sc = ag.local_input_scale_buffer()
+    assert sc.shape == (4 * world, 1)
+    assert sc.reshape(-1).tolist() == [10.0 * r + i for r in range(world) for i in range(4)]
     a2a = flux.All2AllSingle(dist.group.WORLD, 16, 4, world, torch.float32)
     ins = torch.tensor([rank + 1 + d for d in range(world)])       # rows for each destination
     inp = torch.cat([torch.full((int(n), 4), 10.0 * rank + d) for d, n in enumerate(ins.tolist())])

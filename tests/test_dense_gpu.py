@@ -236,6 +236,38 @@ def test_kernel_timeline_records_stamps(dev):
 
 
 
+def test_sm_margin_leaves_sms_to_a_second_stream(dev):
+    """``sm_margin`` shrinks the grid of a fused op (reference: the ``sm_margin`` arguments of the
+    Ulysses and MoE ops, src/gemm_a2a_transpose/ths_op/gemm_all2all_transpose.cc:559-560). With 16
+    SMs left free the op runs beside a stream of elementwise kernels, uses at most 148 - 16 CTAs
+    and still completes with the right result."""
+    import os
+    import torch.distributed as dist
+    import tempname_new_b200 as flux
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29541")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    a, b = _ab(8192, 4096, 1024, dev)                  # more tiles than CTAs at any tile shape
+    ref = a.float() @ b.float().t()
+    rs = flux.GemmRS(dist.group.WORLD, 1, 8192, 4096, torch.bfloat16)
+    rs.sm_margin = 16
+    side = torch.cuda.Stream(dev)
+    busy = torch.ones(64 << 20, device=dev)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        for _ in range(40):
+            busy.mul_(1.0001)
+    with flux.KernelTimeline(dev) as tl:
+        out = rs.forward(a, b)
+        torch.cuda.synchronize()
+    rs.check_status()
+    assert (out.float() - ref).abs().max().item() <= _tol(ref)
+    ctas = int((tl.buf[:, 6] > 0).sum().item())        # CTAs that stamped the end of their epilogue
+    assert 0 < ctas <= sms - 16
+
+
 def test_int8_per_row_and_per_column_scales(dev):
     """The reference's int8 convention: input_scale [M, 1], weight_scale [1, N] - honoured element by
     element on the GPU, and any other shape is refused instead of being cut to its first element."""
