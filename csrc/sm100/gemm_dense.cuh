@@ -984,71 +984,52 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     uint32_t nstore = 0;
     bool started = !(multi && (p.mode == kModeReduceScatter || p.mode == kModeGemmA2A));
 
-    // Reduce-scatter, tiles of the own segment: add the partial results that the W-1 peers stored into
-    // this rank's staging slabs to the staged 32 x 64 tile (16-bit, 16-byte pieces swizzled by row & 7).
-    // Eight lanes read the 128 bytes of one row, so a warp instruction covers four whole lines of each
-    // slab, the loads of all sources of a row group are in flight together, and the next group's are
-    // issued before this one is added. The sum runs in fp32 over 16-bit addends, sources in the order
-    // rank+1, rank+2, ..., like a reduce-scatter of the ranks' 16-bit partial outputs.
+    // Reduce-scatter, tiles of the own segment: add the partial results that the W-1 peers stored
+    // into this rank's staging slabs (64 columns of this thread's row per source, sources in the
+    // order rank+1, rank+2, ...; the loads of the next source are in flight while one is added).
     const uint8_t* rs_stage_b = reinterpret_cast<const uint8_t*>(p.rs_stage);
-    auto add_peers_staged = [&](uint8_t* tile, int col0, int row0) {
+    auto add_peers = [&](uint32_t (&r0)[32], uint32_t (&r1)[32], int col0, int row) {
+      if (row >= p.seg_rows || col0 >= p.N) return;
+      uint4 v[2][8];
       const int64_t row_bytes = static_cast<int64_t>(p.N) * 2;
       const int64_t slab_bytes = row_bytes * p.seg_rows;
-      const int pc = lane & 7;
-      const bool col_ok = col0 + pc * 8 < p.N;
-      // (the promotion warps of the block-scaled variants have no registers to spare: no look-ahead there)
-      constexpr int LOOK = Cfg::BS ? 0 : 1;
-      uint4 v[1 + LOOK][kMaxRanks - 1];
-      auto load_group = [&](uint4 (&dst)[kMaxRanks - 1], int g) {
-        const int r = g * 4 + (lane >> 3);
-        const bool ok = col_ok && row0 + r < p.seg_rows;
-        const uint8_t* base = rs_stage_b + static_cast<int64_t>(row0 + r) * row_bytes +
-                              static_cast<int64_t>(col0 + pc * 8) * 2;
+      const int ncol = p.N - col0;   // valid columns from col0 on (a multiple of 8)
+      auto load_src = [&](uint4 (&dst)[8], int d) {
+        int src = p.rank + d;
+        if (src >= p.world) src -= p.world;
+        const uint8_t* base = rs_stage_b + src * slab_bytes + row * row_bytes + static_cast<int64_t>(col0) * 2;
 #pragma unroll
-        for (int d = 1; d < kMaxRanks; ++d) {
-          if (d < p.world) {
-            int src = p.rank + d;
-            if (src >= p.world) src -= p.world;
-            dst[d - 1] = ok ? ptx::ld_global_cs_v4(base + src * slab_bytes) : make_uint4(0u, 0u, 0u, 0u);
-          }
+        for (int j = 0; j < 8; ++j) {
+          if (8 * j < ncol) dst[j] = ptx::ld_global_cs_v4(base + 16 * j);
+          else dst[j] = make_uint4(0u, 0u, 0u, 0u);
         }
       };
-      if constexpr (LOOK == 1) load_group(v[0], 0);
+      auto add_src = [&](const uint4 (&src)[8]) {
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        if constexpr (LOOK == 1) {
-          if (g + 1 < 8) load_group(v[(g + 1) & LOOK], g + 1);
-        } else {
-          load_group(v[0], g);
-        }
-        const int r = g * 4 + (lane >> 3);
-        uint4* sp = reinterpret_cast<uint4*>(tile + r * 128 + ((pc ^ (r & 7)) << 4));
-        const uint4 own = *sp;
-        const uint32_t ow[4] = {own.x, own.y, own.z, own.w};
-        float acc[8];
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t w[4] = {src[j].x, src[j].y, src[j].z, src[j].w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          acc[2 * e] = ptx::half_bits_to_float(static_cast<uint16_t>(ow[e] & 0xFFFFu), f16);
-          acc[2 * e + 1] = ptx::half_bits_to_float(static_cast<uint16_t>(ow[e] >> 16), f16);
-        }
-#pragma unroll
-        for (int d = 1; d < kMaxRanks; ++d) {
-          if (d < p.world) {
-            const uint4 pv = v[g & LOOK][d - 1];
-            const uint32_t w[4] = {pv.x, pv.y, pv.z, pv.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              acc[2 * e] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] & 0xFFFFu), f16);
-              acc[2 * e + 1] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] >> 16), f16);
+          for (int e = 0; e < 4; ++e) {
+            const int c = 8 * j + 2 * e;   // column inside the 64-column chunk
+            const float lo = ptx::half_bits_to_float(static_cast<uint16_t>(w[e] & 0xFFFFu), f16);
+            const float hi = ptx::half_bits_to_float(static_cast<uint16_t>(w[e] >> 16), f16);
+            if (c < 32) {
+              r0[c] = __float_as_uint(__uint_as_float(r0[c]) + lo);
+              r0[c + 1] = __float_as_uint(__uint_as_float(r0[c + 1]) + hi);
+            } else {
+              r1[c - 32] = __float_as_uint(__uint_as_float(r1[c - 32]) + lo);
+              r1[c - 31] = __float_as_uint(__uint_as_float(r1[c - 31]) + hi);
             }
           }
         }
-        uint4 o;
-        o.x = ptx::pack_half2(f16, acc[0], acc[1]);
-        o.y = ptx::pack_half2(f16, acc[2], acc[3]);
-        o.z = ptx::pack_half2(f16, acc[4], acc[5]);
-        o.w = ptx::pack_half2(f16, acc[6], acc[7]);
-        *sp = o;
+      };
+      load_src(v[1], 1);
+#pragma unroll
+      for (int d = 1; d < kMaxRanks; ++d) {
+        if (d < p.world) {
+          if (d + 1 < p.world) load_src(v[(d + 1) & 1], d + 1);
+          add_src(v[d & 1]);
+        }
       }
     };
 
@@ -1103,6 +1084,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
           r1[j] = __float_as_uint(ptx::activate(__uint_as_float(r1[j]), p.act));
         }
       }
+      if (own_rs) add_peers(r0, r1, col0, row);
       const uint32_t buf = Cfg::EPI_BUFS == 2 ? (nstore & 1u) : 0u;
       if (lane == 0) ptx::bulk_wait_read<Cfg::EPI_BUFS - 1>();
       __syncwarp();
@@ -1124,10 +1106,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         v.z = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
         v.w = ptx::pack_half2(f16, __uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
         *reinterpret_cast<uint4*>(dst + (((j + 4) ^ (lane & 7)) << 4)) = v;
-      }
-      if (own_rs) {
-        __syncwarp();
-        add_peers_staged(my_epi + buf * Cfg::EPI_BUF_BYTES, col0, store_row0);
       }
       ptx::fence_proxy_async_smem();
       __syncwarp();
