@@ -460,7 +460,11 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
   {
     const int64_t row_b = p.mode == kModeA2AGemm ? static_cast<int64_t>(a->K / a->world) * elt
                                                  : static_cast<int64_t>(a->K) * elt;
-    int64_t unit = (32ll << 20) / (row_b > 0 ? row_b : 1);
+    static const int unit_mb_env = [] {
+      const char* e = getenv("FLUXB_AG_UNIT_MB");
+      return e ? atoi(e) : 0;
+    }();
+    int64_t unit = (static_cast<int64_t>(unit_mb_env > 0 ? unit_mb_env : 32) << 20) / (row_b > 0 ? row_b : 1);
     unit = (unit + bm - 1) / bm * bm;
     const int64_t seg_round = (static_cast<int64_t>(p.seg_rows) + bm - 1) / bm * bm;
     if (unit > seg_round || unit * 3 / 2 > seg_round) unit = seg_round;
