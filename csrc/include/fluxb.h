@@ -84,7 +84,8 @@ typedef struct {
    * 0 roles start, 1 start handshake done, 2 pushes of communication warp 2 published, 3 loads of
    * the CTA's first tile issued, 4 loads of its last tile issued, 5 first epilogue store, 6 epilogue
    * done, 7 total ns the producer spent waiting for arrival flags, 8 + j: K slice j of the first tile
-   * became readable (post-attention mode). Null = off. */
+   * became readable (post-attention mode); reduce-scatter: 8 first own tile reached (two ranks), 9 / 10
+   * the tail that sums the slabs entered / left (three ranks and more). Null = off. */
   uint64_t* trace;
   int32_t b_kn;              /* 1: b is [K, N] with N contiguous and ldb elements between k-rows (a weight held
                                 transposed, e.g. for the data gradient): read in place as an MN-major operand;

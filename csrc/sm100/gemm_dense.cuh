@@ -60,6 +60,10 @@ enum TraceSlot : int {
   kTraceFlagWait = 7,     // producer: total time spent waiting for arrival flags
   kTraceSlice0 = 8,       // producer, first tile: 8 + j = K slice j (post-attention) became readable;
                           // reduce-scatter: 8 = first tile of the own segment reached by epilogue warp 4
+                          // (epilogue form), 9 / 10 = the tail that sums the slabs entered / left;
+                          // block-scaled variants of the self-checking build: 8 / 9 = cycles promotion warp 4
+                          // waited for MMAs / read TMEM, 11 = its k-blocks, 12 / 13 = cycles the issuer
+                          // waited for a free TMEM buffer / for operands
 };
 constexpr int kTraceWords = 16;  // words per CTA
 constexpr int kMaxHeadGroups = 3;  // q, k, v

@@ -108,6 +108,9 @@ class KernelTimeline:
     when the start handshake completed, when the pushes of the communication warps were published,
     when the loads of the first / last tile were issued, when the epilogue stored first / finished,
     and how long the producers waited for arrival flags in total. Only the latest launch is kept.
+    ``slice{j}_ready``: post-attention mode - K slice j of the CTA's first tile became readable;
+    reduce-scatter - ``slice0`` the first own tile was reached (two ranks), ``slice1`` / ``slice2`` the
+    tail that sums the staging slabs was entered / left (three ranks and more).
     The reference exposes per-op ``profiling()`` context hooks (python/flux/cpp_mod.pyi); this is the
     device-side counterpart for the fused kernels here."""
 

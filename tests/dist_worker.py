@@ -172,7 +172,8 @@ def check_dense():
                 for _ in range(12):
                     op.forward(a, w)
                 torch.cuda.synchronize()
-            p0(f"GEMM-RS timeline (us; slice0 = first tile of the own segment reached): {tl.summary()}")
+            p0(f"GEMM-RS timeline (us; slice0 = first own tile reached, slice1 / slice2 = reduce tail entered / left): "
+               f"{tl.summary()}")
         op.check_status()
         M, N, K = 8192, 49152, 12288
         a = (torch.randn(M // W, K, device=dev) * 0.5).bfloat16()
