@@ -117,21 +117,25 @@ def cmd_grouped(a):
     E, topk = a.experts, a.topk
     tokens = a.rows // topk
     g = flux.testing.gen_moe_gating_args(E, topk, tokens, device=dev, seed=1)
-    w = (torch.randn(E, a.n, a.k, device=dev) * 0.02).bfloat16()
+    dt = torch.float8_e4m3fn if a.dtype == "fp8" else torch.bfloat16
+    w = (torch.randn(E, a.n, a.k, device=dev) * (0.5 if a.dtype == "fp8" else 0.02)).to(dt)
     out = torch.empty(a.rows, a.n, device=dev, dtype=torch.bfloat16)
     if a.gathered:
+        if a.dtype == "fp8":
+            raise SystemExit("--gathered is measured on bf16 tokens")
         x = torch.randn(tokens, a.k, device=dev).bfloat16()
         env = flux.DistEnvTPWithEP(dist.group.WORLD, 1, None, ep_size=1)
         op = flux.GemmGroupedV3AGScatter(env, flux.MoeArguments(tokens, a.k, a.n, E, topk, torch.bfloat16))
         fn = lambda: op.forward(x, w, g.splits_gpu, g.scatter_index, outputs_buf=out)  # noqa: E731
     else:
-        x = torch.randn(a.rows, a.k, device=dev).bfloat16()
+        x = torch.randn(a.rows, a.k, device=dev).to(dt)
         op = flux.GemmGroupedV3(w, E)
         fn = lambda: op.forward(x, g.splits_gpu)  # noqa: E731
     ms = timed(fn, a.iters, a.warmup, not a.no_flush)
     tf = 2.0 * a.rows * a.n * a.k / ms / 1e9
     pk, _, src = peaks()
-    print(json.dumps({"op": "grouped_gemm", "gathered": bool(a.gathered), "rows": a.rows, "n": a.n, "k": a.k,
+    print(json.dumps({"op": "grouped_gemm", "dtype": a.dtype, "gathered": bool(a.gathered), "rows": a.rows, "n": a.n,
+                      "k": a.k,
                       "experts": E, "ms": ms, "tflops": tf, "frac_of_bf16_peak": tf / pk, "peak": src}))
 
 
@@ -268,6 +272,7 @@ def main(argv=None):
     gg.add_argument("--experts", type=int, default=8)
     gg.add_argument("--topk", type=int, default=8)
     gg.add_argument("--gathered", action="store_true")
+    gg.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"])
     gg.set_defaults(fn=cmd_grouped)
     u = sub.add_parser("ulysses")
     u.add_argument("--which", default="pre", choices=["pre", "post"])
@@ -289,7 +294,13 @@ def main(argv=None):
         p.add_argument("--warmup", type=int, default=3)
         p.add_argument("--no-flush", action="store_true")
     a = ap.parse_args(argv)
-    a.fn(a)
+    try:
+        a.fn(a)
+    finally:
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized():
+            torch.cuda.synchronize()
+            dist.destroy_process_group()
 
 
 if __name__ == "__main__":
