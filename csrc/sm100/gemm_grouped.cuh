@@ -61,6 +61,7 @@ struct GroupedParams {
   uint32_t* local_cnt;             // [W]
   uint32_t* wave_ctr;              // optional: tiles whose loads are all issued (wave-synchronous starts)
   int32_t ring_inflight;           // loads in flight ahead of the stores in the push / gather rings (0 = all slots but one)
+  int32_t comm_split;              // 1: with an all-gather and a pre-gather to do, warp 2 pushes and warp 3 gathers
   // ---- layer 1 with the combine fused in (SCATTER_)
   int32_t topk;
   const int32_t* row_entry;        // [rows of this rank] token * topk + k of every local sorted row
@@ -300,9 +301,17 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
         // push this rank's shard to peer rank-d (d = 0: the own landing slot), then - in pre-gather
         // mode - copy the rows that come from source rank+d, which arrives during the same step
         // because every rank walks the same rotation, into the expert-sorted buffer.
+        // Optional (comm_split): with both jobs to do (all-gather and pre-gather on several ranks) warp 2
+        // pushes all steps and warp 3 gathers all steps, so that the NVLink transfer of step d + 1 does not
+        // wait for the local copies of step d. Measured slower than both warps doing both in turn (layer 0
+        // at four ranks: 1.97 against 1.88 ms), so it is off by default.
+        const bool split = Cfg::PREGATHER && p.do_allgather && p.world > 1 && p.comm_split != 0;
+        const bool do_push = p.do_allgather && (!split || warp == 2);
+        const bool do_gather = Cfg::PREGATHER && (!split || warp == 3);
         const uint32_t ring = comm_base + (warp - 2) * (Cfg::COMM_BYTES / 2);
         const uint32_t rbar = ring_bar_base + (warp - 2) * 4 * 8u;
-        const uint32_t cw = blockIdx.x * 2 + (warp - 2), ncw = gridDim.x * 2;
+        const uint32_t cw = split ? blockIdx.x : blockIdx.x * 2 + (warp - 2);
+        const uint32_t ncw = split ? gridDim.x : gridDim.x * 2;
         const int64_t row_bytes = static_cast<int64_t>(p.K) * Cfg::ELT;
         uint32_t used[4] = {0u, 0u, 0u, 0u};   // loads seen by each ring barrier (their phase)
         struct Item {
@@ -351,7 +360,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
         };
         const int steps = p.do_allgather ? p.world : 1;
         for (int d = 0; d < steps; ++d) {
-          if (p.do_allgather) {
+          if (do_push) {
             constexpr uint32_t CH = Cfg::COMM_BYTES / 2 / 4;   // 4 slots of 4 KiB
             const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ag_src);
             const int64_t bytes = static_cast<int64_t>(p.tokens_per_rank) * row_bytes;
@@ -380,7 +389,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) grouped_gemm_kernel(const __g
               ptx::st_release_sys(p.ag_flags[peer] + p.rank, p.epoch);
             }
           }
-          if constexpr (Cfg::PREGATHER) {
+          if (Cfg::PREGATHER && do_gather) {
             constexpr uint32_t SLOT = Cfg::COMM_BYTES / 2 / 2;  // 2 slots of 8 KiB (over ring slots {0,1}, {2,3})
             const uint8_t* tokens = reinterpret_cast<const uint8_t*>(p.a_tokens);
             uint8_t* sorted = reinterpret_cast<uint8_t*>(p.a_sorted);
