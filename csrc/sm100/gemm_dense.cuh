@@ -1418,21 +1418,19 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
         // Arrival counting runs one tile behind: waiting for this tile's stores to land would
         // stall the warp for an NVLink round trip, so wait only for the previous tile's (all but
         // the store groups committed for this tile) and count that one.
-        const bool stored = true;
-        if (stored) {
-          if (lane == 0) {
-            // store groups this warp committed for a whole tile; a piece of a split tile commits
-            // fewer, so there everything is waited for
-            constexpr int kGroupsPerTile = Cfg::BS ? BN / 128 : Cfg::MT * BN / 64;
-            if (c.shift == 0) ptx::bulk_wait<kGroupsPerTile>();
-            else ptx::bulk_wait<0>();
-            if (pend_seg >= 0) rs_arrive(pend_seg, pend_mt, pend_chunks);
-          }
-          // tiles of the own segment stay here: nobody is told
-          pend_seg = own_rs ? -1 : c.seg;
-          pend_mt = c.m_tile;
-          pend_chunks = Cfg::BS ? static_cast<uint32_t>(BN / 128) : static_cast<uint32_t>(Cfg::MT * ((BN >> c.shift) / 64));
+        if (lane == 0) {
+          // store groups this warp committed for a whole tile; a piece of a split tile commits
+          // fewer, so there everything is waited for
+          constexpr int kGroupsPerTile = Cfg::BS ? BN / 128 : Cfg::MT * BN / 64;
+          if (c.shift == 0) ptx::bulk_wait<kGroupsPerTile>();
+          else ptx::bulk_wait<0>();
+          if (pend_seg >= 0) rs_arrive(pend_seg, pend_mt, pend_chunks);
         }
+        // own tiles that were summed in the epilogue stay here: nobody is told
+        pend_seg = own_rs ? -1 : c.seg;
+        pend_mt = c.m_tile;
+        pend_chunks = Cfg::BS ? static_cast<uint32_t>(BN / 128)
+                              : static_cast<uint32_t>(Cfg::MT * ((BN >> c.shift) / 64));
         __syncwarp();
       }
     }

@@ -74,7 +74,10 @@ class BlockScaleGemm:
             raise TypeError("BlockScaleGemm supports float8_e4m3fn inputs")
         self.input_dtype, self.weight_dtype = input_dtype, weight_dtype
         self.output_dtype = output_dtype or torch.bfloat16
-        self.num_streams = num_streams  # one persistent kernel fills the GPU; no side streams
+        # side streams of the per-expert forms: an expert with fewer tiles than the GPU has SMs leaves the
+        # rest to the next expert's launch
+        self.num_streams = max(1, int(num_streams))
+        self._streams: list = []
 
     def forward(self, input: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
                 output: Optional[torch.Tensor] = None, input_scale: Optional[torch.Tensor] = None,
@@ -110,21 +113,48 @@ class BlockScaleGemm:
         out = output if output is not None else torch.empty((M, N), dtype=self.output_dtype, device=input.device)
         # (splits normally live on the host, as in the reference; a device tensor costs one sync here)
         splits = [int(v) for v in (input_splits.tolist() if torch.is_tensor(input_splits) else input_splits)]
-        row = 0
+        jobs, row = [], 0
         for e, cnt in enumerate(splits):
             if cnt:
                 if row % BLOCK:
                     raise ValueError("expert row ranges must start on multiples of 128 (1x128 scale blocks)")
-                sa_e = input_scale[row // BLOCK:(row + cnt + BLOCK - 1) // BLOCK]
-                self.forward(input[row:row + cnt], weight[e], None if bias is None else bias[e],
-                             out[row:row + cnt], sa_e, weight_scale[e])
+                jobs.append((e, row, cnt))
             row += cnt
+
+        def run(e, row, cnt):
+            sa_e = input_scale[row // BLOCK:(row + cnt + BLOCK - 1) // BLOCK]
+            self.forward(input[row:row + cnt], weight[e], None if bias is None else bias[e],
+                         out[row:row + cnt], sa_e, weight_scale[e])
+
+        n = min(self.num_streams, len(jobs))
+        if n <= 1 or not input.is_cuda:
+            for j in jobs:
+                run(*j)
+            return out
+        # fork: every side stream starts after what the caller's stream has queued so far; join: the
+        # caller's stream continues after all of them
+        cur = torch.cuda.current_stream(input.device)
+        while len(self._streams) < n:
+            self._streams.append(torch.cuda.Stream(input.device))
+        fork = torch.cuda.Event()
+        fork.record(cur)
+        for i in range(n):
+            self._streams[i].wait_event(fork)
+        for i, j in enumerate(jobs):
+            with torch.cuda.stream(self._streams[i % n]):
+                run(*j)
+        for i in range(n):
+            done = torch.cuda.Event()
+            done.record(self._streams[i])
+            cur.wait_event(done)
         return out
 
     def forward_multistream(self, input, input_splits, weight, bias=None, output=None, input_scale=None,
                             weight_scale=None):
         """Per-expert block-scaled GEMMs: ``weight [E, N, K]``, ``weight_scale [E, N/128, K/128]``,
-        rows of ``input`` grouped by expert as given by ``input_splits``."""
+        rows of ``input`` grouped by expert as given by ``input_splits`` (host values, as in the
+        reference). One launch per expert, dealt over ``num_streams`` side streams (reference:
+        ``forward_multi_stream``, python/flux/cpp_mod.pyi:283-292)."""
         return self._per_expert(input, input_splits, weight, bias, output, input_scale, weight_scale)
 
     wgrad_multistream = forward_multistream

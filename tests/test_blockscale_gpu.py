@@ -52,9 +52,37 @@ def test_blockscale_bias_and_grouped(dev):
     assert (out.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
     wq3, sw3 = wq.view(E, N, K), sw.view(E, N // 128, K // 128)
     outg = op.forward_grouped(xq, torch.tensor([256, 256]), wq3, input_scale=sx, weight_scale=sw3)
+    # the same on one stream must give the same bits
+    one = flux.BlockScaleGemm(num_streams=1).forward_multi_stream(xq, [256, 256], wq3, input_scale=sx, weight_scale=sw3)
+    assert torch.equal(outg, one)
     for e in range(E):
         r = flux.blockscale_gemm_torch(xq[e * 256:(e + 1) * 256], wq3[e], sx[e * 2:(e + 1) * 2], sw3[e], torch.float32)
         assert (outg[e * 256:(e + 1) * 256].float() - r).abs().max().item() <= 2e-2 * max(1.0, r.abs().max().item())
+
+
+def test_blockscale_per_expert_forms_on_side_streams(dev):
+    """Experts of different sizes (one empty) dealt over three side streams, called twice in a row and
+    followed at once by work on the caller's stream: the join must order it after every expert."""
+    import tempname_new_b200 as flux
+    N, K, E = 256, 512, 5
+    splits = [128, 384, 0, 256, 640]
+    M = sum(splits)
+    x, w, xq, sx, wq, sw = _quantized(M, N * E, K, dev, seed=3)
+    wq3, sw3 = wq.view(E, N, K), sw.view(E, N // 128, K // 128)
+    op = flux.BlockScaleGemm(num_streams=3)
+    for _ in range(2):
+        out = op.forward_multi_stream(xq, splits, wq3, input_scale=sx, weight_scale=sw3)
+        total = out.float().sum()                       # the caller's stream reads the result right away
+    row = 0
+    ref_total = 0.0
+    for e, cnt in enumerate(splits):
+        if cnt:
+            r = flux.blockscale_gemm_torch(xq[row:row + cnt], wq3[e], sx[row // 128:(row + cnt) // 128], sw3[e],
+                                           torch.float32)
+            assert (out[row:row + cnt].float() - r).abs().max().item() <= 2e-2 * max(1.0, r.abs().max().item())
+            ref_total += out[row:row + cnt].float().sum().item()
+        row += cnt
+    assert abs(total.item() - ref_total) <= 1e-3 * max(1.0, abs(ref_total))
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 384, 512), (1024, 1024, 1024)])
