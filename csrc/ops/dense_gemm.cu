@@ -232,11 +232,10 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
     // chosen by cta_group = 2, but measured slower (977 against 1128 TFLOP/s at 16384 x 3584 x 8192): the
     // k-block hand-over then waits for the slowest of sixteen promotion warps on two SMs.
     cg = (a->cta_group == 2 && a->tile_n != 256 && a->M / (multi ? a->world : 1) >= 256) ? 2 : 1;
-    // 128 x 256 tiles on request (tile_n = 256). Per-tensor fp8 GEMMs on 128 x 128 tiles stop at 1450 TFLOP/s
-    // here (the operand stream into the SM is the bound), on 128 x 256 at 2600; the block-scaled variant on
-    // 128 x 256 tiles measured between 0.6 and 1.1 times the 128 x 128 one depending on where the compiler put
-    // the spills of its 128 accumulator registers per thread, so it is not the default.
-    bn = (cg == 1 && a->tile_n == 256) ? 256 : 128;
+    // 128 x 256 tiles wherever N allows (tile_n = 128 pins the narrow ones): 1330 - 1350 against 1010 - 1060
+    // TFLOP/s. Per-tensor fp8 GEMMs on 128 x 128 tiles stop at 1450 TFLOP/s here (the operand stream into the
+    // SM is the bound), on 128 x 256 at 2600.
+    bn = (cg == 1 && a->tile_n != 128 && (a->N % 256 == 0 || a->N >= 2048)) ? 256 : 128;
   } else if (a->mode == FLUXB_A2A_GEMM) {
     if (cg == 2 && a->M >= 256) bn = 256;
     else { cg = 1; bn = 128; }

@@ -62,8 +62,8 @@ enum TraceSlot : int {
                           // reduce-scatter: 8 = first tile of the own segment reached by epilogue warp 4
                           // (epilogue form), 9 / 10 = the tail that sums the slabs entered / left;
                           // block-scaled variants of the self-checking build: 8 / 9 = cycles promotion warp 4
-                          // waited for MMAs / read TMEM, 11 = its k-blocks, 12 / 13 = cycles the issuer
-                          // waited for a free TMEM buffer / for operands
+                          // waited for MMAs / read TMEM, 10 = its cycles in all, 11 = its k-blocks,
+                          // 12 / 13 = cycles the issuer waited for a free TMEM buffer / for operands
 };
 constexpr int kTraceWords = 16;  // words per CTA
 constexpr int kMaxHeadGroups = 3;  // q, k, v
@@ -1153,7 +1153,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     uint32_t own_seen = 0;   // tile rows of the own segment whose W-1 slabs were seen to have landed
     uint64_t bs_acc[Cfg::BS ? BN / 4 : 1];   // block-scaled: this thread's row x BN / 2 columns, fp32 pairs
 #ifdef FLUXB_DEBUG_CHECKS
-    uint64_t probe_wait = 0, probe_ld = 0, probe_kb = 0;
+    uint64_t probe_wait = 0, probe_ld = 0, probe_kb = 0, probe_total = 0;
+    const long long probe_t0 = clock64();
 #endif
     for (int t = tile_slot; t < total_tiles; t += tile_stride, ++it) {
       if (*abort_word) break;
@@ -1240,22 +1241,24 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
 #pragma unroll
         for (int j = 0; j < NCH * 32; ++j) bs_acc[j] = 0ull;
         const uint32_t n0 = static_cast<uint32_t>(it) * kbs;
-        // Scales are fetched four k-blocks at a time, one group ahead: a fetch per k-block, used one
-        // k-block later, put the latency of a global load into every iteration.
-        float csa[4], csb[4], nsa[4], nsb[4];
+        // Scales are fetched G k-blocks at a time, one group ahead: four with 128-column tiles; two with
+        // 256-column tiles, whose 128 accumulator registers per thread leave little room (one k-block ahead
+        // measured 1170 TFLOP/s, two 1350, four 1320 with more spills).
+        constexpr int G = NCH == 2 ? 2 : 4;
+        float csa[G], csb[G], nsa[G], nsb[G];
         auto load_scales = [&](int kb0, float* dsa, float* dsb) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
+          for (int i = 0; i < G; ++i) {
             const int kk = kb0 + i < kbs ? kb0 + i : kbs - 1;   // past the end: a repeated, unused load
             dsa[i] = sa_ptr[static_cast<int64_t>(kk) * 128];
             dsb[i] = p.sb_groupwise ? 1.f : sb_ptr[kk];
           }
         };
         load_scales(0, csa, csb);
-        for (int kb0 = 0; kb0 < kbs; kb0 += 4) {
-          load_scales(kb0 + 4, nsa, nsb);
+        for (int kb0 = 0; kb0 < kbs; kb0 += G) {
+          load_scales(kb0 + G, nsa, nsb);
 #pragma unroll
-          for (int ki = 0; ki < 4; ++ki) {
+          for (int ki = 0; ki < G; ++ki) {
             const int kb = kb0 + ki;
             if (kb >= kbs) break;
             const uint32_t n = n0 + kb;
@@ -1291,7 +1294,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
                 // The buffer's contents are in registers (wait::ld), so the hand-over needs no release ordering.
                 // A cluster-scope release arrive also waits for the warp's scale loads in flight, which
                 // halved the throughput of CTA pairs.
-                if (CG == 1 || cta_rank == 0) ptx::mbar_arrive(tempty_bar(buf));
+                if (CG == 1 || cta_rank == 0) ptx::mbar_arrive_relaxed(tempty_bar(buf));
                 else ptx::mbar_arrive_remote_relaxed(tempty_bar(buf), 0);
               }
             };
@@ -1305,12 +1308,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
 #ifdef FLUXB_DEBUG_CHECKS
             const long long pc1 = clock64();
 #endif
-            uint32_t r0[32], r1[32];
             const uint32_t taddr = lane_base + buf * BN;
-            ptx::tmem_ld_32x32b_x32(taddr, r0);
-            ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
-            ptx::tmem_ld_wait();
             if constexpr (NCH == 1) {
+              uint32_t r0[32], r1[32];
+              ptx::tmem_ld_32x32b_x32(taddr, r0);
+              ptx::tmem_ld_32x32b_x32(taddr + 32, r1);
+              ptx::tmem_ld_wait();
 #ifdef FLUXB_DEBUG_CHECKS
               probe_ld += static_cast<uint64_t>(clock64() - pc1);
 #endif
@@ -1318,18 +1321,21 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
               promote(r0, 0, 0);
               promote(r1, 16, 32);
             } else {
-              // the second 64 columns are fetched while the first are multiplied
-              promote(r0, 0, 0);
-              ptx::tmem_ld_32x32b_x32(taddr + 64, r0);
-              promote(r1, 16, 32);
-              ptx::tmem_ld_32x32b_x32(taddr + 96, r1);
-              ptx::tmem_ld_wait();
+              // 128 columns, 32 at a time through one set of staging registers: the warp that shares the
+              // scheduler multiplies while this one waits for its read
+              uint32_t r0[32];
+#pragma unroll
+              for (int c4 = 0; c4 < 4; ++c4) {
+                ptx::tmem_ld_32x32b_x32(taddr + 32 * c4, r0);
+                ptx::tmem_ld_wait();
+                if (c4 == 3) {
 #ifdef FLUXB_DEBUG_CHECKS
-              probe_ld += static_cast<uint64_t>(clock64() - pc1);
+                  probe_ld += static_cast<uint64_t>(clock64() - pc1);
 #endif
-              hand_over();
-              promote(r0, 32, 64);
-              promote(r1, 48, 96);
+                  hand_over();
+                }
+                promote(r0, 16 * c4, 32 * c4);
+              }
             }
 #ifdef FLUXB_DEBUG_CHECKS
             // self-checking build: cycles of this warp waiting for the k-block's MMAs (the multiply-adds of
@@ -1337,10 +1343,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
             // reading TMEM (with 256-column tiles: including the first half's multiply-adds)
             probe_wait += static_cast<uint64_t>(pc1 - pc0);
             probe_kb += 1;
+            probe_total = static_cast<uint64_t>(clock64() - probe_t0);   // whole promotion loop of this warp so far
 #endif
           }
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
+          for (int i = 0; i < G; ++i) {
             csa[i] = nsa[i];
             csb[i] = nsb[i];
           }
@@ -1459,6 +1466,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
       tr[8] = probe_wait;
       tr[9] = probe_ld;
       tr[11] = probe_kb;
+      tr[10] = probe_total;   // cycles from this warp's start to the end of its last promotion
     }
 #endif
   }

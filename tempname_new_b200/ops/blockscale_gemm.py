@@ -56,10 +56,10 @@ def blockscale_args(a, w, sa, sb, bias, out_dtype, m, status=None, keep=None) ->
     if tuple(sb.shape) not in ((N // BLOCK, K // BLOCK), (N // BLOCK, K // BLOCK, BLOCK)):
         raise ValueError(f"weight_scale must be [{N // BLOCK}, {K // BLOCK}] or, one per weight row, "
                          f"[{N // BLOCK}, {K // BLOCK}, {BLOCK}]; got {tuple(sb.shape)}")
-    # single CTAs on 128 x 128 tiles; FLUXB_BS_TILE_N=256 asks for 128 x 256, FLUXB_BS_CTA_GROUP=2 for CTA pairs
-    # on 256 x 128 tiles (neither measured faster)
+    # single CTAs on 128 x 256 tiles where N allows (FLUXB_BS_TILE_N=128 pins 128 x 128); FLUXB_BS_CTA_GROUP=2
+    # asks for CTA pairs on 256 x 128 tiles (measured slower)
     cta_group = int(os.environ.get("FLUXB_BS_CTA_GROUP", "1"))
-    tile_n = int(os.environ.get("FLUXB_BS_TILE_N", "128"))
+    tile_n = int(os.environ.get("FLUXB_BS_TILE_N", "128" if cta_group == 2 else "0"))
     args = _dense.base_args(a, w, bias, out_dtype, tile_n=tile_n, cta_group=cta_group, m=m, status=status, keep=keep)
     args.sa, args.sb = sa.data_ptr(), sb.data_ptr()
     args.blockscale = 2 if groupwise else 1

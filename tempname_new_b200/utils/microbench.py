@@ -100,8 +100,26 @@ def cmd_blockscale(a):
                not a.no_flush)
     tf = 2.0 * a.m * a.n * a.k / ms / 1e9
     pk, _, src = peaks()
-    print(json.dumps({"op": "blockscale_gemm", "m": a.m, "n": a.n, "k": a.k, "ms": ms, "tflops": tf,
-                      "frac_of_bf16_peak": tf / pk, "peak": src}))
+    rec = {"op": "blockscale_gemm", "m": a.m, "n": a.n, "k": a.k, "ms": ms, "tflops": tf,
+           "frac_of_bf16_peak": tf / pk, "peak": src}
+    if a.phases:
+        # phase clocks of the promotion (self-checking build only: FLUXB_DEBUG=1), cycles per k-block, median
+        # over the CTAs: timeline slots 8 / 9 / 10 = promotion warp 4 waiting for MMAs / reading TMEM / in all,
+        # 11 = its k-blocks, 12 / 13 = the MMA issuer waiting for a free TMEM buffer / for operands
+        from ..ops import _dense
+        with _dense.KernelTimeline(dev) as tl:
+            op.forward(xq, wq, output=out, input_scale=sx, weight_scale=sw)
+            torch.cuda.synchronize()
+            t = tl.buf.cpu()
+        t = t[t[:, 11] > 0].double()
+        if t.numel() == 0:
+            rec["phases"] = "no phase clocks: load the self-checking build (FLUXB_DEBUG=1)"
+        else:
+            kb = t[:, 11]
+            rec["phases"] = {name: round(float((t[:, col] / kb).median()), 1) for name, col in
+                             (("promotion_waits_for_mma", 8), ("promotion_reads_tmem", 9), ("promotion_all", 10),
+                              ("issuer_waits_for_tmem", 12), ("issuer_waits_for_operands", 13))}
+    print(json.dumps(rec))
 
 
 def cmd_grouped(a):
@@ -264,6 +282,7 @@ def main(argv=None):
     b.add_argument("--m", type=int, default=8192)
     b.add_argument("--n", type=int, default=8192)
     b.add_argument("--k", type=int, default=8192)
+    b.add_argument("--phases", action="store_true", help="print the promotion phase clocks (FLUXB_DEBUG=1)")
     b.set_defaults(fn=cmd_blockscale)
     gg = sub.add_parser("grouped")
     gg.add_argument("--rows", type=int, default=65536)
