@@ -345,8 +345,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
 
   if (warp < 4) {
   // (block-scaled variant) producer, issuer and communication warps give registers to the
-  // promotion warps; all four warps of the group execute the same instruction here
-  if constexpr (Cfg::BS) ptx::setmaxnreg_dec<(BN == 256 ? 56 : 88)>();
+  // promotion warps; all four warps of the group execute the same instruction here. With 256-column
+  // tiles the promotion warps hold 128 accumulators and take all they can get: 40 / 232 measured
+  // 1560 TFLOP/s where 56 / 224 gave 1376 and 24 / 240 the same 1560 (the compiler's spill report:
+  // 168, 176 and 226 bytes per thread, the last mostly in the leading warps).
+  if constexpr (Cfg::BS) ptx::setmaxnreg_dec<(BN == 256 ? 40 : 88)>();
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -971,7 +974,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     }
   }
   } else {
-      if constexpr (Cfg::BS) ptx::setmaxnreg_inc<(BN == 256 ? 224 : 208)>();
+      if constexpr (Cfg::BS) ptx::setmaxnreg_inc<(BN == 256 ? 232 : 208)>();
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;              // TMEM lane quadrant this warp may read
     const int ew = warp - 4;             // epilogue warp index
