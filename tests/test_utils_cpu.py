@@ -235,3 +235,36 @@ def test_source_hygiene_of_the_tree():
     assert {"trailing whitespace", "tab character", "no newline at end of file"} <= kinds
     assert any("outside the source tree" in k for k in kinds)
     assert hygiene.fix_text("a = 1  \n\n\n") == "a = 1\n"
+
+
+def test_weight_layout_helper_and_per_expert_block_scaled_cpu_path():
+    """``as_nk`` hands the kernels [N, K]: a [K, N] weight is a free transposed view when it can be read
+    in place (16-bit, CUDA, aligned) and a re-laid-out copy otherwise; the per-expert block-scaled forms
+    fall back to the PyTorch statement, expert by expert, on CPU tensors."""
+    import torch
+    import tempname_new_b200 as flux
+    from tempname_new_b200.ops import _dense
+    from tempname_new_b200.ops.gemm_only import as_nk
+    w_kn = torch.randn(64, 48).bfloat16()                      # [K, N]
+    v = as_nk(w_kn, True)
+    assert v.shape == (48, 64) and v.stride(-1) == 1           # CPU: copied into the K-major layout
+    assert torch.equal(v, w_kn.t())
+    assert as_nk(v, False) is v                                # already [N, K] with contiguous K
+    # the in-place rule itself: N contiguous, N and pitch multiples of 8, 16-byte aligned, 16-bit
+    assert _dense.kn_in_place(torch.empty(64, 48, dtype=torch.bfloat16).t())
+    assert not _dense.kn_in_place(torch.empty(64, 44, dtype=torch.bfloat16).t())          # N % 8
+    assert not _dense.kn_in_place(torch.empty(64, 48, dtype=torch.float8_e4m3fn).t())     # 8-bit
+    assert not _dense.kn_in_place(torch.empty(64, 48, dtype=torch.bfloat16))              # K contiguous already
+    # block-scaled per-expert forms on CPU tensors
+    E, N, K = 2, 128, 256
+    x = torch.randn(256, K)
+    w = torch.randn(E * N, K) * 0.1
+    qz = flux.Quantization(torch.float32, torch.float8_e4m3fn)
+    xq, sx, _, _ = qz.quantize_vector_blockwise(x, False)
+    wq, sw, _, _ = qz.quantize_square_blockwise(w, False)
+    op = flux.BlockScaleGemm(num_streams=3)
+    out = op.forward_multi_stream(xq, [128, 128], wq.view(E, N, K), input_scale=sx, weight_scale=sw.view(E, 1, K // 128))
+    for e in range(E):
+        ref = flux.blockscale_gemm_torch(xq[e * 128:(e + 1) * 128], wq.view(E, N, K)[e], sx[e:e + 1],
+                                         sw.view(E, 1, K // 128)[e], torch.float32)
+        assert (out[e * 128:(e + 1) * 128].float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
