@@ -159,11 +159,12 @@ struct DenseGemmParams {
 // its 128 * MT_ x BN slice of D in its own TMEM.
 // COMM_ > 0 reserves COMM_ bytes of shared memory as staging rings for the all-gather push.
 // BS_ = true: block-scaled fp8 (1x128 A scales, 128x128 B scales): every 128-deep k-block is
-// accumulated into a fresh TMEM buffer (four of them, so the issuer runs up to four k-blocks ahead)
+// accumulated into a fresh TMEM buffer (512 / BN_ of them: the issuer runs that many k-blocks ahead)
 // and promoted into fp32 registers, multiplied by its scales, by eight epilogue warps: two per
-// TMEM lane quadrant, each owning 64 of the tile's 128 columns for the whole tile. With CG_ = 2 a
-// CTA pair shares a 256 x 128 tile (each CTA loads half of B): 24 KB instead of 32 KB enter an SM
-// per k-block, which matters because at fp8 rates 128 x 128 tiles are bound by L2 -> SM bandwidth.
+// TMEM lane quadrant, each owning half of the tile's columns for the whole tile. BN_ = 256 (one CTA,
+// 128 x 256 tiles) is the faster shape: on 128 x 128 tiles even a kernel that promotes nothing stops at
+// a third of the fp8 rate. With CG_ = 2 and BN_ = 128 a CTA pair shares a 256 x 128 tile (each CTA loads
+// half of B; measured slower than single CTAs).
 template <int BN_, int KIND_, int STAGES_, int CG_ = 1, int COMM_ = 0, bool BS_ = false, int MT_ = 1>
 struct DenseCfg {
   static constexpr int COMM_BYTES = COMM_;
@@ -172,7 +173,7 @@ struct DenseCfg {
   static constexpr int EPI_WARPS = BS_ ? 8 : 4;
   static constexpr int THREADS = 128 + 32 * EPI_WARPS;
   // MT_ == 1: two accumulators used alternately (the epilogue of a tile overlaps the next main loop);
-  // MT_ == 2: the two row halves of one tile; block-scaled: 4 k-block buffers
+  // MT_ == 2: the two row halves of one tile; block-scaled: one buffer per k-block in flight (4 or 2)
   static constexpr int ACC_BUFS = BS_ ? 512 / BN_ : 2;
   static_assert(!BS_ || (KIND_ == 1 && (BN_ == 128 || (BN_ == 256 && CG_ == 1))),
                 "block-scaled variant: fp8; 128 columns (128 or 256 rows) or 128 x 256 tiles");
@@ -193,7 +194,8 @@ struct DenseCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_BUF_BYTES = 32 * 128;           // 32 rows x 64 bf16
   // staging buffers per epilogue warp: the variants with a communication ring give one of the two
-  // to a sixth pipeline stage (the epilogue of a tile hides behind the next tile's main loop anyway)
+  // to a sixth pipeline stage (the epilogue of a tile hides behind the next tile's main loop anyway);
+  // block-scaled 256-column tiles give it to the fourth 48 KB stage
   static constexpr int EPI_BUFS = ((COMM_ > 0 && !BS_) || (BS_ && BN_ == 256)) ? 1 : 2;
   static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUFS * EPI_BUF_BYTES;
   static constexpr int BAR_BYTES = 256;
