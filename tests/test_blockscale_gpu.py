@@ -26,7 +26,8 @@ def _quantized(M, N, K, dev, seed=0):
     return x, w, xq, sx, wq, sw
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (512, 1024, 2048), (1024, 3584, 8192)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (512, 1024, 2048), (1024, 3584, 8192),
+                                   (384, 2176, 640)])   # 128 x 256 tiles with a half-empty last column tile
 def test_blockscale_gemm(dev, M, N, K):
     import tempname_new_b200 as flux
     x, w, xq, sx, wq, sw = _quantized(M, N, K, dev)
