@@ -409,8 +409,9 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
           const char* e = getenv("FLUXB_RS_TAIL");
           return e ? atoi(e) : -1;
         }();
-        // (the block-scaled variants, whose warps 0-3 have given their registers away, keep the epilogue form)
-        p.rs_tail = (multi && !a->blockscale && (tail_env >= 0 ? tail_env != 0 : a->world >= 3)) ? 1 : 0;
+        // (in the block-scaled variants, whose warps 0-3 have given their registers away, the eight promotion
+        // warps run the tail)
+        p.rs_tail = (multi && (tail_env >= 0 ? tail_env != 0 : a->world >= 3)) ? 1 : 0;
         p.rs_claim = a->wave_ctr ? a->wave_ctr + 1 : nullptr;
       }
       for (int r = 0; r < a->world; ++r) {

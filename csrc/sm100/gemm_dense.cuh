@@ -345,6 +345,116 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
   const int k_blocks = (p.K + BK - 1) / BK;
   const bool multi = p.world > 1 && p.mode != kModePlain;
 
+  // -------------------------------------------------------------------- reduce-scatter tail
+  // Run by 256 threads of the CTA (tid 0..255; `sync` is a barrier among exactly those): all threads after
+  // the teardown, or - block-scaled variants, whose leading warps have given their registers away - the
+  // eight promotion warps at the end of their role.
+  auto rs_tail = [&](const int tid, auto&& sync) {
+    // Three ranks and more: the own tiles went to the own staging slab like everybody else's, and
+    // all threads of the grid now sum the W slabs into rs_out (fp32 sums of 16-bit addends, slabs in
+    // rank order). Adding W-1 slabs inside the epilogue of the own tiles, as two ranks do, costs
+    // more here than this tail: those epilogues hold the accumulators that the next tile waits for.
+    // A work unit is kUnit 16-byte pieces of the [seg_rows, N] output; units are claimed from a
+    // counter (every CTA makes exactly one failing claim; whoever makes the very last claim of the
+    // launch puts the counter back to zero), or dealt out round-robin when there is no counter.
+    constexpr int kUnit = 256 * 16;
+    const int64_t pieces_per_row = p.N >> 3;
+    const int64_t total_pieces = static_cast<int64_t>(p.seg_rows) * pieces_per_row;
+    const uint32_t units = static_cast<uint32_t>((total_pieces + kUnit - 1) / kUnit);
+    const uint4* stage = reinterpret_cast<const uint4*>(p.rs_stage);
+    uint4* out = reinterpret_cast<uint4*>(p.rs_out);
+    const bool tail_f16 = p.out_f16 != 0;
+    if (tid == 0) stamp(kTraceSlice0 + 1);      // reduce tail entered
+    uint32_t next_static = blockIdx.x;
+    uint32_t rows_seen = 0;   // (threads 0..W-1) tile rows whose slab of source tid was seen to have landed
+    auto claim = [&]() -> uint32_t {
+      if (*abort_word) return 0xFFFFFFFFu;
+      uint32_t got;
+      if (p.rs_claim != nullptr) {
+        got = atomicAdd(p.rs_claim, 1u);
+        if (got == units + gridDim.x - 1u) atomicExch(p.rs_claim, 0u);
+      } else {
+        got = next_static;
+        next_static += gridDim.x;
+      }
+      return got;
+    };
+    int par = 0;
+    sync();
+    // (claims are made by a thread that does not also look at arrival flags)
+    if (tid == 32) claim_slot[0] = claim();
+    sync();
+    while (true) {
+      const uint32_t u = claim_slot[par];
+      if (u >= units) break;
+      // the next unit is claimed while this one is summed
+      if (tid == 32) claim_slot[par ^ 1] = claim();
+      {
+        // every source's rows of this unit must have landed: one thread per source looks at the flags
+        // of the tile rows that the unit touches (usually one); the block barrier passes it on
+        const int64_t c0 = static_cast<int64_t>(u) * kUnit;
+        const int64_t c1 = (c0 + kUnit < total_pieces ? c0 + kUnit : total_pieces) - 1;
+        const int mt0 = static_cast<int>((c0 / pieces_per_row) / BM);
+        const int mt1 = static_cast<int>((c1 / pieces_per_row) / BM);
+        if (static_cast<int>(tid) < p.world)
+          for (int mt = mt0; mt <= mt1; ++mt) {
+            if (mt < 32 && ((rows_seen >> mt) & 1u)) continue;
+            flag_wait_ge(wc, p.rs_ctr[p.rank] + mt * kMaxRanks + tid, p.epoch, kSiteTileCounter);
+            if (mt < 32) rows_seen |= 1u << mt;
+          }
+        sync();
+      }
+      constexpr int PIECES = 4;          // 16-byte pieces per thread in flight per source
+#pragma unroll 1
+      for (int rep = 0; rep < kUnit / 256; rep += PIECES) {
+        int64_t idx[PIECES];
+        bool ok[PIECES];
+#pragma unroll
+        for (int h = 0; h < PIECES; ++h) {
+          idx[h] = static_cast<int64_t>(u) * kUnit + (rep + h) * 256 + tid;
+          ok[h] = idx[h] < total_pieces;
+        }
+        uint4 v[kMaxRanks][PIECES];
+#pragma unroll
+        for (int sr = 0; sr < kMaxRanks; ++sr)
+#pragma unroll
+          for (int h = 0; h < PIECES; ++h)
+            if (sr < p.world && ok[h]) v[sr][h] = ptx::ld_global_cs_v4(stage + sr * total_pieces + idx[h]);
+        float accv[PIECES][8];
+#pragma unroll
+        for (int h = 0; h < PIECES; ++h)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) accv[h][e] = 0.f;
+#pragma unroll
+        for (int sr = 0; sr < kMaxRanks; ++sr)
+#pragma unroll
+          for (int h = 0; h < PIECES; ++h) {
+            if (sr < p.world && ok[h]) {
+              const uint32_t w[4] = {v[sr][h].x, v[sr][h].y, v[sr][h].z, v[sr][h].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                accv[h][2 * e] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] & 0xFFFFu), tail_f16);
+                accv[h][2 * e + 1] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] >> 16), tail_f16);
+              }
+            }
+          }
+#pragma unroll
+        for (int h = 0; h < PIECES; ++h) {
+          if (!ok[h]) continue;
+          uint4 o;
+          o.x = ptx::pack_half2(tail_f16, accv[h][0], accv[h][1]);
+          o.y = ptx::pack_half2(tail_f16, accv[h][2], accv[h][3]);
+          o.z = ptx::pack_half2(tail_f16, accv[h][4], accv[h][5]);
+          o.w = ptx::pack_half2(tail_f16, accv[h][6], accv[h][7]);
+          out[idx[h]] = o;
+        }
+      }
+      sync();
+      par ^= 1;
+    }
+    if (tid == 0) stamp(kTraceSlice0 + 2);  // reduce tail left
+  };
+
   if (warp < 4) {
   // (block-scaled variant) producer, issuer and communication warps give registers to the
   // promotion warps; all four warps of the group execute the same instruction here. With 256-column
@@ -1449,6 +1559,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
     if (lane == 0) ptx::bulk_wait<0>();
     if (p.mode == kModeReduceScatter && multi && lane == 0 && pend_seg >= 0) rs_arrive(pend_seg, pend_mt, pend_chunks);
     __syncwarp();
+    if constexpr (Cfg::BS) {
+      // (named barrier 1: the eight promotion warps)
+      if (p.mode == kModeReduceScatter && multi && p.rs_tail)
+        rs_tail(static_cast<int>(threadIdx.x) - 128, [] { asm volatile("bar.sync 1, 256;" ::: "memory"); });
+    }
     if (p.mode == kModeGemmA2A && multi) {
       // all stores of this warp have landed; the last warp of the whole grid tells every rank,
       // and everybody stays until all W sources have said so: when this kernel completes, the
@@ -1494,111 +1609,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) dense_gemm_kernel(const __gri
   }
 
   // -------------------------------------------------------------------- reduce-scatter tail
-  if constexpr (!Cfg::BS) if (p.mode == kModeReduceScatter && multi && p.rs_tail) {
-    // Three ranks and more: the own tiles went to the own staging slab like everybody else's, and
-    // all threads of the grid now sum the W slabs into rs_out (fp32 sums of 16-bit addends, slabs in
-    // rank order). Adding W-1 slabs inside the epilogue of the own tiles, as two ranks do, costs
-    // more here than this tail: those epilogues hold the accumulators that the next tile waits for.
-    // A work unit is kUnit 16-byte pieces of the [seg_rows, N] output; units are claimed from a
-    // counter (every CTA makes exactly one failing claim; whoever makes the very last claim of the
-    // launch puts the counter back to zero), or dealt out round-robin when there is no counter.
-    constexpr int kUnit = 256 * 16;
-    const int64_t pieces_per_row = p.N >> 3;
-    const int64_t total_pieces = static_cast<int64_t>(p.seg_rows) * pieces_per_row;
-    const uint32_t units = static_cast<uint32_t>((total_pieces + kUnit - 1) / kUnit);
-    const uint4* stage = reinterpret_cast<const uint4*>(p.rs_stage);
-    uint4* out = reinterpret_cast<uint4*>(p.rs_out);
-    const bool tail_f16 = p.out_f16 != 0;
-    if (threadIdx.x == 0) stamp(kTraceSlice0 + 1);      // reduce tail entered
-    uint32_t next_static = blockIdx.x;
-    uint32_t rows_seen = 0;   // (threads 0..W-1) tile rows whose slab of source threadIdx.x was seen to have landed
-    auto claim = [&]() -> uint32_t {
-      if (*abort_word) return 0xFFFFFFFFu;
-      uint32_t got;
-      if (p.rs_claim != nullptr) {
-        got = atomicAdd(p.rs_claim, 1u);
-        if (got == units + gridDim.x - 1u) atomicExch(p.rs_claim, 0u);
-      } else {
-        got = next_static;
-        next_static += gridDim.x;
-      }
-      return got;
-    };
-    int par = 0;
-    __syncthreads();
-    // (claims are made by a thread that does not also look at arrival flags)
-    if (threadIdx.x == 32) claim_slot[0] = claim();
-    __syncthreads();
-    while (true) {
-      const uint32_t u = claim_slot[par];
-      if (u >= units) break;
-      // the next unit is claimed while this one is summed
-      if (threadIdx.x == 32) claim_slot[par ^ 1] = claim();
-      {
-        // every source's rows of this unit must have landed: one thread per source looks at the flags
-        // of the tile rows that the unit touches (usually one); the block barrier passes it on
-        const int64_t c0 = static_cast<int64_t>(u) * kUnit;
-        const int64_t c1 = (c0 + kUnit < total_pieces ? c0 + kUnit : total_pieces) - 1;
-        const int mt0 = static_cast<int>((c0 / pieces_per_row) / BM);
-        const int mt1 = static_cast<int>((c1 / pieces_per_row) / BM);
-        if (static_cast<int>(threadIdx.x) < p.world)
-          for (int mt = mt0; mt <= mt1; ++mt) {
-            if (mt < 32 && ((rows_seen >> mt) & 1u)) continue;
-            flag_wait_ge(wc, p.rs_ctr[p.rank] + mt * kMaxRanks + threadIdx.x, p.epoch, kSiteTileCounter);
-            if (mt < 32) rows_seen |= 1u << mt;
-          }
-        __syncthreads();
-      }
-      constexpr int PIECES = 4;          // 16-byte pieces per thread in flight per source
-#pragma unroll 1
-      for (int rep = 0; rep < kUnit / 256; rep += PIECES) {
-        int64_t idx[PIECES];
-        bool ok[PIECES];
-#pragma unroll
-        for (int h = 0; h < PIECES; ++h) {
-          idx[h] = static_cast<int64_t>(u) * kUnit + (rep + h) * 256 + threadIdx.x;
-          ok[h] = idx[h] < total_pieces;
-        }
-        uint4 v[kMaxRanks][PIECES];
-#pragma unroll
-        for (int sr = 0; sr < kMaxRanks; ++sr)
-#pragma unroll
-          for (int h = 0; h < PIECES; ++h)
-            if (sr < p.world && ok[h]) v[sr][h] = ptx::ld_global_cs_v4(stage + sr * total_pieces + idx[h]);
-        float accv[PIECES][8];
-#pragma unroll
-        for (int h = 0; h < PIECES; ++h)
-#pragma unroll
-          for (int e = 0; e < 8; ++e) accv[h][e] = 0.f;
-#pragma unroll
-        for (int sr = 0; sr < kMaxRanks; ++sr)
-#pragma unroll
-          for (int h = 0; h < PIECES; ++h) {
-            if (sr < p.world && ok[h]) {
-              const uint32_t w[4] = {v[sr][h].x, v[sr][h].y, v[sr][h].z, v[sr][h].w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                accv[h][2 * e] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] & 0xFFFFu), tail_f16);
-                accv[h][2 * e + 1] += ptx::half_bits_to_float(static_cast<uint16_t>(w[e] >> 16), tail_f16);
-              }
-            }
-          }
-#pragma unroll
-        for (int h = 0; h < PIECES; ++h) {
-          if (!ok[h]) continue;
-          uint4 o;
-          o.x = ptx::pack_half2(tail_f16, accv[h][0], accv[h][1]);
-          o.y = ptx::pack_half2(tail_f16, accv[h][2], accv[h][3]);
-          o.z = ptx::pack_half2(tail_f16, accv[h][4], accv[h][5]);
-          o.w = ptx::pack_half2(tail_f16, accv[h][6], accv[h][7]);
-          out[idx[h]] = o;
-        }
-      }
-      __syncthreads();
-      par ^= 1;
-    }
-    if (threadIdx.x == 0) stamp(kTraceSlice0 + 2);  // reduce tail left
-  }
+  if constexpr (!Cfg::BS)
+    if (p.mode == kModeReduceScatter && multi && p.rs_tail) rs_tail(static_cast<int>(threadIdx.x), [] { __syncthreads(); });
 }
 
 }  // namespace fluxb
