@@ -102,6 +102,13 @@ int fluxb_rs_solo_first(int32_t num_seg);
 int fluxb_decode_tiles(int32_t num_seg, int32_t seg_first, int32_t m_tiles_seg, int32_t n_tiles,
                        int32_t group_m, int32_t seg_span, int32_t seg_solo_first, int32_t bm, int32_t bn,
                        int32_t* out, int32_t n);
+/* The launcher's rule for cutting the tiles of the last, partial wave into column pieces (mode as
+ * FLUXB_TAIL_SPLIT: 0 never, 1 halves or quarters, 2 halves only), and the kernel's order of the resulting
+ * work items: out[4t..4t+3] = (segment, tile row, first column, shift); an item is bn >> shift columns wide. */
+int fluxb_tail_split(int64_t tiles, int64_t slots, int32_t mode, int32_t* split_from, int32_t* split_shift);
+int fluxb_decode_work_items(int32_t num_seg, int32_t seg_first, int32_t m_tiles_seg, int32_t n_tiles,
+                            int32_t group_m, int32_t seg_span, int32_t seg_solo_first, int32_t bm, int32_t bn,
+                            int32_t split_from, int32_t split_shift, int32_t* out, int32_t n);
 /* number of kernels libfluxb launched from this process so far */
 uint64_t fluxb_launch_count(void);
 /* zero the launcher's per-stream wave counters of the current device (synchronises the device);

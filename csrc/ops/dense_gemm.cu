@@ -114,12 +114,30 @@ extern "C" int fluxb_dense_gemm(const fluxb_dense_args_t* a) {
   return dense_impl(a, nullptr);
 }
 
-// The tile order of the dense kernel, evaluated on the host by the same function the kernel
-// calls: out[3 * t .. 3 * t + 2] = (segment, tile row inside the segment, first column) of tile t.
 // Reduce-scatter with bands that span two segments: whether the first visited segment is a group of
 // its own, so that the last one (the own segment) is too: W even -> 1 | 2 2 ... 2 | 1, W odd -> 2 ... 2 | 1.
 extern "C" int fluxb_rs_solo_first(int32_t num_seg) { return num_seg % 2 == 0 ? 1 : 0; }
 
+// The last, partial wave: its tiles are cut into 2 or 4 column pieces when all the pieces still fit one
+// wave of `slots` CTAs (or CTA pairs); a problem smaller than one wave is all "last wave". mode: 0 = never,
+// 1 = halves or quarters, 2 = halves only. Returns the first tile that is cut and the shift (pieces = 1 << shift).
+extern "C" int fluxb_tail_split(int64_t tiles, int64_t slots, int32_t mode, int32_t* split_from, int32_t* split_shift) {
+  FLUXB_REQUIRE(tiles >= 0 && slots >= 1 && split_from != nullptr && split_shift != nullptr, "tail split arguments");
+  *split_from = static_cast<int32_t>(tiles);
+  *split_shift = 0;
+  const int64_t rest = tiles % slots;
+  if (mode == 0 || rest == 0) return kOk;
+  int shift = 0;
+  if (4 * rest <= slots) shift = 2;
+  else if (2 * rest <= slots) shift = 1;
+  if (mode == 2 && shift > 1) shift = 1;
+  *split_from = static_cast<int32_t>(tiles - rest);
+  *split_shift = shift;
+  return kOk;
+}
+
+// The tile order of the dense kernel, evaluated on the host by the same function the kernel
+// calls: out[3 * t .. 3 * t + 2] = (segment, tile row inside the segment, first column) of tile t.
 extern "C" int fluxb_decode_tiles(int32_t num_seg, int32_t seg_first, int32_t m_tiles_seg, int32_t n_tiles,
                                   int32_t group_m, int32_t seg_span, int32_t seg_solo_first, int32_t bm,
                                   int32_t bn, int32_t* out, int32_t n) {
@@ -137,6 +155,35 @@ extern "C" int fluxb_decode_tiles(int32_t num_seg, int32_t seg_first, int32_t m_
     out[3 * t] = c.seg;
     out[3 * t + 1] = c.m_tile;
     out[3 * t + 2] = c.n0;
+  }
+  return kOk;
+}
+
+// The same for the work items of a launch whose last wave is cut into column pieces (split_from /
+// split_shift as fluxb_tail_split returns them): out[4 * t .. 4 * t + 3] = (segment, tile row, first column,
+// shift) of work item t; an item is bn >> shift columns wide.
+extern "C" int fluxb_decode_work_items(int32_t num_seg, int32_t seg_first, int32_t m_tiles_seg, int32_t n_tiles,
+                                       int32_t group_m, int32_t seg_span, int32_t seg_solo_first, int32_t bm,
+                                       int32_t bn, int32_t split_from, int32_t split_shift, int32_t* out, int32_t n) {
+  FLUXB_REQUIRE(out != nullptr && num_seg >= 1 && m_tiles_seg >= 1 && n_tiles >= 1 && group_m >= 1, "tile grid");
+  const int64_t tiles = static_cast<int64_t>(num_seg) * m_tiles_seg * n_tiles;
+  FLUXB_REQUIRE(split_from >= 0 && split_from <= tiles && split_shift >= 0 && split_shift <= 2, "split");
+  FLUXB_REQUIRE(n <= split_from + ((tiles - split_from) << split_shift), "more work items asked for than there are");
+  DenseGemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.num_seg = num_seg;
+  p.seg_first = seg_first;
+  p.group_m = group_m;
+  p.seg_span = seg_span;
+  p.seg_solo_first = seg_solo_first;
+  p.split_from = split_from;
+  p.split_shift = split_shift;
+  for (int t = 0; t < n; ++t) {
+    const TileCoord c = decode_tile(p, t, m_tiles_seg, n_tiles, bm, bn);
+    out[4 * t] = c.seg;
+    out[4 * t + 1] = c.m_tile;
+    out[4 * t + 2] = c.n0;
+    out[4 * t + 3] = c.shift;
   }
   return kOk;
 }
@@ -531,16 +578,8 @@ static int dense_impl(const fluxb_dense_args_t* a, const fluxb_a2a_args_t* x) {
       const char* e = getenv("FLUXB_TAIL_SPLIT");
       return e ? atoi(e) : 1;
     }();
-    const int64_t slots = grid / cg;
-    const int64_t rest = tiles % slots;
-    if (split_env != 0 && bn == 256 && !a->blockscale && !a->b_kn && rest > 0) {
-      int shift = 0;
-      if (4 * rest <= slots && split_env >= 1) shift = 2;
-      else if (2 * rest <= slots) shift = 1;
-      if (split_env == 2 && shift > 1) shift = 1;   // FLUXB_TAIL_SPLIT=2: halves only
-      p.split_from = static_cast<int32_t>(tiles - rest);
-      p.split_shift = shift;
-    }
+    if (bn == 256 && !a->blockscale && !a->b_kn)
+      if ((rc = fluxb_tail_split(tiles, grid / cg, split_env, &p.split_from, &p.split_shift))) return rc;
   }
   p.total_vtiles = p.split_from + static_cast<int32_t>((tiles - p.split_from) << p.split_shift);
   if (!multi && !a2a && static_cast<int64_t>(p.total_vtiles) * cg < grid) grid = p.total_vtiles * cg;

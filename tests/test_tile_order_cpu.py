@@ -71,6 +71,52 @@ def test_reduce_scatter_keeps_the_own_segment_in_a_group_of_its_own(W, rank):
     assert any(len(set(t[i:i + G * nt, 0].tolist())) == 2 for i in range(start, len(t) - per_seg, G * nt))
 
 
+@pytest.mark.parametrize("mts,nt,slots,mode", [
+    (32, 24, 74, 1),     # 8192 x 6144 on 256 x 256 pair tiles: 768 tiles, 28 left over -> halves
+    (16, 24, 74, 1),     # the same on 512 x 256 tiles: 384 tiles, 14 left over -> quarters
+    (16, 24, 74, 2),     # halves only
+    (16, 48, 74, 1),     # 768 tiles: 28 left over
+    (4, 4, 74, 1),       # smaller than one wave: every tile is "last wave"
+    (37, 2, 74, 1),      # exactly one wave: nothing is cut
+    (10, 7, 74, 0),      # switched off
+])
+def test_last_wave_is_cut_into_column_pieces(mts, nt, slots, mode):
+    """The launcher's rule (``fluxb_tail_split``) and the kernel's decoding of the resulting work items
+    (``decode_tile`` through ``fluxb_decode_work_items``): the pieces fit one wave, every tile is covered
+    exactly once by whole items or by all of its pieces, and whole tiles keep their order."""
+    from tempname_new_b200 import _native
+    lib = _native.lib()
+    tiles = mts * nt
+    sf, sh = ctypes.c_int32(), ctypes.c_int32()
+    _native.check(lib.fluxb_tail_split(ctypes.c_int64(tiles), ctypes.c_int64(slots), mode, ctypes.byref(sf),
+                                       ctypes.byref(sh)), "fluxb_tail_split")
+    sf, sh = sf.value, sh.value
+    rest = tiles % slots
+    if mode == 0 or rest == 0:
+        assert (sf, sh) == (tiles, 0)
+    else:
+        assert sf == tiles - rest and (rest << sh) <= slots        # the pieces fit one wave
+        assert sh <= (1 if mode == 2 else 2)
+        assert sh == 2 or mode == 2 or (rest << (sh + 1)) > slots   # and are as narrow as that allows
+    n = sf + ((tiles - sf) << sh)
+    out = np.zeros(4 * n, dtype=np.int32)
+    _native.check(lib.fluxb_decode_work_items(1, 0, mts, nt, min(8, mts), 1, 0, 512, 256, sf, sh,
+                                              out.ctypes.data_as(ctypes.c_void_p), n), "fluxb_decode_work_items")
+    items = out.reshape(n, 4)
+    whole = _decode(1, 0, mts, nt, min(8, mts), 1, 0, bm=512, bn=256)
+    assert np.array_equal(items[:sf, :3], whole[:sf]) and not items[:sf, 3].any()
+    covered = {}
+    for seg, mt, n0, shift in items[sf:].tolist():
+        assert shift == sh
+        width = 256 >> shift
+        tile = (seg, mt, n0 // 256)
+        covered.setdefault(tile, []).append(n0 % 256)
+        assert n0 % width == 0
+    assert set(covered) == {(s, m, c // 256) for s, m, c in whole[sf:].tolist()}
+    for offs in covered.values():
+        assert sorted(offs) == [i * (256 >> sh) for i in range(1 << sh)]
+
+
 def test_decode_rejects_a_bad_grid():
     from tempname_new_b200 import _native
     out = np.zeros(3, dtype=np.int32)
